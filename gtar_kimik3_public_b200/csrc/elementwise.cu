@@ -1,0 +1,222 @@
+// Token-wise kernels: embedding gather, residual add + RMSNorm, SwiGLU, and per-head
+// q/k RMSNorm + rotary position encoding fused with the write of K and V into the paged cache.
+//
+// Formulas (reference): RMSNorm  w * (x * rsqrt(mean(x^2) + eps))   src/layers/rmsnorm.py:11-16
+//                       rotary   x*cos + rotate_half(x)*sin         src/layers/rope.py:17-33
+//                       SwiGLU   silu(gate) * up                    src/layers/swiglu.py:14
+// All arithmetic is 32-bit; inputs and outputs may be bfloat16.
+
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding gather
+template <typename TT>
+__global__ void embed_rows_kernel(const TT* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                                  int hidden) {
+    const int t = blockIdx.x;
+    const TT* row = table + (size_t)ids[t] * hidden;
+    float* dst = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(row[i]);
+}
+
+GK_EXPORT int gk_embed_rows(const void* table, int table_dtype, const int* ids, float* out, int n_tokens, int hidden,
+                            void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(table_dtype), "embed_rows: bad table dtype %d", table_dtype);
+    GK_REQUIRE(n_tokens >= 0 && hidden > 0, "embed_rows: bad sizes n_tokens=%d hidden=%d", n_tokens, hidden);
+    if (n_tokens == 0) return GK_OK;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    GK_DISPATCH_DTYPE(table_dtype, TT, {
+        embed_rows_kernel<TT><<<n_tokens, threads, 0, (cudaStream_t)stream>>>((const TT*)table, ids, out, hidden);
+    })
+    GK_CHECK_LAUNCH("embed_rows");
+    return GK_OK;
+}
+
+// ---------------------------------------------------------------- residual add + RMSNorm
+// One block per output row.  h (32-bit residual stream) gets `delta` added in place when
+// `rows` is null; with `rows`, only the listed rows are read and h is left as it is (the
+// last norm of a step, taken at the wanted positions only).
+template <typename TD, typename TW, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const TW* __restrict__ w,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* hrow = h + (size_t)src * hidden;
+    const TD* drow = delta ? delta + (size_t)src * hidden : nullptr;
+    TO* orow = out + (size_t)blockIdx.x * hidden;
+    const bool write_back = (rows == nullptr) && (drow != nullptr);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = hrow[i];
+        if (drow) v += to_float(drow[i]);
+        if (write_back) hrow[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = hrow[i];
+        if (drow && !write_back) v += to_float(drow[i]);
+        orow[i] = from_float<TO>((v * inv) * to_float(w[i]));
+    }
+}
+
+GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, const void* weight, int weight_dtype,
+                             void* out, int out_dtype, const int* rows, int n_out_rows, int hidden, float eps,
+                             void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(delta_dtype) && GK_VALID_DTYPE(weight_dtype) && GK_VALID_DTYPE(out_dtype),
+               "add_rmsnorm: bad dtype code");
+    GK_REQUIRE(n_out_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_out_rows, hidden);
+    GK_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
+    if (n_out_rows == 0) return GK_OK;
+    // A fixed block size: the order of the sum of squares must not depend on anything but the row.
+    const int threads = 256;
+    cudaStream_t s = (cudaStream_t)stream;
+    GK_DISPATCH_DTYPE(delta_dtype, TD, {
+        GK_DISPATCH_DTYPE(weight_dtype, TW, {
+            GK_DISPATCH_DTYPE(out_dtype, TO, {
+                add_rmsnorm_kernel<TD, TW, TO><<<n_out_rows, threads, 0, s>>>(h, (const TD*)delta, (const TW*)weight,
+                                                                             (TO*)out, rows, hidden, eps);
+            })
+        })
+    })
+    GK_CHECK_LAUNCH("add_rmsnorm");
+    return GK_OK;
+}
+
+// ---------------------------------------------------------------- SwiGLU on a packed [gate | up] row
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, long long total) {
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = to_float(gate_up[t * 2 * inter + i]);
+    const float u = to_float(gate_up[t * 2 * inter + inter + i]);
+    const float act = g / (1.0f + expf(-g));
+    out[idx] = from_float<T>(act * u);
+}
+
+GK_EXPORT int gk_swiglu(const void* gate_up, void* out, int dtype, int n_tokens, int inter, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype), "swiglu: bad dtype %d", dtype);
+    GK_REQUIRE(n_tokens >= 0 && inter > 0, "swiglu: bad sizes");
+    const long long total = (long long)n_tokens * inter;
+    if (total == 0) return GK_OK;
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    GK_REQUIRE(blocks < 2147483647LL, "swiglu: too many elements");
+    GK_DISPATCH_DTYPE(dtype, T, {
+        swiglu_kernel<T><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, inter, total);
+    })
+    GK_CHECK_LAUNCH("swiglu");
+    return GK_OK;
+}
+
+// ---------------------------------------------------------------- q/k norm + rotary + cache write
+// One warp per (token, head) of the packed projection row [q heads | k heads | v heads].
+//   q head: normalise, rotate, store to q_out[token, head, :]
+//   k head: normalise, rotate, store to the token's place in the K pages
+//   v head: copy to the token's place in the V pages
+// Page of token: block_table[slot, pos / page_size]; place in page: pos % page_size.
+// Pages are laid out [page, kv_head, page_size, head_dim].
+// `use_norm` = 0 skips the normalisation, `cos_table` = null skips the rotation, so that the
+// same kernel serves a mixer without q/k norm or without positions.
+template <typename T, typename TW>
+__global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* __restrict__ wq,
+                                          const TW* __restrict__ wk, const float* __restrict__ cos_table,
+                                          const float* __restrict__ sin_table, const int* __restrict__ tok_pos,
+                                          const int* __restrict__ tok_seq, const int* __restrict__ slots,
+                                          const int* __restrict__ block_table, T* __restrict__ q_out,
+                                          T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int n_q,
+                                          int n_kv, int head_dim, int max_pages, int page_size, float eps,
+                                          int use_norm) {
+    const int warps_per_block = blockDim.x >> 5;
+    const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int n_heads = n_q + 2 * n_kv;
+    if (wid >= (long long)n_tokens * n_heads) return;
+    const int t = (int)(wid / n_heads);
+    const int head = (int)(wid - (long long)t * n_heads);
+    const T* src = qkv + ((size_t)t * n_heads + head) * head_dim;
+    const int pos = tok_pos[t];
+    T* dst;
+    const TW* w = nullptr;
+    bool rotate = true;
+    if (head < n_q) {
+        dst = q_out + ((size_t)t * n_q + head) * head_dim;
+        w = wq;
+    } else {
+        const int hk = head < n_q + n_kv ? head - n_q : head - n_q - n_kv;
+        const int slot = slots[tok_seq[t]];
+        const int page = block_table[(size_t)slot * max_pages + pos / page_size];
+        const size_t at = (((size_t)page * n_kv + hk) * page_size + (pos % page_size)) * head_dim;
+        if (head < n_q + n_kv) {
+            dst = k_pages + at;
+            w = wk;
+        } else {
+            dst = v_pages + at;
+            rotate = false;
+        }
+    }
+    if (!rotate) {
+        for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+        return;
+    }
+    const int half = head_dim >> 1;
+    float inv = 1.0f;
+    if (use_norm) {
+        float ss = 0.f;
+        for (int p = lane; p < half; p += 32) {
+            const float a = to_float(src[p]), b = to_float(src[p + half]);
+            ss += a * a + b * b;
+        }
+        ss = warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+    }
+    for (int p = lane; p < half; p += 32) {
+        float a = to_float(src[p]), b = to_float(src[p + half]);
+        if (use_norm) {
+            a = (a * inv) * to_float(w[p]);
+            b = (b * inv) * to_float(w[p + half]);
+        }
+        float ra = a, rb = b;
+        if (cos_table) {
+            const float c = cos_table[(size_t)pos * half + p], s = sin_table[(size_t)pos * half + p];
+            ra = a * c - b * s;
+            rb = b * c + a * s;
+        }
+        dst[p] = from_float<T>(ra);
+        dst[p + half] = from_float<T>(rb);
+    }
+}
+
+GK_EXPORT int gk_qk_norm_rope_write(const void* qkv, int dtype, const void* wq, const void* wk, int weight_dtype,
+                                    const float* cos_table, const float* sin_table, int table_positions,
+                                    const int* tok_pos, const int* tok_seq, const int* slots, const int* block_table,
+                                    void* q_out, void* k_pages, void* v_pages, int n_tokens, int n_q, int n_kv,
+                                    int head_dim, int max_pages, int page_size, float eps, int use_norm,
+                                    int max_position, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(weight_dtype), "qk_norm_rope_write: bad dtype code");
+    GK_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && head_dim > 0 && head_dim % 2 == 0,
+               "qk_norm_rope_write: bad sizes n_q=%d n_kv=%d head_dim=%d", n_q, n_kv, head_dim);
+    GK_REQUIRE(page_size > 0 && max_pages > 0, "qk_norm_rope_write: bad page geometry");
+    GK_REQUIRE(!use_norm || (wq && wk), "qk_norm_rope_write: norm weights missing");
+    GK_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "qk_norm_rope_write: cos and sin tables go together");
+    GK_REQUIRE(cos_table == nullptr || max_position < table_positions,
+               "qk_norm_rope_write: position %d is beyond the rotary table (%d positions)", max_position,
+               table_positions);
+    if (n_tokens == 0) return GK_OK;
+    const int threads = 128;
+    const long long warps = (long long)n_tokens * (n_q + 2 * n_kv);
+    const long long blocks = (warps + 3) / 4;
+    GK_REQUIRE(blocks < 2147483647LL, "qk_norm_rope_write: too many tokens");
+    cudaStream_t s = (cudaStream_t)stream;
+    GK_DISPATCH_DTYPE(dtype, T, {
+        GK_DISPATCH_DTYPE(weight_dtype, TW, {
+            qk_norm_rope_write_kernel<T, TW><<<(unsigned)blocks, threads, 0, s>>>(
+                (const T*)qkv, (const TW*)wq, (const TW*)wk, cos_table, sin_table, tok_pos, tok_seq, slots, block_table,
+                (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, n_q, n_kv, head_dim, max_pages, page_size, eps, use_norm);
+        })
+    })
+    GK_CHECK_LAUNCH("qk_norm_rope_write");
+    return GK_OK;
+}

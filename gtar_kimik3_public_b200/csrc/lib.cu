@@ -1,0 +1,31 @@
+// Library-wide pieces of the C interface: the per-thread error message and a version probe.
+
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_last_error[512] = "";
+
+int gk_fail(int status, const char* fmt, ...) {
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(g_last_error, sizeof(g_last_error), fmt, args);
+    va_end(args);
+    return status;
+}
+
+GK_EXPORT const char* gk_last_error() { return g_last_error; }
+
+// Interface revision: the Python side refuses a library built from other sources.
+GK_EXPORT int gk_interface_version() { return 1; }
+
+// Compute capability of the current device as major * 10 + minor, or a negative CUDA error.
+GK_EXPORT int gk_device_capability() {
+    int device = 0, major = 0, minor = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device);
+    if (err != cudaSuccess) return -(int)err;
+    return major * 10 + minor;
+}
