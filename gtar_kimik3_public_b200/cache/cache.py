@@ -1,0 +1,249 @@
+"""The cache: a slot for each live sequence; keys and values in pages; per-sequence state.
+
+The reference keeps, per layer, dense ``[batch, kv_heads, max_seq_len, head_dim]`` buffers and one
+length for the whole batch (src/cache.py:4-17), and for its other architecture a state of
+fixed size per batch row (src/cache.py:48-57).  Here
+
+* a *slot* stands for one sequence: it has its own length, a row of every group's page table
+  and a row of every state tensor; slots are given back when a sequence ends and used again;
+* keys and values live in *pages* of ``page_size`` positions, ``[page, kv_head, page_size,
+  head_dim]`` per layer, handed to a sequence as it grows, so the pool is sized by the tokens that
+  live sequences hold (each rounded up to a page) and not by slots times the longest context;
+* layers whose mixers ask for the same kind of storage form a *group* with tensors and a page
+  pool of its own: one group for "all positions", one per window length (pages that have left
+  the window go back to the pool), one per shape of fixed-size state;
+* stale data is never cleared from pages: nothing reads beyond a sequence's length (the
+  reference argues the same for its rollback, src/cache.py:37-45).  State rows are zeroed when
+  a slot is handed out.
+
+Which entry of the model's run list uses which storage is given by ``CacheLayout``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..ops.functional import PagedKV
+from ..parts.base import KVRequest, StateRequest
+from .allocators import CacheFull, PageAllocator, SlotAllocator
+
+PAGE_SIZE = 64
+
+
+@dataclass
+class CacheLayout:
+    """``requests[e]`` is what entry ``e`` of the model's run list needs kept (or None); an entry
+    may instead read the storage of an earlier entry: ``shared_with[e] = e'``."""
+
+    requests: list[KVRequest | StateRequest | None]
+    shared_with: dict[int, int] = field(default_factory=dict)
+
+
+class _KVGroup:
+    def __init__(self, request: KVRequest, entries: list[int], n_slots: int, n_pages: int, max_pages_per_seq: int,
+                 page_size: int, dtype: torch.dtype, device: torch.device):
+        self.request, self.entries, self.page_size = request, entries, page_size
+        self.index_of = {e: i for i, e in enumerate(entries)}
+        shape = (len(entries), n_pages, request.n_kv_heads, page_size, request.head_dim)
+        self.k = torch.empty(shape, dtype=dtype, device=device)
+        self.v = torch.empty(shape, dtype=dtype, device=device)
+        self.pages = PageAllocator(n_pages)
+        self.max_pages_per_seq = max_pages_per_seq
+        self.table_host = torch.zeros((n_slots, max_pages_per_seq), dtype=torch.int32)
+        if device.type == "cuda":
+            self.table_host = self.table_host.pin_memory()
+        self.table = torch.zeros((n_slots, max_pages_per_seq), dtype=torch.int32, device=device)
+        self.owned: dict[int, dict[int, int]] = {}  # slot -> {page index in sequence: page}
+        self.dirty: set[int] = set()
+
+    def open_slot(self, slot: int) -> None:
+        self.owned[slot] = {}
+
+    def close_slot(self, slot: int) -> None:
+        self.pages.free(self.owned.pop(slot).values())
+
+    def pages_needed(self, slot: int, old_len: int, new_len: int) -> int:
+        first, last = self._span(old_len, new_len)
+        return sum(1 for i in range(first, last + 1) if i not in self.owned[slot])
+
+    def _span(self, old_len: int, new_len: int) -> tuple[int, int]:
+        """Page indices that hold positions a step from old_len to new_len reads or writes."""
+        first = 0
+        if self.request.window is not None:
+            first = max(0, old_len - self.request.window + 1) // self.page_size
+        return first, (new_len - 1) // self.page_size
+
+    def grow(self, slot: int, old_len: int, new_len: int) -> None:
+        if new_len <= 0:
+            return
+        first, last = self._span(old_len, new_len)
+        if last >= self.max_pages_per_seq:
+            raise CacheFull(f"a sequence of {new_len} tokens exceeds the longest the cache was sized for "
+                            f"({self.max_pages_per_seq * self.page_size})")
+        owned = self.owned[slot]
+        if self.request.window is not None:  # pages wholly before the window go back to the pool
+            gone = [i for i in owned if i < first]
+            if gone:
+                self.pages.free([owned.pop(i) for i in gone])
+        missing = [i for i in range(first, last + 1) if i not in owned]
+        if missing:
+            for i, page in zip(missing, self.pages.alloc(len(missing))):
+                owned[i] = page
+                self.table_host[slot, i] = page
+            self.dirty.add(slot)
+
+    def sync(self) -> None:
+        if not self.dirty:
+            return
+        if len(self.dirty) * 4 >= self.table.shape[0]:
+            self.table.copy_(self.table_host, non_blocking=True)
+        else:
+            for slot in self.dirty:
+                self.table[slot].copy_(self.table_host[slot], non_blocking=True)
+        self.dirty.clear()
+
+    def view(self, entry: int) -> PagedKV:
+        i = self.index_of[entry]
+        return PagedKV(self.k[i], self.v[i], self.table)
+
+
+class _StateGroup:
+    def __init__(self, request: StateRequest, entries: list[int], n_slots: int, device: torch.device):
+        self.request, self.entries = request, entries
+        self.index_of = {e: i for i, e in enumerate(entries)}
+        self.state = torch.zeros((len(entries), n_slots, *request.shape), dtype=request.dtype, device=device)
+
+    def open_slot(self, slot: int) -> None:
+        self.state[:, slot].zero_()
+
+    def view(self, entry: int) -> torch.Tensor:
+        return self.state[self.index_of[entry]]
+
+
+class Cache:
+    """Storage for up to ``max_seqs`` live sequences holding at most ``max_tokens`` tokens in all,
+    each sequence's count rounded up to a multiple of the page size."""
+
+    def __init__(self, layout: CacheLayout, max_tokens: int, dtype: torch.dtype, device: torch.device | str,
+                 max_seqs: int | None = None, max_seq_len: int | None = None, page_size: int = PAGE_SIZE):
+        device = torch.device(device)
+        if max_tokens <= 0:
+            raise ValueError("max_tokens must be positive")
+        if page_size % 32:
+            raise ValueError("page_size must be a multiple of 32")
+        self.layout, self.dtype, self.device, self.page_size = layout, dtype, device, page_size
+        self.n_pages = -(-max_tokens // page_size)
+        self.max_seqs = min(self.n_pages, max_seqs if max_seqs else 256)
+        pages_per_seq = self.n_pages if max_seq_len is None else min(self.n_pages, -(-max_seq_len // page_size))
+        self.max_seq_len = pages_per_seq * page_size if max_seq_len is None else min(max_seq_len, pages_per_seq * page_size)
+        self.slots = SlotAllocator(self.max_seqs)
+        self.length: dict[int, int] = {}
+        self.kv_groups: list[_KVGroup] = []
+        self.state_groups: list[_StateGroup] = []
+        self._where: dict[int, object] = {}
+        by_request: dict[object, list[int]] = {}
+        for entry, request in enumerate(layout.requests):
+            if entry in layout.shared_with:
+                continue
+            if request is not None:
+                by_request.setdefault(request, []).append(entry)
+        for request, entries in by_request.items():
+            if isinstance(request, KVRequest):
+                n_pages = self.n_pages
+                if request.window is not None:
+                    n_pages = min(n_pages, self.max_seqs * (-(-request.window // page_size) + 1))
+                group = _KVGroup(request, entries, self.max_seqs, n_pages, pages_per_seq, page_size, dtype, device)
+                self.kv_groups.append(group)
+            elif isinstance(request, StateRequest):
+                group = _StateGroup(request, entries, self.max_seqs, device)
+                self.state_groups.append(group)
+            else:
+                raise TypeError(f"unknown cache request {request!r}")
+            for entry in entries:
+                self._where[entry] = group
+        for entry, source in layout.shared_with.items():
+            if source not in self._where:
+                raise ValueError(f"run-list entry {entry} shares the cache of entry {source}, which keeps nothing")
+            self._where[entry] = self._where[source]
+
+    # ------------------------------------------------------------------ slots
+    def open(self) -> int:
+        """A slot for a new sequence: length 0, no pages, zero state."""
+        slot = self.slots.alloc()
+        self.length[slot] = 0
+        for group in self.kv_groups:
+            group.open_slot(slot)
+        for group in self.state_groups:
+            group.open_slot(slot)
+        return slot
+
+    def close(self, slot: int) -> None:
+        """Gives back the slot and everything the sequence holds."""
+        self.slots.free(slot)
+        del self.length[slot]
+        for group in self.kv_groups:
+            group.close_slot(slot)
+
+    def can_grow(self, growth: dict[int, int]) -> bool:
+        """Whether ``growth[slot]`` more tokens for each listed slot fit in the free pages."""
+        for group in self.kv_groups:
+            need = sum(group.pages_needed(s, self.length[s], self.length[s] + n) for s, n in growth.items() if n > 0)
+            if need > group.pages.n_free:
+                return False
+        return all(self.length[s] + n <= self.max_seq_len for s, n in growth.items())
+
+    def grow(self, slot: int, n_new: int) -> int:
+        """Makes room for ``n_new`` more tokens of the sequence in ``slot`` and counts them in.
+        Returns the length before."""
+        if not self.slots.in_use(slot):
+            raise ValueError(f"slot {slot} is not in use")
+        old = self.length[slot]
+        new = old + n_new
+        if new > self.max_seq_len:
+            raise CacheFull(f"sequence would reach {new} tokens; the cache holds sequences up to {self.max_seq_len}")
+        for group in self.kv_groups:
+            group.grow(slot, old, new)
+        self.length[slot] = new
+        return old
+
+    def sync(self) -> None:
+        """Brings the device page tables up to date; call after ``grow`` and before the step runs."""
+        for group in self.kv_groups:
+            group.sync()
+
+    # ------------------------------------------------------------------ views
+    def view(self, entry: int):
+        """Storage of run-list entry ``entry``: a ``PagedKV``, a state tensor ``[n_slots, ...]`` or None."""
+        group = self._where.get(entry)
+        if group is None:
+            return None
+        source = self.layout.shared_with.get(entry, entry)
+        return group.view(source)
+
+    def is_shared(self, entry: int) -> bool:
+        return entry in self.layout.shared_with
+
+    # ------------------------------------------------------------------ accounting
+    def live_tokens(self) -> int:
+        return sum(self.length.values())
+
+    def kv_bytes_per_token(self) -> int:
+        total = 0
+        for group in self.kv_groups:
+            r = group.request
+            total += 2 * len(group.entries) * r.n_kv_heads * r.head_dim * self.k_element_size()
+        return total
+
+    def k_element_size(self) -> int:
+        return torch.empty((), dtype=self.dtype).element_size()
+
+    def check_invariants(self) -> None:
+        """No page held twice, none lost, lengths only for slots in use."""
+        for group in self.kv_groups:
+            held = [p for owned in group.owned.values() for p in owned.values()]
+            assert len(held) == len(set(held)), "a page is held by two sequences"
+            assert len(held) == group.pages.n_used, "pages were lost"
+            assert set(group.owned) == set(self.length), "a group tracks other slots than the cache"
+        assert len(self.length) == self.slots.n_used

@@ -119,7 +119,8 @@ GK_EXPORT int gk_swiglu(const void* gate_up, void* out, int dtype, int n_tokens,
 // Page of token: block_table[slot, pos / page_size]; place in page: pos % page_size.
 // Pages are laid out [page, kv_head, page_size, head_dim].
 // `use_norm` = 0 skips the normalisation, `cos_table` = null skips the rotation, so that the
-// same kernel serves a mixer without q/k norm or without positions.
+// same kernel serves a mixer without q/k norm or without positions; `k_pages` = null writes no
+// keys and values (a layer that reads the storage another layer fills).
 template <typename T, typename TW>
 __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* __restrict__ wq,
                                           const TW* __restrict__ wk, const float* __restrict__ cos_table,
@@ -145,6 +146,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* _
         dst = q_out + ((size_t)t * n_q + head) * head_dim;
         w = wq;
     } else {
+        if (k_pages == nullptr) return;  // this layer reads another layer's keys and values
         const int hk = head < n_q + n_kv ? head - n_q : head - n_q - n_kv;
         const int slot = slots[tok_seq[t]];
         const int page = block_table[(size_t)slot * max_pages + pos / page_size];

@@ -1,0 +1,102 @@
+"""The engine: a model, its cache, and the one step function that everything above uses
+(generation, trace replay, the benchmark).
+
+It is the successor of the reference's ``Engine`` + model call (src/engine.py:15-46,
+src/models/transformer.py:99-101), with three differences that the reference's design cannot
+express: sequences of a batch have their own lengths, logits are computed only at the wanted
+places, and a sequence that ends gives its storage back while the others go on.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..cache import Cache, CacheFull
+from ..models.model import Model
+from .step import SequenceStep, plan_step
+
+
+@dataclass
+class StepEntry:
+    """A request's part of a step: its next tokens and the places among them whose logits are wanted."""
+
+    id: object
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)
+
+
+class Engine:
+    def __init__(self, model: Model, max_tokens: int, max_seqs: int | None = None):
+        self.model = model
+        self.cache: Cache = model.make_cache(max_tokens, max_seqs)
+        self.slot_of: dict[object, int] = {}
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ requests
+    def live(self) -> list[object]:
+        return list(self.slot_of)
+
+    def length(self, request_id) -> int:
+        return self.cache.length[self.slot_of[request_id]]
+
+    def end(self, request_ids) -> None:
+        """The listed requests are finished: their slots and pages are given back."""
+        for request_id in request_ids:
+            if request_id not in self.slot_of:
+                raise KeyError(f"request {request_id!r} is not live")
+            self.cache.close(self.slot_of.pop(request_id))
+
+    def end_all(self) -> None:
+        self.end(list(self.slot_of))
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """Runs the entries' tokens as one batch from the cache and returns float32 logits
+        ``[n_wanted, vocab]`` in the order of the entries and of each entry's ``want``.
+
+        A request seen for the first time gets a slot; the others continue where they are.
+        Nothing is changed when the step cannot run (no slot, not enough pages, a bad token).
+        """
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        ids = [e.id for e in entries]
+        if len(set(ids)) != len(ids):
+            raise ValueError("a request appears twice in one step")
+        vocab = self.model.vocab_size
+        for entry in entries:
+            if not entry.tokens:
+                raise ValueError(f"request {entry.id!r} brings no token")
+            for token in entry.tokens:
+                if not 0 <= int(token) < vocab:
+                    raise ValueError(f"request {entry.id!r}: token id {token} is outside the vocabulary of {vocab}")
+        new_ids = [e.id for e in entries if e.id not in self.slot_of]
+        if len(new_ids) > self.cache.slots.n_free:
+            raise CacheFull(f"{len(new_ids)} new requests but only {self.cache.slots.n_free} free slots")
+        opened = []
+        try:
+            for request_id in new_ids:
+                slot = self.cache.open()
+                self.slot_of[request_id] = slot
+                opened.append(request_id)
+            growth = {self.slot_of[e.id]: len(e.tokens) for e in entries}
+            if not self.cache.can_grow(growth):
+                raise CacheFull(
+                    f"the step's {sum(growth.values())} tokens do not fit: the cache holds "
+                    f"{self.cache.n_pages * self.cache.page_size} tokens in pages of {self.cache.page_size} and "
+                    f"sequences up to {self.cache.max_seq_len}")
+        except Exception:
+            for request_id in opened:
+                self.cache.close(self.slot_of.pop(request_id))
+            raise
+        sequences = []
+        for entry in entries:
+            slot = self.slot_of[entry.id]
+            past = self.cache.grow(slot, len(entry.tokens))
+            sequences.append(SequenceStep(slot, past, [int(t) for t in entry.tokens], [int(w) for w in entry.want]))
+        self.cache.sync()
+        ctx = plan_step(sequences, self.model.dtype, self.model.device, vocab)
+        logits = self.model.step(ctx, self.cache)
+        self.steps_run += 1
+        return logits

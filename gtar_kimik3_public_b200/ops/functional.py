@@ -1,0 +1,283 @@
+"""Python faces of the kernels: argument checks, then one call into the kernel library.
+
+Every function works on CUDA tensors on the current stream and allocates at most its own
+output.  Shapes follow the packed ("varlen") convention of the step function: activations are
+``[n_tokens, width]`` with the tokens of all sequences of a step one after another.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .library import KernelError, call, dtype_code, ptr, require_device, stream_ptr
+
+
+def _check(tensor: torch.Tensor, name: str, dtype=None, dims: int | None = None) -> None:
+    if not tensor.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+    if dims is not None and tensor.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, got shape {tuple(tensor.shape)}")
+
+
+@dataclass
+class PagedKV:
+    """One layer's keys and values in pages, and the table that maps a sequence's pages.
+
+    ``k``, ``v``: ``[n_pages, n_kv_heads, page_size, head_dim]``; ``block_table``:
+    ``[n_slots, max_pages]`` int32, entry ``[slot, i]`` = page that holds positions
+    ``i*page_size .. (i+1)*page_size-1`` of the sequence in ``slot``.
+    """
+
+    k: torch.Tensor
+    v: torch.Tensor
+    block_table: torch.Tensor
+
+    @property
+    def page_size(self) -> int:
+        return self.k.shape[2]
+
+    @property
+    def max_pages(self) -> int:
+        return self.block_table.shape[1]
+
+
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]]`` widened to float32 (the residual stream's type)."""
+    require_device(table.device)
+    _check(table, "table", dims=2)
+    _check(ids, "ids", torch.int32, 1)
+    n, hidden = ids.shape[0], table.shape[1]
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _check(out, "out", torch.float32, 2)
+    call("gk_embed_rows", ptr(table), dtype_code(table.dtype), ptr(ids), ptr(out), n, hidden, stream_ptr())
+    return out
+
+
+def add_rmsnorm(
+    h: torch.Tensor,
+    delta: torch.Tensor | None,
+    weight: torch.Tensor,
+    eps: float,
+    out_dtype: torch.dtype,
+    rows: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """``h += delta`` (in place, skipped when ``delta`` is None), then RMSNorm of ``h`` times ``weight``.
+
+    With ``rows`` (int32 indices) only those rows are normalised and ``h`` is not written: the
+    sum ``h + delta`` of such a row is formed on the fly.
+    """
+    require_device(h.device)
+    _check(h, "h", torch.float32, 2)
+    _check(weight, "weight", dims=1)
+    hidden = h.shape[1]
+    if weight.shape[0] != hidden:
+        raise KernelError(f"norm weight has {weight.shape[0]} entries for rows of {hidden}")
+    delta_code = 0
+    if delta is not None:
+        _check(delta, "delta", dims=2)
+        if delta.shape != h.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
+        delta_code = dtype_code(delta.dtype)
+    n_out = h.shape[0]
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        n_out = rows.shape[0]
+    if out is None:
+        out = torch.empty((n_out, hidden), dtype=out_dtype, device=h.device)
+    _check(out, "out", out_dtype, 2)
+    call(
+        "gk_add_rmsnorm", ptr(h), ptr(delta), delta_code, ptr(weight), dtype_code(weight.dtype), ptr(out),
+        dtype_code(out_dtype), ptr(rows), n_out, hidden, float(eps), stream_ptr(),
+    )
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(gate) * up`` for rows packed as ``[gate (I) | up (I)]``."""
+    require_device(gate_up.device)
+    _check(gate_up, "gate_up", dims=2)
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gate_up rows must hold gate and up halves of equal width")
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _check(out, "out", gate_up.dtype, 2)
+    call("gk_swiglu", ptr(gate_up), ptr(out), dtype_code(gate_up.dtype), n, inter, stream_ptr())
+    return out
+
+
+def qk_norm_rope_write(
+    qkv: torch.Tensor,
+    n_q: int,
+    n_kv: int,
+    head_dim: int,
+    q_weight: torch.Tensor | None,
+    k_weight: torch.Tensor | None,
+    eps: float,
+    cos: torch.Tensor | None,
+    sin: torch.Tensor | None,
+    tok_pos: torch.Tensor,
+    tok_seq: torch.Tensor,
+    slots: torch.Tensor,
+    kv: PagedKV,
+    max_position: int,
+    q_out: torch.Tensor | None = None,
+    write_kv: bool = True,
+) -> torch.Tensor:
+    """Per-head RMSNorm of q and k, rotation by position, and the write of k and v into the pages.
+
+    ``qkv``: ``[n_tokens, (n_q + 2 n_kv) * head_dim]``.  Returns the finished queries
+    ``[n_tokens, n_q, head_dim]``.  ``max_position`` is the largest entry of ``tok_pos`` (known on
+    the host) and is checked against the rotary table.  ``write_kv=False`` leaves the pages alone
+    (a layer that attends over keys and values written by another layer).
+    """
+    require_device(qkv.device)
+    _check(qkv, "qkv", dims=2)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_q + 2 * n_kv) * head_dim:
+        raise KernelError(f"qkv rows are {qkv.shape[1]} wide, expected {(n_q + 2 * n_kv) * head_dim}")
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    _check(kv.block_table, "block_table", torch.int32, 2)
+    _check(kv.k, "k pages", qkv.dtype, 4)
+    _check(kv.v, "v pages", qkv.dtype, 4)
+    if kv.k.shape[1] != n_kv or kv.k.shape[3] != head_dim or kv.v.shape != kv.k.shape:
+        raise KernelError(f"pages {tuple(kv.k.shape)} do not fit n_kv={n_kv}, head_dim={head_dim}")
+    use_norm = q_weight is not None
+    weight_code = 0
+    if use_norm:
+        _check(q_weight, "q_weight", dims=1)
+        _check(k_weight, "k_weight", q_weight.dtype, 1)
+        if q_weight.shape[0] != head_dim or k_weight.shape[0] != head_dim:
+            raise KernelError("q/k norm weights must have head_dim entries")
+        weight_code = dtype_code(q_weight.dtype)
+    table_positions = 0
+    if cos is not None:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+            raise KernelError("rotary tables must be [positions, head_dim / 2]")
+        table_positions = cos.shape[0]
+    if q_out is None:
+        q_out = torch.empty((n, n_q, head_dim), dtype=qkv.dtype, device=qkv.device)
+    _check(q_out, "q_out", qkv.dtype, 3)
+    call(
+        "gk_qk_norm_rope_write", ptr(qkv), dtype_code(qkv.dtype), ptr(q_weight), ptr(k_weight), weight_code, ptr(cos),
+        ptr(sin), table_positions, ptr(tok_pos), ptr(tok_seq), ptr(slots), ptr(kv.block_table), ptr(q_out),
+        ptr(kv.k) if write_kv else None, ptr(kv.v) if write_kv else None, n, n_q, n_kv, head_dim, kv.max_pages, kv.page_size, float(eps), int(use_norm), int(max_position),
+        stream_ptr(),
+    )
+    return q_out
+
+
+def linear_f32(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T`` on the FP32 pipes: ``weight`` float32 ``[N, K]``, ``x`` float32 or bfloat16 ``[M, K]``."""
+    require_device(x.device)
+    _check(x, "x", dims=2)
+    _check(weight, "weight", torch.float32, 2)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"x is [{m}, {k}] but weight is {tuple(weight.shape)}")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    _check(out, "out", out_dtype, 2)
+    call("gk_gemm_f32", ptr(x), dtype_code(x.dtype), ptr(weight), ptr(out), dtype_code(out_dtype), m, n, k, k, k, n,
+         stream_ptr())
+    return out
+
+
+def attention_exact(
+    q: torch.Tensor,
+    kv: PagedKV,
+    tok_pos: torch.Tensor,
+    tok_seq: torch.Tensor,
+    slots: torch.Tensor,
+    scale: float,
+    window: int = 0,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Causal grouped-query attention of ``q [n_tokens, n_q, d]`` over the pages (exact kernel)."""
+    require_device(q.device)
+    _check(q, "q", dims=3)
+    n, n_q, d = q.shape
+    _check(kv.k, "k pages", q.dtype, 4)
+    _check(kv.v, "v pages", q.dtype, 4)
+    n_kv = kv.k.shape[1]
+    if kv.k.shape[3] != d:
+        raise KernelError(f"pages have head_dim {kv.k.shape[3]}, queries {d}")
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    if out is None:
+        out = torch.empty_like(q)
+    call(
+        "gk_attention_exact", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), dtype_code(q.dtype), ptr(tok_pos), ptr(tok_seq),
+        ptr(slots), ptr(kv.block_table), n, n_q, n_kv, d, kv.max_pages, kv.page_size, float(scale), int(window),
+        stream_ptr(),
+    )
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Index of the largest logit of each row (lowest index on ties), int32."""
+    require_device(logits.device)
+    _check(logits, "logits", torch.float32, 2)
+    n, vocab = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(out, "out", torch.int32, 1)
+    call("gk_argmax", ptr(logits), vocab, n, vocab, ptr(out), stream_ptr())
+    return out
+
+
+def sample(
+    logits: torch.Tensor,
+    temperature: float,
+    top_k: int,
+    seed: int,
+    request_ids: torch.Tensor,
+    steps: torch.Tensor,
+    advance_steps: bool = False,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Temperature (+ top-k) sampling by the Gumbel-max rule with counter-based uniforms.
+
+    Row ``r`` draws with the key ``(seed, request_ids[r], steps[r])``; with ``advance_steps`` the
+    kernel adds one to ``steps[r]`` afterwards, so a loop replayed from a CUDA graph needs no host
+    work between tokens.
+    """
+    require_device(logits.device)
+    _check(logits, "logits", torch.float32, 2)
+    n, vocab = logits.shape
+    _check(request_ids, "request_ids", torch.int32, 1)
+    _check(steps, "steps", torch.int32, 1)
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(out, "out", torch.int32, 1)
+    call(
+        "gk_sample", ptr(logits), vocab, n, vocab, float(temperature), int(top_k or 0), int(seed) & (2**64 - 1),
+        ptr(request_ids), ptr(steps), int(advance_steps), ptr(out), stream_ptr(),
+    )
+    return out
+
+
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``x @ weight.T`` for bfloat16 operands with 32-bit accumulation (library matrix product,
+    as the reference's nn.Linear under autocast is: src/engine.py:35)."""
+    require_device(x.device)
+    _check(x, "x", torch.bfloat16, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    if weight.shape[1] != x.shape[1]:
+        raise KernelError(f"x is {tuple(x.shape)} but weight is {tuple(weight.shape)}")
+    y = torch.mm(x, weight.t())
+    return y if out_dtype == torch.bfloat16 else y.to(out_dtype)

@@ -1,0 +1,77 @@
+"""Grouped-query attention with optional per-head q/k RMSNorm and a position encoding.
+
+The reference's ``Attention`` (src/layers/attention.py:49-121): bias-free q/k/v/o projections,
+RMSNorm over ``head_dim`` of q and k with one weight each (applied before the rotation),
+rotation, cache write, causal attention where consecutive query heads share a kv head, scale
+``head_dim ** -0.5``.  Here the three input projections are one packed matrix product, and
+norm + rotation + cache write are one kernel.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import attention as attention_ops
+from ..ops import functional as F
+from ..ops.linear import linear
+from .base import KVRequest, Mixer, PositionEncoding, StepContext, TensorSpec, register_part
+
+
+class GQAAttention(Mixer):
+    def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int, qk_norm_eps: float | None,
+                 position: PositionEncoding | None, window: int | None = None):
+        if n_q_heads % n_kv_heads:
+            raise ValueError("query heads must be a multiple of kv heads")
+        self.hidden_size, self.n_q, self.n_kv, self.head_dim = int(hidden_size), int(n_q_heads), int(n_kv_heads), int(head_dim)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.position = position
+        self.window = window
+        self.scale = float(self.head_dim) ** -0.5
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+
+    def tensor_specs(self):
+        d, h = self.head_dim, self.hidden_size
+        specs = {
+            "q_proj.weight": TensorSpec((self.n_q * d, h)),
+            "k_proj.weight": TensorSpec((self.n_kv * d, h)),
+            "v_proj.weight": TensorSpec((self.n_kv * d, h)),
+            "o_proj.weight": TensorSpec((h, self.n_q * d)),
+        }
+        if self.qk_norm_eps is not None:
+            specs["q_norm.weight"] = TensorSpec((d,), "vector")
+            specs["k_norm.weight"] = TensorSpec((d,), "vector")
+        return specs
+
+    def load(self, tensors):
+        parts = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        if len({p.dtype for p in parts}) != 1:  # a file that mixes 32-bit and 16-bit projections
+            parts = [p.float() for p in parts]
+        self.w_qkv = torch.cat(parts, dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"].contiguous()
+        if self.qk_norm_eps is not None:
+            q_w, k_w = tensors["q_norm.weight"], tensors["k_norm.weight"]
+            if q_w.dtype != k_w.dtype:
+                q_w, k_w = q_w.float(), k_w.float()
+            self.q_norm, self.k_norm = q_w.contiguous(), k_w.contiguous()
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
+
+    def cache_request(self):
+        return KVRequest(self.n_kv, self.head_dim, self.window)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: F.PagedKV) -> torch.Tensor:
+        qkv = linear(x, self.w_qkv)
+        cos = sin = None
+        if self.position is not None:
+            cos, sin = self.position.cos, self.position.sin
+        q = F.qk_norm_rope_write(
+            qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm, self.qk_norm_eps or 1.0, cos, sin,
+            ctx.tok_pos, ctx.tok_seq, ctx.slots, cache, ctx.max_position,
+            write_kv=not ctx.extras.get("cache_read_only", False),
+        )
+        o = attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
+        return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
+
+
+register_part("mixer", "gqa_attention", GQAAttention)

@@ -1,0 +1,41 @@
+"""SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))`` (src/layers/swiglu.py:9-14), with the gate
+and up projections as one packed matrix product."""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import functional as F
+from ..ops.linear import linear
+from .base import FeedForward, StepContext, TensorSpec, register_part
+
+
+class SwiGLUFeedForward(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return {
+            "gate_proj.weight": TensorSpec((i, h)),
+            "up_proj.weight": TensorSpec((i, h)),
+            "down_proj.weight": TensorSpec((h, i)),
+        }
+
+    def load(self, tensors):
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        if gate.dtype != up.dtype:
+            gate, up = gate.float(), up.float()
+        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"].contiguous()
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        gate_up = linear(x, self.w_gate_up)
+        return linear(F.swiglu(gate_up), self.w_down)
+
+
+register_part("feed_forward", "swiglu", SwiGLUFeedForward)

@@ -75,7 +75,7 @@ class SafetensorsFile:
                     raise SafetensorsError(
                         f"{self.path}: truncated: tensor {name!r} ends at byte {end} of a {data_size}-byte data section"
                     )
-            self._map = mmap.mmap(handle.fileno(), 0, access=mmap.ACCESS_READ) if size > 0 else None
+            self._map = mmap.mmap(handle.fileno(), 0, access=mmap.ACCESS_COPY) if size > 0 else None
 
     def names(self) -> list[str]:
         return list(self.entries)
@@ -87,7 +87,8 @@ class SafetensorsFile:
         return _DTYPES[self.entries[name]["dtype"]]
 
     def tensor(self, name: str) -> torch.Tensor:
-        """A CPU tensor that aliases the mapped file (read-only: clone or copy before writing)."""
+        """A CPU tensor that aliases the mapped file (a private copy-on-write mapping: writing to the
+        tensor never reaches the file)."""
         entry = self.entries[name]
         begin, end = entry["data_offsets"]
         dtype = _DTYPES[entry["dtype"]]

@@ -14,6 +14,20 @@ from __future__ import annotations
 
 import torch
 
+# When set to torch.bfloat16, every matrix product rounds its operands and its result to that
+# type while norms, rotation, softmax and the residual stream stay in the working precision:
+# what the reference does on a GPU under torch.autocast (src/engine.py:35).  It is the "standard
+# low-precision implementation" whose error the bfloat16 tests measure the library against.
+LOWP: torch.dtype | None = None
+
+
+def mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a @ b, optionally with operands and result rounded to LOWP."""
+    if LOWP is None:
+        return a @ b
+    wide = a.dtype
+    return (a.to(LOWP).to(wide) @ b.to(LOWP).to(wide)).to(LOWP).to(wide)
+
 
 def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     """h0[t] = E[ids[t]]  — src/models/transformer.py:55,61 (no scale, no position added)."""
@@ -73,9 +87,9 @@ def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, wind
         visible &= idx[None, :] > idx[:, None] - window
     for hq in range(n_q):
         hk = hq // group
-        scores = (q[:, hq, :] @ k[:, hk, :].T) * (d**-0.5)
+        scores = mm(q[:, hq, :], k[:, hk, :].T) * (d**-0.5)
         scores = scores.masked_fill(~visible, float("-inf"))
-        out[:, hq, :] = torch.softmax(scores, dim=-1) @ v[:, hk, :]
+        out[:, hq, :] = mm(torch.softmax(scores, dim=-1), v[:, hk, :])
     return out
 
 
@@ -89,23 +103,23 @@ def attention_mixer(x: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, cf
     n_q, n_kv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     eps = cfg["rms_norm_eps"]
     n_tokens = x.shape[0]
-    q = (x @ w[prefix + "q_proj.weight"].T).view(n_tokens, n_q, d)
-    k = (x @ w[prefix + "k_proj.weight"].T).view(n_tokens, n_kv, d)
-    v = (x @ w[prefix + "v_proj.weight"].T).view(n_tokens, n_kv, d)
+    q = mm(x, w[prefix + "q_proj.weight"].T).view(n_tokens, n_q, d)
+    k = mm(x, w[prefix + "k_proj.weight"].T).view(n_tokens, n_kv, d)
+    v = mm(x, w[prefix + "v_proj.weight"].T).view(n_tokens, n_kv, d)
     q = rms_norm(q, w[prefix + "q_norm.weight"], eps)
     k = rms_norm(k, w[prefix + "k_norm.weight"], eps)
     cos, sin = rotary_tables(torch.arange(n_tokens), d, cfg["rope_theta"])
     q = apply_rotary(q, cos, sin)
     k = apply_rotary(k, cos, sin)
     o = causal_gqa_attention(q, k, v)
-    return o.reshape(n_tokens, n_q * d) @ w[prefix + "o_proj.weight"].T
+    return mm(o.reshape(n_tokens, n_q * d), w[prefix + "o_proj.weight"].T)
 
 
 def swiglu(x: torch.Tensor, w: dict[str, torch.Tensor], prefix: str) -> torch.Tensor:
     """down(silu(gate(x)) * up(x)),  silu(z) = z * sigmoid(z)  — src/layers/swiglu.py:9-14."""
-    gate = x @ w[prefix + "gate_proj.weight"].T
-    up = x @ w[prefix + "up_proj.weight"].T
-    return ((gate * torch.sigmoid(gate)) * up) @ w[prefix + "down_proj.weight"].T
+    gate = mm(x, w[prefix + "gate_proj.weight"].T)
+    up = mm(x, w[prefix + "up_proj.weight"].T)
+    return mm((gate * torch.sigmoid(gate)) * up, w[prefix + "down_proj.weight"].T)
 
 
 def block(h: torch.Tensor, w: dict[str, torch.Tensor], layer: int, cfg: dict) -> torch.Tensor:
@@ -127,7 +141,7 @@ def forward(ids: torch.Tensor, w: dict[str, torch.Tensor], cfg: dict, dtype: tor
         h = block(h, w, layer, cfg)
     z = rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
-    return z @ head.T
+    return mm(z, head.T)
 
 
 def greedy_generate(prompt: list[int], w: dict, cfg: dict, max_new_tokens: int, stop_ids=(),
