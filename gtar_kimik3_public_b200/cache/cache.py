@@ -151,9 +151,10 @@ class Cache:
                 by_request.setdefault(request, []).append(entry)
         for request, entries in by_request.items():
             if isinstance(request, KVRequest):
+                # A windowed group draws on a pool as large as the others': a long prompt needs all its
+                # pages while its step runs.  What the window saves is returned at the sequence's
+                # next step, so fewer pages are *in use*, and more sequences fit, than without it.
                 n_pages = self.n_pages
-                if request.window is not None:
-                    n_pages = min(n_pages, self.max_seqs * (-(-request.window // page_size) + 1))
                 group = _KVGroup(request, entries, self.max_seqs, n_pages, pages_per_seq, page_size, dtype, device)
                 self.kv_groups.append(group)
             elif isinstance(request, StateRequest):

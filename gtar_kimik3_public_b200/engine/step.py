@@ -66,5 +66,5 @@ def plan_step(sequences: list[SequenceStep], dtype: torch.dtype, device: torch.d
         n_tokens=len(tokens), n_seqs=len(sequences), dtype=dtype,
         tokens=views[0], tok_pos=views[1], tok_seq=views[2], cu_q=views[3], slots=views[4], kv_len=views[5],
         want_rows=views[6], max_q_len=max(q_lens), max_kv_len=max(kv_len), max_position=max(kv_len) - 1,
-        all_single=all(n == 1 for n in q_lens), host_q_len=q_lens, host_past_len=[s.past_len for s in sequences],
+        all_single=all(n == 1 for n in q_lens), host_q_len=q_lens, host_past_len=[s.past_len for s in sequences], host_slots=slots,
     )

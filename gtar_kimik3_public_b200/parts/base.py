@@ -78,6 +78,7 @@ class StepContext:
     all_single: bool  # every sequence brings exactly one token (a decode step)
     host_q_len: list[int] = field(default_factory=list)
     host_past_len: list[int] = field(default_factory=list)
+    host_slots: list[int] = field(default_factory=list)
     extras: dict[str, Any] = field(default_factory=dict)
 
 

@@ -1,0 +1,314 @@
+"""Each kernel alone against a plain float64 formula, at sizes other than the tiny models':
+widths and vocabularies that are no power of two, head sizes 16/48/80/128, groups of 1/2/3/4,
+lengths 1/777/1000.  Where random inputs would hide a fault the inputs are made to show it: one
+far key whose score stands out, a key at the window's edge, pages handed out in scrambled order
+with every unused place poisoned."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain import model as plain
+from tests.plain import sampling as plain_sampling
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+BF16_ULP = 2.0**-8  # one unit in the last place of bfloat16, relative
+
+
+def F():
+    from gtar_kimik3_public_b200.ops import functional
+
+    return functional
+
+
+def rand(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed), dtype=torch.float64) * scale
+
+
+def close(got, want, dtype, what, atol=1e-5):
+    got, want = got.double().cpu(), want.double()
+    assert torch.isfinite(got).all(), what
+    if dtype == torch.float32:
+        err = ((got - want).abs() / (want.abs() + 1)).max().item()
+        assert err < atol, f"{what}: {err:.3e}"
+    else:  # a bfloat16 result is the rounded 32-bit value: within one unit in the last place
+        err = ((got - want).abs() / (want.abs() + 1e-2)).max().item()
+        assert err < 1.01 * BF16_ULP, f"{what}: {err:.3e}"
+
+
+# ------------------------------------------------------------------ token-wise kernels
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab,hidden", [(37, 80), (1000, 1536)])
+def test_embed_rows(dtype, vocab, hidden):
+    table = rand(vocab, hidden).to(dtype)
+    ids = torch.tensor([0, vocab - 1, 5, 5, vocab // 2], dtype=torch.int32)
+    out = F().embed_rows(table.to(DEV), ids.to(DEV))
+    assert out.dtype == torch.float32 and torch.equal(out.cpu(), table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("hidden", [80, 1000, 5120])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("weight_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(hidden, out_dtype, weight_dtype):
+    n, eps = 7, 3e-5
+    h = rand(n, hidden, seed=1, scale=3.0).float()
+    delta = rand(n, hidden, seed=2).to(out_dtype)
+    w = (1 + 0.1 * rand(hidden, seed=3)).to(weight_dtype)
+    want_h = h.double() + delta.double()
+    want = plain.rms_norm(want_h, w.double(), eps)
+    hd = h.to(DEV)
+    got = F().add_rmsnorm(hd, delta.to(DEV), w.to(DEV), eps, out_dtype)
+    close(got, want, out_dtype, "add_rmsnorm out")
+    assert torch.equal(hd.cpu(), (h + delta.float()))  # the stream holds the 32-bit sum
+    # without delta the stream is left alone
+    hd2 = h.to(DEV)
+    got2 = F().add_rmsnorm(hd2, None, w.to(DEV), eps, out_dtype)
+    close(got2, plain.rms_norm(h.double(), w.double(), eps), out_dtype, "rmsnorm without delta")
+    assert torch.equal(hd2.cpu(), h)
+    # chosen rows: same numbers as the full call, stream untouched
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    hd3 = h.to(DEV)
+    got3 = F().add_rmsnorm(hd3, delta.to(DEV), w.to(DEV), eps, out_dtype, rows=rows.to(DEV))
+    assert torch.equal(got3.cpu(), got.cpu()[rows.long()]) and torch.equal(hd3.cpu(), h)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    n, inter = 5, 224 + 3
+    gu = rand(n, 2 * inter, seed=4, scale=3.0).to(dtype)
+    g, u = gu[:, :inter].double(), gu[:, inter:].double()
+    close(F().swiglu(gu.to(DEV)), g * torch.sigmoid(g) * u, dtype, "swiglu")
+
+
+def scrambled_pages(n_seqs, max_len, n_kv, d, dtype, seed=0, page=64, extra=3):
+    """A PagedKV whose pages are handed out in random order, every place poisoned with NaN."""
+    per_seq = -(-max_len // page)
+    n_pages = n_seqs * per_seq + extra
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed))
+    table = torch.full((n_seqs + 2, per_seq), -1, dtype=torch.int32)
+    slots = torch.randperm(n_seqs + 2, generator=torch.Generator().manual_seed(seed + 1))[:n_seqs].to(torch.int32)
+    for i in range(n_seqs):
+        table[slots[i]] = perm[i * per_seq:(i + 1) * per_seq].to(torch.int32)
+    k = torch.full((n_pages, n_kv, page, d), float("nan"), dtype=dtype)
+    v = torch.full((n_pages, n_kv, page, d), float("nan"), dtype=dtype)
+    return F().PagedKV(k.to(DEV), v.to(DEV), table.clamp(min=0).to(DEV)), slots, table
+
+
+def fill_pages(kv, table, slot, keys, values):
+    """Writes a sequence's keys and values [len, n_kv, d] into its pages (test-side, with torch)."""
+    page = kv.page_size
+    for start in range(0, keys.shape[0], page):
+        p = int(table[slot, start // page])
+        n = min(page, keys.shape[0] - start)
+        kv.k[p, :, :n] = keys[start:start + n].transpose(0, 1).to(kv.k.dtype).to(DEV)
+        kv.v[p, :, :n] = values[start:start + n].transpose(0, 1).to(kv.v.dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d,theta", [(6, 3, 48, 1e4), (4, 1, 128, 1e6), (5, 5, 16, 5e5)])
+def test_qk_norm_rope_write(dtype, n_q, n_kv, d, theta):
+    eps = 2e-6
+    lens = [70, 1, 130]
+    past = [60, 0, 3]  # tokens already cached; the step brings the rest
+    kv, slots, table = scrambled_pages(3, 130, n_kv, d, dtype, seed=5)
+    width = (n_q + 2 * n_kv) * d
+    rows, pos, seq = [], [], []
+    for i, (n, p) in enumerate(zip(lens, past)):
+        rows.append(rand(n - p, width, seed=10 + i).to(dtype))
+        pos += list(range(p, n))
+        seq += [i] * (n - p)
+    qkv = torch.cat(rows)
+    wq = (1 + 0.1 * rand(d, seed=20)).float()
+    wk = (1 + 0.1 * rand(d, seed=21)).float()
+    cos, sin = plain.rotary_tables(torch.arange(131), d, theta)
+    tok_pos = torch.tensor(pos, dtype=torch.int32)
+    q = F().qk_norm_rope_write(
+        qkv.to(DEV), n_q, n_kv, d, wq.to(DEV), wk.to(DEV), eps, cos[:, : d // 2].contiguous().to(DEV),
+        sin[:, : d // 2].contiguous().to(DEV), tok_pos.to(DEV), torch.tensor(seq, dtype=torch.int32).to(DEV),
+        slots.to(DEV), kv, max(pos))
+    x = qkv.double().view(-1, n_q + 2 * n_kv, d)
+    c, s = cos[tok_pos.long()].double(), sin[tok_pos.long()].double()
+    want_q = plain.apply_rotary(plain.rms_norm(x[:, :n_q], wq.double(), eps), c, s)
+    want_k = plain.apply_rotary(plain.rms_norm(x[:, n_q:n_q + n_kv], wk.double(), eps), c, s)
+    want_v = x[:, n_q + n_kv:]
+    close(q, want_q, dtype, "q")
+    written = torch.zeros(kv.k.shape[0], kv.page_size, dtype=torch.bool)
+    for t, (p, i) in enumerate(zip(pos, seq)):
+        page = int(table[slots[i], p // 64])
+        close(kv.k[page, :, p % 64], want_k[t], dtype, f"k of token {t}")
+        close(kv.v[page, :, p % 64], want_v[t], dtype, f"v of token {t}", atol=1e-7)
+        written[page, p % 64] = True
+    # nothing else was written: every other place still holds its poison
+    assert torch.isnan(kv.k.cpu().float()[~written[:, None, :].expand(-1, n_kv, -1)]).all()
+
+
+def test_qk_write_without_norm_or_rotation_and_read_only():
+    n_q, n_kv, d = 2, 2, 32
+    kv, slots, table = scrambled_pages(1, 10, n_kv, d, torch.float32)
+    qkv = rand(10, (n_q + 2 * n_kv) * d).float()
+    ids = torch.arange(10, dtype=torch.int32).to(DEV)
+    zeros = torch.zeros(10, dtype=torch.int32).to(DEV)
+    q = F().qk_norm_rope_write(qkv.to(DEV), n_q, n_kv, d, None, None, 1.0, None, None, ids, zeros, slots.to(DEV), kv, 9,
+                               write_kv=False)
+    assert torch.equal(q.cpu().view(10, -1), qkv[:, : n_q * d]) and torch.isnan(kv.k).all()
+    F().qk_norm_rope_write(qkv.to(DEV), n_q, n_kv, d, None, None, 1.0, None, None, ids, zeros, slots.to(DEV), kv, 9)
+    page = int(table[slots[0], 0])
+    assert torch.equal(kv.k[page, :, :10].cpu().transpose(0, 1).reshape(10, -1), qkv[:, n_q * d:(n_q + n_kv) * d])
+
+
+# ------------------------------------------------------------------ 32-bit matrix product
+@pytest.mark.parametrize("m,n,k", [(1, 71, 53), (37, 300, 1000), (130, 129, 257), (64, 1000, 7)])
+@pytest.mark.parametrize("a_dtype,c_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+def test_gemm_f32_is_true_32_bit(m, n, k, a_dtype, c_dtype):
+    a = rand(m, k, seed=1).to(a_dtype)
+    w = rand(n, k, seed=2).float()
+    got = F().linear_f32(a.to(DEV), w.to(DEV), c_dtype)
+    want = a.double() @ w.double().T
+    if c_dtype == torch.float32:
+        # TF32 or bfloat16 products would miss by ~1e-3 * sqrt(k); float32 chains stay near 1e-6 * sqrt(k)
+        err = (got.double().cpu() - want).abs().max().item()
+        assert err < 2e-6 * math.sqrt(k) * 4, f"{err:.3e}"
+    else:
+        close(got, want, c_dtype, "gemm bf16 out")
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch():
+    a = rand(200, 333, seed=3).float().to(DEV)
+    w = rand(150, 333, seed=4).float().to(DEV)
+    whole = F().linear_f32(a, w)
+    for start, stop in ((0, 1), (7, 8), (100, 164), (199, 200)):
+        assert torch.equal(F().linear_f32(a[start:stop].contiguous(), w), whole[start:stop])
+
+
+# ------------------------------------------------------------------ attention
+def dense_attention(q, k, v, past, window=None):
+    """Plain attention of the last len(q) positions of one sequence: q [T, n_q, d], k/v [S, n_kv, d]."""
+    n_kv = k.shape[1]
+    full_q = torch.zeros(k.shape[0], q.shape[1], q.shape[2], dtype=torch.float64)
+    full_q[past:] = q
+    return plain.causal_gqa_attention(full_q, k, v, window)[past:]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d", [(4, 4, 16), (4, 2, 48), (6, 2, 80), (8, 2, 128)])
+def test_attention_exact_varlen(dtype, n_q, n_kv, d):
+    lens, past = [1, 777, 1000, 64], [0, 700, 999, 0]  # whole prompts, a continuation, a decode step
+    kv, slots, table = scrambled_pages(4, 1000, n_kv, d, dtype, seed=8)
+    qs, pos, seq, wants = [], [], [], []
+    for i, (n, p) in enumerate(zip(lens, past)):
+        k = rand(n, n_kv, d, seed=30 + i).to(dtype)
+        v = rand(n, n_kv, d, seed=40 + i).to(dtype)
+        q = rand(n - p, n_q, d, seed=50 + i).to(dtype)
+        fill_pages(kv, table, int(slots[i]), k, v)
+        qs.append(q)
+        pos += list(range(p, n))
+        seq += [i] * (n - p)
+        wants.append(dense_attention(q.double(), k.double(), v.double(), p))
+    out = F().attention_exact(torch.cat(qs).to(DEV), kv, torch.tensor(pos, dtype=torch.int32).to(DEV),
+                              torch.tensor(seq, dtype=torch.int32).to(DEV), slots.to(DEV), d**-0.5)
+    want = torch.cat(wants)
+    got = out.double().cpu()
+    assert torch.isfinite(got).all()  # no poisoned place was read
+    tol = 2e-5 if dtype == torch.float32 else 1.5 * BF16_ULP * want.abs().max().item() + 1e-3
+    assert (got - want).abs().max().item() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    n_q, n_kv, d, n = 4, 2, 64, 900
+    kv, slots, table = scrambled_pages(1, n, n_kv, d, dtype, seed=9)
+    k = rand(n, n_kv, d, seed=1, scale=0.1)
+    v = rand(n, n_kv, d, seed=2)
+    q = rand(1, n_q, d, seed=3, scale=0.1)
+    far = {0: 3, 1: 517}  # kv head -> the key that must win, one near the start, one deep inside
+    for hk, j in far.items():
+        direction = torch.ones(d, dtype=torch.float64)
+        k[j, hk] = 6.0 * direction
+        q[0, 2 * hk] = 6.0 * direction  # query heads 0 and 2: score 36*64/8 = 288 against O(1) elsewhere
+    fill_pages(kv, table, int(slots[0]), k.to(dtype), v.to(dtype))
+    out = F().attention_exact(q.to(dtype).to(DEV), kv, torch.tensor([n - 1], dtype=torch.int32).to(DEV),
+                              torch.zeros(1, dtype=torch.int32).to(DEV), slots.to(DEV), d**-0.5).double().cpu()
+    for hk, j in far.items():
+        assert (out[0, 2 * hk] - v[j, hk].to(dtype).double()).abs().max() < 1e-5, f"kv head {hk}: key {j} was not found"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_window_edge(dtype):
+    n_q, n_kv, d, n, window = 2, 1, 32, 300, 100
+    kv, slots, table = scrambled_pages(1, n, n_kv, d, dtype, seed=10)
+    k = rand(n, n_kv, d, seed=1, scale=0.1)
+    v = rand(n, n_kv, d, seed=2)
+    q = rand(1, n_q, d, seed=3, scale=0.1)
+    pos = n - 1
+    inside, outside = pos - window + 1, pos - window  # the last key inside the window, the first outside
+    k[inside, 0] = 4.0
+    k[outside, 0] = 8.0  # would win by far if it were visible
+    q[0, :] = 4.0
+    fill_pages(kv, table, int(slots[0]), k.to(dtype), v.to(dtype))
+    args = (q.to(dtype).to(DEV), kv, torch.tensor([pos], dtype=torch.int32).to(DEV),
+            torch.zeros(1, dtype=torch.int32).to(DEV), slots.to(DEV), d**-0.5)
+    out = F().attention_exact(*args, window=window).double().cpu()
+    assert (out[0, 0] - v[inside, 0].to(dtype).double()).abs().max() < 1e-5
+    out_all = F().attention_exact(*args, window=0).double().cpu()
+    assert (out_all[0, 0] - v[outside, 0].to(dtype).double()).abs().max() < 1e-5
+    want = dense_attention(q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double(), pos, window)
+    assert (out - want).abs().max() < (2e-5 if dtype == torch.float32 else 2e-2)
+
+
+def test_attention_exact_is_the_same_for_any_cut():
+    n_q, n_kv, d, n = 4, 2, 48, 200
+    kv, slots, table = scrambled_pages(1, n, n_kv, d, torch.float32, seed=11)
+    fill_pages(kv, table, int(slots[0]), rand(n, n_kv, d, seed=1).float(), rand(n, n_kv, d, seed=2).float())
+    q = rand(n, n_q, d, seed=3).float().to(DEV)
+    zeros = torch.zeros(n, dtype=torch.int32).to(DEV)
+    pos = torch.arange(n, dtype=torch.int32).to(DEV)
+    whole = F().attention_exact(q, kv, pos, zeros, slots.to(DEV), d**-0.5)
+    for t in (0, 31, 32, 63, 64, 199):
+        one = F().attention_exact(q[t:t + 1].contiguous(), kv, pos[t:t + 1].contiguous(), zeros[:1].contiguous(),
+                                  slots.to(DEV), d**-0.5)
+        assert torch.equal(one[0], whole[t])
+
+
+# ------------------------------------------------------------------ token choice
+@pytest.mark.parametrize("vocab", [384, 1000 + 7, 151936])
+def test_argmax_lowest_index_wins(vocab):
+    logits = rand(5, vocab, seed=1).float()
+    logits[1, 17] = logits[1, vocab - 1] = 50.0
+    logits[2, vocab - 1] = 60.0
+    logits[3, 0] = 60.0
+    logits[4] = -3.0  # all equal
+    got = F().argmax(logits.to(DEV)).cpu().tolist()
+    assert got == [int(logits[0].argmax()), 17, vocab - 1, 0, 0]
+
+
+@pytest.mark.parametrize("vocab,top_k", [(384, 0), (1007, 50), (1007, 1), (151936, 50), (4000, 5000)])
+def test_sample_matches_the_plain_sampler(vocab, top_k):
+    n, seed, temperature = 6, 1234, 0.8
+    logits = rand(n, vocab, seed=2, scale=2.0).float()
+    if top_k:
+        logits[0, :100] = logits[0, 0]  # a hundred-way tie around the threshold
+    requests = torch.tensor([0, 1, 2, 77, 4, 5], dtype=torch.int32)
+    steps = torch.tensor([0, 0, 9, 3, 100000, 1], dtype=torch.int32)
+    steps_dev = steps.to(DEV)
+    got = F().sample(logits.to(DEV), temperature, top_k, seed, requests.to(DEV), steps_dev, advance_steps=True).cpu().tolist()
+    want = [plain_sampling.sample(logits[i].numpy(), temperature, top_k, seed, int(requests[i]), int(steps[i]))
+            for i in range(n)]
+    assert got == want
+    assert torch.equal(steps_dev.cpu(), steps + 1)
+
+
+def test_sample_follows_the_softmax():
+    logits = torch.tensor([[1.0, 0.0, -1.0, 2.0, 0.5]]).repeat(4096, 1)
+    z = logits[0].double() / 0.7
+    p = torch.softmax(z, 0)
+    counts = torch.zeros(5)
+    requests = torch.arange(4096, dtype=torch.int32).to(DEV)
+    for step in range(4):
+        steps = torch.full((4096,), step, dtype=torch.int32).to(DEV)
+        tokens = F().sample(logits.to(DEV), 0.7, 0, 9, requests, steps).cpu()
+        counts += torch.bincount(tokens.long(), minlength=5)
+    assert (counts / counts.sum() - p).abs().max() < 0.015
