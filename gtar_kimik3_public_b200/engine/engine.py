@@ -100,3 +100,21 @@ class Engine:
         logits = self.model.step(ctx, self.cache)
         self.steps_run += 1
         return logits
+
+    def decode_on_device(self, request_ids: list, tokens: torch.Tensor) -> torch.Tensor:
+        """One token for each of the listed live requests, the token ids being on the device already
+        (int32 ``[n]``, for instance the sampler's output): no token crosses to the host.  Returns
+        float32 logits ``[n, vocab]``.  The ids are trusted to lie inside the vocabulary."""
+        if tokens.dtype != torch.int32 or tokens.dim() != 1 or tokens.shape[0] != len(request_ids):
+            raise ValueError("tokens must be int32 [n] with one entry per request")
+        slots = [self.slot_of[r] for r in request_ids]
+        growth = {slot: 1 for slot in slots}
+        if len(growth) != len(slots):
+            raise ValueError("a request appears twice in one step")
+        if not self.cache.can_grow(growth):
+            raise CacheFull("no room in the cache for one more token of every request")
+        sequences = [SequenceStep(slot, self.cache.grow(slot, 1), [0], [0]) for slot in slots]
+        self.cache.sync()
+        ctx = plan_step(sequences, self.model.dtype, self.model.device, self.model.vocab_size, device_tokens=tokens)
+        self.steps_run += 1
+        return self.model.step(ctx, self.cache)

@@ -26,7 +26,10 @@ class SequenceStep:
     want: list[int]  # places among ``tokens`` whose logits are asked for
 
 
-def plan_step(sequences: list[SequenceStep], dtype: torch.dtype, device: torch.device, vocab_size: int) -> StepContext:
+def plan_step(sequences: list[SequenceStep], dtype: torch.dtype, device: torch.device, vocab_size: int,
+              device_tokens: torch.Tensor | None = None) -> StepContext:
+    """Builds the step's context.  With ``device_tokens`` (int32, one per packed token, already on
+    the device — e.g. the sampler's output) the sequences' ``tokens`` only give the counts."""
     if not sequences:
         raise ValueError("a step needs at least one sequence")
     tokens: list[int] = []
@@ -42,9 +45,10 @@ def plan_step(sequences: list[SequenceStep], dtype: torch.dtype, device: torch.d
             if not 0 <= place < n:
                 raise ValueError(f"wanted place {place} is outside the {n} tokens sequence {index} brings")
             want_rows.append(cu_q[-1] + place)
-        for token in seq.tokens:
-            if not 0 <= token < vocab_size:
-                raise ValueError(f"token id {token} is outside the vocabulary of {vocab_size}")
+        if device_tokens is None:
+            for token in seq.tokens:
+                if not 0 <= token < vocab_size:
+                    raise ValueError(f"token id {token} is outside the vocabulary of {vocab_size}")
         tokens.extend(seq.tokens)
         tok_pos.extend(range(seq.past_len, seq.past_len + n))
         tok_seq.extend([index] * n)
@@ -64,7 +68,7 @@ def plan_step(sequences: list[SequenceStep], dtype: torch.dtype, device: torch.d
     q_lens = [len(s.tokens) for s in sequences]
     return StepContext(
         n_tokens=len(tokens), n_seqs=len(sequences), dtype=dtype,
-        tokens=views[0], tok_pos=views[1], tok_seq=views[2], cu_q=views[3], slots=views[4], kv_len=views[5],
+        tokens=views[0] if device_tokens is None else device_tokens, tok_pos=views[1], tok_seq=views[2], cu_q=views[3], slots=views[4], kv_len=views[5],
         want_rows=views[6], max_q_len=max(q_lens), max_kv_len=max(kv_len), max_position=max(kv_len) - 1,
         all_single=all(n == 1 for n in q_lens), host_q_len=q_lens, host_past_len=[s.past_len for s in sequences], host_slots=slots,
     )

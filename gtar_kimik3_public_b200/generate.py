@@ -57,7 +57,9 @@ class Generator:
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64, temperature: float = 1.0,
                  top_k: int | None = None, eos_token_id: int | None = None, stop_ids: Sequence[int] = (),
-                 seed: int = 42) -> list[list[int]]:
+                 seed: int = 42, on_step=None) -> list[list[int]]:
+        """``on_step(live, tokens)``, if given, is called after every step once the step's tokens
+        have reached the host (``tokens``: one id per live sequence)."""
         stops = set(int(s) for s in stop_ids)
         if eos_token_id is not None:
             stops.add(int(eos_token_id))
@@ -73,7 +75,7 @@ class Generator:
             tokens = choose(logits, sampling, keys[0], keys[1])
             return tokens.cpu().tolist()
 
-        return run_generation(self.engine, prompts, params, chooser)
+        return run_generation(self.engine, prompts, params, chooser, on_step=on_step)
 
 
 def generate(model: Model, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64, temperature: float = 1.0,

@@ -97,7 +97,12 @@ def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+launch_count = 0  # entries into the kernel library since import (each is one or more kernel launches)
+
+
 def call(name: str, *args) -> None:
+    global launch_count
+    launch_count += 1
     lib = library()
     status = getattr(lib, name)(*args)
     if status != 0:
