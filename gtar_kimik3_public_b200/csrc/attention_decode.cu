@@ -1,0 +1,232 @@
+// Decode attention in bfloat16: one new token per sequence attends over its cached keys and
+// values in the paged cache.  Memory-bound: every cached key and value is read once per step
+// and is shared by all query heads of its group, which form the 16 rows of the tensor-core
+// tile (the reference expands nothing either: kv head = query head / group,
+// src/ops/flash_attention_2.py:33-34; visibility rule of src/layers/attention.py:116-119 with
+// one query at the last position).
+//
+// Grid (split, kv head, sequence).  A sequence's pages are divided among `n_splits` blocks so
+// that small batches still fill the GPU; each block streams its pages through a multi-stage
+// cp.async pipeline, its four warps taking 16 keys of a page each, and leaves an unnormalised
+// partial result (max, sum, output) in scratch memory; a second kernel merges the splits.
+// Lengths come from device memory, so a captured launch stays valid as sequences grow.
+//
+// Softmax statistics and accumulators are 32-bit; probabilities are rounded to bfloat16 for
+// the second product, as in the reference's kernel (flash_attention_2.py:55).
+
+#include "attention_mma.cuh"
+
+namespace {
+
+using namespace attn;
+
+constexpr int WARPS = 4;
+constexpr int STAGES = 3;
+
+template <int D>
+struct DecodeSmem {
+    __nv_bfloat16 k[STAGES][PAGE * D];
+    __nv_bfloat16 v[STAGES][PAGE * D];
+};
+
+template <int D>
+__global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+    const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+    float* __restrict__ part_ml, const int* __restrict__ kv_len, const int* __restrict__ slots,
+    const int* __restrict__ block_table, int n_q, int n_kv, int max_pages, float sl2, int window, int n_splits) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    DecodeSmem<D>& sm = *reinterpret_cast<DecodeSmem<D>*>(smem_raw);
+    const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int group = n_q / n_kv;
+    const int len = kv_len[seq];
+    const int lo = (window > 0 && len - window > 0) ? len - window : 0;  // first visible key
+    const int* pages = block_table + (size_t)slots[seq] * max_pages;
+    const int first_page = lo / PAGE, end_page = (len + PAGE - 1) / PAGE;
+    const int per_split = (end_page - first_page + n_splits - 1) / n_splits;
+    const int p_begin = first_page + split * per_split;
+    const int p_end = min(p_begin + per_split, end_page);
+    const int n_iter = max(p_end - p_begin, 0);
+
+    // Query fragments: row r of the tile is query head hk*group + r (rows >= group are zero).
+    uint32_t qf[D / 16][4];
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+        const __nv_bfloat16* qbase = q + ((size_t)seq * n_q + (size_t)hk * group) * D;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = r0 + (i & 1) * 8, c = ks * 16 + c0 + (i >> 1) * 8;
+                qf[ks][i] = r < group ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + c) : 0u;
+            }
+        }
+    }
+
+    auto issue = [&](int it) {
+        if (it < n_iter) {
+            const int p = p_begin + it;
+            const int page = pages[p];
+            const int valid = min(PAGE, len - p * PAGE);
+            const size_t base = ((size_t)page * n_kv + hk) * PAGE * D;
+            const int stage = it % STAGES;
+            load_tile_async<D>(sm.k[stage], k_pages + base, D, PAGE, valid, tid, WARPS * 32);
+            load_tile_async<D>(sm.v[stage], v_pages + base, D, PAGE, valid, tid, WARPS * 32);
+        }
+        cp_async_commit();
+    };
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    for (int it = 0; it < n_iter; ++it) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();  // page `it` has landed for everyone; the stage issued next was consumed an iteration ago
+        issue(it + STAGES - 1);
+        const int stage = it % STAGES;
+        const int key0 = warp * 16;
+        const int abs0 = (p_begin + it) * PAGE + key0;
+        if (abs0 < len && abs0 + 16 > lo) {  // warp-uniform: skip sixteen keys that are all hidden
+            float s[2][4];
+            qk_16keys<D>(s, qf, sm.k[stage], key0, lane);
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int key = abs0 + n * 8 + (lane & 3) * 2 + c;
+                    if (key >= len || key < lo) s[n][c] = s[n][2 + c] = -INFINITY;
+                }
+            uint32_t p[4];
+            softmax_update<D>(s, m, l, o, p, sl2);
+            pv_16keys<D>(o, p, sm.v[stage], key0, lane);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // Merge the four warps through shared memory (the stages are free now).
+    float* red_o = reinterpret_cast<float*>(smem_raw);          // [WARPS][16][D]
+    float* red_ml = red_o + WARPS * 16 * D;                    // [WARPS][16][2]
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = r0 + 8 * h;
+            if ((lane & 3) == 0) {
+                red_ml[(warp * 16 + r) * 2] = m[h];
+                red_ml[(warp * 16 + r) * 2 + 1] = l[h];
+            }
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) {
+                red_o[(warp * 16 + r) * D + j * 8 + c0] = o[j][2 * h];
+                red_o[(warp * 16 + r) * D + j * 8 + c0 + 1] = o[j][2 * h + 1];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < group * D; idx += WARPS * 32) {
+        const int r = idx / D, c = idx % D;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, red_ml[(w * 16 + r) * 2]);
+        float ll = 0.f, acc = 0.f;
+        if (mm != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float f = exp2f(red_ml[(w * 16 + r) * 2] - mm);
+                ll += red_ml[(w * 16 + r) * 2 + 1] * f;
+                acc += red_o[(w * 16 + r) * D + c] * f;
+            }
+        }
+        const int hq = hk * group + r;
+        if (n_splits == 1) {
+            out[((size_t)seq * n_q + hq) * D + c] = __float2bfloat16_rn(acc / ll);
+        } else {
+            const size_t at = ((size_t)seq * n_q + hq) * n_splits + split;
+            part_o[at * D + c] = acc;
+            if (c == 0) {
+                part_ml[at * 2] = mm;
+                part_ml[at * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+// out[seq, head, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),  M = max_s m_s
+template <int D>
+__global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              __nv_bfloat16* __restrict__ out, int n_splits) {
+    const size_t row = blockIdx.x;  // seq * n_q + head
+    const float* ml = part_ml + row * n_splits * 2;
+    float mm = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, ml[2 * s]);
+    float ll = 0.f;
+    for (int s = 0; s < n_splits; ++s)
+        if (ml[2 * s] != -INFINITY) ll += ml[2 * s + 1] * exp2f(ml[2 * s] - mm);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s)
+            if (ml[2 * s] != -INFINITY) acc += part_o[(row * n_splits + s) * D + c] * exp2f(ml[2 * s] - mm);
+        out[row * D + c] = __float2bfloat16_rn(acc / ll);
+    }
+}
+
+template <int D>
+int launch_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o, float* part_ml,
+                  const int* kv_len, const int* slots, const int* block_table, int n_seqs, int n_q, int n_kv,
+                  int max_pages, float scale, int window, int n_splits, cudaStream_t stream) {
+    const size_t stage_bytes = sizeof(DecodeSmem<D>);
+    const size_t merge_bytes = (size_t)WARPS * 16 * (D + 2) * sizeof(float);
+    const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
+    static bool configured = false;  // per template instance; the attribute is per device function
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem);
+        if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "attention_decode: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    const float sl2 = scale * 1.4426950408889634f;
+    dim3 grid(n_splits, n_kv, n_seqs);
+    attention_decode_kernel<D><<<grid, WARPS * 32, smem, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
+        part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits);
+    GK_CHECK_LAUNCH("attention_decode");
+    if (n_splits > 1) {
+        attention_decode_merge_kernel<D><<<n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml,
+                                                                                          (__nv_bfloat16*)out, n_splits);
+        GK_CHECK_LAUNCH("attention_decode_merge");
+    }
+    return GK_OK;
+}
+
+}  // namespace
+
+// Scratch the caller provides when n_splits > 1:
+//   part_o  float [n_seqs * n_q * n_splits * head_dim],  part_ml  float [n_seqs * n_q * n_splits * 2].
+GK_EXPORT int gk_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                       float* part_o, float* part_ml, const int* kv_len, const int* slots,
+                                       const int* block_table, int n_seqs, int n_q, int n_kv, int head_dim,
+                                       int max_pages, int page_size, float scale, int window, int n_splits,
+                                       void* stream) {
+    GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: bad head counts %d/%d", n_q, n_kv);
+    GK_REQUIRE(n_q / n_kv <= 16, "attention_decode: groups of more than 16 query heads per kv head are not supported");
+    GK_REQUIRE(page_size == attn::PAGE, "attention_decode: page_size must be %d, got %d", attn::PAGE, page_size);
+    GK_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode: head_dim %d is not 64 or 128 (use the exact kernel)", head_dim);
+    GK_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_kv <= 65535 && n_seqs <= 65535, "attention_decode: grid too large");
+    GK_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: scratch is needed for more than one split");
+    GK_REQUIRE(window >= 0, "attention_decode: window must be >= 0");
+    if (n_seqs == 0) return GK_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (head_dim == 64)
+        return launch_decode<64>(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv,
+                                 max_pages, scale, window, n_splits, s);
+    return launch_decode<128>(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv,
+                              max_pages, scale, window, n_splits, s);
+}

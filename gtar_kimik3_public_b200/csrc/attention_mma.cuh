@@ -1,0 +1,148 @@
+// Building blocks of the bfloat16 tensor-core attention kernels: asynchronous copies of a
+// page of keys or values into swizzled shared memory, matrix fragments, and the running
+// softmax of a 16-row tile.  Scores, maxima, sums and the output accumulator are 32-bit.
+#pragma once
+
+#include "common.cuh"
+
+namespace attn {
+
+constexpr int PAGE = 64;  // keys per page (the cache's page size)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// 16-byte asynchronous copy; `valid` = false writes zeros instead (nothing is read).
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+// A tile of rows x D bfloat16 in shared memory, rows of D*2 bytes, 16-byte chunks XOR-swizzled
+// with the row so that the eight rows of an ldmatrix fall into different banks.
+template <int D>
+__device__ __forceinline__ int swz(int row, int chunk) {
+    return row * (D / 8) + (chunk ^ (row & 7));
+}
+
+// Copies `rows` rows (each D bfloat16, contiguous, `src_row_stride` elements apart) into a swizzled
+// tile; rows at or beyond `valid_rows` are zero-filled.  All `n_threads` threads of the group take part.
+template <int D>
+__device__ __forceinline__ void load_tile_async(__nv_bfloat16* tile, const __nv_bfloat16* src, size_t src_row_stride,
+                                                int rows, int valid_rows, int tid, int n_threads) {
+    constexpr int CHUNKS = D / 8;
+    for (int c = tid; c < rows * CHUNKS; c += n_threads) {
+        const int row = c / CHUNKS, chunk = c % CHUNKS;
+        const bool valid = row < valid_rows;
+        const __nv_bfloat16* g = src + (valid ? (size_t)row * src_row_stride + chunk * 8 : 0);
+        cp_async_16(reinterpret_cast<uint4*>(tile) + swz<D>(row, chunk), g, valid);
+    }
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_row)));
+}
+
+// D(16x8, f32) += A(16x16, bf16, row) * B(16x8, bf16, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// S(16 x 16 keys) = Q(16 x D) K^T for the 16 keys starting at row `key0` of a swizzled K tile.
+// q[ks] are the A fragments of Q for the k-step ks.  s[0] holds keys key0..key0+7, s[1] the next 8.
+template <int D>
+__device__ __forceinline__ void qk_16keys(float (&s)[2][4], const uint32_t (&q)[D / 16][4], const __nv_bfloat16* k_tile,
+                                          int key0, int lane) {
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+    // ldmatrix.x4: lanes 0-7 give the rows of matrix 0 (keys 0-7, dims 0-7), 8-15 matrix 1 (keys 0-7, dims 8-15),
+    // 16-23 matrix 2 (keys 8-15, dims 0-7), 24-31 matrix 3 (keys 8-15, dims 8-15).
+    const int row = key0 + (lane & 7) + ((lane >> 4) << 3);
+    const int chunk_in_step = (lane >> 3) & 1;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t b[4];
+        ldmatrix_x4(b, reinterpret_cast<const uint4*>(k_tile) + swz<D>(row, ks * 2 + chunk_in_step));
+        mma_16816(s[0], q[ks], b[0], b[1]);
+        mma_16816(s[1], q[ks], b[2], b[3]);
+    }
+}
+
+// O(16 x D) += P(16 x 16 keys) V(16 keys x D) for the 16 keys starting at row `key0` of a swizzled V tile.
+template <int D>
+__device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (&p)[4], const __nv_bfloat16* v_tile,
+                                          int key0, int lane) {
+    // ldmatrix.x4.trans: matrix 0 = keys 0-7 x dims 0-7, 1 = keys 8-15 x dims 0-7, 2 = keys 0-7 x dims 8-15,
+    // 3 = keys 8-15 x dims 8-15  ->  (b0, b1) of the dim tile 2j and (b0, b1) of the dim tile 2j+1.
+    const int row = key0 + (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int chunk_in_pair = lane >> 4;
+#pragma unroll
+    for (int j = 0; j < D / 16; ++j) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, reinterpret_cast<const uint4*>(v_tile) + swz<D>(row, j * 2 + chunk_in_pair));
+        mma_16816(o[2 * j], p, b[0], b[1]);
+        mma_16816(o[2 * j + 1], p, b[2], b[3]);
+    }
+}
+
+// Running softmax over a 16-row tile.  A thread owns rows r0 = lane/4 and r0 + 8; index h = 0, 1.
+// Scores arrive raw; `sl2` = scale * log2(e).  Entries already set to -inf are masked.
+template <int D>
+__device__ __forceinline__ void softmax_update(float (&s)[2][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4],
+                                               uint32_t (&p)[4], float sl2) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float mx = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m[h], mx * sl2);
+        // a row that has seen no visible key yet keeps m = -inf; use 0 as the reference so exp2 gives 0, not NaN
+        const float ref = m_new == -INFINITY ? 0.f : m_new;
+        const float corr = exp2f(m[h] - ref);
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const float e = exp2f(s[n][2 * h + c] * sl2 - ref);
+                s[n][2 * h + c] = e;
+                sum += e;
+            }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l[h] = l[h] * corr + sum;
+        m[h] = m_new;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+            o[j][2 * h] *= corr;
+            o[j][2 * h + 1] *= corr;
+        }
+    }
+    p[0] = pack_bf16(s[0][0], s[0][1]);
+    p[1] = pack_bf16(s[0][2], s[0][3]);
+    p[2] = pack_bf16(s[1][0], s[1][1]);
+    p[3] = pack_bf16(s[1][2], s[1][3]);
+}
+
+}  // namespace attn

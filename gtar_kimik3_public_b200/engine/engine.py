@@ -28,11 +28,16 @@ class StepEntry:
 
 
 class Engine:
-    def __init__(self, model: Model, max_tokens: int, max_seqs: int | None = None):
+    def __init__(self, model: Model, max_tokens: int, max_seqs: int | None = None, use_graphs: bool = True):
         self.model = model
         self.cache: Cache = model.make_cache(max_tokens, max_seqs)
         self.slot_of: dict[object, int] = {}
         self.steps_run = 0
+        self.graphs = None
+        if use_graphs and model.device.type == "cuda" and model.graph_safe():
+            from .graphs import DecodeGraphs
+
+            self.graphs = DecodeGraphs(model, self.cache)
 
     # ------------------------------------------------------------------ requests
     def live(self) -> list[object]:
@@ -52,9 +57,12 @@ class Engine:
         self.end(list(self.slot_of))
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+    def step(self, entries: list[StepEntry], keep_output: bool = True) -> torch.Tensor:
         """Runs the entries' tokens as one batch from the cache and returns float32 logits
         ``[n_wanted, vocab]`` in the order of the entries and of each entry's ``want``.
+
+        ``keep_output=False`` allows the result to be a buffer that the next step overwrites (the
+        generation loop, which consumes the logits at once, asks for that).
 
         A request seen for the first time gets a slot; the others continue where they are.
         Nothing is changed when the step cannot run (no slot, not enough pages, a bad token).
@@ -96,15 +104,19 @@ class Engine:
             past = self.cache.grow(slot, len(entry.tokens))
             sequences.append(SequenceStep(slot, past, [int(t) for t in entry.tokens], [int(w) for w in entry.want]))
         self.cache.sync()
-        ctx = plan_step(sequences, self.model.dtype, self.model.device, vocab)
-        logits = self.model.step(ctx, self.cache)
         self.steps_run += 1
-        return logits
+        if self.graphs is not None and not new_ids and all(len(s.tokens) == 1 and s.want == [0] for s in sequences):
+            logits = self.graphs.run([s.slot for s in sequences], [s.past_len for s in sequences],
+                                     [s.tokens[0] for s in sequences])
+            return logits.clone() if keep_output else logits
+        ctx = plan_step(sequences, self.model.dtype, self.model.device, vocab)
+        return self.model.step(ctx, self.cache)
 
     def decode_on_device(self, request_ids: list, tokens: torch.Tensor) -> torch.Tensor:
         """One token for each of the listed live requests, the token ids being on the device already
         (int32 ``[n]``, for instance the sampler's output): no token crosses to the host.  Returns
-        float32 logits ``[n, vocab]``.  The ids are trusted to lie inside the vocabulary."""
+        float32 logits ``[n, vocab]`` in a buffer that the next step may overwrite.  The ids are
+        trusted to lie inside the vocabulary."""
         if tokens.dtype != torch.int32 or tokens.dim() != 1 or tokens.shape[0] != len(request_ids):
             raise ValueError("tokens must be int32 [n] with one entry per request")
         slots = [self.slot_of[r] for r in request_ids]
@@ -115,6 +127,8 @@ class Engine:
             raise CacheFull("no room in the cache for one more token of every request")
         sequences = [SequenceStep(slot, self.cache.grow(slot, 1), [0], [0]) for slot in slots]
         self.cache.sync()
-        ctx = plan_step(sequences, self.model.dtype, self.model.device, self.model.vocab_size, device_tokens=tokens)
         self.steps_run += 1
+        if self.graphs is not None:
+            return self.graphs.run(slots, [s.past_len for s in sequences], None, device_tokens=tokens)
+        ctx = plan_step(sequences, self.model.dtype, self.model.device, self.model.vocab_size, device_tokens=tokens)
         return self.model.step(ctx, self.cache)

@@ -96,7 +96,7 @@ def run_generation(engine, prompts: Sequence[Sequence[int]], params: GenerationP
         entries = [StepEntry(s.request_id, list(prompts[s.index]), [len(prompts[s.index]) - 1]) for s in live]
         try:
             while live:
-                logits = engine.step(entries)
+                logits = engine.step(entries, keep_output=False)
                 tokens = choose(logits, [request_offset + s.index for s in live], [len(s.produced) for s in live])
                 if on_step is not None:
                     on_step(live, tokens)

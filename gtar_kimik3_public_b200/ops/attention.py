@@ -1,4 +1,10 @@
-"""Attention over the paged cache: picks the kernel for the step's shape and dtype."""
+"""Attention over the paged cache: picks the kernel for the step's shape and dtype.
+
+* float32, or a head size the tensor-core kernels do not take: the exact kernel (any cut of the
+  work gives bit-equal results);
+* bfloat16, every sequence bringing one token: the split-KV decode kernel;
+* bfloat16 otherwise: the exact kernel until the step is a prefill the flash kernel takes.
+"""
 
 from __future__ import annotations
 
@@ -6,8 +12,16 @@ import torch
 
 from . import functional as F
 
+FAST_HEAD_DIMS = (64, 128)
+
 
 def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: int = 0) -> torch.Tensor:
     """Causal grouped-query attention of the step's queries ``[n_tokens, n_q, d]`` over each
     sequence's cached keys and values (the new tokens' own are already written)."""
+    n_q, d = q.shape[1], q.shape[2]
+    n_kv = kv.k.shape[1]
+    fast = q.dtype == torch.bfloat16 and d in FAST_HEAD_DIMS and kv.page_size == 64 and n_q // n_kv <= 16
+    if fast and ctx.all_single:
+        splits = ctx.extras.get("decode_splits") or F.decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len, kv.page_size)
+        return F.attention_decode(q, kv, ctx.kv_len, ctx.slots, scale, window, splits)
     return F.attention_exact(q, kv, ctx.tok_pos, ctx.tok_seq, ctx.slots, scale, window)

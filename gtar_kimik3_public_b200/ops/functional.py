@@ -228,6 +228,52 @@ def attention_exact(
     return out
 
 
+def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_count: int = 148) -> int:
+    """How many blocks share a sequence's pages in decode attention: enough that about two blocks
+    per SM are busy, never more than the longest sequence has pages."""
+    want = -(-2 * sm_count // max(1, n_seqs * n_kv))
+    return max(1, min(want, -(-max_kv_len // page_size), 64))
+
+
+def attention_decode(
+    q: torch.Tensor,
+    kv: PagedKV,
+    kv_len: torch.Tensor,
+    slots: torch.Tensor,
+    scale: float,
+    window: int = 0,
+    n_splits: int = 1,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Attention of one new token per sequence (``q [n_seqs, n_q, d]`` bfloat16, ``d`` 64 or 128) over
+    the pages; ``kv_len[i]`` counts the sequence's cached tokens including the new one.  With
+    ``n_splits > 1`` the partial results go through scratch memory allocated here."""
+    require_device(q.device)
+    _check(q, "q", torch.bfloat16, 3)
+    n, n_q, d = q.shape
+    _check(kv.k, "k pages", torch.bfloat16, 4)
+    _check(kv.v, "v pages", torch.bfloat16, 4)
+    _check(kv_len, "kv_len", torch.int32, 1)
+    _check(slots, "slots", torch.int32, 1)
+    if kv_len.shape[0] != n or slots.shape[0] != n:
+        raise KernelError("kv_len and slots need one entry per sequence")
+    n_kv = kv.k.shape[1]
+    if kv.k.shape[3] != d:
+        raise KernelError(f"pages have head_dim {kv.k.shape[3]}, queries {d}")
+    if out is None:
+        out = torch.empty_like(q)
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((n * n_q * n_splits * d,), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n * n_q * n_splits * 2,), dtype=torch.float32, device=q.device)
+    call(
+        "gk_attention_decode_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(part_o), ptr(part_ml), ptr(kv_len),
+        ptr(slots), ptr(kv.block_table), n, n_q, n_kv, d, kv.max_pages, kv.page_size, float(scale), int(window),
+        int(n_splits), stream_ptr(),
+    )
+    return out
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """Index of the largest logit of each row (lowest index on ties), int32."""
     require_device(logits.device)

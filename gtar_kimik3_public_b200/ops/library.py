@@ -35,6 +35,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_qk_norm_rope_write": [P, I, P, P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_gemm_f32": [P, I, P, P, I, I, I, I, L, L, L, P],
     "gk_attention_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "gk_attention_decode_bf16": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_argmax": [P, L, I, I, P, P],
     "gk_sample": [P, L, I, I, F, I, U, P, P, I, P, P],
 }

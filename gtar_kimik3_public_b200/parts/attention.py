@@ -18,6 +18,8 @@ from .base import KVRequest, Mixer, PositionEncoding, StepContext, TensorSpec, r
 
 
 class GQAAttention(Mixer):
+    graph_safe = True  # all per-step numbers are read from device memory by the kernels
+
     def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int, qk_norm_eps: float | None,
                  position: PositionEncoding | None, window: int | None = None):
         if n_q_heads % n_kv_heads:

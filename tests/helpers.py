@@ -11,9 +11,9 @@ import torch
 
 from tests.plain import model as plain
 from tests.plain.weights import read_safetensors
-from tests.tiny_configs import TINY_A, TINY_B
+from tests.tiny_configs import TINY_A, TINY_B, TINY_C
 
-CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B}
+CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
 WEIGHT_STD = 0.08  # wide enough that logits are O(1) and an error of 1e-3 is an error
 
 _folders: dict[tuple, tempfile.TemporaryDirectory] = {}
@@ -68,12 +68,12 @@ def plain_logits(tag: str, tokens: list[int], mode: str = "f64", seed: int = 0) 
     return _plain_cache[key]
 
 
-def load_engine(tag: str, dtype: str, max_tokens: int, seed: int = 0, max_seqs: int | None = None):
+def load_engine(tag: str, dtype: str, max_tokens: int, seed: int = 0, max_seqs: int | None = None, **options):
     from gtar_kimik3_public_b200.engine import Engine
     from gtar_kimik3_public_b200.generate import load
 
     model = load(model_folder(tag, seed), dtype, "cuda:0")
-    return Engine(model, max_tokens, max_seqs=max_seqs)
+    return Engine(model, max_tokens, max_seqs=max_seqs, **options)
 
 
 def poison(engine) -> None:

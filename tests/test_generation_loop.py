@@ -20,7 +20,8 @@ class ScriptedEngine:
         self.peak_live = 0
         self.ended = []
 
-    def step(self, entries):
+    def step(self, entries, keep_output=True):
+        assert keep_output is False  # the loop consumes the logits at once
         ids = [e.id for e in entries]
         lengths = {len(e.tokens) for e in entries}
         new = [i for i in ids if i not in self.slot_of]

@@ -312,3 +312,58 @@ def test_sample_follows_the_softmax():
         tokens = F().sample(logits.to(DEV), 0.7, 0, 9, requests, steps).cpu()
         counts += torch.bincount(tokens.long(), minlength=5)
     assert (counts / counts.sum() - p).abs().max() < 0.015
+
+
+# ------------------------------------------------------------------ bfloat16 decode attention (split-KV)
+@pytest.mark.parametrize("n_q,n_kv,d", [(4, 4, 64), (16, 8, 128), (6, 2, 128), (16, 1, 64)])
+@pytest.mark.parametrize("n_splits", [1, 3, 40])
+def test_attention_decode_bf16(n_q, n_kv, d, n_splits):
+    dtype = torch.bfloat16
+    lens = [1, 63, 64, 65, 777, 1000, 130]
+    kv, slots, table = scrambled_pages(len(lens), 1000, n_kv, d, dtype, seed=12)
+    qs, wants = [], []
+    for i, n in enumerate(lens):
+        k = rand(n, n_kv, d, seed=60 + i).to(dtype)
+        v = rand(n, n_kv, d, seed=70 + i).to(dtype)
+        q = rand(1, n_q, d, seed=80 + i).to(dtype)
+        fill_pages(kv, table, int(slots[i]), k, v)
+        qs.append(q)
+        wants.append(dense_attention(q.double(), k.double(), v.double(), n - 1))
+    kv_len = torch.tensor(lens, dtype=torch.int32).to(DEV)
+    out = F().attention_decode(torch.cat(qs).to(DEV), kv, kv_len, slots.to(DEV), d**-0.5, 0, n_splits)
+    got, want = out.double().cpu(), torch.cat(wants)
+    assert torch.isfinite(got).all()  # the poisoned places beyond each length were not used
+    # the yardstick: the exact kernel on the same bfloat16 inputs rounds its output once
+    assert (got - want).abs().max().item() < 1.5 * BF16_ULP * want.abs().max().item() + 2e-3
+
+
+def test_attention_decode_bf16_far_key_and_window():
+    dtype, n_q, n_kv, d, n = torch.bfloat16, 8, 2, 128, 900
+    kv, slots, table = scrambled_pages(1, n, n_kv, d, dtype, seed=13)
+    k = rand(n, n_kv, d, seed=1, scale=0.1)
+    v = rand(n, n_kv, d, seed=2)
+    q = rand(1, n_q, d, seed=3, scale=0.1)
+    k[5, 0] = 3.0
+    q[0, 1] = 3.0   # query head 1 (kv head 0) must find key 5: score 9*128/sqrt(128) = 102
+    k[517, 1] = 3.0
+    q[0, 6] = 3.0   # query head 6 (kv head 1) must find key 517
+    fill_pages(kv, table, int(slots[0]), k.to(dtype), v.to(dtype))
+    kv_len = torch.tensor([n], dtype=torch.int32).to(DEV)
+    for splits in (1, 7):
+        out = F().attention_decode(q.to(dtype).to(DEV), kv, kv_len, slots.to(DEV), d**-0.5, 0, splits).double().cpu()
+        assert (out[0, 1] - v[5, 0].to(dtype).double()).abs().max() < 1e-2
+        assert (out[0, 6] - v[517, 1].to(dtype).double()).abs().max() < 1e-2
+        # a window of 400 hides key 5 (visible keys are 500..899) but not key 517
+        win = F().attention_decode(q.to(dtype).to(DEV), kv, kv_len, slots.to(DEV), d**-0.5, 400, splits).double().cpu()
+        want = dense_attention(q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double(), n - 1, 400)
+        assert (win - want).abs().max() < 2e-2
+        assert (win[0, 1] - v[5, 0].to(dtype).double()).abs().max() > 0.1
+        # the key at the window's edge: 500 is the last one inside, 499 the first outside
+        k2 = k.clone()
+        k2[499, 0] = 6.0
+        k2[500, 0] = 3.0
+        k2[5, 0] = 0.0
+        fill_pages(kv, table, int(slots[0]), k2.to(dtype), v.to(dtype))
+        edge = F().attention_decode(q.to(dtype).to(DEV), kv, kv_len, slots.to(DEV), d**-0.5, 400, splits).double().cpu()
+        assert (edge[0, 1] - v[500, 0].to(dtype).double()).abs().max() < 1e-2
+        fill_pages(kv, table, int(slots[0]), k.to(dtype), v.to(dtype))

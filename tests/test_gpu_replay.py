@@ -10,8 +10,9 @@ from tests.helpers import CONFIGS, check_against_plain, load_engine, poison, req
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"tiny_a": [1, 5, 33, 64, 65, 100, 128], "tiny_b": [1, 9, 40, 64, 129, 200, 256]}
-CASES = [(tag, dtype) for tag in ("tiny_a", "tiny_b") for dtype in ("float32", "bfloat16")]
+LENGTHS = {"tiny_a": [1, 5, 33, 64, 65, 100, 128], "tiny_b": [1, 9, 40, 64, 129, 200, 256],
+           "tiny_c": [1, 31, 64, 130, 257, 400, 512]}
+CASES = [(tag, dtype) for tag in ("tiny_a", "tiny_b", "tiny_c") for dtype in ("float32", "bfloat16")]
 
 
 def _entry(request_id, tokens, want):
@@ -22,7 +23,7 @@ def _entry(request_id, tokens, want):
 
 @pytest.mark.parametrize("tag,dtype", CASES)
 def test_each_request_alone_and_whole(tag, dtype):
-    engine = load_engine(tag, dtype, max_tokens=256)
+    engine = load_engine(tag, dtype, max_tokens=512)
     poison(engine)
     for r, tokens in enumerate(requests_for(tag, LENGTHS[tag])):
         places = list(range(len(tokens)))
@@ -36,7 +37,7 @@ def test_each_request_alone_and_whole(tag, dtype):
 
 @pytest.mark.parametrize("tag,dtype", CASES)
 def test_last_32_tokens_one_by_one(tag, dtype):
-    engine = load_engine(tag, dtype, max_tokens=256)
+    engine = load_engine(tag, dtype, max_tokens=512)
     poison(engine)
     for r, tokens in enumerate(requests_for(tag, LENGTHS[tag])):
         if len(tokens) <= 32:
@@ -113,3 +114,27 @@ def test_wanted_places_subset_and_empty(tag, dtype):
     nxt = engine.step([_entry("a", [a[0]], []), _entry("b", [b[0]], [0])])
     check_against_plain(tag, dtype, b + [b[0]], [70], nxt, "continuation after a step without wanted places")
     engine.end(["a", "b"])
+
+
+@pytest.mark.parametrize("tag,dtype", CASES)
+def test_replayed_graph_steps_equal_plain_launches(tag, dtype):
+    """Decode steps run from a captured CUDA graph give the very numbers of kernels launched one by one."""
+    requests = requests_for(tag, [70, 3, 64], seed=13)
+    results = []
+    for use_graphs in (False, True):
+        engine = load_engine(tag, dtype, max_tokens=3 * 128, max_seqs=3, use_graphs=use_graphs)
+        assert (engine.graphs is not None) == use_graphs
+        poison(engine)
+        engine.step([_entry(r, requests[r][:-20] or requests[r][:1], []) for r in range(3)])
+        fed = {r: max(1, len(requests[r]) - 20) for r in range(3)}
+        rows = []
+        live = [0, 1, 2]
+        while live:
+            rows.append(engine.step([_entry(r, [requests[r][fed[r]]], [0]) for r in live]))
+            for r in live:
+                fed[r] += 1
+            done = [r for r in live if fed[r] == len(requests[r])]
+            engine.end(done)
+            live = [r for r in live if r not in done]
+        results.append(torch.cat(rows))
+    assert torch.equal(results[0], results[1])

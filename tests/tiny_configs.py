@@ -34,3 +34,21 @@ TINY_B = {
     "initializer_range": 0.02,
     "max_position_embeddings": 256,
 }
+
+# A third small model whose head size (64) is one the bfloat16 tensor-core attention kernels take,
+# so that the engine's fast paths run in the replay tests too (group of 4, untied, another eps).
+TINY_C = {
+    "arch": "transformer",
+    "vocab_size": 320,
+    "hidden_size": 96,
+    "intermediate_size": 160,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 1,
+    "head_dim": 64,
+    "rms_norm_eps": 3e-6,
+    "rope_theta": 100000.0,
+    "tie_word_embeddings": False,
+    "initializer_range": 0.02,
+    "max_position_embeddings": 512,
+}
