@@ -52,8 +52,6 @@ class _KVGroup:
         self.pages = PageAllocator(n_pages)
         self.max_pages_per_seq = max_pages_per_seq
         self.table_host = torch.zeros((n_slots, max_pages_per_seq), dtype=torch.int32)
-        if device.type == "cuda":
-            self.table_host = self.table_host.pin_memory()
         self.table = torch.zeros((n_slots, max_pages_per_seq), dtype=torch.int32, device=device)
         self.owned: dict[int, dict[int, int]] = {}  # slot -> {page index in sequence: page}
         self.dirty: set[int] = set()
@@ -95,13 +93,18 @@ class _KVGroup:
             self.dirty.add(slot)
 
     def sync(self) -> None:
+        """Sends the changed rows of the page table to the device.  The rows are copied into a
+        pinned buffer of their own first: the host goes on changing ``table_host`` (a slot that is
+        given back and used again) while earlier copies may still wait in the stream, and a copy
+        must carry the numbers of the step it was issued for."""
         if not self.dirty:
             return
-        if len(self.dirty) * 4 >= self.table.shape[0]:
-            self.table.copy_(self.table_host, non_blocking=True)
-        else:
-            for slot in self.dirty:
-                self.table[slot].copy_(self.table_host[slot], non_blocking=True)
+        slots = sorted(self.dirty)
+        staged = self.table_host[slots]
+        if self.table.is_cuda:
+            staged = staged.pin_memory()
+        for i, slot in enumerate(slots):
+            self.table[slot].copy_(staged[i], non_blocking=True)
         self.dirty.clear()
 
     def view(self, entry: int) -> PagedKV:
