@@ -1,0 +1,372 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:  OUT[a, b] = sum_k A[a, k] * B[b, k]
+// for two K-major operands (every projection of the model is  y = x W^T  with x [M, K] and W [N, K],
+// src/layers/attention.py:62-65, src/layers/swiglu.py:9-11, so either may be "A").
+//
+//   prefill  (many tokens):  A = activations, B = weights   -> OUT row-major [M, N]
+//   decode   (M <= 64):      A = weights,     B = activations (swap-AB: the 128 rows of the MMA are
+//                            filled by weight rows, the few tokens sit on the MMA's N)  -> OUT^T
+//
+// One block computes a 128 x BN tile.  Operands come in through TMA (cp.async.bulk.tensor, 128-byte
+// swizzle, no multicast) into a ring of shared-memory stages guarded by mbarriers; one elected thread
+// issues tcgen05.mma with the accumulator in tensor memory; four warps read the accumulator back
+// with tcgen05.ld and write the result.  Warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// owner, warps 2-5 = epilogue.  Accumulation is 32-bit.
+//
+// Epilogues: plain store (bfloat16 or float32), SwiGLU over row pairs (gate and up rows interleaved:
+// even index = gate, odd = up, src/layers/swiglu.py:14), and split-K partial sums (float32, one
+// slab per split, summed by the consumer in a fixed order).
+//
+// Every wait on an mbarrier is bounded: after GK_SPIN_LIMIT polls the thread records a code in
+// *error_flag and leaves its loop; the block still drains its own copies, frees its tensor memory
+// and returns.
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;     // rows of A per tile = MMA M
+constexpr int BK = 64;      // k elements per stage = one 128-byte swizzle row
+constexpr int UMMA_K = 16;  // k per tcgen05.mma for 16-bit inputs
+constexpr int THREADS = 192;
+constexpr uint32_t GK_SPIN_LIMIT = 1u << 24;
+
+enum Epilogue : int { EPI_STORE = 0, EPI_SWIGLU_A = 1, EPI_SWIGLU_B = 2 };
+
+struct GemmParams {
+    int rows_a, rows_b, k_blocks;      // k_blocks = ceil(K / BK)
+    int k_blocks_per_split;
+    void* out;
+    long long stride_a, stride_b;      // element strides of OUT for the A index and the B index
+    long long split_stride;            // elements between split slabs (0 without split-K)
+    int out_dtype;                     // GK_F32 or GK_BF16
+    int epilogue;
+    int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < GK_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
+// swizzle: start address / 16, leading byte offset 1 (unused for swizzled K-major), stride byte
+// offset 1024 / 16 between groups of eight rows, descriptor version 1, layout type SWIZZLE_128B = 2.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: float32 accumulator, bfloat16 A and B, both K-major, M x N.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+
+template <typename T>
+__device__ __forceinline__ void store_out(void* out, long long index, float v) {
+    reinterpret_cast<T*>(out)[index] = from_float<T>(v);
+}
+
+template <int BN, int STAGES>
+struct alignas(1024) GemmSmem {
+    __nv_bfloat16 a[STAGES][BM * BK];
+    __nv_bfloat16 b[STAGES][BN * BK];
+    uint64_t full[STAGES], empty[STAGES], acc_ready;
+    uint32_t tmem_base;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                             const __grid_constant__ CUtensorMap map_b,
+                                                             const GemmParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    // the swizzled tiles must start on a 1024-byte boundary
+    GemmSmem<BN, STAGES>& sm =
+        *reinterpret_cast<GemmSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;  // a power of two >= 32 (BN is 16, 32, 64, 128 or 256)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    const int kb_begin = split * p.k_blocks_per_split;
+    const int kb_end = min(kb_begin + p.k_blocks_per_split, p.k_blocks);
+    const int n_kb = max(kb_end - kb_begin, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], 1);
+        }
+        mbar_init(&sm.acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_acc = sm.tmem_base;
+    constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * sizeof(__nv_bfloat16);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: stream A and B tiles of each k-block into the ring
+            int issued = 0;
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES) ok = mbar_wait(&sm.empty[s], ((i / STAGES) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+                const int k = (kb_begin + i) * BK;
+                tma_load_2d(sm.a[s], &map_a, k, tile_a * BM, &sm.full[s]);
+                tma_load_2d(sm.b[s], &map_b, k, tile_b * BN, &sm.full[s]);
+                issued = i + 1;
+            }
+            if (!ok) {
+                atomicExch(p.error_flag, 1);
+                // drain: copies already issued must land before this block's shared memory is given up
+                for (int i = max(issued - STAGES, 0); i < issued; ++i) mbar_wait(&sm.full[i % STAGES], (i / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            const uint32_t idesc = umma_idesc(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                ok = mbar_wait(&sm.full[s], (i / STAGES) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t da = umma_desc(a_addr + k * UMMA_K * 2), db = umma_desc(b_addr + k * UMMA_K * 2);
+                    umma(tmem_acc, da, db, idesc, i > 0 || k > 0);
+                }
+                umma_commit(&sm.empty[s]);  // the stage is free once these MMAs have read it
+            }
+            if (!ok) atomicExch(p.error_flag, 2);
+            umma_commit(&sm.acc_ready);  // arrives when every MMA issued above has finished
+        }
+    } else {
+        // ---- epilogue warps 2..5: TMEM lane quarter = warp % 4
+        const int quarter = warp & 3;
+        const int row_a = tile_a * BM + quarter * 32 + lane;
+        bool ok = true;
+        if (n_kb > 0) {
+            ok = mbar_wait(&sm.acc_ready, 0);
+            if (!ok && lane == 0) atomicExch(p.error_flag, 3);
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        char* out = reinterpret_cast<char*>(p.out);
+        const long long slab = (long long)split * p.split_stride;
+        const bool a_ok = row_a < p.rows_a;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            if (n_kb > 0 && ok) {
+                tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+            }
+            const int col0 = tile_b * BN + c0;
+            if (p.epilogue == EPI_STORE) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int rb = col0 + i;
+                    if (a_ok && rb < p.rows_b) {
+                        const long long at = slab + (long long)row_a * p.stride_a + (long long)rb * p.stride_b;
+                        if (p.out_dtype == GK_F32) store_out<float>(out, at, v[i]);
+                        else store_out<__nv_bfloat16>(out, at, v[i]);
+                    }
+                }
+            } else if (p.epilogue == EPI_SWIGLU_A) {
+                // gate and up alternate along A (TMEM lanes): even lane = gate, odd lane = up of channel row_a / 2
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
+                    const int rb = col0 + i;
+                    if ((lane & 1) == 0 && a_ok && rb < p.rows_b) {
+                        const long long at = (long long)(row_a >> 1) * p.stride_a + (long long)rb * p.stride_b;
+                        store_out<__nv_bfloat16>(out, at, silu(v[i]) * other);
+                    }
+                }
+            } else {
+                // gate and up alternate along B (TMEM columns)
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    const int rb = col0 + i;
+                    if (a_ok && rb + 1 < p.rows_b) {
+                        const long long at = (long long)row_a * p.stride_a + (long long)(rb >> 1) * p.stride_b;
+                        store_out<__nv_bfloat16>(out, at, silu(v[i]) * v[i + 1]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS));
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// A K-major matrix [rows, k] of bfloat16 with `ld` elements between rows; boxes of box_rows x 64.
+int make_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return gk_fail(GK_CUDA_ERROR, "gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(__nv_bfloat16)};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return gk_fail(GK_CUDA_ERROR, "gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return GK_OK;
+}
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, smem, stream>>>(ma, mb, p);
+    GK_CHECK_LAUNCH("gemm_tc");
+    return GK_OK;
+}
+
+}  // namespace
+
+// OUT[a, b] = sum_k A[a, k] B[b, k].  `bn` (16, 32, 64, 128 or 256) is the tile width along B.
+// With `splits` > 1, `out` must be float32 scratch of `splits` slabs `split_stride` elements apart;
+// each slab holds the partial sum of one range of k.  `error_flag` is a device int that stays 0
+// unless a wait inside the kernel gave up.
+GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const void* b, int rows_b, long long ldb, int k,
+                              void* out, int out_dtype, long long stride_a, long long stride_b, int epilogue, int bn,
+                              int splits, long long split_stride, int* error_flag, void* stream) {
+    GK_REQUIRE(rows_a > 0 && rows_b > 0 && k > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, k);
+    GK_REQUIRE(k % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
+               "gemm_tc: k and the row strides must be multiples of 8 elements (16 bytes for TMA); got k=%d lda=%lld ldb=%lld",
+               k, lda, ldb);
+    GK_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)b & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
+    GK_REQUIRE(GK_VALID_DTYPE(out_dtype), "gemm_tc: bad output dtype");
+    GK_REQUIRE(epilogue >= EPI_STORE && epilogue <= EPI_SWIGLU_B, "gemm_tc: bad epilogue %d", epilogue);
+    GK_REQUIRE(splits >= 1 && (splits == 1 || (epilogue == EPI_STORE && out_dtype == GK_F32)),
+               "gemm_tc: split-K writes float32 partial sums with the plain epilogue");
+    GK_REQUIRE(epilogue == EPI_STORE || out_dtype == GK_BF16, "gemm_tc: the SwiGLU epilogue writes bfloat16");
+    GK_REQUIRE(error_flag != nullptr, "gemm_tc: error_flag is required");
+    CUtensorMap ma, mb;
+    int status = make_map(&ma, a, rows_a, k, lda, BM);
+    if (status) return status;
+    status = make_map(&mb, b, rows_b, k, ldb, bn);
+    if (status) return status;
+    GemmParams p;
+    p.rows_a = rows_a;
+    p.rows_b = rows_b;
+    p.k_blocks = (k + BK - 1) / BK;
+    p.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
+    p.out = out;
+    p.stride_a = stride_a;
+    p.stride_b = stride_b;
+    p.split_stride = splits > 1 ? split_stride : 0;
+    p.out_dtype = out_dtype;
+    p.epilogue = epilogue;
+    p.error_flag = error_flag;
+    dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
+    GK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (bn) {
+        case 16: return launch<16, 8>(ma, mb, p, grid, s);
+        case 32: return launch<32, 8>(ma, mb, p, grid, s);
+        case 64: return launch<64, 6>(ma, mb, p, grid, s);
+        case 128: return launch<128, 3>(ma, mb, p, grid, s);
+        case 256: return launch<256, 4>(ma, mb, p, grid, s);
+        default: return gk_fail(GK_BAD_ARGUMENT, "gemm_tc: bn must be 16, 32, 64, 128 or 256, got %d", bn);
+    }
+}

@@ -228,6 +228,70 @@ def attention_exact(
     return out
 
 
+_error_flags: dict[int, torch.Tensor] = {}
+
+
+def error_flag(device: torch.device) -> torch.Tensor:
+    """The device int that kernels with bounded waits set when a wait gives up (0 = all well)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _error_flags:
+        _error_flags[index] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[index]
+
+
+def check_kernel_errors(device: torch.device | str = "cuda:0") -> None:
+    """Raises if a kernel gave up a wait since the last check (synchronises the device)."""
+    flag = error_flag(torch.device(device))
+    code = int(flag.item())
+    if code:
+        flag.zero_()
+        raise KernelError(f"a kernel gave up waiting on a barrier (code {code}); its output is not valid")
+
+
+EPI_STORE, EPI_SWIGLU_A, EPI_SWIGLU_B = 0, 1, 2
+SKINNY_M = 64  # up to this many tokens the weights take the MMA's 128 rows (swap-AB)
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
+            splits: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x [M, K] @ weight[N, K].T`` in bfloat16 on the tcgen05 tensor cores, float32 accumulation.
+
+    ``swiglu=True``: the rows of ``weight`` alternate gate, up, gate, up, ...; the result is
+    ``silu(gate) * up`` of width ``N / 2``.  ``splits > 1`` divides K among that many blocks per tile
+    and returns float32 partial sums ``[splits, M, N]`` for the consumer to add up.
+    """
+    require_device(x.device)
+    _check(x, "x", torch.bfloat16, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"x is {tuple(x.shape)} but weight is {tuple(weight.shape)}")
+    if swiglu and (n % 2 or splits != 1):
+        raise KernelError("the SwiGLU epilogue needs an even number of weight rows and no split-K")
+    n_out = n // 2 if swiglu else n
+    if splits > 1:
+        out_dtype = torch.float32
+        shape = (splits, m, n_out)
+    else:
+        shape = (m, n_out)
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=x.device)
+    _check(out, "out", out_dtype, len(shape))
+    if tuple(out.shape) != shape:
+        raise KernelError(f"out has shape {tuple(out.shape)}, expected {shape}")
+    flag = error_flag(x.device)
+    if m <= SKINNY_M:
+        bn = 16 if m <= 16 else 32 if m <= 32 else 64
+        call("gk_gemm_bf16_tc", ptr(weight), n, k, ptr(x), m, k, k, ptr(out), dtype_code(out_dtype), 1, n_out,
+             EPI_SWIGLU_A if swiglu else EPI_STORE, bn, splits, m * n_out, ptr(flag), stream_ptr())
+    else:
+        bn = 128 if n >= 128 else 64 if n >= 64 else 32 if n >= 32 else 16
+        call("gk_gemm_bf16_tc", ptr(x), m, k, ptr(weight), n, k, k, ptr(out), dtype_code(out_dtype), n_out, 1,
+             EPI_SWIGLU_B if swiglu else EPI_STORE, bn, splits, m * n_out, ptr(flag), stream_ptr())
+    return out
+
+
 def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_count: int = 148) -> int:
     """How many blocks share a sequence's pages in decode attention: enough that about two blocks
     per SM are busy, never more than the longest sequence has pages."""

@@ -367,3 +367,50 @@ def test_attention_decode_bf16_far_key_and_window():
         edge = F().attention_decode(q.to(dtype).to(DEV), kv, kv_len, slots.to(DEV), d**-0.5, 400, splits).double().cpu()
         assert (edge[0, 1] - v[500, 0].to(dtype).double()).abs().max() < 1e-2
         fill_pages(kv, table, int(slots[0]), k.to(dtype), v.to(dtype))
+
+
+# ------------------------------------------------------------------ tcgen05 matrix product
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 256, 128), (8, 4096, 1024), (13, 1000, 200), (64, 384, 1024),
+                                   (65, 128, 64), (128, 128, 128), (200, 1000, 520), (2048, 1024, 3072), (300, 151936, 1024)])
+def test_gemm_tc_plain(m, n, k):
+    x = rand(m, k, seed=1).to(torch.bfloat16)
+    w = rand(n, k, seed=2, scale=0.05).to(torch.bfloat16)
+    if n > 100000:  # compare a slice of the very wide case on the host
+        got = F().gemm_tc(x.to(DEV), w.to(DEV), torch.float32)
+        F().check_kernel_errors()
+        cols = torch.cat([torch.arange(0, 300), torch.arange(n - 300, n), torch.arange(70000, 70300)])
+        want = x.double() @ w.double()[cols].T
+        assert (got.cpu().double()[:, cols] - want).abs().max() < 1e-3 * (k ** 0.5)
+        return
+    want = x.double() @ w.double().T
+    for out_dtype in (torch.bfloat16, torch.float32):
+        got = F().gemm_tc(x.to(DEV), w.to(DEV), out_dtype)
+        F().check_kernel_errors()
+        err = (got.cpu().double() - want).abs().max().item()
+        bound = 2e-5 * (k ** 0.5) if out_dtype == torch.float32 else BF16_ULP * want.abs().max().item() + 1e-4
+        assert err < bound, f"{out_dtype}: {err:.3e} >= {bound:.3e}"
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(8, 1024, 2048, 16), (3, 256, 192, 2), (64, 1024, 3072, 7), (8, 128, 64, 4)])
+def test_gemm_tc_split_k(m, n, k, splits):
+    x = rand(m, k, seed=3).to(torch.bfloat16)
+    w = rand(n, k, seed=4, scale=0.05).to(torch.bfloat16)
+    parts = F().gemm_tc(x.to(DEV), w.to(DEV), splits=splits)
+    F().check_kernel_errors()
+    assert parts.shape == (splits, m, n) and parts.dtype == torch.float32
+    want = x.double() @ w.double().T
+    assert (parts.cpu().double().sum(0) - want).abs().max() < 2e-5 * (k ** 0.5)
+
+
+@pytest.mark.parametrize("m,inter,k", [(8, 3072, 1024), (5, 100, 72), (64, 224, 80), (300, 224, 136), (2048, 3072, 1024)])
+def test_gemm_tc_swiglu(m, inter, k):
+    x = rand(m, k, seed=5).to(torch.bfloat16)
+    gate = rand(inter, k, seed=6, scale=0.1).to(torch.bfloat16)
+    up = rand(inter, k, seed=7, scale=0.1).to(torch.bfloat16)
+    packed = torch.stack([gate, up], dim=1).reshape(2 * inter, k).contiguous()  # gate0, up0, gate1, up1, ...
+    got = F().gemm_tc(x.to(DEV), packed.to(DEV), swiglu=True)
+    F().check_kernel_errors()
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = g * torch.sigmoid(g) * u
+    assert got.shape == (m, inter)
+    assert (got.cpu().double() - want).abs().max() < BF16_ULP * want.abs().max().item() + 1e-3
