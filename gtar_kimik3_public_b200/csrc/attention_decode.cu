@@ -40,6 +40,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = n_q / n_kv;
+    pdl_wait();
+    pdl_launch_dependents();
     const int len = kv_len[seq];
     const int lo = (window > 0 && len - window > 0) ? len - window : 0;  // first visible key
     const int* pages = block_table + (size_t)slots[seq] * max_pages;
@@ -163,6 +165,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               __nv_bfloat16* __restrict__ out, int n_splits) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t row = blockIdx.x;  // seq * n_q + head
     const float* ml = part_ml + row * n_splits * 2;
     float mm = -INFINITY;
@@ -194,13 +198,13 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
     }
     const float sl2 = scale * 1.4426950408889634f;
     dim3 grid(n_splits, n_kv, n_seqs);
-    attention_decode_kernel<D><<<grid, WARPS * 32, smem, stream>>>(
+    gk_launch(attention_decode_kernel<D>, grid, dim3(WARPS * 32), smem, stream,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
         part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits);
     GK_CHECK_LAUNCH("attention_decode");
     if (n_splits > 1) {
-        attention_decode_merge_kernel<D><<<n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml,
-                                                                                          (__nv_bfloat16*)out, n_splits);
+        gk_launch(attention_decode_merge_kernel<D>, dim3(n_seqs * n_q), dim3(D <= 64 ? 64 : 128), 0, stream,
+                  (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, n_splits);
         GK_CHECK_LAUNCH("attention_decode_merge");
     }
     return GK_OK;

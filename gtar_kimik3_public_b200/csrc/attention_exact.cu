@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_exact_kernel(
     const int* __restrict__ block_table, int n_tokens, int n_q, int n_kv, int head_dim, int max_pages, int page_size,
     float scale, int window) {
     extern __shared__ float q_smem[];  // WARPS * head_dim
+    pdl_wait();
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * WARPS + warp;
     if (wid >= (long long)n_tokens * n_q) return;  // whole warp leaves together; no block-wide sync below
@@ -138,7 +140,7 @@ GK_EXPORT int gk_attention_exact(const void* q, const void* k_pages, const void*
     const size_t smem = (size_t)WARPS * head_dim * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     GK_DISPATCH_DTYPE(dtype, T, {
-        attention_exact_kernel<T><<<(unsigned)blocks, WARPS * 32, smem, s>>>(
+        gk_launch(attention_exact_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, s,
             (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, tok_pos, tok_seq, slots, block_table, n_tokens,
             n_q, n_kv, head_dim, max_pages, page_size, scale, window);
     })

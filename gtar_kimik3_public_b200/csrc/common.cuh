@@ -30,6 +30,33 @@ int gk_fail(int status, const char* fmt, ...);
             return gk_fail(GK_CUDA_ERROR, "%s: launch failed: %s", name, cudaGetErrorString(gk_err__)); \
     } while (0)
 
+// Programmatic dependent launch.  A kernel launched with the attribute may start while the kernel
+// before it in the stream still runs; it must call pdl_wait() before it touches anything that
+// kernel writes (or overwrites anything it reads).  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_gk_pdl;  // set through gk_set_pdl(): launch kernels with programmatic stream serialization
+
+// Launches `kernel` on `stream`, with the programmatic-dependent-launch attribute when it is switched on.
+template <typename... KArgs, typename... Args>
+inline cudaError_t gk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (g_gk_pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
 

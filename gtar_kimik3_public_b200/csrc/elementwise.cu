@@ -5,6 +5,9 @@
 //                       rotary   x*cos + rotate_half(x)*sin         src/layers/rope.py:17-33
 //                       SwiGLU   silu(gate) * up                    src/layers/swiglu.py:14
 // All arithmetic is 32-bit; inputs and outputs may be bfloat16.
+//
+// Where a kernel's input comes from a split-K matrix product it may arrive as `n_splits` float32
+// slabs (`split_stride` elements apart) that are summed here, slab 0 first, before anything else.
 
 #include "common.cuh"
 
@@ -12,6 +15,7 @@
 template <typename TT>
 __global__ void embed_rows_kernel(const TT* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                                   int hidden) {
+    pdl_wait();
     const int t = blockIdx.x;
     const TT* row = table + (size_t)ids[t] * hidden;
     float* dst = out + (size_t)t * hidden;
@@ -25,48 +29,61 @@ GK_EXPORT int gk_embed_rows(const void* table, int table_dtype, const int* ids, 
     if (n_tokens == 0) return GK_OK;
     const int threads = hidden >= 1024 ? 256 : 128;
     GK_DISPATCH_DTYPE(table_dtype, TT, {
-        embed_rows_kernel<TT><<<n_tokens, threads, 0, (cudaStream_t)stream>>>((const TT*)table, ids, out, hidden);
+        gk_launch(embed_rows_kernel<TT>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (const TT*)table, ids, out,
+                  hidden);
     })
     GK_CHECK_LAUNCH("embed_rows");
     return GK_OK;
 }
 
 // ---------------------------------------------------------------- residual add + RMSNorm
+template <typename TD>
+__device__ __forceinline__ float sum_slabs(const TD* __restrict__ p, size_t index, int n_splits, long long split_stride) {
+    float v = to_float(p[index]);
+    for (int s = 1; s < n_splits; ++s) v += to_float(p[index + (size_t)s * split_stride]);
+    return v;
+}
+
 // One block per output row.  h (32-bit residual stream) gets `delta` added in place when
 // `rows` is null; with `rows`, only the listed rows are read and h is left as it is (the
 // last norm of a step, taken at the wanted positions only).
 template <typename TD, typename TW, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const TW* __restrict__ w,
-                                   TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_splits,
+                                   long long split_stride, const TW* __restrict__ w, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float scratch[33];
+    pdl_wait();
     const int src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* hrow = h + (size_t)src * hidden;
-    const TD* drow = delta ? delta + (size_t)src * hidden : nullptr;
+    const bool has_delta = delta != nullptr;
+    const size_t dbase = (size_t)src * hidden;
     TO* orow = out + (size_t)blockIdx.x * hidden;
-    const bool write_back = (rows == nullptr) && (drow != nullptr);
+    const bool write_back = (rows == nullptr) && has_delta;
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = hrow[i];
-        if (drow) v += to_float(drow[i]);
+        if (has_delta) v += sum_slabs(delta, dbase + i, n_splits, split_stride);
         if (write_back) hrow[i] = v;
         ss += v * v;
     }
     ss = block_sum(ss, scratch);
+    pdl_launch_dependents();
     const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = hrow[i];
-        if (drow && !write_back) v += to_float(drow[i]);
+        if (has_delta && !write_back) v += sum_slabs(delta, dbase + i, n_splits, split_stride);
         orow[i] = from_float<TO>((v * inv) * to_float(w[i]));
     }
 }
 
-GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, const void* weight, int weight_dtype,
-                             void* out, int out_dtype, const int* rows, int n_out_rows, int hidden, float eps,
-                             void* stream) {
+GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, int n_splits, long long split_stride,
+                             const void* weight, int weight_dtype, void* out, int out_dtype, const int* rows,
+                             int n_out_rows, int hidden, float eps, void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(delta_dtype) && GK_VALID_DTYPE(weight_dtype) && GK_VALID_DTYPE(out_dtype),
                "add_rmsnorm: bad dtype code");
     GK_REQUIRE(n_out_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_out_rows, hidden);
     GK_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
+    GK_REQUIRE(n_splits >= 1, "add_rmsnorm: n_splits must be >= 1");
     if (n_out_rows == 0) return GK_OK;
     // A fixed block size: the order of the sum of squares must not depend on anything but the row.
     const int threads = 256;
@@ -74,8 +91,8 @@ GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, const
     GK_DISPATCH_DTYPE(delta_dtype, TD, {
         GK_DISPATCH_DTYPE(weight_dtype, TW, {
             GK_DISPATCH_DTYPE(out_dtype, TO, {
-                add_rmsnorm_kernel<TD, TW, TO><<<n_out_rows, threads, 0, s>>>(h, (const TD*)delta, (const TW*)weight,
-                                                                             (TO*)out, rows, hidden, eps);
+                gk_launch(add_rmsnorm_kernel<TD, TW, TO>, dim3(n_out_rows), dim3(threads), 0, s, h, (const TD*)delta,
+                          n_splits, split_stride, (const TW*)weight, (TO*)out, rows, hidden, eps);
             })
         })
     })
@@ -83,20 +100,25 @@ GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, const
     return GK_OK;
 }
 
-// ---------------------------------------------------------------- SwiGLU on a packed [gate | up] row
+// ---------------------------------------------------------------- SwiGLU on a packed row
+// interleaved = 0: rows are [gate (I) | up (I)];  1: gate and up alternate (g0 u0 g1 u1 ...).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, long long total) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, long long total,
+                              int interleaved) {
+    pdl_wait();
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const long long t = idx / inter;
     const int i = (int)(idx - t * inter);
-    const float g = to_float(gate_up[t * 2 * inter + i]);
-    const float u = to_float(gate_up[t * 2 * inter + inter + i]);
+    const T* row = gate_up + t * 2 * inter;
+    const float g = to_float(interleaved ? row[2 * i] : row[i]);
+    const float u = to_float(interleaved ? row[2 * i + 1] : row[inter + i]);
     const float act = g / (1.0f + expf(-g));
     out[idx] = from_float<T>(act * u);
 }
 
-GK_EXPORT int gk_swiglu(const void* gate_up, void* out, int dtype, int n_tokens, int inter, void* stream) {
+GK_EXPORT int gk_swiglu(const void* gate_up, void* out, int dtype, int n_tokens, int inter, int interleaved,
+                        void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(dtype), "swiglu: bad dtype %d", dtype);
     GK_REQUIRE(n_tokens >= 0 && inter > 0, "swiglu: bad sizes");
     const long long total = (long long)n_tokens * inter;
@@ -105,7 +127,8 @@ GK_EXPORT int gk_swiglu(const void* gate_up, void* out, int dtype, int n_tokens,
     const long long blocks = (total + threads - 1) / threads;
     GK_REQUIRE(blocks < 2147483647LL, "swiglu: too many elements");
     GK_DISPATCH_DTYPE(dtype, T, {
-        swiglu_kernel<T><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, inter, total);
+        gk_launch(swiglu_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream, (const T*)gate_up,
+                  (T*)out, inter, total, interleaved);
     })
     GK_CHECK_LAUNCH("swiglu");
     return GK_OK;
@@ -121,15 +144,18 @@ GK_EXPORT int gk_swiglu(const void* gate_up, void* out, int dtype, int n_tokens,
 // `use_norm` = 0 skips the normalisation, `cos_table` = null skips the rotation, so that the
 // same kernel serves a mixer without q/k norm or without positions; `k_pages` = null writes no
 // keys and values (a layer that reads the storage another layer fills).
-template <typename T, typename TW>
-__global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* __restrict__ wq,
-                                          const TW* __restrict__ wk, const float* __restrict__ cos_table,
-                                          const float* __restrict__ sin_table, const int* __restrict__ tok_pos,
-                                          const int* __restrict__ tok_seq, const int* __restrict__ slots,
-                                          const int* __restrict__ block_table, T* __restrict__ q_out,
-                                          T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int n_q,
-                                          int n_kv, int head_dim, int max_pages, int page_size, float eps,
-                                          int use_norm) {
+// TI is the projection's type (float32 slabs when it comes from a split-K product), T the type of
+// the queries and of the cache.
+template <typename TI, typename T, typename TW>
+__global__ void qk_norm_rope_write_kernel(const TI* __restrict__ qkv, int n_splits, long long split_stride,
+                                          const TW* __restrict__ wq, const TW* __restrict__ wk,
+                                          const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                          const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                          const int* __restrict__ slots, const int* __restrict__ block_table,
+                                          T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                          int n_tokens, int n_q, int n_kv, int head_dim, int max_pages, int page_size,
+                                          float eps, int use_norm) {
+    pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -137,7 +163,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* _
     if (wid >= (long long)n_tokens * n_heads) return;
     const int t = (int)(wid / n_heads);
     const int head = (int)(wid - (long long)t * n_heads);
-    const T* src = qkv + ((size_t)t * n_heads + head) * head_dim;
+    const size_t src = ((size_t)t * n_heads + head) * head_dim;
     const int pos = tok_pos[t];
     T* dst;
     const TW* w = nullptr;
@@ -160,7 +186,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* _
         }
     }
     if (!rotate) {
-        for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+        for (int i = lane; i < head_dim; i += 32) dst[i] = from_float<T>(sum_slabs(qkv, src + i, n_splits, split_stride));
         return;
     }
     const int half = head_dim >> 1;
@@ -168,14 +194,16 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* _
     if (use_norm) {
         float ss = 0.f;
         for (int p = lane; p < half; p += 32) {
-            const float a = to_float(src[p]), b = to_float(src[p + half]);
+            const float a = sum_slabs(qkv, src + p, n_splits, split_stride);
+            const float b = sum_slabs(qkv, src + p + half, n_splits, split_stride);
             ss += a * a + b * b;
         }
         ss = warp_sum(ss);
         inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
     }
     for (int p = lane; p < half; p += 32) {
-        float a = to_float(src[p]), b = to_float(src[p + half]);
+        float a = sum_slabs(qkv, src + p, n_splits, split_stride);
+        float b = sum_slabs(qkv, src + p + half, n_splits, split_stride);
         if (use_norm) {
             a = (a * inv) * to_float(w[p]);
             b = (b * inv) * to_float(w[p + half]);
@@ -191,13 +219,18 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* _
     }
 }
 
-GK_EXPORT int gk_qk_norm_rope_write(const void* qkv, int dtype, const void* wq, const void* wk, int weight_dtype,
-                                    const float* cos_table, const float* sin_table, int table_positions,
-                                    const int* tok_pos, const int* tok_seq, const int* slots, const int* block_table,
-                                    void* q_out, void* k_pages, void* v_pages, int n_tokens, int n_q, int n_kv,
-                                    int head_dim, int max_pages, int page_size, float eps, int use_norm,
-                                    int max_position, void* stream) {
-    GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(weight_dtype), "qk_norm_rope_write: bad dtype code");
+GK_EXPORT int gk_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits, long long split_stride, int dtype,
+                                    const void* wq, const void* wk, int weight_dtype, const float* cos_table,
+                                    const float* sin_table, int table_positions, const int* tok_pos,
+                                    const int* tok_seq, const int* slots, const int* block_table, void* q_out,
+                                    void* k_pages, void* v_pages, int n_tokens, int n_q, int n_kv, int head_dim,
+                                    int max_pages, int page_size, float eps, int use_norm, int max_position,
+                                    void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(weight_dtype) && GK_VALID_DTYPE(in_dtype),
+               "qk_norm_rope_write: bad dtype code");
+    GK_REQUIRE(in_dtype == dtype || in_dtype == GK_F32,
+               "qk_norm_rope_write: the projection is either of the cache's type or float32");
+    GK_REQUIRE(n_splits >= 1 && (n_splits == 1 || in_dtype == GK_F32), "qk_norm_rope_write: slabs are float32");
     GK_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && head_dim > 0 && head_dim % 2 == 0,
                "qk_norm_rope_write: bad sizes n_q=%d n_kv=%d head_dim=%d", n_q, n_kv, head_dim);
     GK_REQUIRE(page_size > 0 && max_pages > 0, "qk_norm_rope_write: bad page geometry");
@@ -212,13 +245,21 @@ GK_EXPORT int gk_qk_norm_rope_write(const void* qkv, int dtype, const void* wq, 
     const long long blocks = (warps + 3) / 4;
     GK_REQUIRE(blocks < 2147483647LL, "qk_norm_rope_write: too many tokens");
     cudaStream_t s = (cudaStream_t)stream;
+#define GK_QK_LAUNCH(TI)                                                                                             \
+    gk_launch(qk_norm_rope_write_kernel<TI, T, TW>, dim3((unsigned)blocks), dim3(threads), 0, s, (const TI*)qkv,      \
+              n_splits, split_stride, (const TW*)wq, (const TW*)wk, cos_table, sin_table, tok_pos, tok_seq, slots,    \
+              block_table, (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, n_q, n_kv, head_dim, max_pages, page_size,  \
+              eps, use_norm)
     GK_DISPATCH_DTYPE(dtype, T, {
         GK_DISPATCH_DTYPE(weight_dtype, TW, {
-            qk_norm_rope_write_kernel<T, TW><<<(unsigned)blocks, threads, 0, s>>>(
-                (const T*)qkv, (const TW*)wq, (const TW*)wk, cos_table, sin_table, tok_pos, tok_seq, slots, block_table,
-                (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, n_q, n_kv, head_dim, max_pages, page_size, eps, use_norm);
+            if (in_dtype == GK_F32) {
+                GK_QK_LAUNCH(float);
+            } else {
+                GK_QK_LAUNCH(T);
+            }
         })
     })
+#undef GK_QK_LAUNCH
     GK_CHECK_LAUNCH("qk_norm_rope_write");
     return GK_OK;
 }

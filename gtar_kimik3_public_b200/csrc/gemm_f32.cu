@@ -20,6 +20,8 @@ __global__ void __launch_bounds__(THREADS) gemm_f32_kernel(const TA* __restrict_
                                                            long long ldw, long long ldc) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_wait();
+    pdl_launch_dependents();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int ty = tid / (BN / TN), tx = tid % (BN / TN);
@@ -85,7 +87,7 @@ GK_EXPORT int gk_gemm_f32(const void* A, int a_dtype, const float* W, void* C, i
     cudaStream_t s = (cudaStream_t)stream;
     GK_DISPATCH_DTYPE(a_dtype, TA, {
         GK_DISPATCH_DTYPE(c_dtype, TC, {
-            gemm_f32_kernel<TA, TC><<<grid, THREADS, 0, s>>>((const TA*)A, W, (TC*)C, M, N, K, lda, ldw, ldc);
+            gk_launch(gemm_f32_kernel<TA, TC>, grid, dim3(THREADS), 0, s, (const TA*)A, W, (TC*)C, M, N, K, lda, ldw, ldc);
         })
     })
     GK_CHECK_LAUNCH("gemm_f32");

@@ -42,6 +42,9 @@ struct GemmParams {
     long long split_stride;            // elements between split slabs (0 without split-K)
     int out_dtype;                     // GK_F32 or GK_BF16
     int epilogue;
+    int vector_ok;                     // rows of OUT start on 16-byte boundaries (stride_b == 1 case)
+    int a_static, b_static;            // the operand is not written by the kernel before (weights): it may
+                                       // be fetched before that kernel has finished
     int* error_flag;
 };
 
@@ -135,7 +138,7 @@ struct alignas(1024) GemmSmem {
 };
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                              const __grid_constant__ CUtensorMap map_b,
                                                              const GemmParams p) {
     extern __shared__ unsigned char smem_raw[];
@@ -156,6 +159,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
         }
         mbar_init(&sm.acc_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        pdl_launch_dependents();
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
@@ -173,9 +177,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
             // ---- producer: stream A and B tiles of each k-block into the ring
             int issued = 0;
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
+            // the first ring of stages: what does not depend on the kernel before is fetched at once,
+            // the rest after that kernel has finished
+            const int pre = min(STAGES, n_kb);
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&sm.full[i], STAGE_BYTES);
+                const int k = (kb_begin + i) * BK;
+                if (p.a_static) tma_load_2d(sm.a[i], &map_a, k, tile_a * BM, &sm.full[i]);
+                if (p.b_static) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                const int k = (kb_begin + i) * BK;
+                if (!p.a_static) tma_load_2d(sm.a[i], &map_a, k, tile_a * BM, &sm.full[i]);
+                if (!p.b_static) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
+            }
+            issued = pre;
+            for (int i = pre; i < n_kb && ok; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES) ok = mbar_wait(&sm.empty[s], ((i / STAGES) - 1) & 1);
+                ok = mbar_wait(&sm.empty[s], ((i / STAGES) - 1) & 1);
                 if (!ok) break;
                 mbar_expect_tx(&sm.full[s], STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
@@ -220,6 +240,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
             if (!ok && lane == 0) atomicExch(p.error_flag, 3);
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        pdl_wait();  // the kernel before may still read what is overwritten here
         char* out = reinterpret_cast<char*>(p.out);
         const long long slab = (long long)split * p.split_stride;
         const bool a_ok = row_a < p.rows_a;
@@ -233,7 +254,30 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
                 for (int i = 0; i < 16; ++i) v[i] = 0.f;
             }
             const int col0 = tile_b * BN + c0;
-            if (p.epilogue == EPI_STORE) {
+            if (p.epilogue == EPI_STORE && p.stride_b == 1 && a_ok && col0 + 16 <= p.rows_b && p.vector_ok) {
+                // sixteen consecutive outputs of one row: 32 bytes (bfloat16) or 64 bytes (float32) in 16-byte stores
+                const long long at = slab + (long long)row_a * p.stride_a + col0;
+                if (p.out_dtype == GK_F32) {
+                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + at);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        uint4 w;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                        w.x = *reinterpret_cast<uint32_t*>(&h0);
+                        w.y = *reinterpret_cast<uint32_t*>(&h1);
+                        w.z = *reinterpret_cast<uint32_t*>(&h2);
+                        w.w = *reinterpret_cast<uint32_t*>(&h3);
+                        dst[i] = w;
+                    }
+                }
+            } else if (p.epilogue == EPI_STORE) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int rb = col0 + i;
@@ -316,7 +360,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
         if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
         configured = true;
     }
-    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, smem, stream>>>(ma, mb, p);
+    gk_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, ma, mb, p);
     GK_CHECK_LAUNCH("gemm_tc");
     return GK_OK;
 }
@@ -325,11 +369,14 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 
 // OUT[a, b] = sum_k A[a, k] B[b, k].  `bn` (16, 32, 64, 128 or 256) is the tile width along B.
 // With `splits` > 1, `out` must be float32 scratch of `splits` slabs `split_stride` elements apart;
-// each slab holds the partial sum of one range of k.  `error_flag` is a device int that stays 0
-// unless a wait inside the kernel gave up.
+// each slab holds the partial sum of one range of k.  `a_static` / `b_static` mark an operand that no
+// kernel earlier in the stream writes (weights): under programmatic dependent launch its first tiles
+// are fetched while the kernel before still runs.  `error_flag` is a device int that stays 0 unless a
+// wait inside the kernel gave up.
 GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const void* b, int rows_b, long long ldb, int k,
                               void* out, int out_dtype, long long stride_a, long long stride_b, int epilogue, int bn,
-                              int splits, long long split_stride, int* error_flag, void* stream) {
+                              int splits, long long split_stride, int a_static, int b_static, int* error_flag,
+                              void* stream) {
     GK_REQUIRE(rows_a > 0 && rows_b > 0 && k > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, k);
     GK_REQUIRE(k % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
                "gemm_tc: k and the row strides must be multiples of 8 elements (16 bytes for TMA); got k=%d lda=%lld ldb=%lld",
@@ -357,14 +404,18 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     p.split_stride = splits > 1 ? split_stride : 0;
     p.out_dtype = out_dtype;
     p.epilogue = epilogue;
+    p.vector_ok = stride_b == 1 && ((uintptr_t)out & 15) == 0 &&
+                  (stride_a * (out_dtype == GK_F32 ? 4 : 2)) % 16 == 0 && (split_stride * 4) % 16 == 0;
+    p.a_static = a_static;
+    p.b_static = b_static;
     p.error_flag = error_flag;
     dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
     GK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
-        case 16: return launch<16, 8>(ma, mb, p, grid, s);
-        case 32: return launch<32, 8>(ma, mb, p, grid, s);
-        case 64: return launch<64, 6>(ma, mb, p, grid, s);
+        case 16: return launch<16, 4>(ma, mb, p, grid, s);
+        case 32: return launch<32, 4>(ma, mb, p, grid, s);
+        case 64: return launch<64, 4>(ma, mb, p, grid, s);
         case 128: return launch<128, 3>(ma, mb, p, grid, s);
         case 256: return launch<256, 4>(ma, mb, p, grid, s);
         default: return gk_fail(GK_BAD_ARGUMENT, "gemm_tc: bn must be 16, 32, 64, 128 or 256, got %d", bn);

@@ -15,6 +15,16 @@ int gk_fail(int status, const char* fmt, ...) {
     return status;
 }
 
+int g_gk_pdl = 0;
+
+// Switches programmatic dependent launch on (1) or off (0) for every later kernel launch of the
+// library; returns the previous setting.
+GK_EXPORT int gk_set_pdl(int on) {
+    const int before = g_gk_pdl;
+    g_gk_pdl = on ? 1 : 0;
+    return before;
+}
+
 GK_EXPORT const char* gk_last_error() { return g_last_error; }
 
 // Interface revision: the Python side refuses a library built from other sources.

@@ -77,6 +77,8 @@ __device__ __forceinline__ Best block_best(Best mine, Best* scratch) {
 __global__ void argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
                               int* __restrict__ out) {
     __shared__ Best scratch[32];
+    pdl_wait();
+    pdl_launch_dependents();
     const float* row = logits + (size_t)blockIdx.x * row_stride;
     Best mine{-INFINITY, 0x7fffffff};
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) mine = better(mine, Best{row[i], i});
@@ -90,6 +92,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long row_st
     __shared__ Best scratch[32];
     __shared__ unsigned int hist[256];
     __shared__ unsigned int sel_prefix, sel_remaining;
+    pdl_wait();
+    pdl_launch_dependents();
     const float* row = logits + (size_t)blockIdx.x * row_stride;
 
     unsigned int threshold_key = 0;  // keep everything
@@ -146,7 +150,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long row_st
 GK_EXPORT int gk_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int* out, void* stream) {
     GK_REQUIRE(n_rows >= 0 && vocab > 0 && row_stride >= vocab, "argmax: bad sizes rows=%d vocab=%d", n_rows, vocab);
     if (n_rows == 0) return GK_OK;
-    argmax_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, out);
+    gk_launch(argmax_kernel, dim3(n_rows), dim3(1024), 0, (cudaStream_t)stream, logits, row_stride, vocab, out);
     GK_CHECK_LAUNCH("argmax");
     return GK_OK;
 }
@@ -158,8 +162,8 @@ GK_EXPORT int gk_sample(const float* logits, long long row_stride, int n_rows, i
     GK_REQUIRE(temperature > 0.f, "sample: temperature must be positive (0 means greedy: call argmax)");
     GK_REQUIRE(top_k >= 0, "sample: top_k must be >= 0 (0 = off)");
     if (n_rows == 0) return GK_OK;
-    sample_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, temperature, top_k, seed,
-                                                             request_ids, steps, advance_steps, out);
+    gk_launch(sample_kernel, dim3(n_rows), dim3(1024), 0, (cudaStream_t)stream, logits, row_stride, vocab, temperature,
+              top_k, seed, request_ids, steps, advance_steps, out);
     GK_CHECK_LAUNCH("sample");
     return GK_OK;
 }

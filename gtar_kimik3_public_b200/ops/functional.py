@@ -71,6 +71,9 @@ def add_rmsnorm(
 ) -> torch.Tensor:
     """``h += delta`` (in place, skipped when ``delta`` is None), then RMSNorm of ``h`` times ``weight``.
 
+    ``delta`` is ``[n, hidden]``, or ``[splits, n, hidden]`` float32 partial sums of a split-K product,
+    which are added up here (slab 0 first).
+
     With ``rows`` (int32 indices) only those rows are normalised and ``h`` is not written: the
     sum ``h + delta`` of such a row is formed on the fly.
     """
@@ -80,11 +83,17 @@ def add_rmsnorm(
     hidden = h.shape[1]
     if weight.shape[0] != hidden:
         raise KernelError(f"norm weight has {weight.shape[0]} entries for rows of {hidden}")
-    delta_code = 0
+    delta_code, n_splits, split_stride = 0, 1, 0
     if delta is not None:
-        _check(delta, "delta", dims=2)
-        if delta.shape != h.shape:
-            raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
+        if delta.dim() == 3:  # float32 slabs of a split-K product, summed in the kernel
+            _check(delta, "delta", torch.float32, 3)
+            n_splits, split_stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+            if delta.shape[1:] != h.shape:
+                raise KernelError(f"delta slabs {tuple(delta.shape)} do not match h {tuple(h.shape)}")
+        else:
+            _check(delta, "delta", dims=2)
+            if delta.shape != h.shape:
+                raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
         delta_code = dtype_code(delta.dtype)
     n_out = h.shape[0]
     if rows is not None:
@@ -94,14 +103,15 @@ def add_rmsnorm(
         out = torch.empty((n_out, hidden), dtype=out_dtype, device=h.device)
     _check(out, "out", out_dtype, 2)
     call(
-        "gk_add_rmsnorm", ptr(h), ptr(delta), delta_code, ptr(weight), dtype_code(weight.dtype), ptr(out),
+        "gk_add_rmsnorm", ptr(h), ptr(delta), delta_code, n_splits, split_stride, ptr(weight), dtype_code(weight.dtype), ptr(out),
         dtype_code(out_dtype), ptr(rows), n_out, hidden, float(eps), stream_ptr(),
     )
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``silu(gate) * up`` for rows packed as ``[gate (I) | up (I)]``."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, interleaved: bool = False) -> torch.Tensor:
+    """``silu(gate) * up`` for rows packed as ``[gate (I) | up (I)]``, or with ``interleaved`` as
+    ``g0 u0 g1 u1 ...``."""
     require_device(gate_up.device)
     _check(gate_up, "gate_up", dims=2)
     n, two_i = gate_up.shape
@@ -111,7 +121,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tens
     if out is None:
         out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
     _check(out, "out", gate_up.dtype, 2)
-    call("gk_swiglu", ptr(gate_up), ptr(out), dtype_code(gate_up.dtype), n, inter, stream_ptr())
+    call("gk_swiglu", ptr(gate_up), ptr(out), dtype_code(gate_up.dtype), n, inter, int(interleaved), stream_ptr())
     return out
 
 
@@ -135,21 +145,30 @@ def qk_norm_rope_write(
 ) -> torch.Tensor:
     """Per-head RMSNorm of q and k, rotation by position, and the write of k and v into the pages.
 
-    ``qkv``: ``[n_tokens, (n_q + 2 n_kv) * head_dim]``.  Returns the finished queries
+    ``qkv``: ``[n_tokens, (n_q + 2 n_kv) * head_dim]`` in the cache's dtype or float32, or
+    ``[splits, n_tokens, ...]`` float32 partial sums of a split-K product.  Returns the finished queries
     ``[n_tokens, n_q, head_dim]``.  ``max_position`` is the largest entry of ``tok_pos`` (known on
     the host) and is checked against the rotary table.  ``write_kv=False`` leaves the pages alone
     (a layer that attends over keys and values written by another layer).
     """
     require_device(qkv.device)
-    _check(qkv, "qkv", dims=2)
-    n = qkv.shape[0]
-    if qkv.shape[1] != (n_q + 2 * n_kv) * head_dim:
-        raise KernelError(f"qkv rows are {qkv.shape[1]} wide, expected {(n_q + 2 * n_kv) * head_dim}")
+    n_splits, split_stride = 1, 0
+    if qkv.dim() == 3:  # float32 slabs of a split-K product
+        _check(qkv, "qkv", torch.float32, 3)
+        n_splits, split_stride = qkv.shape[0], qkv.shape[1] * qkv.shape[2]
+    else:
+        _check(qkv, "qkv", dims=2)
+    n = qkv.shape[-2]
+    if qkv.shape[-1] != (n_q + 2 * n_kv) * head_dim:
+        raise KernelError(f"qkv rows are {qkv.shape[-1]} wide, expected {(n_q + 2 * n_kv) * head_dim}")
+    cache_dtype = kv.k.dtype
+    if qkv.dtype not in (cache_dtype, torch.float32):
+        raise KernelError(f"projection of {qkv.dtype} does not fit a cache of {cache_dtype}")
     for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("slots", slots)):
         _check(t, name, torch.int32, 1)
     _check(kv.block_table, "block_table", torch.int32, 2)
-    _check(kv.k, "k pages", qkv.dtype, 4)
-    _check(kv.v, "v pages", qkv.dtype, 4)
+    _check(kv.k, "k pages", cache_dtype, 4)
+    _check(kv.v, "v pages", cache_dtype, 4)
     if kv.k.shape[1] != n_kv or kv.k.shape[3] != head_dim or kv.v.shape != kv.k.shape:
         raise KernelError(f"pages {tuple(kv.k.shape)} do not fit n_kv={n_kv}, head_dim={head_dim}")
     use_norm = q_weight is not None
@@ -168,10 +187,11 @@ def qk_norm_rope_write(
             raise KernelError("rotary tables must be [positions, head_dim / 2]")
         table_positions = cos.shape[0]
     if q_out is None:
-        q_out = torch.empty((n, n_q, head_dim), dtype=qkv.dtype, device=qkv.device)
-    _check(q_out, "q_out", qkv.dtype, 3)
+        q_out = torch.empty((n, n_q, head_dim), dtype=cache_dtype, device=qkv.device)
+    _check(q_out, "q_out", cache_dtype, 3)
     call(
-        "gk_qk_norm_rope_write", ptr(qkv), dtype_code(qkv.dtype), ptr(q_weight), ptr(k_weight), weight_code, ptr(cos),
+        "gk_qk_norm_rope_write", ptr(qkv), dtype_code(qkv.dtype), n_splits, split_stride, dtype_code(cache_dtype),
+        ptr(q_weight), ptr(k_weight), weight_code, ptr(cos),
         ptr(sin), table_positions, ptr(tok_pos), ptr(tok_seq), ptr(slots), ptr(kv.block_table), ptr(q_out),
         ptr(kv.k) if write_kv else None, ptr(kv.v) if write_kv else None, n, n_q, n_kv, head_dim, kv.max_pages, kv.page_size, float(eps), int(use_norm), int(max_position),
         stream_ptr(),
@@ -252,6 +272,22 @@ EPI_STORE, EPI_SWIGLU_A, EPI_SWIGLU_B = 0, 1, 2
 SKINNY_M = 64  # up to this many tokens the weights take the MMA's 128 rows (swap-AB)
 
 
+def split_k_for(m: int, n: int, k: int, sm_count: int = 148) -> int:
+    """How many blocks share the K range of one output tile of a skinny product (m <= SKINNY_M):
+    enough that about one block per SM streams weights, each with at least two k-blocks of 64."""
+    if m > SKINNY_M:
+        return 1
+    tiles = -(-n // 128)
+    return max(1, min(sm_count // tiles, (k // 64) // 2, 16))
+
+
+def set_pdl(on: bool) -> bool:
+    """Switches programmatic dependent launch for all later kernel launches; returns the old setting."""
+    from .library import library
+
+    return bool(library().gk_set_pdl(int(on)))
+
+
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
             splits: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` in bfloat16 on the tcgen05 tensor cores, float32 accumulation.
@@ -284,11 +320,11 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
     if m <= SKINNY_M:
         bn = 16 if m <= 16 else 32 if m <= 32 else 64
         call("gk_gemm_bf16_tc", ptr(weight), n, k, ptr(x), m, k, k, ptr(out), dtype_code(out_dtype), 1, n_out,
-             EPI_SWIGLU_A if swiglu else EPI_STORE, bn, splits, m * n_out, ptr(flag), stream_ptr())
+             EPI_SWIGLU_A if swiglu else EPI_STORE, bn, splits, m * n_out, 1, 0, ptr(flag), stream_ptr())
     else:
         bn = 128 if n >= 128 else 64 if n >= 64 else 32 if n >= 32 else 16
         call("gk_gemm_bf16_tc", ptr(x), m, k, ptr(weight), n, k, k, ptr(out), dtype_code(out_dtype), n_out, 1,
-             EPI_SWIGLU_B if swiglu else EPI_STORE, bn, splits, m * n_out, ptr(flag), stream_ptr())
+             EPI_SWIGLU_B if swiglu else EPI_STORE, bn, splits, m * n_out, 0, 1, ptr(flag), stream_ptr())
     return out
 
 

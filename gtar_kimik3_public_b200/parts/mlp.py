@@ -1,5 +1,7 @@
 """SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))`` (src/layers/swiglu.py:9-14), with the gate
-and up projections as one packed matrix product."""
+and up projections as one packed matrix product whose rows alternate gate, up, gate, up, ... so
+that the activation can be applied where the product is written (each output channel's two
+numbers sit side by side in the accumulator)."""
 
 from __future__ import annotations
 
@@ -27,15 +29,15 @@ class SwiGLUFeedForward(FeedForward):
         gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         if gate.dtype != up.dtype:
             gate, up = gate.float(), up.float()
-        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], gate.shape[1]).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gate_up = linear(x, self.w_gate_up)
-        return linear(F.swiglu(gate_up), self.w_down)
+        act = linear(x, self.w_gate_up, swiglu=True)
+        return linear(act, self.w_down, partial_ok=True)
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)

@@ -101,10 +101,14 @@ def test_dtype_rule(tmp_path):
     load_weights(f32, folder)
     assert all(t.dtype == torch.float32 for t in (f32.plan.layers[1].mixer.w_qkv, f32.plan.layers[1].input_norm.weight,
                                                    f32.plan.embedding.weight))
-    # packing keeps the order q | k | v and gate | up
+    # packing: q | k | v one after another; gate and up rows alternate
     packed = f32.plan.layers[1].feed_forward.w_gate_up
-    assert torch.equal(packed[:192], tensors["model.layers.1.mlp.gate_proj.weight"].float())
-    assert torch.equal(packed[192:], tensors["model.layers.1.mlp.up_proj.weight"].float())
+    assert torch.equal(packed[0::2], tensors["model.layers.1.mlp.gate_proj.weight"].float())
+    assert torch.equal(packed[1::2], tensors["model.layers.1.mlp.up_proj.weight"].float())
+    qkv = f32.plan.layers[1].mixer.w_qkv
+    assert torch.equal(qkv[:64], tensors["model.layers.1.self_attn.q_proj.weight"].float())
+    assert torch.equal(qkv[64:96], tensors["model.layers.1.self_attn.k_proj.weight"].float())
+    assert torch.equal(qkv[96:], tensors["model.layers.1.self_attn.v_proj.weight"].float())
 
 
 def test_tied_model_accepts_a_stored_head(tmp_path):
