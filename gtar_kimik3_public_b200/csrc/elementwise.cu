@@ -5,9 +5,6 @@
 //                       rotary   x*cos + rotate_half(x)*sin         src/layers/rope.py:17-33
 //                       SwiGLU   silu(gate) * up                    src/layers/swiglu.py:14
 // All arithmetic is 32-bit; inputs and outputs may be bfloat16.
-//
-// Where a kernel's input comes from a split-K matrix product it may arrive as `n_splits` float32
-// slabs (`split_stride` elements apart) that are summed here, slab 0 first, before anything else.
 
 #include "common.cuh"
 
@@ -37,20 +34,12 @@ GK_EXPORT int gk_embed_rows(const void* table, int table_dtype, const int* ids, 
 }
 
 // ---------------------------------------------------------------- residual add + RMSNorm
-template <typename TD>
-__device__ __forceinline__ float sum_slabs(const TD* __restrict__ p, size_t index, int n_splits, long long split_stride) {
-    float v = to_float(p[index]);
-    for (int s = 1; s < n_splits; ++s) v += to_float(p[index + (size_t)s * split_stride]);
-    return v;
-}
-
 // One block per output row.  h (32-bit residual stream) gets `delta` added in place when
 // `rows` is null; with `rows`, only the listed rows are read and h is left as it is (the
 // last norm of a step, taken at the wanted positions only).
 template <typename TD, typename TW, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_splits,
-                                   long long split_stride, const TW* __restrict__ w, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int hidden, float eps) {
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const TW* __restrict__ w,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float scratch[33];
     pdl_wait();
     const int src = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -62,7 +51,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = hrow[i];
-        if (has_delta) v += sum_slabs(delta, dbase + i, n_splits, split_stride);
+        if (has_delta) v += to_float(delta[dbase + i]);
         if (write_back) hrow[i] = v;
         ss += v * v;
     }
@@ -71,19 +60,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = hrow[i];
-        if (has_delta && !write_back) v += sum_slabs(delta, dbase + i, n_splits, split_stride);
+        if (has_delta && !write_back) v += to_float(delta[dbase + i]);
         orow[i] = from_float<TO>((v * inv) * to_float(w[i]));
     }
 }
 
-GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, int n_splits, long long split_stride,
-                             const void* weight, int weight_dtype, void* out, int out_dtype, const int* rows,
-                             int n_out_rows, int hidden, float eps, void* stream) {
+GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, const void* weight, int weight_dtype,
+                             void* out, int out_dtype, const int* rows, int n_out_rows, int hidden, float eps,
+                             void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(delta_dtype) && GK_VALID_DTYPE(weight_dtype) && GK_VALID_DTYPE(out_dtype),
                "add_rmsnorm: bad dtype code");
     GK_REQUIRE(n_out_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_out_rows, hidden);
     GK_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
-    GK_REQUIRE(n_splits >= 1, "add_rmsnorm: n_splits must be >= 1");
     if (n_out_rows == 0) return GK_OK;
     // A fixed block size: the order of the sum of squares must not depend on anything but the row.
     const int threads = 256;
@@ -92,7 +80,7 @@ GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, int n
         GK_DISPATCH_DTYPE(weight_dtype, TW, {
             GK_DISPATCH_DTYPE(out_dtype, TO, {
                 gk_launch(add_rmsnorm_kernel<TD, TW, TO>, dim3(n_out_rows), dim3(threads), 0, s, h, (const TD*)delta,
-                          n_splits, split_stride, (const TW*)weight, (TO*)out, rows, hidden, eps);
+                          (const TW*)weight, (TO*)out, rows, hidden, eps);
             })
         })
     })
@@ -144,11 +132,8 @@ GK_EXPORT int gk_swiglu(const void* gate_up, void* out, int dtype, int n_tokens,
 // `use_norm` = 0 skips the normalisation, `cos_table` = null skips the rotation, so that the
 // same kernel serves a mixer without q/k norm or without positions; `k_pages` = null writes no
 // keys and values (a layer that reads the storage another layer fills).
-// TI is the projection's type (float32 slabs when it comes from a split-K product), T the type of
-// the queries and of the cache.
-template <typename TI, typename T, typename TW>
-__global__ void qk_norm_rope_write_kernel(const TI* __restrict__ qkv, int n_splits, long long split_stride,
-                                          const TW* __restrict__ wq, const TW* __restrict__ wk,
+template <typename T, typename TW>
+__global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* __restrict__ wq, const TW* __restrict__ wk,
                                           const float* __restrict__ cos_table, const float* __restrict__ sin_table,
                                           const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                           const int* __restrict__ slots, const int* __restrict__ block_table,
@@ -186,7 +171,7 @@ __global__ void qk_norm_rope_write_kernel(const TI* __restrict__ qkv, int n_spli
         }
     }
     if (!rotate) {
-        for (int i = lane; i < head_dim; i += 32) dst[i] = from_float<T>(sum_slabs(qkv, src + i, n_splits, split_stride));
+        for (int i = lane; i < head_dim; i += 32) dst[i] = qkv[src + i];
         return;
     }
     const int half = head_dim >> 1;
@@ -194,16 +179,14 @@ __global__ void qk_norm_rope_write_kernel(const TI* __restrict__ qkv, int n_spli
     if (use_norm) {
         float ss = 0.f;
         for (int p = lane; p < half; p += 32) {
-            const float a = sum_slabs(qkv, src + p, n_splits, split_stride);
-            const float b = sum_slabs(qkv, src + p + half, n_splits, split_stride);
+            const float a = to_float(qkv[src + p]), b = to_float(qkv[src + p + half]);
             ss += a * a + b * b;
         }
         ss = warp_sum(ss);
         inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
     }
     for (int p = lane; p < half; p += 32) {
-        float a = sum_slabs(qkv, src + p, n_splits, split_stride);
-        float b = sum_slabs(qkv, src + p + half, n_splits, split_stride);
+        float a = to_float(qkv[src + p]), b = to_float(qkv[src + p + half]);
         if (use_norm) {
             a = (a * inv) * to_float(w[p]);
             b = (b * inv) * to_float(w[p + half]);
@@ -219,18 +202,14 @@ __global__ void qk_norm_rope_write_kernel(const TI* __restrict__ qkv, int n_spli
     }
 }
 
-GK_EXPORT int gk_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits, long long split_stride, int dtype,
+GK_EXPORT int gk_qk_norm_rope_write(const void* qkv, int dtype,
                                     const void* wq, const void* wk, int weight_dtype, const float* cos_table,
                                     const float* sin_table, int table_positions, const int* tok_pos,
                                     const int* tok_seq, const int* slots, const int* block_table, void* q_out,
                                     void* k_pages, void* v_pages, int n_tokens, int n_q, int n_kv, int head_dim,
                                     int max_pages, int page_size, float eps, int use_norm, int max_position,
                                     void* stream) {
-    GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(weight_dtype) && GK_VALID_DTYPE(in_dtype),
-               "qk_norm_rope_write: bad dtype code");
-    GK_REQUIRE(in_dtype == dtype || in_dtype == GK_F32,
-               "qk_norm_rope_write: the projection is either of the cache's type or float32");
-    GK_REQUIRE(n_splits >= 1 && (n_splits == 1 || in_dtype == GK_F32), "qk_norm_rope_write: slabs are float32");
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(weight_dtype), "qk_norm_rope_write: bad dtype code");
     GK_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && head_dim > 0 && head_dim % 2 == 0,
                "qk_norm_rope_write: bad sizes n_q=%d n_kv=%d head_dim=%d", n_q, n_kv, head_dim);
     GK_REQUIRE(page_size > 0 && max_pages > 0, "qk_norm_rope_write: bad page geometry");
@@ -245,21 +224,13 @@ GK_EXPORT int gk_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits,
     const long long blocks = (warps + 3) / 4;
     GK_REQUIRE(blocks < 2147483647LL, "qk_norm_rope_write: too many tokens");
     cudaStream_t s = (cudaStream_t)stream;
-#define GK_QK_LAUNCH(TI)                                                                                             \
-    gk_launch(qk_norm_rope_write_kernel<TI, T, TW>, dim3((unsigned)blocks), dim3(threads), 0, s, (const TI*)qkv,      \
-              n_splits, split_stride, (const TW*)wq, (const TW*)wk, cos_table, sin_table, tok_pos, tok_seq, slots,    \
-              block_table, (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, n_q, n_kv, head_dim, max_pages, page_size,  \
-              eps, use_norm)
     GK_DISPATCH_DTYPE(dtype, T, {
         GK_DISPATCH_DTYPE(weight_dtype, TW, {
-            if (in_dtype == GK_F32) {
-                GK_QK_LAUNCH(float);
-            } else {
-                GK_QK_LAUNCH(T);
-            }
+            gk_launch(qk_norm_rope_write_kernel<T, TW>, dim3((unsigned)blocks), dim3(threads), 0, s, (const T*)qkv,
+                      (const TW*)wq, (const TW*)wk, cos_table, sin_table, tok_pos, tok_seq, slots, block_table, (T*)q_out,
+                      (T*)k_pages, (T*)v_pages, n_tokens, n_q, n_kv, head_dim, max_pages, page_size, eps, use_norm);
         })
     })
-#undef GK_QK_LAUNCH
     GK_CHECK_LAUNCH("qk_norm_rope_write");
     return GK_OK;
 }

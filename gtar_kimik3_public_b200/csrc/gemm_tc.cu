@@ -12,9 +12,9 @@
 // with tcgen05.ld and write the result.  Warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
 // owner, warps 2-5 = epilogue.  Accumulation is 32-bit.
 //
-// Epilogues: plain store (bfloat16 or float32), SwiGLU over row pairs (gate and up rows interleaved:
-// even index = gate, odd = up, src/layers/swiglu.py:14), and split-K partial sums (float32, one
-// slab per split, summed by the consumer in a fixed order).
+// Epilogues: plain store (bfloat16 or float32) and SwiGLU over row pairs (gate and up rows
+// interleaved: even index = gate, odd = up, src/layers/swiglu.py:14).  With split-K the blocks of a
+// tile leave float32 partial tiles in scratch and the last one to finish sums them in split order.
 //
 // Every wait on an mbarrier is bounded: after GK_SPIN_LIMIT polls the thread records a code in
 // *error_flag and leaves its loop; the block still drains its own copies, frees its tensor memory
@@ -39,7 +39,8 @@ struct GemmParams {
     int k_blocks_per_split;
     void* out;
     long long stride_a, stride_b;      // element strides of OUT for the A index and the B index
-    long long split_stride;            // elements between split slabs (0 without split-K)
+    float* slabs;                      // split-K scratch: [splits][tiles][BN][128] float32
+    int* counters;                     // split-K: one arrival counter per tile, zero between launches
     int out_dtype;                     // GK_F32 or GK_BF16
     int epilogue;
     int vector_ok;                     // rows of OUT start on 16-byte boundaries (stride_b == 1 case)
@@ -129,12 +130,73 @@ __device__ __forceinline__ void store_out(void* out, long long index, float v) {
     reinterpret_cast<T*>(out)[index] = from_float<T>(v);
 }
 
+// The output stage for sixteen consecutive B indices (col0 .. col0 + 15) of the A index `row_a`.
+__device__ __forceinline__ void write_chunk(const GemmParams& p, float (&v)[16], int row_a, bool a_ok, int col0, int lane) {
+    char* out = reinterpret_cast<char*>(p.out);
+    if (p.epilogue == EPI_STORE && p.stride_b == 1 && a_ok && col0 + 16 <= p.rows_b && p.vector_ok) {
+        // sixteen consecutive outputs of one row: 32 bytes (bfloat16) or 64 bytes (float32) in 16-byte stores
+        const long long at = (long long)row_a * p.stride_a + col0;
+        if (p.out_dtype == GK_F32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + at);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                uint4 w;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                w.x = *reinterpret_cast<uint32_t*>(&h0);
+                w.y = *reinterpret_cast<uint32_t*>(&h1);
+                w.z = *reinterpret_cast<uint32_t*>(&h2);
+                w.w = *reinterpret_cast<uint32_t*>(&h3);
+                dst[i] = w;
+            }
+        }
+    } else if (p.epilogue == EPI_STORE) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int rb = col0 + i;
+            if (a_ok && rb < p.rows_b) {
+                const long long at = (long long)row_a * p.stride_a + (long long)rb * p.stride_b;
+                if (p.out_dtype == GK_F32) store_out<float>(out, at, v[i]);
+                else store_out<__nv_bfloat16>(out, at, v[i]);
+            }
+        }
+    } else if (p.epilogue == EPI_SWIGLU_A) {
+        // gate and up alternate along A (TMEM lanes): even lane = gate, odd lane = up of channel row_a / 2
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
+            const int rb = col0 + i;
+            if ((lane & 1) == 0 && a_ok && rb < p.rows_b) {
+                const long long at = (long long)(row_a >> 1) * p.stride_a + (long long)rb * p.stride_b;
+                store_out<__nv_bfloat16>(out, at, silu(v[i]) * other);
+            }
+        }
+    } else {
+        // gate and up alternate along B (TMEM columns)
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            const int rb = col0 + i;
+            if (a_ok && rb + 1 < p.rows_b) {
+                const long long at = (long long)row_a * p.stride_a + (long long)(rb >> 1) * p.stride_b;
+                store_out<__nv_bfloat16>(out, at, silu(v[i]) * v[i + 1]);
+            }
+        }
+    }
+}
+
 template <int BN, int STAGES>
 struct alignas(1024) GemmSmem {
     __nv_bfloat16 a[STAGES][BM * BK];
     __nv_bfloat16 b[STAGES][BN * BK];
     uint64_t full[STAGES], empty[STAGES], acc_ready;
     uint32_t tmem_base;
+    int is_last;
 };
 
 template <int BN, int STAGES>
@@ -241,73 +303,66 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         pdl_wait();  // the kernel before may still read what is overwritten here
-        char* out = reinterpret_cast<char*>(p.out);
-        const long long slab = (long long)split * p.split_stride;
         const bool a_ok = row_a < p.rows_a;
+        const bool have_acc = n_kb > 0 && ok;
+        const uint32_t t_row = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+        if (gridDim.z == 1) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-            float v[16];
-            if (n_kb > 0 && ok) {
-                tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = 0.f;
-            }
-            const int col0 = tile_b * BN + c0;
-            if (p.epilogue == EPI_STORE && p.stride_b == 1 && a_ok && col0 + 16 <= p.rows_b && p.vector_ok) {
-                // sixteen consecutive outputs of one row: 32 bytes (bfloat16) or 64 bytes (float32) in 16-byte stores
-                const long long at = slab + (long long)row_a * p.stride_a + col0;
-                if (p.out_dtype == GK_F32) {
-                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                if (have_acc) {
+                    tmem_ld16(t_row + c0, v);
                 } else {
-                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + at);
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        uint4 w;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]);
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
-                        w.x = *reinterpret_cast<uint32_t*>(&h0);
-                        w.y = *reinterpret_cast<uint32_t*>(&h1);
-                        w.z = *reinterpret_cast<uint32_t*>(&h2);
-                        w.w = *reinterpret_cast<uint32_t*>(&h3);
-                        dst[i] = w;
-                    }
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
                 }
-            } else if (p.epilogue == EPI_STORE) {
+                write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
+            }
+        } else {
+            // split-K: leave this block's partial tile in scratch; the block that arrives last at the
+            // tile's counter adds the partial tiles up in the order of the splits (so the sum does not
+            // depend on which block that is) and writes the result.
+            const int n_tiles = gridDim.x * gridDim.y;
+            const int tile = tile_b * gridDim.x + tile_a;
+            const int row_in_tile = quarter * 32 + lane;
+            float* mine = p.slabs + ((size_t)split * n_tiles + tile) * (BM * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                if (have_acc) {
+                    tmem_ld16(t_row + c0, v);
+                } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int rb = col0 + i;
-                    if (a_ok && rb < p.rows_b) {
-                        const long long at = slab + (long long)row_a * p.stride_a + (long long)rb * p.stride_b;
-                        if (p.out_dtype == GK_F32) store_out<float>(out, at, v[i]);
-                        else store_out<__nv_bfloat16>(out, at, v[i]);
-                    }
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
                 }
-            } else if (p.epilogue == EPI_SWIGLU_A) {
-                // gate and up alternate along A (TMEM lanes): even lane = gate, odd lane = up of channel row_a / 2
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
-                    const int rb = col0 + i;
-                    if ((lane & 1) == 0 && a_ok && rb < p.rows_b) {
-                        const long long at = (long long)(row_a >> 1) * p.stride_a + (long long)rb * p.stride_b;
-                        store_out<__nv_bfloat16>(out, at, silu(v[i]) * other);
-                    }
-                }
-            } else {
-                // gate and up alternate along B (TMEM columns)
+                for (int i = 0; i < 16; ++i) __stcg(mine + (c0 + i) * BM + row_in_tile, v[i]);
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == 2 && lane == 0) sm.is_last = atomicAdd(p.counters + tile, 1) == (int)gridDim.z - 1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (sm.is_last) {
+                __threadfence();
+                const float* first = p.slabs + (size_t)tile * (BM * BN);
+                const size_t slab_stride = (size_t)n_tiles * (BM * BN);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
 #pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    const int rb = col0 + i;
-                    if (a_ok && rb + 1 < p.rows_b) {
-                        const long long at = (long long)row_a * p.stride_a + (long long)(rb >> 1) * p.stride_b;
-                        store_out<__nv_bfloat16>(out, at, silu(v[i]) * v[i + 1]);
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+#pragma unroll 2
+                    for (int sp = 0; sp < (int)gridDim.z; ++sp) {
+                        const float* src = first + sp * slab_stride + c0 * BM + row_in_tile;
+                        float w[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) w[i] = __ldcg(src + i * BM);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] += w[i];
                     }
+                    write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
                 }
+                if (warp == 2 && lane == 0) p.counters[tile] = 0;  // ready for the next launch
             }
         }
     }
@@ -368,15 +423,17 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 }  // namespace
 
 // OUT[a, b] = sum_k A[a, k] B[b, k].  `bn` (16, 32, 64, 128 or 256) is the tile width along B.
-// With `splits` > 1, `out` must be float32 scratch of `splits` slabs `split_stride` elements apart;
-// each slab holds the partial sum of one range of k.  `a_static` / `b_static` mark an operand that no
+// With `splits` > 1 the K range of a tile is shared by that many blocks; they leave partial tiles in
+// `slabs` (scratch of `slab_floats` floats) and the last to arrive at the tile's counter (`counters`,
+// `n_counters` ints that are zero between launches) sums them in split order and writes OUT.
+// Launches that share the scratch must follow one another in one stream.  `a_static` / `b_static` mark an operand that no
 // kernel earlier in the stream writes (weights): under programmatic dependent launch its first tiles
 // are fetched while the kernel before still runs.  `error_flag` is a device int that stays 0 unless a
 // wait inside the kernel gave up.
 GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const void* b, int rows_b, long long ldb, int k,
                               void* out, int out_dtype, long long stride_a, long long stride_b, int epilogue, int bn,
-                              int splits, long long split_stride, int a_static, int b_static, int* error_flag,
-                              void* stream) {
+                              int splits, float* slabs, long long slab_floats, int* counters, int n_counters,
+                              int a_static, int b_static, int* error_flag, void* stream) {
     GK_REQUIRE(rows_a > 0 && rows_b > 0 && k > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, k);
     GK_REQUIRE(k % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
                "gemm_tc: k and the row strides must be multiples of 8 elements (16 bytes for TMA); got k=%d lda=%lld ldb=%lld",
@@ -384,8 +441,7 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     GK_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)b & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
     GK_REQUIRE(GK_VALID_DTYPE(out_dtype), "gemm_tc: bad output dtype");
     GK_REQUIRE(epilogue >= EPI_STORE && epilogue <= EPI_SWIGLU_B, "gemm_tc: bad epilogue %d", epilogue);
-    GK_REQUIRE(splits >= 1 && (splits == 1 || (epilogue == EPI_STORE && out_dtype == GK_F32)),
-               "gemm_tc: split-K writes float32 partial sums with the plain epilogue");
+    GK_REQUIRE(splits >= 1, "gemm_tc: splits must be >= 1");
     GK_REQUIRE(epilogue == EPI_STORE || out_dtype == GK_BF16, "gemm_tc: the SwiGLU epilogue writes bfloat16");
     GK_REQUIRE(error_flag != nullptr, "gemm_tc: error_flag is required");
     CUtensorMap ma, mb;
@@ -401,16 +457,24 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     p.out = out;
     p.stride_a = stride_a;
     p.stride_b = stride_b;
-    p.split_stride = splits > 1 ? split_stride : 0;
+    p.slabs = slabs;
+    p.counters = counters;
     p.out_dtype = out_dtype;
     p.epilogue = epilogue;
-    p.vector_ok = stride_b == 1 && ((uintptr_t)out & 15) == 0 &&
-                  (stride_a * (out_dtype == GK_F32 ? 4 : 2)) % 16 == 0 && (split_stride * 4) % 16 == 0;
+    p.vector_ok = stride_b == 1 && ((uintptr_t)out & 15) == 0 && (stride_a * (out_dtype == GK_F32 ? 4 : 2)) % 16 == 0;
     p.a_static = a_static;
     p.b_static = b_static;
     p.error_flag = error_flag;
     dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
     GK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
+    if (splits > 1) {
+        const long long tiles = (long long)grid.x * grid.y;
+        GK_REQUIRE(slabs && counters, "gemm_tc: split-K needs scratch and counters");
+        GK_REQUIRE(tiles <= n_counters, "gemm_tc: %lld tiles but only %d counters", tiles, n_counters);
+        GK_REQUIRE((long long)splits * tiles * BM * bn <= slab_floats,
+                   "gemm_tc: split-K scratch of %lld floats is too small for %d splits of %lld tiles", slab_floats,
+                   splits, tiles);
+    }
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
         case 16: return launch<16, 4>(ma, mb, p, grid, s);

@@ -9,6 +9,7 @@ places, and a sequence that ends gives its storage back while the others go on.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -28,7 +29,8 @@ class StepEntry:
 
 
 class Engine:
-    def __init__(self, model: Model, max_tokens: int, max_seqs: int | None = None, use_graphs: bool = True):
+    def __init__(self, model: Model, max_tokens: int, max_seqs: int | None = None, use_graphs: bool = True,
+                 use_pdl: bool | None = None):
         self.model = model
         self.cache: Cache = model.make_cache(max_tokens, max_seqs)
         self.slot_of: dict[object, int] = {}
@@ -37,7 +39,9 @@ class Engine:
         if use_graphs and model.device.type == "cuda" and model.graph_safe():
             from .graphs import DecodeGraphs
 
-            self.graphs = DecodeGraphs(model, self.cache)
+            if use_pdl is None:
+                use_pdl = os.environ.get("GTAR_B200_PDL", "1") != "0"
+            self.graphs = DecodeGraphs(model, self.cache, use_pdl)
 
     # ------------------------------------------------------------------ requests
     def live(self) -> list[object]:

@@ -18,8 +18,8 @@ from ..parts.base import StepContext
 class DecodeGraphs:
     RING = 8
 
-    def __init__(self, model, cache):
-        self.model, self.cache = model, cache
+    def __init__(self, model, cache, use_pdl: bool = True):
+        self.model, self.cache, self.use_pdl = model, cache, use_pdl
         self.n_max = cache.max_seqs
         device = model.device
         n = self.n_max
@@ -84,8 +84,17 @@ class DecodeGraphs:
             self.model.step(ctx, self.cache)  # a plain run first: one-time set-up must not be captured
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, pool=self.pool):
-                logits = self.model.step(ctx, self.cache)
+            # Inside the graph every kernel is launched with programmatic stream serialization: it may
+            # start (and fetch weights) while the kernel before it drains, and waits for that kernel's
+            # results only where it first needs them.
+            from ..ops.functional import set_pdl
+
+            before = set_pdl(self.use_pdl)
+            try:
+                with torch.cuda.graph(graph, pool=self.pool):
+                    logits = self.model.step(ctx, self.cache)
+            finally:
+                set_pdl(before)
             if self.pool is None:
                 self.pool = graph.pool()
             self.graphs[n] = (graph, logits)

@@ -71,9 +71,6 @@ def add_rmsnorm(
 ) -> torch.Tensor:
     """``h += delta`` (in place, skipped when ``delta`` is None), then RMSNorm of ``h`` times ``weight``.
 
-    ``delta`` is ``[n, hidden]``, or ``[splits, n, hidden]`` float32 partial sums of a split-K product,
-    which are added up here (slab 0 first).
-
     With ``rows`` (int32 indices) only those rows are normalised and ``h`` is not written: the
     sum ``h + delta`` of such a row is formed on the fly.
     """
@@ -83,17 +80,11 @@ def add_rmsnorm(
     hidden = h.shape[1]
     if weight.shape[0] != hidden:
         raise KernelError(f"norm weight has {weight.shape[0]} entries for rows of {hidden}")
-    delta_code, n_splits, split_stride = 0, 1, 0
+    delta_code = 0
     if delta is not None:
-        if delta.dim() == 3:  # float32 slabs of a split-K product, summed in the kernel
-            _check(delta, "delta", torch.float32, 3)
-            n_splits, split_stride = delta.shape[0], delta.shape[1] * delta.shape[2]
-            if delta.shape[1:] != h.shape:
-                raise KernelError(f"delta slabs {tuple(delta.shape)} do not match h {tuple(h.shape)}")
-        else:
-            _check(delta, "delta", dims=2)
-            if delta.shape != h.shape:
-                raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
+        _check(delta, "delta", dims=2)
+        if delta.shape != h.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
         delta_code = dtype_code(delta.dtype)
     n_out = h.shape[0]
     if rows is not None:
@@ -103,7 +94,7 @@ def add_rmsnorm(
         out = torch.empty((n_out, hidden), dtype=out_dtype, device=h.device)
     _check(out, "out", out_dtype, 2)
     call(
-        "gk_add_rmsnorm", ptr(h), ptr(delta), delta_code, n_splits, split_stride, ptr(weight), dtype_code(weight.dtype), ptr(out),
+        "gk_add_rmsnorm", ptr(h), ptr(delta), delta_code, ptr(weight), dtype_code(weight.dtype), ptr(out),
         dtype_code(out_dtype), ptr(rows), n_out, hidden, float(eps), stream_ptr(),
     )
     return out
@@ -145,25 +136,17 @@ def qk_norm_rope_write(
 ) -> torch.Tensor:
     """Per-head RMSNorm of q and k, rotation by position, and the write of k and v into the pages.
 
-    ``qkv``: ``[n_tokens, (n_q + 2 n_kv) * head_dim]`` in the cache's dtype or float32, or
-    ``[splits, n_tokens, ...]`` float32 partial sums of a split-K product.  Returns the finished queries
+    ``qkv``: ``[n_tokens, (n_q + 2 n_kv) * head_dim]``.  Returns the finished queries
     ``[n_tokens, n_q, head_dim]``.  ``max_position`` is the largest entry of ``tok_pos`` (known on
     the host) and is checked against the rotary table.  ``write_kv=False`` leaves the pages alone
     (a layer that attends over keys and values written by another layer).
     """
     require_device(qkv.device)
-    n_splits, split_stride = 1, 0
-    if qkv.dim() == 3:  # float32 slabs of a split-K product
-        _check(qkv, "qkv", torch.float32, 3)
-        n_splits, split_stride = qkv.shape[0], qkv.shape[1] * qkv.shape[2]
-    else:
-        _check(qkv, "qkv", dims=2)
-    n = qkv.shape[-2]
-    if qkv.shape[-1] != (n_q + 2 * n_kv) * head_dim:
-        raise KernelError(f"qkv rows are {qkv.shape[-1]} wide, expected {(n_q + 2 * n_kv) * head_dim}")
-    cache_dtype = kv.k.dtype
-    if qkv.dtype not in (cache_dtype, torch.float32):
-        raise KernelError(f"projection of {qkv.dtype} does not fit a cache of {cache_dtype}")
+    _check(qkv, "qkv", dims=2)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_q + 2 * n_kv) * head_dim:
+        raise KernelError(f"qkv rows are {qkv.shape[1]} wide, expected {(n_q + 2 * n_kv) * head_dim}")
+    cache_dtype = qkv.dtype
     for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("slots", slots)):
         _check(t, name, torch.int32, 1)
     _check(kv.block_table, "block_table", torch.int32, 2)
@@ -190,8 +173,7 @@ def qk_norm_rope_write(
         q_out = torch.empty((n, n_q, head_dim), dtype=cache_dtype, device=qkv.device)
     _check(q_out, "q_out", cache_dtype, 3)
     call(
-        "gk_qk_norm_rope_write", ptr(qkv), dtype_code(qkv.dtype), n_splits, split_stride, dtype_code(cache_dtype),
-        ptr(q_weight), ptr(k_weight), weight_code, ptr(cos),
+        "gk_qk_norm_rope_write", ptr(qkv), dtype_code(qkv.dtype), ptr(q_weight), ptr(k_weight), weight_code, ptr(cos),
         ptr(sin), table_positions, ptr(tok_pos), ptr(tok_seq), ptr(slots), ptr(kv.block_table), ptr(q_out),
         ptr(kv.k) if write_kv else None, ptr(kv.v) if write_kv else None, n, n_q, n_kv, head_dim, kv.max_pages, kv.page_size, float(eps), int(use_norm), int(max_position),
         stream_ptr(),
@@ -265,6 +247,8 @@ def check_kernel_errors(device: torch.device | str = "cuda:0") -> None:
     code = int(flag.item())
     if code:
         flag.zero_()
+        for _, counters in _split_scratch.values():
+            counters.zero_()
         raise KernelError(f"a kernel gave up waiting on a barrier (code {code}); its output is not valid")
 
 
@@ -288,13 +272,32 @@ def set_pdl(on: bool) -> bool:
     return bool(library().gk_set_pdl(int(on)))
 
 
+_split_scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+SPLIT_SCRATCH_FLOATS = 1 << 22  # 16 MB of partial tiles: 16 splits of 128 tiles of 128 x 16
+SPLIT_COUNTERS = 4096
+
+
+def split_scratch(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Scratch of the split-K products of one device: float32 partial tiles and per-tile arrival
+    counters (zero between launches).  One set per device: launches that use it must follow one
+    another in one stream, as the steps of an engine do."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _split_scratch:
+        _split_scratch[index] = (
+            torch.empty(SPLIT_SCRATCH_FLOATS, dtype=torch.float32, device=device),
+            torch.zeros(SPLIT_COUNTERS, dtype=torch.int32, device=device),
+        )
+    return _split_scratch[index]
+
+
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
             splits: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` in bfloat16 on the tcgen05 tensor cores, float32 accumulation.
 
     ``swiglu=True``: the rows of ``weight`` alternate gate, up, gate, up, ...; the result is
-    ``silu(gate) * up`` of width ``N / 2``.  ``splits > 1`` divides K among that many blocks per tile
-    and returns float32 partial sums ``[splits, M, N]`` for the consumer to add up.
+    ``silu(gate) * up`` of width ``N / 2``.  ``splits > 1`` shares the K range of every output tile
+    among that many blocks (a skinny product then keeps all SMs streaming weights); the partial tiles
+    meet in scratch memory and are summed in a fixed order, so the result does not depend on timing.
     """
     require_device(x.device)
     _check(x, "x", torch.bfloat16, 2)
@@ -303,28 +306,27 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
     n = weight.shape[0]
     if weight.shape[1] != k:
         raise KernelError(f"x is {tuple(x.shape)} but weight is {tuple(weight.shape)}")
-    if swiglu and (n % 2 or splits != 1):
-        raise KernelError("the SwiGLU epilogue needs an even number of weight rows and no split-K")
+    if swiglu and n % 2:
+        raise KernelError("the SwiGLU epilogue needs an even number of weight rows")
     n_out = n // 2 if swiglu else n
-    if splits > 1:
-        out_dtype = torch.float32
-        shape = (splits, m, n_out)
-    else:
-        shape = (m, n_out)
     if out is None:
-        out = torch.empty(shape, dtype=out_dtype, device=x.device)
-    _check(out, "out", out_dtype, len(shape))
-    if tuple(out.shape) != shape:
-        raise KernelError(f"out has shape {tuple(out.shape)}, expected {shape}")
+        out = torch.empty((m, n_out), dtype=out_dtype, device=x.device)
+    _check(out, "out", out_dtype, 2)
+    if tuple(out.shape) != (m, n_out):
+        raise KernelError(f"out has shape {tuple(out.shape)}, expected {(m, n_out)}")
     flag = error_flag(x.device)
+    slabs = counters = None
+    if splits > 1:
+        slabs, counters = split_scratch(x.device)
+    scratch = (ptr(slabs), SPLIT_SCRATCH_FLOATS if splits > 1 else 0, ptr(counters), SPLIT_COUNTERS if splits > 1 else 0)
     if m <= SKINNY_M:
         bn = 16 if m <= 16 else 32 if m <= 32 else 64
         call("gk_gemm_bf16_tc", ptr(weight), n, k, ptr(x), m, k, k, ptr(out), dtype_code(out_dtype), 1, n_out,
-             EPI_SWIGLU_A if swiglu else EPI_STORE, bn, splits, m * n_out, 1, 0, ptr(flag), stream_ptr())
+             EPI_SWIGLU_A if swiglu else EPI_STORE, bn, splits, *scratch, 1, 0, ptr(flag), stream_ptr())
     else:
         bn = 128 if n >= 128 else 64 if n >= 64 else 32 if n >= 32 else 16
         call("gk_gemm_bf16_tc", ptr(x), m, k, ptr(weight), n, k, k, ptr(out), dtype_code(out_dtype), n_out, 1,
-             EPI_SWIGLU_B if swiglu else EPI_STORE, bn, splits, m * n_out, 0, 1, ptr(flag), stream_ptr())
+             EPI_SWIGLU_B if swiglu else EPI_STORE, bn, splits, *scratch, 0, 1, ptr(flag), stream_ptr())
     return out
 
 

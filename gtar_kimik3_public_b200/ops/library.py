@@ -30,13 +30,13 @@ P, I, L, F, U = c_void_p, c_int, c_longlong, c_float, c_ulonglong
 
 _SIGNATURES: dict[str, list] = {
     "gk_embed_rows": [P, I, P, P, I, I, P],
-    "gk_add_rmsnorm": [P, P, I, I, L, P, I, P, I, P, I, I, F, P],
+    "gk_add_rmsnorm": [P, P, I, P, I, P, I, P, I, I, F, P],
     "gk_swiglu": [P, P, I, I, I, I, P],
-    "gk_qk_norm_rope_write": [P, I, I, L, I, P, P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    "gk_qk_norm_rope_write": [P, I, P, P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_gemm_f32": [P, I, P, P, I, I, I, I, L, L, L, P],
     "gk_attention_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "gk_attention_decode_bf16": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
-    "gk_gemm_bf16_tc": [P, I, L, P, I, L, I, P, I, L, L, I, I, I, L, I, I, P, P],
+    "gk_gemm_bf16_tc": [P, I, L, P, I, L, I, P, I, L, L, I, I, I, P, L, P, I, I, I, P, P],
     "gk_set_pdl": [I],
     "gk_argmax": [P, L, I, I, P, P],
     "gk_sample": [P, L, I, I, F, I, U, P, P, I, P, P],

@@ -20,12 +20,11 @@ def _tc_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-           partial_ok: bool = False, swiglu: bool = False) -> torch.Tensor:
+           swiglu: bool = False) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T -> [M, N]`` in ``out_dtype`` (default: ``x.dtype``).
 
-    ``partial_ok``: the caller can add up float32 slabs ``[splits, M, N]`` itself (the norm and the
-    q/k kernels can), which lets a skinny product spread its K range over more blocks.
-    ``swiglu``: ``weight`` holds gate and up rows alternately and the result is ``silu(gate) * up``.
+    ``swiglu``: ``weight`` holds gate and up rows alternately and the result is ``silu(gate) * up``
+    of width ``N / 2``.
     """
     require_device(x.device)
     out_dtype = out_dtype or x.dtype
@@ -39,7 +38,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if not _tc_ok(x, weight):
         y = F.linear_bf16(x, weight, torch.bfloat16 if swiglu else out_dtype)
         return F.swiglu(y, interleaved=True) if swiglu else y
-    if swiglu:
-        return F.gemm_tc(x, weight, torch.bfloat16, swiglu=True)
-    splits = F.split_k_for(x.shape[0], weight.shape[0], x.shape[1]) if partial_ok else 1
-    return F.gemm_tc(x, weight, out_dtype, splits=splits)
+    splits = F.split_k_for(x.shape[0], weight.shape[0], x.shape[1])
+    return F.gemm_tc(x, weight, torch.bfloat16 if swiglu else out_dtype, swiglu=swiglu, splits=splits)

@@ -63,7 +63,7 @@ class GQAAttention(Mixer):
         return KVRequest(self.n_kv, self.head_dim, self.window)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: F.PagedKV) -> torch.Tensor:
-        qkv = linear(x, self.w_qkv, partial_ok=True)
+        qkv = linear(x, self.w_qkv)
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.cos, self.position.sin
@@ -73,7 +73,7 @@ class GQAAttention(Mixer):
             write_kv=not ctx.extras.get("cache_read_only", False),
         )
         o = attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
-        return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o, partial_ok=True)
+        return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -114,8 +114,7 @@ class Mixer(Part):
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Any) -> torch.Tensor:
-        """``x``: normalised activations ``[n_tokens, hidden]``; returns the branch output, same shape —
-        or ``[splits, n_tokens, hidden]`` float32 partial sums, which the next norm adds up."""
+        """``x``: normalised activations ``[n_tokens, hidden]``; returns the branch output, same shape."""
         raise NotImplementedError
 
 

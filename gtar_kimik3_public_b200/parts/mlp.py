@@ -37,7 +37,7 @@ class SwiGLUFeedForward(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = linear(x, self.w_gate_up, swiglu=True)
-        return linear(act, self.w_down, partial_ok=True)
+        return linear(act, self.w_down)
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
