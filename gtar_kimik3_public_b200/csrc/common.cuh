@@ -38,23 +38,39 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 extern int g_gk_pdl;  // set through gk_set_pdl(): launch kernels with programmatic stream serialization
 
-// Launches `kernel` on `stream`, with the programmatic-dependent-launch attribute when it is switched on.
+// Launches `kernel` on `stream`, with the programmatic-dependent-launch attribute when it is switched
+// on, and as thread-block clusters of (1, 1, cluster_z) blocks when cluster_z > 1.
 template <typename... KArgs, typename... Args>
-inline cudaError_t gk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             Args... args) {
+inline cudaError_t gk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     int cluster_z, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    int n = 0;
     if (g_gk_pdl) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
     }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        ++n;
+    }
+    cfg.attrs = n ? attr : nullptr;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t gk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    return gk_launch_cluster(kernel, grid, block, smem, stream, 1, args...);
 }
 
 __device__ __forceinline__ float to_float(float x) { return x; }

@@ -13,8 +13,10 @@
 // owner, warps 2-5 = epilogue.  Accumulation is 32-bit.
 //
 // Epilogues: plain store (bfloat16 or float32) and SwiGLU over row pairs (gate and up rows
-// interleaved: even index = gate, odd = up, src/layers/swiglu.py:14).  With split-K the blocks of a
-// tile leave float32 partial tiles in scratch and the last one to finish sums them in split order.
+// interleaved: even index = gate, odd = up, src/layers/swiglu.py:14).  With split-K (2, 4 or 8
+// ways) the blocks of one tile form a thread-block cluster: each leaves its float32 partial tile in
+// its own shared memory, and after a cluster barrier every block sums one slice of the tile over all
+// blocks through distributed shared memory, in the order of the splits, and writes that slice.
 //
 // Every wait on an mbarrier is bounded: after GK_SPIN_LIMIT polls the thread records a code in
 // *error_flag and leaves its loop; the block still drains its own copies, frees its tensor memory
@@ -39,8 +41,6 @@ struct GemmParams {
     int k_blocks_per_split;
     void* out;
     long long stride_a, stride_b;      // element strides of OUT for the A index and the B index
-    float* slabs;                      // split-K scratch: [splits][tiles][BN][128] float32
-    int* counters;                     // split-K: one arrival counter per tile, zero between launches
     int out_dtype;                     // GK_F32 or GK_BF16
     int epilogue;
     int vector_ok;                     // rows of OUT start on 16-byte boundaries (stride_b == 1 case)
@@ -196,7 +196,6 @@ struct alignas(1024) GemmSmem {
     __nv_bfloat16 b[STAGES][BN * BK];
     uint64_t full[STAGES], empty[STAGES], acc_ready;
     uint32_t tmem_base;
-    int is_last;
 };
 
 template <int BN, int STAGES>
@@ -319,13 +318,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
             }
         } else {
-            // split-K: leave this block's partial tile in scratch; the block that arrives last at the
-            // tile's counter adds the partial tiles up in the order of the splits (so the sum does not
-            // depend on which block that is) and writes the result.
-            const int n_tiles = gridDim.x * gridDim.y;
-            const int tile = tile_b * gridDim.x + tile_a;
+            // split-K: this block's partial tile goes to its own shared memory, [column][row] float32,
+            // over the pipeline stages (every copy has landed and every MMA has read them by now)
+            float* stage = reinterpret_cast<float*>(sm.a[0]);
             const int row_in_tile = quarter * 32 + lane;
-            float* mine = p.slabs + ((size_t)split * n_tiles + tile) * (BM * BN);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
@@ -336,35 +332,95 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;
                 }
 #pragma unroll
-                for (int i = 0; i < 16; ++i) __stcg(mine + (c0 + i) * BM + row_in_tile, v[i]);
-            }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (warp == 2 && lane == 0) sm.is_last = atomicAdd(p.counters + tile, 1) == (int)gridDim.z - 1;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (sm.is_last) {
-                __threadfence();
-                const float* first = p.slabs + (size_t)tile * (BM * BN);
-                const size_t slab_stride = (size_t)n_tiles * (BM * BN);
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    float v[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
-#pragma unroll 2
-                    for (int sp = 0; sp < (int)gridDim.z; ++sp) {
-                        const float* src = first + sp * slab_stride + c0 * BM + row_in_tile;
-                        float w[16];
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) w[i] = __ldcg(src + i * BM);
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] += w[i];
-                    }
-                    write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
-                }
-                if (warp == 2 && lane == 0) p.counters[tile] = 0;  // ready for the next launch
+                for (int i = 0; i < 16; ++i) stage[(c0 + i) * BM + row_in_tile] = v[i];
             }
         }
+    }
+    if (gridDim.z > 1) {
+        // every thread of every block of the cluster: the partial tiles are complete and visible
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp >= 2) {
+            // this block sums rows [rank * rows_per, (rank + 1) * rows_per) of the tile over all blocks
+            const int n_ranks = gridDim.z, rank = blockIdx.z;
+            const int rows_per = BM / n_ranks;
+            const uint32_t stage_addr = smem_u32(sm.a[0]);
+            const int e = (warp - 2) * 32 + lane;
+            // Elements of the slice are taken four at a time per thread: the loads of all partial sums
+            // of the four are issued before the first is used, then added in the order of the splits.
+            auto load_parts = [&](int row, int col, float (&part)[8]) {
+                const uint32_t local = stage_addr + (uint32_t)(col * BM + row) * 4u;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    part[r] = 0.f;
+                    if (r < n_ranks) {
+                        uint32_t remote;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(r));
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[r]) : "r"(remote) : "memory");
+                    }
+                }
+            };
+            auto add_up = [&](const float (&part)[8]) {
+                float acc = part[0];
+#pragma unroll
+                for (int r = 1; r < 8; ++r)
+                    if (r < n_ranks) acc += part[r];
+                return acc;
+            };
+            char* out = reinterpret_cast<char*>(p.out);
+            constexpr int U = 4;
+            if (p.epilogue == EPI_STORE) {
+                const int count = rows_per * BN;
+                for (int base = e; base < count; base += 128 * U) {
+                    float part[U][8];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int idx = base + u * 128;
+                        if (idx < count) load_parts(rank * rows_per + idx % rows_per, idx / rows_per, part[u]);
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int idx = base + u * 128;
+                        if (idx >= count) continue;
+                        const int row_a = tile_a * BM + rank * rows_per + idx % rows_per, rb = tile_b * BN + idx / rows_per;
+                        if (row_a < p.rows_a && rb < p.rows_b) {
+                            const float v = add_up(part[u]);
+                            const long long at = (long long)row_a * p.stride_a + (long long)rb * p.stride_b;
+                            if (p.out_dtype == GK_F32) store_out<float>(out, at, v);
+                            else store_out<__nv_bfloat16>(out, at, v);
+                        }
+                    }
+                }
+            } else {  // EPI_SWIGLU_A: rows alternate gate, up
+                const int pairs = rows_per / 2, count = pairs * BN;
+                for (int base = e; base < count; base += 128 * (U / 2)) {
+                    float part[U][8];
+#pragma unroll
+                    for (int u = 0; u < U / 2; ++u) {
+                        const int idx = base + u * 128;
+                        if (idx < count) {
+                            const int row_g = rank * rows_per + 2 * (idx % pairs);
+                            load_parts(row_g, idx / pairs, part[2 * u]);
+                            load_parts(row_g + 1, idx / pairs, part[2 * u + 1]);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U / 2; ++u) {
+                        const int idx = base + u * 128;
+                        if (idx >= count) continue;
+                        const int row_a = tile_a * BM + rank * rows_per + 2 * (idx % pairs), rb = tile_b * BN + idx / pairs;
+                        if (row_a < p.rows_a && rb < p.rows_b) {
+                            const float g = add_up(part[2 * u]), u_val = add_up(part[2 * u + 1]);
+                            const long long at = (long long)(row_a >> 1) * p.stride_a + (long long)rb * p.stride_b;
+                            store_out<__nv_bfloat16>(out, at, silu(g) * u_val);
+                        }
+                    }
+                }
+            }
+        }
+        // nobody leaves while its shared memory may still be read
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -408,6 +464,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, 
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    static_assert(STAGES * (BM + BN) * BK * 2 >= BM * BN * 4, "the partial tile must fit in the pipeline stages");
     const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -415,7 +472,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
         if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
         configured = true;
     }
-    gk_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, ma, mb, p);
+    gk_launch_cluster(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, (int)grid.z, ma, mb, p);
     GK_CHECK_LAUNCH("gemm_tc");
     return GK_OK;
 }
@@ -423,17 +480,13 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 }  // namespace
 
 // OUT[a, b] = sum_k A[a, k] B[b, k].  `bn` (16, 32, 64, 128 or 256) is the tile width along B.
-// With `splits` > 1 the K range of a tile is shared by that many blocks; they leave partial tiles in
-// `slabs` (scratch of `slab_floats` floats) and the last to arrive at the tile's counter (`counters`,
-// `n_counters` ints that are zero between launches) sums them in split order and writes OUT.
-// Launches that share the scratch must follow one another in one stream.  `a_static` / `b_static` mark an operand that no
+// With `splits` = 2, 4 or 8 the K range of a tile is shared by that many blocks (one cluster).  `a_static` / `b_static` mark an operand that no
 // kernel earlier in the stream writes (weights): under programmatic dependent launch its first tiles
 // are fetched while the kernel before still runs.  `error_flag` is a device int that stays 0 unless a
 // wait inside the kernel gave up.
 GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const void* b, int rows_b, long long ldb, int k,
                               void* out, int out_dtype, long long stride_a, long long stride_b, int epilogue, int bn,
-                              int splits, float* slabs, long long slab_floats, int* counters, int n_counters,
-                              int a_static, int b_static, int* error_flag, void* stream) {
+                              int splits, int a_static, int b_static, int* error_flag, void* stream) {
     GK_REQUIRE(rows_a > 0 && rows_b > 0 && k > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, k);
     GK_REQUIRE(k % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
                "gemm_tc: k and the row strides must be multiples of 8 elements (16 bytes for TMA); got k=%d lda=%lld ldb=%lld",
@@ -441,7 +494,8 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     GK_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)b & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
     GK_REQUIRE(GK_VALID_DTYPE(out_dtype), "gemm_tc: bad output dtype");
     GK_REQUIRE(epilogue >= EPI_STORE && epilogue <= EPI_SWIGLU_B, "gemm_tc: bad epilogue %d", epilogue);
-    GK_REQUIRE(splits >= 1, "gemm_tc: splits must be >= 1");
+    GK_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "gemm_tc: splits must be 1, 2, 4 or 8, got %d", splits);
+    GK_REQUIRE(splits == 1 || epilogue != EPI_SWIGLU_B, "gemm_tc: split-K does not go with the SwiGLU-over-B epilogue");
     GK_REQUIRE(epilogue == EPI_STORE || out_dtype == GK_BF16, "gemm_tc: the SwiGLU epilogue writes bfloat16");
     GK_REQUIRE(error_flag != nullptr, "gemm_tc: error_flag is required");
     CUtensorMap ma, mb;
@@ -457,8 +511,6 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     p.out = out;
     p.stride_a = stride_a;
     p.stride_b = stride_b;
-    p.slabs = slabs;
-    p.counters = counters;
     p.out_dtype = out_dtype;
     p.epilogue = epilogue;
     p.vector_ok = stride_b == 1 && ((uintptr_t)out & 15) == 0 && (stride_a * (out_dtype == GK_F32 ? 4 : 2)) % 16 == 0;
@@ -467,19 +519,12 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     p.error_flag = error_flag;
     dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
     GK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
-    if (splits > 1) {
-        const long long tiles = (long long)grid.x * grid.y;
-        GK_REQUIRE(slabs && counters, "gemm_tc: split-K needs scratch and counters");
-        GK_REQUIRE(tiles <= n_counters, "gemm_tc: %lld tiles but only %d counters", tiles, n_counters);
-        GK_REQUIRE((long long)splits * tiles * BM * bn <= slab_floats,
-                   "gemm_tc: split-K scratch of %lld floats is too small for %d splits of %lld tiles", slab_floats,
-                   splits, tiles);
-    }
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
-        case 16: return launch<16, 4>(ma, mb, p, grid, s);
-        case 32: return launch<32, 4>(ma, mb, p, grid, s);
-        case 64: return launch<64, 4>(ma, mb, p, grid, s);
+        // skinny products are bound by memory latency: as many bytes in flight per block as fit
+        case 16: return launch<16, 10>(ma, mb, p, grid, s);
+        case 32: return launch<32, 9>(ma, mb, p, grid, s);
+        case 64: return launch<64, 8>(ma, mb, p, grid, s);
         case 128: return launch<128, 3>(ma, mb, p, grid, s);
         case 256: return launch<256, 4>(ma, mb, p, grid, s);
         default: return gk_fail(GK_BAD_ARGUMENT, "gemm_tc: bn must be 16, 32, 64, 128 or 256, got %d", bn);

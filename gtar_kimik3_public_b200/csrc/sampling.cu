@@ -74,16 +74,40 @@ __device__ __forceinline__ Best block_best(Best mine, Best* scratch) {
     return scratch[0];
 }
 
+// Grid (parts, rows): block (p, r) scans its slice of row r and leaves its best (value, index) in
+// `partial[r * parts + p]`; with one part it writes the answer itself.
 __global__ void argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
-                              int* __restrict__ out) {
+                              int* __restrict__ out, Best* __restrict__ partial) {
     __shared__ Best scratch[32];
     pdl_wait();
     pdl_launch_dependents();
-    const float* row = logits + (size_t)blockIdx.x * row_stride;
+    const int parts = gridDim.x, part = blockIdx.x, r = blockIdx.y;
+    const float* row = logits + (size_t)r * row_stride;
+    const int per = (vocab + parts - 1) / parts;
+    const int begin = part * per, end = min(begin + per, vocab);
     Best mine{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mine = better(mine, Best{row[i], i});
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) mine = better(mine, Best{row[i], i});
     Best b = block_best(mine, scratch);
-    if (threadIdx.x == 0) out[blockIdx.x] = b.index == 0x7fffffff ? 0 : b.index;
+    if (threadIdx.x == 0) {
+        if (parts == 1) out[r] = b.index == 0x7fffffff ? 0 : b.index;
+        else partial[(size_t)r * parts + part] = b;
+    }
+}
+
+__global__ void argmax_merge_kernel(const Best* __restrict__ partial, int parts, int* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    Best mine{-INFINITY, 0x7fffffff};
+    for (int p = threadIdx.x; p < parts; p += 32) mine = better(mine, partial[(size_t)r * parts + p]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other;
+        other.value = __shfl_xor_sync(0xffffffffu, mine.value, o);
+        other.index = __shfl_xor_sync(0xffffffffu, mine.index, o);
+        mine = better(mine, other);
+    }
+    if (threadIdx.x == 0) out[r] = mine.index == 0x7fffffff ? 0 : mine.index;
 }
 
 __global__ void sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab, float temperature,
@@ -147,11 +171,21 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long row_st
 
 }  // namespace
 
-GK_EXPORT int gk_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int* out, void* stream) {
+// `scratch` (8 bytes * n_rows * parts) is needed when `parts` > 1: a row is then scanned by that many
+// blocks and a second kernel picks among their results (ties still go to the lowest index).
+GK_EXPORT int gk_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int* out, int parts,
+                        void* scratch, void* stream) {
     GK_REQUIRE(n_rows >= 0 && vocab > 0 && row_stride >= vocab, "argmax: bad sizes rows=%d vocab=%d", n_rows, vocab);
+    GK_REQUIRE(parts >= 1 && parts <= 1024 && n_rows <= 65535, "argmax: bad split %d of %d rows", parts, n_rows);
+    GK_REQUIRE(parts == 1 || scratch, "argmax: scratch is needed when a row is split");
     if (n_rows == 0) return GK_OK;
-    gk_launch(argmax_kernel, dim3(n_rows), dim3(1024), 0, (cudaStream_t)stream, logits, row_stride, vocab, out);
+    gk_launch(argmax_kernel, dim3(parts, n_rows), dim3(parts == 1 ? 1024 : 256), 0, (cudaStream_t)stream, logits,
+              row_stride, vocab, out, (Best*)scratch);
     GK_CHECK_LAUNCH("argmax");
+    if (parts > 1) {
+        gk_launch(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, (cudaStream_t)stream, (const Best*)scratch, parts, out);
+        GK_CHECK_LAUNCH("argmax_merge");
+    }
     return GK_OK;
 }
 

@@ -247,8 +247,6 @@ def check_kernel_errors(device: torch.device | str = "cuda:0") -> None:
     code = int(flag.item())
     if code:
         flag.zero_()
-        for _, counters in _split_scratch.values():
-            counters.zero_()
         raise KernelError(f"a kernel gave up waiting on a barrier (code {code}); its output is not valid")
 
 
@@ -257,12 +255,14 @@ SKINNY_M = 64  # up to this many tokens the weights take the MMA's 128 rows (swa
 
 
 def split_k_for(m: int, n: int, k: int, sm_count: int = 148) -> int:
-    """How many blocks share the K range of one output tile of a skinny product (m <= SKINNY_M):
-    enough that about one block per SM streams weights, each with at least two k-blocks of 64."""
+    """How many blocks share the K range of one output tile of a skinny product (m <= SKINNY_M).
+    More blocks stream weights from more SMs: about 64 blocks in all, at least four k-blocks of 64
+    each, and 1, 2, 4 or 8 ways (the blocks of a tile form one cluster)."""
     if m > SKINNY_M:
         return 1
     tiles = -(-n // 128)
-    return max(1, min(sm_count // tiles, (k // 64) // 2, 16))
+    limit = min(64 // tiles, (k // 64) // 4, 8)
+    return 8 if limit >= 8 else 4 if limit >= 4 else 2 if limit >= 2 else 1
 
 
 def set_pdl(on: bool) -> bool:
@@ -272,32 +272,14 @@ def set_pdl(on: bool) -> bool:
     return bool(library().gk_set_pdl(int(on)))
 
 
-_split_scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
-SPLIT_SCRATCH_FLOATS = 1 << 22  # 16 MB of partial tiles: 16 splits of 128 tiles of 128 x 16
-SPLIT_COUNTERS = 4096
-
-
-def split_scratch(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
-    """Scratch of the split-K products of one device: float32 partial tiles and per-tile arrival
-    counters (zero between launches).  One set per device: launches that use it must follow one
-    another in one stream, as the steps of an engine do."""
-    index = device.index if device.index is not None else torch.cuda.current_device()
-    if index not in _split_scratch:
-        _split_scratch[index] = (
-            torch.empty(SPLIT_SCRATCH_FLOATS, dtype=torch.float32, device=device),
-            torch.zeros(SPLIT_COUNTERS, dtype=torch.int32, device=device),
-        )
-    return _split_scratch[index]
-
-
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
             splits: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` in bfloat16 on the tcgen05 tensor cores, float32 accumulation.
 
     ``swiglu=True``: the rows of ``weight`` alternate gate, up, gate, up, ...; the result is
     ``silu(gate) * up`` of width ``N / 2``.  ``splits > 1`` shares the K range of every output tile
-    among that many blocks (a skinny product then keeps all SMs streaming weights); the partial tiles
-    meet in scratch memory and are summed in a fixed order, so the result does not depend on timing.
+    among 2, 4 or 8 blocks (a skinny product then streams weights from more SMs); the blocks form a
+    cluster and add their partial tiles through distributed shared memory in a fixed order.
     """
     require_device(x.device)
     _check(x, "x", torch.bfloat16, 2)
@@ -315,18 +297,14 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
     if tuple(out.shape) != (m, n_out):
         raise KernelError(f"out has shape {tuple(out.shape)}, expected {(m, n_out)}")
     flag = error_flag(x.device)
-    slabs = counters = None
-    if splits > 1:
-        slabs, counters = split_scratch(x.device)
-    scratch = (ptr(slabs), SPLIT_SCRATCH_FLOATS if splits > 1 else 0, ptr(counters), SPLIT_COUNTERS if splits > 1 else 0)
     if m <= SKINNY_M:
         bn = 16 if m <= 16 else 32 if m <= 32 else 64
         call("gk_gemm_bf16_tc", ptr(weight), n, k, ptr(x), m, k, k, ptr(out), dtype_code(out_dtype), 1, n_out,
-             EPI_SWIGLU_A if swiglu else EPI_STORE, bn, splits, *scratch, 1, 0, ptr(flag), stream_ptr())
+             EPI_SWIGLU_A if swiglu else EPI_STORE, bn, splits, 1, 0, ptr(flag), stream_ptr())
     else:
         bn = 128 if n >= 128 else 64 if n >= 64 else 32 if n >= 32 else 16
         call("gk_gemm_bf16_tc", ptr(x), m, k, ptr(weight), n, k, k, ptr(out), dtype_code(out_dtype), n_out, 1,
-             EPI_SWIGLU_B if swiglu else EPI_STORE, bn, splits, *scratch, 0, 1, ptr(flag), stream_ptr())
+             EPI_SWIGLU_B if swiglu else EPI_STORE, bn, splits, 0, 1, ptr(flag), stream_ptr())
     return out
 
 
@@ -384,7 +362,10 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     if out is None:
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
     _check(out, "out", torch.int32, 1)
-    call("gk_argmax", ptr(logits), vocab, n, vocab, ptr(out), stream_ptr())
+    # few rows of a wide vocabulary: several blocks share a row so that the scan uses the whole GPU
+    parts = max(1, min(296 // max(n, 1), vocab // 4096, 64))
+    scratch = torch.empty((n * parts * 2,), dtype=torch.int32, device=logits.device) if parts > 1 else None
+    call("gk_argmax", ptr(logits), vocab, n, vocab, ptr(out), parts, ptr(scratch), stream_ptr())
     return out
 
 
