@@ -3,7 +3,7 @@
 * float32, or a head size the tensor-core kernels do not take: the exact kernel (any cut of the
   work gives bit-equal results);
 * bfloat16, every sequence bringing one token: the split-KV decode kernel;
-* bfloat16 otherwise: the exact kernel until the step is a prefill the flash kernel takes.
+* bfloat16 otherwise (prompts, or continuations of several tokens): the flash prefill kernel.
 """
 
 from __future__ import annotations
@@ -24,4 +24,6 @@ def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: i
     if fast and ctx.all_single:
         splits = ctx.extras.get("decode_splits") or F.decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len, kv.page_size)
         return F.attention_decode(q, kv, ctx.kv_len, ctx.slots, scale, window, splits)
+    if fast:
+        return F.attention_prefill(q, kv, ctx.cu_q, ctx.kv_len, ctx.slots, ctx.max_q_len, scale, window)
     return F.attention_exact(q, kv, ctx.tok_pos, ctx.tok_seq, ctx.slots, scale, window)

@@ -354,6 +354,43 @@ def attention_decode(
     return out
 
 
+def attention_prefill(
+    q: torch.Tensor,
+    kv: PagedKV,
+    cu_q: torch.Tensor,
+    kv_len: torch.Tensor,
+    slots: torch.Tensor,
+    max_q_len: int,
+    scale: float,
+    window: int = 0,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Causal attention of the packed new tokens ``q [n_tokens, n_q, d]`` (bfloat16, ``d`` 64 or 128) of
+    ``n_seqs`` sequences over the pages.  Sequence ``i`` owns tokens ``cu_q[i] .. cu_q[i+1]-1``, which
+    are its last positions: ``kv_len[i]`` counts its cached tokens including them."""
+    require_device(q.device)
+    _check(q, "q", torch.bfloat16, 3)
+    n, n_q, d = q.shape
+    _check(kv.k, "k pages", torch.bfloat16, 4)
+    _check(kv.v, "v pages", torch.bfloat16, 4)
+    for name, t in (("cu_q", cu_q), ("kv_len", kv_len), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    n_seqs = kv_len.shape[0]
+    if cu_q.shape[0] != n_seqs + 1 or slots.shape[0] != n_seqs:
+        raise KernelError("cu_q needs n_seqs + 1 entries, slots and kv_len n_seqs")
+    n_kv = kv.k.shape[1]
+    if kv.k.shape[3] != d:
+        raise KernelError(f"pages have head_dim {kv.k.shape[3]}, queries {d}")
+    if out is None:
+        out = torch.empty_like(q)
+    call(
+        "gk_attention_prefill_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(cu_q), ptr(kv_len), ptr(slots),
+        ptr(kv.block_table), n_seqs, int(max_q_len), n_q, n_kv, d, kv.max_pages, kv.page_size, float(scale), int(window),
+        stream_ptr(),
+    )
+    return out
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """Index of the largest logit of each row (lowest index on ties), int32."""
     require_device(logits.device)
