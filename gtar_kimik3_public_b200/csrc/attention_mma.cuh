@@ -145,4 +145,92 @@ __device__ __forceinline__ void softmax_update(float (&s)[2][4], float (&m)[2], 
     p[3] = pack_bf16(s[1][2], s[1][3]);
 }
 
+// ---- a whole page (64 keys) at a time: one maximum, one rescale of the accumulator per page ----
+
+// S(16 x 64) = Q K^T for the first `n16` groups of 16 keys of a swizzled K page; s[2g], s[2g+1] hold group g.
+template <int D, bool FULL>
+__device__ __forceinline__ void qk_page(float (&s)[8][4], const uint32_t (&q)[D / 16][4], const __nv_bfloat16* k_tile,
+                                        int n16, int lane) {
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+    const int row = (lane & 7) + ((lane >> 4) << 3);
+    const int chunk_in_step = (lane >> 3) & 1;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            if (FULL || g < n16) {
+                uint32_t b[4];
+                ldmatrix_x4(b, reinterpret_cast<const uint4*>(k_tile) + swz<D>(g * 16 + row, ks * 2 + chunk_in_step));
+                mma_16816(s[2 * g], q[ks], b[0], b[1]);
+                mma_16816(s[2 * g + 1], q[ks], b[2], b[3]);
+            }
+        }
+    }
+}
+
+// Running softmax over a 16 x 64 score tile (entries set to -inf are masked); p[g] = the A fragment of group g.
+template <int D>
+__device__ __forceinline__ void softmax_page(float (&s)[8][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4],
+                                             uint32_t (&p)[4][4], float sl2) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * h], s[n][2 * h + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m[h], mx * sl2);
+        const float ref = m_new == -INFINITY ? 0.f : m_new;
+        const float corr = exp2f(m[h] - ref);
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const float e = exp2f(fmaf(s[n][2 * h + c], sl2, -ref));
+                s[n][2 * h + c] = e;
+                sum += e;
+            }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l[h] = l[h] * corr + sum;
+        m[h] = m_new;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+            o[j][2 * h] *= corr;
+            o[j][2 * h + 1] *= corr;
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        p[g][0] = pack_bf16(s[2 * g][0], s[2 * g][1]);
+        p[g][1] = pack_bf16(s[2 * g][2], s[2 * g][3]);
+        p[g][2] = pack_bf16(s[2 * g + 1][0], s[2 * g + 1][1]);
+        p[g][3] = pack_bf16(s[2 * g + 1][2], s[2 * g + 1][3]);
+    }
+}
+
+// O(16 x D) += P(16 x 64) V for the first `n16` groups of 16 keys of a swizzled V page.
+template <int D, bool FULL>
+__device__ __forceinline__ void pv_page(float (&o)[D / 8][4], const uint32_t (&p)[4][4], const __nv_bfloat16* v_tile,
+                                        int n16, int lane) {
+    const int row = (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int chunk_in_pair = lane >> 4;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        if (FULL || g < n16) {
+#pragma unroll
+            for (int j = 0; j < D / 16; ++j) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, reinterpret_cast<const uint4*>(v_tile) + swz<D>(g * 16 + row, j * 2 + chunk_in_pair));
+                mma_16816(o[2 * j], p[g], b[0], b[1]);
+                mma_16816(o[2 * j + 1], p[g], b[2], b[3]);
+            }
+        }
+    }
+}
+
 }  // namespace attn

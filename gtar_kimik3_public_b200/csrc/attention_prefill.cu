@@ -7,7 +7,7 @@
 //
 // The rows of a block's tile are (token, query head of one kv group) pairs, token-major, so the
 // `group` query heads that share a kv head share every loaded page.  Grid (row block, kv head,
-// sequence); a warp owns 16 rows; K and V pages stream through a cp.async double buffer.
+// sequence); a warp owns 16 rows; K and V pages stream through a three-stage cp.async ring.
 // Scores, softmax statistics and the output accumulator are 32-bit; probabilities are rounded to
 // bfloat16 for the second product (flash_attention_2.py:55).
 
@@ -17,9 +17,9 @@ namespace {
 
 using namespace attn;
 
-constexpr int PF_WARPS = 8;
+constexpr int PF_WARPS = 4;
 constexpr int PF_ROWS = PF_WARPS * 16;
-constexpr int PF_STAGES = 2;
+constexpr int PF_STAGES = 3;
 
 template <int D>
 struct PrefillSmem {
@@ -108,40 +108,41 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
 
-    issue(0);
+#pragma unroll
+    for (int st = 0; st < PF_STAGES - 1; ++st) issue(st);
     for (int it = 0; it < n_iter; ++it) {
-        issue(it + 1);             // into the other buffer: its last reader finished before the barrier below
-        cp_async_wait<1>();        // page `it` has landed (one newer group may be in flight)
-        __syncthreads();
+        cp_async_wait<PF_STAGES - 2>();  // page `it` has landed
+        __syncthreads();                 // for everyone; and the stage refilled next was read an iteration ago
+        issue(it + PF_STAGES - 1);
         const int stage = it % PF_STAGES;
         const int key_base = (p_begin + it) * PAGE;
         if (key_base <= w_max_pos && key_base + PAGE > w_lo) {  // warp-uniform
+            // groups of 16 keys beyond the warp's last position are in the future of all its rows
+            const int n16 = min(PAGE / 16, (w_max_pos - key_base) / 16 + 1);
             const bool need_mask = key_base + PAGE - 1 > w_min_pos || key_base < w_lo || window > 0;
+            float s[8][4];
+            uint32_t p[4][4];
+            if (!need_mask) {  // the common case: a page wholly in the past of all the warp's rows
+                qk_page<D, true>(s, qf, sm.k[stage], 4, lane);
+                softmax_page<D>(s, m, l, o, p, sl2);
+                pv_page<D, true>(o, p, sm.v[stage], 4, lane);
+            } else {
+                qk_page<D, false>(s, qf, sm.k[stage], n16, lane);
 #pragma unroll
-            for (int kk = 0; kk < PAGE / 16; ++kk) {
-                const int abs0 = key_base + kk * 16;
-                if (abs0 > w_max_pos) break;  // warp-uniform: the rest of the page is in the future of all rows
-                float s[2][4];
-                qk_16keys<D>(s, qf, sm.k[stage], kk * 16, lane);
-                if (need_mask) {
+                for (int n = 0; n < 8; ++n)
 #pragma unroll
-                    for (int n = 0; n < 2; ++n)
+                    for (int c = 0; c < 2; ++c) {
+                        const int key = key_base + n * 8 + (lane & 3) * 2 + c;
 #pragma unroll
-                        for (int c = 0; c < 2; ++c) {
-                            const int key = abs0 + n * 8 + (lane & 3) * 2 + c;
-#pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                const bool hidden = key > pos[h] || (window > 0 && key <= pos[h] - window);
-                                if (hidden) s[n][2 * h + c] = -INFINITY;
-                            }
+                        for (int h = 0; h < 2; ++h) {
+                            const bool hidden = key > pos[h] || (window > 0 && key <= pos[h] - window);
+                            if (hidden) s[n][2 * h + c] = -INFINITY;
                         }
-                }
-                uint32_t p[4];
-                softmax_update<D>(s, m, l, o, p, sl2);
-                pv_16keys<D>(o, p, sm.v[stage], kk * 16, lane);
+                    }
+                softmax_page<D>(s, m, l, o, p, sl2);
+                pv_page<D, false>(o, p, sm.v[stage], n16, lane);
             }
         }
-        __syncthreads();  // everyone is done with this stage before it is refilled
     }
     cp_async_wait<0>();
 

@@ -44,6 +44,7 @@ struct GemmParams {
     int out_dtype;                     // GK_F32 or GK_BF16
     int epilogue;
     int vector_ok;                     // rows of OUT start on 16-byte boundaries (stride_b == 1 case)
+    int swiglu_vector_ok;              // rows of the SwiGLU output start on 16-byte boundaries
     int a_static, b_static;            // the operand is not written by the kernel before (weights): it may
                                        // be fetched before that kernel has finished
     int* error_flag;
@@ -177,6 +178,19 @@ __device__ __forceinline__ void write_chunk(const GemmParams& p, float (&v)[16],
                 store_out<__nv_bfloat16>(out, at, silu(v[i]) * other);
             }
         }
+    } else if (a_ok && col0 + 16 <= p.rows_b && p.stride_b == 1 && p.swiglu_vector_ok) {
+        // gate and up alternate along B (TMEM columns): eight outputs, one 16-byte store
+        const long long at = (long long)row_a * p.stride_a + (col0 >> 1);
+        uint4 w;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(silu(v[0]) * v[1], silu(v[2]) * v[3]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(silu(v[4]) * v[5], silu(v[6]) * v[7]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(silu(v[8]) * v[9], silu(v[10]) * v[11]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(silu(v[12]) * v[13], silu(v[14]) * v[15]);
+        w.x = *reinterpret_cast<uint32_t*>(&h0);
+        w.y = *reinterpret_cast<uint32_t*>(&h1);
+        w.z = *reinterpret_cast<uint32_t*>(&h2);
+        w.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + at) = w;
     } else {
         // gate and up alternate along B (TMEM columns)
 #pragma unroll
@@ -514,6 +528,7 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     p.out_dtype = out_dtype;
     p.epilogue = epilogue;
     p.vector_ok = stride_b == 1 && ((uintptr_t)out & 15) == 0 && (stride_a * (out_dtype == GK_F32 ? 4 : 2)) % 16 == 0;
+    p.swiglu_vector_ok = ((uintptr_t)out & 15) == 0 && (stride_a * 2) % 16 == 0;
     p.a_static = a_static;
     p.b_static = b_static;
     p.error_flag = error_flag;

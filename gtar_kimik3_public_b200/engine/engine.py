@@ -16,7 +16,7 @@ import torch
 
 from ..cache import Cache, CacheFull
 from ..models.model import Model
-from .step import SequenceStep, plan_step
+from .step import SequenceStep, pack_step, plan_step
 
 
 @dataclass
@@ -37,11 +37,11 @@ class Engine:
         self.steps_run = 0
         self.graphs = None
         if use_graphs and model.device.type == "cuda" and model.graph_safe():
-            from .graphs import DecodeGraphs
+            from .graphs import StepGraphs
 
             if use_pdl is None:
                 use_pdl = os.environ.get("GTAR_B200_PDL", "1") != "0"
-            self.graphs = DecodeGraphs(model, self.cache, use_pdl)
+            self.graphs = StepGraphs(model, self.cache, use_pdl)
 
     # ------------------------------------------------------------------ requests
     def live(self) -> list[object]:
@@ -109,10 +109,11 @@ class Engine:
             sequences.append(SequenceStep(slot, past, [int(t) for t in entry.tokens], [int(w) for w in entry.want]))
         self.cache.sync()
         self.steps_run += 1
-        if self.graphs is not None and not new_ids and all(len(s.tokens) == 1 and s.want == [0] for s in sequences):
-            logits = self.graphs.run([s.slot for s in sequences], [s.past_len for s in sequences],
-                                     [s.tokens[0] for s in sequences])
-            return logits.clone() if keep_output else logits
+        if self.graphs is not None:
+            packed = pack_step(sequences, vocab, check_tokens=False)
+            if packed.n_want > 0 and self.graphs.wants_graph(packed):
+                logits = self.graphs.run(packed)
+                return logits.clone() if keep_output else logits
         ctx = plan_step(sequences, self.model.dtype, self.model.device, vocab)
         return self.model.step(ctx, self.cache)
 
@@ -133,6 +134,6 @@ class Engine:
         self.cache.sync()
         self.steps_run += 1
         if self.graphs is not None:
-            return self.graphs.run(slots, [s.past_len for s in sequences], None, device_tokens=tokens)
+            return self.graphs.run(pack_step(sequences, self.model.vocab_size, check_tokens=False), device_tokens=tokens)
         ctx = plan_step(sequences, self.model.dtype, self.model.device, self.model.vocab_size, device_tokens=tokens)
         return self.model.step(ctx, self.cache)

@@ -1,103 +1,141 @@
-"""Decode steps replayed from CUDA graphs.
+"""Steps replayed from CUDA graphs.
 
-A decode step launches some hundred small kernels; issued one by one from Python they cost
-far more host time than device time.  The whole step — embedding to logits — is therefore
-captured once per batch size and replayed.  Everything that changes from step to step lives in
-device memory that the kernels read (token ids, positions, slots, lengths, the page table), so
-one graph serves any set of sequences of that size, at any lengths, in any slots; the host's
-work per step is one small pinned copy of those numbers.
+A step launches some hundred kernels; issued one by one from Python they cost more host time
+than device time for all but the longest prompts.  A step's launches depend only on its *shape*
+— how many tokens, sequences and wanted rows, the longest sequence part — while everything else
+(token ids, positions, slots, lengths, the page table) lives in device memory that the kernels
+read.  So the whole step, embedding to logits, is captured once per shape and replayed; the
+host's work per step is one small pinned copy of those numbers.  Decode steps (one token per
+sequence) are captured at their first use, other shapes when they are seen a second time; the
+least recently used graphs are dropped beyond a limit.
+
+Inside a graph every kernel is launched with programmatic stream serialization: it may start
+(and fetch weights) while the kernel before it drains, and waits for that kernel's results only
+where it first needs them.
 """
 
 from __future__ import annotations
 
+from collections import OrderedDict
+
+import numpy as np
 import torch
 
-from ..parts.base import StepContext
+from ..ops.functional import decode_splits, set_pdl
+from .step import PackedStep, context_from_views
 
 
-class DecodeGraphs:
+class StepGraphs:
     RING = 8
+    MAX_PREFILL_GRAPHS = 12
 
     def __init__(self, model, cache, use_pdl: bool = True):
         self.model, self.cache, self.use_pdl = model, cache, use_pdl
-        self.n_max = cache.max_seqs
         device = model.device
-        n = self.n_max
-        # device-side step inputs at fixed addresses: tokens | positions | slots | lengths
-        self.meta = torch.zeros(4 * n, dtype=torch.int32, device=device)
-        self.arange = torch.arange(n + 1, dtype=torch.int32, device=device)
-        self.host = [torch.zeros(4 * n, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.t_max = cache.n_pages * cache.page_size  # no step can bring more tokens than the cache holds
+        self.s_max = cache.max_seqs
+        # tokens | positions | sequence of token | starts | slots | lengths | wanted rows, one after
+        # another from the front of the buffer: for a given shape every field has a fixed address
+        total = 4 * self.t_max + 3 * self.s_max + 1
+        self.meta = torch.zeros(total, dtype=torch.int32, device=device)
+        self.host = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.host_np = [h.numpy() for h in self.host]
-        self.events = [None] * self.RING
+        self.events: list[torch.cuda.Event | None] = [None] * self.RING
         self.turn = 0
-        self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self.graphs: OrderedDict[tuple, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = OrderedDict()
+        self.seen: set[tuple] = set()
         self.pool = None
+        self.launches: dict[tuple, int] = {}
+        layout = cache.layout.requests
+        self.n_kv = max((r.n_kv_heads for r in layout if hasattr(r, "n_kv_heads")), default=1)
 
-    def context(self, n: int, max_kv_len: int) -> StepContext:
-        big = self.n_max
-        ctx = StepContext(
-            n_tokens=n, n_seqs=n, dtype=self.model.dtype, tokens=self.meta[0:n], tok_pos=self.meta[big:big + n],
-            tok_seq=self.arange[:n], cu_q=self.arange[:n + 1], slots=self.meta[2 * big:2 * big + n],
-            kv_len=self.meta[3 * big:3 * big + n], want_rows=self.arange[:n], max_q_len=1, max_kv_len=max_kv_len,
-            max_position=max_kv_len - 1, all_single=True,
-        )
-        # launch shapes inside a graph must not depend on the lengths of the day
-        from ..ops.functional import decode_splits
+    # ------------------------------------------------------------------ step inputs
+    @staticmethod
+    def offsets(packed: PackedStep) -> list[int]:
+        out, at = [], 0
+        for field in packed.fields:
+            out.append(at)
+            at += len(field)
+        return out + [at]
 
-        layout = self.cache.layout.requests
-        n_kv = max((r.n_kv_heads for r in layout if hasattr(r, "n_kv_heads")), default=1)
-        ctx.extras["decode_splits"] = decode_splits(n, n_kv, self.cache.max_seq_len, self.cache.page_size)
-        return ctx
+    def views(self, packed: PackedStep) -> list[torch.Tensor]:
+        offsets = self.offsets(packed)
+        return [self.meta[o:o + len(f)] for o, f in zip(offsets, packed.fields)]
 
-    def upload(self, slots: list[int], past: list[int], tokens: list[int] | None) -> None:
-        """Puts the step's numbers where the captured kernels read them (one pinned copy)."""
-        n, big = len(slots), self.n_max
+    def upload(self, packed: PackedStep, skip_tokens: bool) -> None:
+        """Puts the step's numbers where the captured kernels read them.  The pinned buffers are
+        used in turn, each guarded by an event, so that a copy still waiting in the stream is never
+        overwritten by the host."""
         turn = self.turn
         self.turn = (turn + 1) % self.RING
         if self.events[turn] is not None:
-            self.events[turn].synchronize()  # the copy that last used this buffer has been done
-        buf = self.host_np[turn]
-        if tokens is not None:
-            buf[0:n] = tokens
-        buf[big:big + n] = past
-        buf[2 * big:2 * big + n] = slots
-        buf[3 * big:3 * big + n] = [p + 1 for p in past]
-        if tokens is not None:
-            self.meta.copy_(self.host[turn], non_blocking=True)
-        else:
-            self.meta[big:].copy_(self.host[turn][big:], non_blocking=True)
+            self.events[turn].synchronize()
+        buf, pinned = self.host_np[turn], self.host[turn]
+        offsets = self.offsets(packed)
+        for offset, field in zip(offsets, packed.fields):
+            buf[offset:offset + len(field)] = field
+        begin = offsets[1] if skip_tokens else 0  # the token ids come from the device in that case
+        self.meta[begin:offsets[-1]].copy_(pinned[begin:offsets[-1]], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self.events[turn] = event
 
-    def run(self, slots: list[int], past: list[int], tokens: list[int] | None,
-            device_tokens: torch.Tensor | None = None) -> torch.Tensor:
-        """Logits ``[n, vocab]`` of one token per sequence.  The returned tensor is the graph's own
-        output buffer: the next replay of the same batch size overwrites it."""
-        n = len(slots)
-        self.upload(slots, past, tokens)
-        if device_tokens is not None:
-            self.meta[0:n].copy_(device_tokens)
-        if n not in self.graphs:
-            self.model.prepare(self.cache.max_seq_len - 1)
-            ctx = self.context(n, self.cache.max_seq_len)
-            self.model.step(ctx, self.cache)  # a plain run first: one-time set-up must not be captured
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            # Inside the graph every kernel is launched with programmatic stream serialization: it may
-            # start (and fetch weights) while the kernel before it drains, and waits for that kernel's
-            # results only where it first needs them.
-            from ..ops.functional import set_pdl
+    # ------------------------------------------------------------------ graphs
+    @staticmethod
+    def key_of(packed: PackedStep) -> tuple:
+        return (packed.n_tokens, packed.n_seqs, packed.n_want, packed.max_q_len if not packed.all_single else 1)
 
-            before = set_pdl(self.use_pdl)
-            try:
-                with torch.cuda.graph(graph, pool=self.pool):
-                    logits = self.model.step(ctx, self.cache)
-            finally:
-                set_pdl(before)
-            if self.pool is None:
-                self.pool = graph.pool()
-            self.graphs[n] = (graph, logits)
-        graph, logits = self.graphs[n]
+    def wants_graph(self, packed: PackedStep) -> bool:
+        """Decode shapes always; other shapes from their second appearance on."""
+        key = self.key_of(packed)
+        if key in self.graphs or packed.all_single:
+            return True
+        if key in self.seen:
+            return True
+        self.seen.add(key)
+        if len(self.seen) > 4096:
+            self.seen.clear()
+        return False
+
+    def run(self, packed: PackedStep, device_tokens: torch.Tensor | None = None) -> torch.Tensor:
+        """Logits ``[n_want, vocab]``.  The returned tensor is the graph's own output buffer: the next
+        replay of the same shape overwrites it."""
+        key = self.key_of(packed)
+        self.upload(packed, skip_tokens=device_tokens is not None)
+        if device_tokens is not None:
+            self.meta[0:packed.n_tokens].copy_(device_tokens)
+        if key not in self.graphs:
+            self._capture(key, packed)
+        self.graphs.move_to_end(key)
+        graph, logits = self.graphs[key]
         graph.replay()
+        from ..ops import library
+
+        library.launch_count += self.launches[key]
         return logits
+
+    def _capture(self, key: tuple, packed: PackedStep) -> None:
+        from ..ops import library
+
+        longest = self.cache.max_seq_len
+        self.model.prepare(longest - 1)
+        # launch shapes inside a graph must not depend on the lengths of the day: bounds of the cache
+        ctx = context_from_views(packed, self.views(packed), self.model.dtype, max_kv_len=longest)
+        ctx.extras["decode_splits"] = decode_splits(packed.n_seqs, self.n_kv, longest, self.cache.page_size)
+        self.model.step(ctx, self.cache)  # a plain run first: one-time set-up must not be captured
+        torch.cuda.synchronize()
+        while len(self.graphs) >= self.MAX_PREFILL_GRAPHS + self.s_max:
+            self.graphs.popitem(last=False)
+        graph = torch.cuda.CUDAGraph()
+        before = set_pdl(self.use_pdl)
+        count = library.launch_count
+        try:
+            with torch.cuda.graph(graph, pool=self.pool):
+                logits = self.model.step(ctx, self.cache)
+        finally:
+            set_pdl(before)
+        self.launches[key] = library.launch_count - count
+        library.launch_count = count
+        if self.pool is None:
+            self.pool = graph.pool()
+        self.graphs[key] = (graph, logits)

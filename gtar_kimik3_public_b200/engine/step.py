@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from ..parts.base import StepContext
@@ -26,49 +27,94 @@ class SequenceStep:
     want: list[int]  # places among ``tokens`` whose logits are asked for
 
 
-def plan_step(sequences: list[SequenceStep], dtype: torch.dtype, device: torch.device, vocab_size: int,
-              device_tokens: torch.Tensor | None = None) -> StepContext:
-    """Builds the step's context.  With ``device_tokens`` (int32, one per packed token, already on
-    the device — e.g. the sampler's output) the sequences' ``tokens`` only give the counts."""
+@dataclass
+class PackedStep:
+    """The numbers of a step on the host, in the order they are laid out for the device:
+    tokens | positions | sequence of each token | starts | slots | lengths | wanted rows."""
+
+    fields: list[np.ndarray]
+    q_lens: list[int]
+    past: list[int]
+    slots: list[int]
+
+    @property
+    def n_tokens(self) -> int:
+        return len(self.fields[0])
+
+    @property
+    def n_seqs(self) -> int:
+        return len(self.slots)
+
+    @property
+    def n_want(self) -> int:
+        return len(self.fields[6])
+
+    @property
+    def all_single(self) -> bool:
+        return self.n_tokens == self.n_seqs
+
+    @property
+    def max_q_len(self) -> int:
+        return max(self.q_lens)
+
+    @property
+    def max_kv_len(self) -> int:
+        return max(p + n for p, n in zip(self.past, self.q_lens))
+
+
+def pack_step(sequences: list[SequenceStep], vocab_size: int, check_tokens: bool = True) -> PackedStep:
     if not sequences:
         raise ValueError("a step needs at least one sequence")
-    tokens: list[int] = []
-    tok_pos: list[int] = []
-    tok_seq: list[int] = []
-    cu_q = [0]
-    want_rows: list[int] = []
+    q_lens = [len(s.tokens) for s in sequences]
+    if min(q_lens) == 0:
+        raise ValueError(f"sequence {q_lens.index(0)} of the step brings no token")
+    past = [s.past_len for s in sequences]
+    starts = np.zeros(len(sequences) + 1, dtype=np.int32)
+    np.cumsum(q_lens, out=starts[1:])
+    tokens = np.fromiter((t for s in sequences for t in s.tokens), dtype=np.int64, count=int(starts[-1]))
+    if check_tokens and tokens.size and (tokens.min() < 0 or tokens.max() >= vocab_size):
+        bad = int(tokens[(tokens < 0) | (tokens >= vocab_size)][0])
+        raise ValueError(f"token id {bad} is outside the vocabulary of {vocab_size}")
+    tok_seq = np.repeat(np.arange(len(sequences), dtype=np.int32), q_lens)
+    tok_pos = np.arange(int(starts[-1]), dtype=np.int32) - starts[:-1][tok_seq] + np.asarray(past, dtype=np.int32)[tok_seq]
+    want_rows = []
     for index, seq in enumerate(sequences):
-        n = len(seq.tokens)
-        if n == 0:
-            raise ValueError(f"sequence {index} of the step brings no token")
         for place in seq.want:
-            if not 0 <= place < n:
-                raise ValueError(f"wanted place {place} is outside the {n} tokens sequence {index} brings")
-            want_rows.append(cu_q[-1] + place)
-        if device_tokens is None:
-            for token in seq.tokens:
-                if not 0 <= token < vocab_size:
-                    raise ValueError(f"token id {token} is outside the vocabulary of {vocab_size}")
-        tokens.extend(seq.tokens)
-        tok_pos.extend(range(seq.past_len, seq.past_len + n))
-        tok_seq.extend([index] * n)
-        cu_q.append(cu_q[-1] + n)
+            if not 0 <= place < q_lens[index]:
+                raise ValueError(f"wanted place {place} is outside the {q_lens[index]} tokens sequence {index} brings")
+            want_rows.append(int(starts[index]) + place)
     slots = [s.slot for s in sequences]
-    kv_len = [s.past_len + len(s.tokens) for s in sequences]
-    fields = [tokens, tok_pos, tok_seq, cu_q, slots, kv_len, want_rows]
-    flat = torch.tensor([x for f in fields for x in f], dtype=torch.int32)
+    fields = [
+        tokens.astype(np.int32), tok_pos.astype(np.int32), tok_seq, starts, np.asarray(slots, dtype=np.int32),
+        np.asarray([p + n for p, n in zip(past, q_lens)], dtype=np.int32), np.asarray(want_rows, dtype=np.int32),
+    ]
+    return PackedStep(fields, q_lens, past, slots)
+
+
+def context_from_views(packed: PackedStep, views: list[torch.Tensor], dtype: torch.dtype, max_kv_len: int | None = None,
+                       device_tokens: torch.Tensor | None = None) -> StepContext:
+    max_kv = packed.max_kv_len if max_kv_len is None else max_kv_len
+    return StepContext(
+        n_tokens=packed.n_tokens, n_seqs=packed.n_seqs, dtype=dtype,
+        tokens=views[0] if device_tokens is None else device_tokens, tok_pos=views[1], tok_seq=views[2], cu_q=views[3],
+        slots=views[4], kv_len=views[5], want_rows=views[6], max_q_len=packed.max_q_len, max_kv_len=max_kv,
+        max_position=max_kv - 1, all_single=packed.all_single, host_q_len=packed.q_lens, host_past_len=packed.past,
+        host_slots=packed.slots,
+    )
+
+
+def plan_step(sequences: list[SequenceStep], dtype: torch.dtype, device: torch.device, vocab_size: int,
+              device_tokens: torch.Tensor | None = None) -> StepContext:
+    """Builds the step's context in fresh device memory (one pinned copy).  With ``device_tokens``
+    (int32, one per packed token, already on the device — e.g. the sampler's output) the
+    sequences' ``tokens`` only give the counts."""
+    packed = pack_step(sequences, vocab_size, check_tokens=device_tokens is None)
+    flat = torch.from_numpy(np.concatenate(packed.fields))
     if device.type == "cuda":
         flat = flat.pin_memory()
     dev = flat.to(device, non_blocking=True)
-    views = []
-    start = 0
-    for f in fields:
+    views, start = [], 0
+    for f in packed.fields:
         views.append(dev[start:start + len(f)])
         start += len(f)
-    q_lens = [len(s.tokens) for s in sequences]
-    return StepContext(
-        n_tokens=len(tokens), n_seqs=len(sequences), dtype=dtype,
-        tokens=views[0] if device_tokens is None else device_tokens, tok_pos=views[1], tok_seq=views[2], cu_q=views[3], slots=views[4], kv_len=views[5],
-        want_rows=views[6], max_q_len=max(q_lens), max_kv_len=max(kv_len), max_position=max(kv_len) - 1,
-        all_single=all(n == 1 for n in q_lens), host_q_len=q_lens, host_past_len=[s.past_len for s in sequences], host_slots=slots,
-    )
+    return context_from_views(packed, views, dtype, device_tokens=device_tokens)
