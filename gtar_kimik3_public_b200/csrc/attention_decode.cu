@@ -15,6 +15,7 @@
 // the second product, as in the reference's kernel (flash_attention_2.py:55).
 
 #include "attention_mma.cuh"
+#include "no_alloc.h"
 
 namespace {
 
@@ -233,4 +234,43 @@ GK_EXPORT int gk_attention_decode_bf16(const void* q, const void* k_pages, const
                                  max_pages, scale, window, n_splits, s);
     return launch_decode<128>(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv,
                               max_pages, scale, window, n_splits, s);
+}
+
+// ---------------------------------------------------------------- the entry point that allocates nothing
+// Scratch for the partial results of the splits, owned by the library.  In host code this name is
+// only a handle for cudaGetSymbolAddress; the kernels get the device address looked up below.
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[GK_NO_ALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_no_alloc_ptr[MAX_DEVICES] = {};  // device address of the scratch, per device, once looked up
+}  // namespace
+
+GK_EXPORT int gk_attention_decode_bf16_no_alloc(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                                const int* kv_len, const int* slots, const int* block_table,
+                                                int n_seqs, int n_q, int n_kv, int head_dim, int max_pages,
+                                                int page_size, float scale, int window, int n_splits, void* stream) {
+    GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && (head_dim == 64 || head_dim == 128),
+               "attention_decode_no_alloc: bad sizes n_seqs=%d n_q=%d n_splits=%d head_dim=%d", n_seqs, n_q, n_splits, head_dim);
+    const unsigned long long need = (unsigned long long)n_seqs * n_q * n_splits * (head_dim + 2) * sizeof(float);
+    GK_REQUIRE(need <= GK_NO_ALLOC_SCRATCH_BYTES,
+               "attention_decode_no_alloc: %d sequences x %d heads x %d splits need %llu bytes of scratch; the "
+               "built-in scratch holds %u (use fewer splits, or gk_attention_decode_bf16 with scratch of your own)",
+               n_seqs, n_q, n_splits, need, (unsigned)GK_NO_ALLOC_SCRATCH_BYTES);
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "attention_decode_no_alloc: cudaGetDevice: %s", cudaGetErrorString(err));
+    GK_REQUIRE(device >= 0 && device < MAX_DEVICES, "attention_decode_no_alloc: device %d is out of range", device);
+    if (g_no_alloc_ptr[device] == nullptr) {
+        // once per device, with that device current: the array's address on THIS device
+        void* ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_no_alloc_scratch);
+        if (err != cudaSuccess || ptr == nullptr)
+            return gk_fail(GK_CUDA_ERROR, "attention_decode_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+        g_no_alloc_ptr[device] = static_cast<float*>(ptr);
+    }
+    float* part_o = g_no_alloc_ptr[device];
+    float* part_ml = part_o + (size_t)n_seqs * n_q * n_splits * head_dim;
+    return gk_attention_decode_bf16(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q,
+                                    n_kv, head_dim, max_pages, page_size, scale, window, n_splits, stream);
 }
