@@ -7,8 +7,10 @@
 //
 // Grid (split, kv head, sequence).  A sequence's pages are divided among `n_splits` blocks so
 // that small batches still fill the GPU; each block streams its pages through a multi-stage
-// cp.async pipeline, its four warps taking 16 keys of a page each, and leaves an unnormalised
-// partial result (max, sum, output) in scratch memory; a second kernel merges the splits.
+// cp.async pipeline, its four warps taking 16 keys of a page each, and ends with an unnormalised
+// partial result (max, sum, output).  Up to eight splits form a thread-block cluster and are merged
+// by its first block through distributed shared memory; more splits leave their partial results in
+// scratch memory and a second kernel merges them.
 // Lengths come from device memory, so a captured launch stays valid as sequences grow.
 //
 // Softmax statistics and accumulators are 32-bit; probabilities are rounded to bfloat16 for
@@ -35,7 +37,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
     float* __restrict__ part_ml, const int* __restrict__ kv_len, const int* __restrict__ slots,
-    const int* __restrict__ block_table, int n_q, int n_kv, int max_pages, float sl2, int window, int n_splits) {
+    const int* __restrict__ block_table, int n_q, int n_kv, int max_pages, float sl2, int window, int n_splits,
+    int cluster_merge) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     DecodeSmem<D>& sm = *reinterpret_cast<DecodeSmem<D>*>(smem_raw);
     const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
@@ -134,6 +137,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         }
     }
     __syncthreads();
+    float* cl_o = red_ml + WARPS * 16 * 2;   // [group][D]   this block's result, for the cluster merge
+    float* cl_ml = cl_o + 16 * D;            // [group][2]
     for (int idx = tid; idx < group * D; idx += WARPS * 32) {
         const int r = idx / D, c = idx % D;
         float mm = -INFINITY;
@@ -151,6 +156,12 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         const int hq = hk * group + r;
         if (n_splits == 1) {
             out[((size_t)seq * n_q + hq) * D + c] = __float2bfloat16_rn(acc / ll);
+        } else if (cluster_merge) {
+            cl_o[r * D + c] = acc;
+            if (c == 0) {
+                cl_ml[r * 2] = mm;
+                cl_ml[r * 2 + 1] = ll;
+            }
         } else {
             const size_t at = ((size_t)seq * n_q + hq) * n_splits + split;
             part_o[at * D + c] = acc;
@@ -159,6 +170,46 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
                 part_ml[at * 2 + 1] = ll;
             }
         }
+    }
+    if (n_splits > 1 && cluster_merge) {
+        // The splits of one (sequence, kv head) are one cluster: block 0 merges the partial results of
+        // all of them through distributed shared memory, in split order; no scratch, no second kernel.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (split == 0) {
+            const uint32_t o_addr = smem_u32(cl_o), ml_addr = smem_u32(cl_ml);
+            for (int idx = tid; idx < group * D; idx += WARPS * 32) {
+                const int r = idx / D;
+                float ms[8], ls[8], os[8];
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) {
+                    ms[sp] = -INFINITY;
+                    ls[sp] = os[sp] = 0.f;
+                    if (sp < n_splits) {
+                        uint32_t ra, rb;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(ml_addr + (uint32_t)r * 8u), "r"(sp));
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(o_addr + (uint32_t)idx * 4u), "r"(sp));
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ms[sp]) : "r"(ra) : "memory");
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ls[sp]) : "r"(ra + 4u) : "memory");
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(os[sp]) : "r"(rb) : "memory");
+                    }
+                }
+                float mm = -INFINITY;
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) mm = fmaxf(mm, ms[sp]);
+                float ll = 0.f, acc = 0.f;
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp)
+                    if (sp < n_splits && ms[sp] != -INFINITY) {
+                        const float f = exp2f(ms[sp] - mm);
+                        ll += ls[sp] * f;
+                        acc += os[sp] * f;
+                    }
+                out[((size_t)seq * n_q + hk * group + r) * D + (idx % D)] = __float2bfloat16_rn(acc / ll);
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
 }
 
@@ -188,7 +239,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
                   const int* kv_len, const int* slots, const int* block_table, int n_seqs, int n_q, int n_kv,
                   int max_pages, float scale, int window, int n_splits, cudaStream_t stream) {
     const size_t stage_bytes = sizeof(DecodeSmem<D>);
-    const size_t merge_bytes = (size_t)WARPS * 16 * (D + 2) * sizeof(float);
+    const size_t merge_bytes = ((size_t)WARPS * 16 * (D + 2) + 16 * (D + 2)) * sizeof(float);
     const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
     static bool configured = false;  // per template instance; the attribute is per device function
     if (!configured) {
@@ -199,11 +250,14 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
     }
     const float sl2 = scale * 1.4426950408889634f;
     dim3 grid(n_splits, n_kv, n_seqs);
-    gk_launch(attention_decode_kernel<D>, grid, dim3(WARPS * 32), smem, stream,
+    // up to eight splits without scratch: they form a cluster and merge through distributed shared memory
+    const int cluster_merge = n_splits > 1 && n_splits <= 8 && part_o == nullptr;
+    gk_launch_cluster(attention_decode_kernel<D>, grid, dim3(WARPS * 32), smem, stream,
+        dim3(cluster_merge ? n_splits : 1, 1, 1),
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
-        part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits);
+        part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits, cluster_merge);
     GK_CHECK_LAUNCH("attention_decode");
-    if (n_splits > 1) {
+    if (n_splits > 1 && !cluster_merge) {
         gk_launch(attention_decode_merge_kernel<D>, dim3(n_seqs * n_q), dim3(D <= 64 ? 64 : 128), 0, stream,
                   (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, n_splits);
         GK_CHECK_LAUNCH("attention_decode_merge");
@@ -213,8 +267,10 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
 
 }  // namespace
 
-// Scratch the caller provides when n_splits > 1:
+// With scratch (any number of splits; a second kernel merges them):
 //   part_o  float [n_seqs * n_q * n_splits * head_dim],  part_ml  float [n_seqs * n_q * n_splits * 2].
+// Without scratch (null pointers; up to 8 splits): the splits of a (sequence, kv head) run as one
+// thread-block cluster and merge through distributed shared memory.
 GK_EXPORT int gk_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
                                        float* part_o, float* part_ml, const int* kv_len, const int* slots,
                                        const int* block_table, int n_seqs, int n_q, int n_kv, int head_dim,
@@ -225,7 +281,8 @@ GK_EXPORT int gk_attention_decode_bf16(const void* q, const void* k_pages, const
     GK_REQUIRE(page_size == attn::PAGE, "attention_decode: page_size must be %d, got %d", attn::PAGE, page_size);
     GK_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode: head_dim %d is not 64 or 128 (use the exact kernel)", head_dim);
     GK_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_kv <= 65535 && n_seqs <= 65535, "attention_decode: grid too large");
-    GK_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: scratch is needed for more than one split");
+    GK_REQUIRE(n_splits <= 8 || (part_o && part_ml), "attention_decode: scratch is needed for more than eight splits");
+    GK_REQUIRE((part_o == nullptr) == (part_ml == nullptr), "attention_decode: both scratch arrays or neither");
     GK_REQUIRE(window >= 0, "attention_decode: window must be >= 0");
     if (n_seqs == 0) return GK_OK;
     cudaStream_t s = (cudaStream_t)stream;

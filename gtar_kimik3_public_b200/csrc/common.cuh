@@ -39,10 +39,10 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 extern int g_gk_pdl;  // set through gk_set_pdl(): launch kernels with programmatic stream serialization
 
 // Launches `kernel` on `stream`, with the programmatic-dependent-launch attribute when it is switched
-// on, and as thread-block clusters of (1, 1, cluster_z) blocks when cluster_z > 1.
+// on, and as thread-block clusters of `cluster` blocks when that is more than one block.
 template <typename... KArgs, typename... Args>
 inline cudaError_t gk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                     int cluster_z, Args... args) {
+                                     dim3 cluster, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -55,11 +55,11 @@ inline cudaError_t gk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 b
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
-    if (cluster_z > 1) {
+    if (cluster.x * cluster.y * cluster.z > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 1;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        attr[n].val.clusterDim.x = cluster.x;
+        attr[n].val.clusterDim.y = cluster.y;
+        attr[n].val.clusterDim.z = cluster.z;
         ++n;
     }
     cfg.attrs = n ? attr : nullptr;
@@ -70,7 +70,7 @@ inline cudaError_t gk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 b
 template <typename... KArgs, typename... Args>
 inline cudaError_t gk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                              Args... args) {
-    return gk_launch_cluster(kernel, grid, block, smem, stream, 1, args...);
+    return gk_launch_cluster(kernel, grid, block, smem, stream, dim3(1, 1, 1), args...);
 }
 
 __device__ __forceinline__ float to_float(float x) { return x; }

@@ -360,73 +360,85 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             const int rows_per = BM / n_ranks;
             const uint32_t stage_addr = smem_u32(sm.a[0]);
             const int e = (warp - 2) * 32 + lane;
-            // Elements of the slice are taken four at a time per thread: the loads of all partial sums
-            // of the four are issued before the first is used, then added in the order of the splits.
-            auto load_parts = [&](int row, int col, float (&part)[8]) {
+            // A thread takes four consecutive rows of one column at a time: one 16-byte load from every
+            // block's partial tile (all issued before the first is used), added in the order of the
+            // splits; two such groups are in flight per thread.
+            auto load_parts = [&](int row, int col, float4 (&part)[8]) {
                 const uint32_t local = stage_addr + (uint32_t)(col * BM + row) * 4u;
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
-                    part[r] = 0.f;
+                    part[r] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (r < n_ranks) {
                         uint32_t remote;
                         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(r));
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[r]) : "r"(remote) : "memory");
+                        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                     : "=f"(part[r].x), "=f"(part[r].y), "=f"(part[r].z), "=f"(part[r].w)
+                                     : "r"(remote)
+                                     : "memory");
                     }
                 }
             };
-            auto add_up = [&](const float (&part)[8]) {
-                float acc = part[0];
+            auto add_up = [&](const float4 (&part)[8]) {
+                float4 acc = part[0];
 #pragma unroll
                 for (int r = 1; r < 8; ++r)
-                    if (r < n_ranks) acc += part[r];
+                    if (r < n_ranks) {
+                        acc.x += part[r].x;
+                        acc.y += part[r].y;
+                        acc.z += part[r].z;
+                        acc.w += part[r].w;
+                    }
                 return acc;
             };
             char* out = reinterpret_cast<char*>(p.out);
-            constexpr int U = 4;
-            if (p.epilogue == EPI_STORE) {
-                const int count = rows_per * BN;
-                for (int base = e; base < count; base += 128 * U) {
-                    float part[U][8];
+            const int quads = rows_per / 4, count = quads * BN;
+            const bool swiglu = p.epilogue == EPI_SWIGLU_A;
+            // 8-byte (plain, bfloat16) / 16-byte (plain, float32) / 4-byte (SwiGLU) stores need aligned rows
+            const bool vec = p.stride_a == 1 && !swiglu && ((uintptr_t)out & 15) == 0 &&
+                             (p.stride_b * (p.out_dtype == GK_F32 ? 4 : 2)) % 16 == 0;
+            constexpr int U = 2;
+            for (int base = e; base < count; base += 128 * U) {
+                float4 part[U][8];
 #pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        const int idx = base + u * 128;
-                        if (idx < count) load_parts(rank * rows_per + idx % rows_per, idx / rows_per, part[u]);
-                    }
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        const int idx = base + u * 128;
-                        if (idx >= count) continue;
-                        const int row_a = tile_a * BM + rank * rows_per + idx % rows_per, rb = tile_b * BN + idx / rows_per;
-                        if (row_a < p.rows_a && rb < p.rows_b) {
-                            const float v = add_up(part[u]);
-                            const long long at = (long long)row_a * p.stride_a + (long long)rb * p.stride_b;
-                            if (p.out_dtype == GK_F32) store_out<float>(out, at, v);
-                            else store_out<__nv_bfloat16>(out, at, v);
-                        }
-                    }
+                for (int u = 0; u < U; ++u) {
+                    const int idx = base + u * 128;
+                    if (idx < count) load_parts(rank * rows_per + 4 * (idx % quads), idx / quads, part[u]);
                 }
-            } else {  // EPI_SWIGLU_A: rows alternate gate, up
-                const int pairs = rows_per / 2, count = pairs * BN;
-                for (int base = e; base < count; base += 128 * (U / 2)) {
-                    float part[U][8];
 #pragma unroll
-                    for (int u = 0; u < U / 2; ++u) {
-                        const int idx = base + u * 128;
-                        if (idx < count) {
-                            const int row_g = rank * rows_per + 2 * (idx % pairs);
-                            load_parts(row_g, idx / pairs, part[2 * u]);
-                            load_parts(row_g + 1, idx / pairs, part[2 * u + 1]);
+                for (int u = 0; u < U; ++u) {
+                    const int idx = base + u * 128;
+                    if (idx >= count) continue;
+                    const int row_a = tile_a * BM + rank * rows_per + 4 * (idx % quads), rb = tile_b * BN + idx / quads;
+                    if (row_a >= p.rows_a || rb >= p.rows_b) continue;
+                    const float4 v = add_up(part[u]);
+                    const float vs[4] = {v.x, v.y, v.z, v.w};
+                    if (swiglu) {
+#pragma unroll
+                        for (int i = 0; i < 4; i += 2) {
+                            if (row_a + i + 1 < p.rows_a) {
+                                const long long at = (long long)((row_a + i) >> 1) * p.stride_a + (long long)rb * p.stride_b;
+                                store_out<__nv_bfloat16>(out, at, silu(vs[i]) * vs[i + 1]);
+                            }
                         }
-                    }
+                    } else if (vec && row_a + 3 < p.rows_a) {
+                        const long long at = (long long)row_a + (long long)rb * p.stride_b;
+                        if (p.out_dtype == GK_F32) {
+                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at) = v;
+                        } else {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                            uint2 w;
+                            w.x = *reinterpret_cast<uint32_t*>(&lo);
+                            w.y = *reinterpret_cast<uint32_t*>(&hi);
+                            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + at) = w;
+                        }
+                    } else {
 #pragma unroll
-                    for (int u = 0; u < U / 2; ++u) {
-                        const int idx = base + u * 128;
-                        if (idx >= count) continue;
-                        const int row_a = tile_a * BM + rank * rows_per + 2 * (idx % pairs), rb = tile_b * BN + idx / pairs;
-                        if (row_a < p.rows_a && rb < p.rows_b) {
-                            const float g = add_up(part[2 * u]), u_val = add_up(part[2 * u + 1]);
-                            const long long at = (long long)(row_a >> 1) * p.stride_a + (long long)rb * p.stride_b;
-                            store_out<__nv_bfloat16>(out, at, silu(g) * u_val);
+                        for (int i = 0; i < 4; ++i) {
+                            if (row_a + i < p.rows_a) {
+                                const long long at = (long long)(row_a + i) * p.stride_a + (long long)rb * p.stride_b;
+                                if (p.out_dtype == GK_F32) store_out<float>(out, at, vs[i]);
+                                else store_out<__nv_bfloat16>(out, at, vs[i]);
+                            }
                         }
                     }
                 }
@@ -486,7 +498,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
         if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
         configured = true;
     }
-    gk_launch_cluster(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, (int)grid.z, ma, mb, p);
+    gk_launch_cluster(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, dim3(1, 1, grid.z), ma, mb, p);
     GK_CHECK_LAUNCH("gemm_tc");
     return GK_OK;
 }

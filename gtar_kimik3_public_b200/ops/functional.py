@@ -254,14 +254,19 @@ EPI_STORE, EPI_SWIGLU_A, EPI_SWIGLU_B = 0, 1, 2
 SKINNY_M = 64  # up to this many tokens the weights take the MMA's 128 rows (swap-AB)
 
 
+SPLIT_TARGET_BLOCKS = 128
+SKINNY_BN_MAX = 64
+SPLIT_MIN_K_BLOCKS = 4
+
+
 def split_k_for(m: int, n: int, k: int, sm_count: int = 148) -> int:
     """How many blocks share the K range of one output tile of a skinny product (m <= SKINNY_M).
     More blocks stream weights from more SMs: about 64 blocks in all, at least four k-blocks of 64
     each, and 1, 2, 4 or 8 ways (the blocks of a tile form one cluster)."""
     if m > SKINNY_M:
         return 1
-    tiles = -(-n // 128)
-    limit = min(64 // tiles, (k // 64) // 4, 8)
+    tiles = -(-n // 128) * -(-m // min(SKINNY_BN_MAX, 16 if m <= 16 else 32 if m <= 32 else 64))
+    limit = min(SPLIT_TARGET_BLOCKS // tiles, (k // 64) // SPLIT_MIN_K_BLOCKS, 8)
     return 8 if limit >= 8 else 4 if limit >= 4 else 2 if limit >= 2 else 1
 
 
@@ -299,6 +304,7 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
     flag = error_flag(x.device)
     if m <= SKINNY_M:
         bn = 16 if m <= 16 else 32 if m <= 32 else 64
+        bn = min(bn, SKINNY_BN_MAX)
         call("gk_gemm_bf16_tc", ptr(weight), n, k, ptr(x), m, k, k, ptr(out), dtype_code(out_dtype), 1, n_out,
              EPI_SWIGLU_A if swiglu else EPI_STORE, bn, splits, 1, 0, ptr(flag), stream_ptr())
     else:
@@ -311,8 +317,9 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
 def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_count: int = 148) -> int:
     """How many blocks share a sequence's pages in decode attention: enough that about two blocks
     per SM are busy, never more than the longest sequence has pages."""
-    want = -(-2 * sm_count // max(1, n_seqs * n_kv))
-    return max(1, min(want, -(-max_kv_len // page_size), 64))
+    want = (2 * sm_count) // max(1, n_seqs * n_kv)  # rounded down: one wave of two blocks per SM
+    want = max(1, min(want, -(-max_kv_len // page_size), 64))
+    return want if want > 16 else min(want, 8)  # up to eight merge in-kernel; scratch pays off only well beyond
 
 
 def attention_decode(
@@ -324,10 +331,12 @@ def attention_decode(
     window: int = 0,
     n_splits: int = 1,
     out: torch.Tensor | None = None,
+    use_scratch: bool = False,
 ) -> torch.Tensor:
     """Attention of one new token per sequence (``q [n_seqs, n_q, d]`` bfloat16, ``d`` 64 or 128) over
-    the pages; ``kv_len[i]`` counts the sequence's cached tokens including the new one.  With
-    ``n_splits > 1`` the partial results go through scratch memory allocated here."""
+    the pages; ``kv_len[i]`` counts the sequence's cached tokens including the new one.  Up to eight
+    splits merge inside one kernel (a cluster per sequence and kv head); more, or ``use_scratch``, go
+    through scratch memory allocated here and a second kernel."""
     require_device(q.device)
     _check(q, "q", torch.bfloat16, 3)
     n, n_q, d = q.shape
@@ -343,7 +352,7 @@ def attention_decode(
     if out is None:
         out = torch.empty_like(q)
     part_o = part_ml = None
-    if n_splits > 1:
+    if n_splits > 8 or (n_splits > 1 and use_scratch):
         part_o = torch.empty((n * n_q * n_splits * d,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n * n_q * n_splits * 2,), dtype=torch.float32, device=q.device)
     call(

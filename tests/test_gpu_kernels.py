@@ -316,8 +316,8 @@ def test_sample_follows_the_softmax():
 
 # ------------------------------------------------------------------ bfloat16 decode attention (split-KV)
 @pytest.mark.parametrize("n_q,n_kv,d", [(4, 4, 64), (16, 8, 128), (6, 2, 128), (16, 1, 64)])
-@pytest.mark.parametrize("n_splits", [1, 3, 40])
-def test_attention_decode_bf16(n_q, n_kv, d, n_splits):
+@pytest.mark.parametrize("n_splits,use_scratch", [(1, False), (3, False), (8, False), (3, True), (40, False)])
+def test_attention_decode_bf16(n_q, n_kv, d, n_splits, use_scratch):
     dtype = torch.bfloat16
     lens = [1, 63, 64, 65, 777, 1000, 130]
     kv, slots, table = scrambled_pages(len(lens), 1000, n_kv, d, dtype, seed=12)
@@ -330,7 +330,7 @@ def test_attention_decode_bf16(n_q, n_kv, d, n_splits):
         qs.append(q)
         wants.append(dense_attention(q.double(), k.double(), v.double(), n - 1))
     kv_len = torch.tensor(lens, dtype=torch.int32).to(DEV)
-    out = F().attention_decode(torch.cat(qs).to(DEV), kv, kv_len, slots.to(DEV), d**-0.5, 0, n_splits)
+    out = F().attention_decode(torch.cat(qs).to(DEV), kv, kv_len, slots.to(DEV), d**-0.5, 0, n_splits, use_scratch=use_scratch)
     got, want = out.double().cpu(), torch.cat(wants)
     assert torch.isfinite(got).all()  # the poisoned places beyond each length were not used
     # the yardstick: the exact kernel on the same bfloat16 inputs rounds its output once

@@ -56,7 +56,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
 
     for seed, lens, n_q, n_kv, d, n_splits in ((1, [700, 64, 1, 333], 16, 8, 128, 5), (2, [100, 900, 65], 4, 1, 64, 7)):
         q, kv, kv_len, slots = _inputs(seed, lens, n_q, n_kv, d)
-        want = F.attention_decode(q, kv, kv_len, slots, d**-0.5, 0, n_splits)
+        want = F.attention_decode(q, kv, kv_len, slots, d**-0.5, 0, n_splits, use_scratch=True)
         torch.cuda.synchronize()
         status, got, message = _call_no_alloc(q, kv, kv_len, slots, d**-0.5, n_splits)
         torch.cuda.synchronize()
