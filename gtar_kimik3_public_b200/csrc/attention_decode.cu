@@ -44,8 +44,11 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = n_q / n_kv;
-    pdl_wait();
     pdl_launch_dependents();
+    // Lengths, slots and the page table are step inputs (copied in before the step's first kernel),
+    // and every page but the one holding the new token was written by earlier steps: all of that may
+    // be read while the kernel before this one (which writes the new token's key and value and the
+    // queries) is still running.
     const int len = kv_len[seq];
     const int lo = (window > 0 && len - window > 0) ? len - window : 0;  // first visible key
     const int* pages = block_table + (size_t)slots[seq] * max_pages;
@@ -54,6 +57,31 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const int p_begin = first_page + split * per_split;
     const int p_end = min(p_begin + per_split, end_page);
     const int n_iter = max(p_end - p_begin, 0);
+    const int new_page = (len - 1) / PAGE;
+
+    auto issue = [&](int it) {
+        if (it < n_iter) {
+            const int p = p_begin + it;
+            const int page = pages[p];
+            const int valid = min(PAGE, len - p * PAGE);
+            const size_t base = ((size_t)page * n_kv + hk) * PAGE * D;
+            const int stage = it % STAGES;
+            load_tile_async<D>(sm.k[stage], k_pages + base, D, PAGE, valid, tid, WARPS * 32);
+            load_tile_async<D>(sm.v[stage], v_pages + base, D, PAGE, valid, tid, WARPS * 32);
+        }
+        cp_async_commit();
+    };
+    int early = 0;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s)
+        if (early == s && s < n_iter && p_begin + s < new_page) {
+            issue(s);
+            early = s + 1;
+        }
+    pdl_wait();
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s)
+        if (s >= early) issue(s);
 
     // Query fragments: row r of the tile is query head hk*group + r (rows >= group are zero).
     uint32_t qf[D / 16][4];
@@ -70,19 +98,6 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         }
     }
 
-    auto issue = [&](int it) {
-        if (it < n_iter) {
-            const int p = p_begin + it;
-            const int page = pages[p];
-            const int valid = min(PAGE, len - p * PAGE);
-            const size_t base = ((size_t)page * n_kv + hk) * PAGE * D;
-            const int stage = it % STAGES;
-            load_tile_async<D>(sm.k[stage], k_pages + base, D, PAGE, valid, tid, WARPS * 32);
-            load_tile_async<D>(sm.v[stage], v_pages + base, D, PAGE, valid, tid, WARPS * 32);
-        }
-        cp_async_commit();
-    };
-
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[D / 8][4];
 #pragma unroll
@@ -90,8 +105,6 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
 
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) issue(s);
     for (int it = 0; it < n_iter; ++it) {
         cp_async_wait<STAGES - 2>();
         __syncthreads();  // page `it` has landed for everyone; the stage issued next was consumed an iteration ago

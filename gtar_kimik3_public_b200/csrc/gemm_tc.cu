@@ -549,7 +549,7 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
         // skinny products are bound by memory latency: as many bytes in flight per block as fit
-        case 16: return launch<16, 10>(ma, mb, p, grid, s);
+        case 16: return launch<16, 5>(ma, mb, p, grid, s);
         case 32: return launch<32, 9>(ma, mb, p, grid, s);
         case 64: return launch<64, 8>(ma, mb, p, grid, s);
         case 128: return launch<128, 3>(ma, mb, p, grid, s);

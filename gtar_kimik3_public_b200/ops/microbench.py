@@ -1,0 +1,130 @@
+"""Micro-benchmarks of single kernels at the shapes of a model's step.
+
+    python -m gtar_kimik3_public_b200.ops.microbench --kernel gemm --m 8 --n 4096 --k 1024
+    python -m gtar_kimik3_public_b200.ops.microbench --kernel attention_decode --batch 8 --context 2048
+    python -m gtar_kimik3_public_b200.ops.microbench --kernel attention_prefill --tokens 2048
+
+Each run launches the kernel on fresh inputs (a ring of operand sets larger than the L2 cache, so
+that every launch reads from HBM), times it with CUDA events over a graph replay, and prints one
+JSON line with microseconds per launch, the bytes or flops the kernel has to move or do, and the
+rate they amount to.  The same command line under ``ncu -k regex:<kernel> -c 3`` gives a profile of
+exactly that kernel on a case of a few hundred megabytes.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import functional as F
+
+DEV = "cuda:0"
+
+
+def _time_graph(fn, iters: int) -> float:
+    """Microseconds per call of ``fn`` replayed from a CUDA graph (median of ``iters`` replays)."""
+    fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    times = []
+    for _ in range(iters):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(begin.elapsed_time(end) * 1e3)
+    return sorted(times)[len(times) // 2]
+
+
+def bench_gemm(args) -> dict:
+    m, n, k = args.m, args.n, args.k
+    ring = max(2, min(64, (256 << 20) // (n * k * 2) + 1))
+    weights = [torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(ring)]
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    splits = args.splits or F.split_k_for(m, n, k)
+
+    def run():
+        for w in weights:
+            F.gemm_tc(x, w, torch.bfloat16, swiglu=args.swiglu, splits=splits)
+
+    us = _time_graph(run, args.iters) / ring
+    return {"kernel": "gemm_tc", "m": m, "n": n, "k": k, "splits": splits, "swiglu": args.swiglu, "us": round(us, 2),
+            "weight_gb_s": round(n * k * 2 / us / 1e3, 1), "tflop_s": round(2 * m * n * k / us / 1e6, 1)}
+
+
+def _paged(batch: int, context: int, n_kv: int, d: int):
+    per_seq = -(-context // 64)
+    n_pages = batch * per_seq
+    k = torch.randn(n_pages, n_kv, 64, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(n_pages, n_kv, 64, d, device=DEV, dtype=torch.bfloat16)
+    table = torch.randperm(n_pages, device=DEV).to(torch.int32).view(batch, per_seq).contiguous()
+    return F.PagedKV(k, v, table)
+
+
+def bench_attention_decode(args) -> dict:
+    b, s, n_q, n_kv, d = args.batch, args.context, args.q_heads, args.kv_heads, args.head_dim
+    ring = max(2, min(16, (256 << 20) // (b * s * n_kv * d * 4) + 1))
+    caches = [_paged(b, s, n_kv, d) for _ in range(ring)]
+    q = torch.randn(b, n_q, d, device=DEV, dtype=torch.bfloat16)
+    kv_len = torch.full((b,), s, dtype=torch.int32, device=DEV)
+    slots = torch.arange(b, dtype=torch.int32, device=DEV)
+    splits = args.splits or F.decode_splits(b, n_kv, s, 64)
+
+    def run():
+        for kv in caches:
+            F.attention_decode(q, kv, kv_len, slots, d**-0.5, 0, splits)
+
+    us = _time_graph(run, args.iters) / ring
+    nbytes = b * s * n_kv * d * 2 * 2
+    return {"kernel": "attention_decode", "batch": b, "context": s, "q_heads": n_q, "kv_heads": n_kv, "head_dim": d,
+            "splits": splits, "us": round(us, 2), "kv_gb_s": round(nbytes / us / 1e3, 1)}
+
+
+def bench_attention_prefill(args) -> dict:
+    t, n_q, n_kv, d = args.tokens, args.q_heads, args.kv_heads, args.head_dim
+    kv = _paged(1, t, n_kv, d)
+    q = torch.randn(t, n_q, d, device=DEV, dtype=torch.bfloat16)
+    cu_q = torch.tensor([0, t], dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor([t], dtype=torch.int32, device=DEV)
+    slots = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def run():
+        F.attention_prefill(q, kv, cu_q, kv_len, slots, t, d**-0.5)
+
+    us = _time_graph(run, args.iters)
+    flops = 4 * n_q * d * t * t / 2
+    return {"kernel": "attention_prefill", "tokens": t, "q_heads": n_q, "kv_heads": n_kv, "head_dim": d,
+            "us": round(us, 2), "tflop_s": round(flops / us / 1e6, 1)}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    parser.add_argument("--kernel", required=True, choices=["gemm", "attention_decode", "attention_prefill"])
+    parser.add_argument("--m", type=int, default=8)
+    parser.add_argument("--n", type=int, default=4096)
+    parser.add_argument("--k", type=int, default=1024)
+    parser.add_argument("--splits", type=int, default=0)
+    parser.add_argument("--swiglu", action="store_true")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=2048)
+    parser.add_argument("--tokens", type=int, default=2048)
+    parser.add_argument("--q-heads", type=int, default=16)
+    parser.add_argument("--kv-heads", type=int, default=8)
+    parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--iters", type=int, default=5)
+    args = parser.parse_args()
+    F.require_device(torch.device(DEV))
+    result = {"gemm": bench_gemm, "attention_decode": bench_attention_decode,
+              "attention_prefill": bench_attention_prefill}[args.kernel](args)
+    F.check_kernel_errors(DEV)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
