@@ -3,6 +3,7 @@
     python -m gtar_kimik3_public_b200.ops.microbench --kernel gemm --m 8 --n 4096 --k 1024
     python -m gtar_kimik3_public_b200.ops.microbench --kernel attention_decode --batch 8 --context 2048
     python -m gtar_kimik3_public_b200.ops.microbench --kernel attention_prefill --tokens 2048
+    python -m gtar_kimik3_public_b200.ops.microbench --kernel step --batch 8 --context 2048
 
 Each run launches the kernel on fresh inputs (a ring of operand sets larger than the L2 cache, so
 that every launch reads from HBM), times it with CUDA events over a graph replay, and prints one
@@ -102,9 +103,54 @@ def bench_attention_prefill(args) -> dict:
             "us": round(us, 2), "tflop_s": round(flops / us / 1e6, 1)}
 
 
+def bench_step(args) -> dict:
+    """One decode step of a random model of the Qwen3-0.6B layer sizes, launched kernel by kernel (no
+    graph) between cudaProfilerStart/Stop, so that ``ncu --profile-from-start off`` lists exactly
+    the step's launches."""
+    import tempfile
+
+    from ..engine import Engine, StepEntry
+    from ..generate import load
+    from ..registry import config_from_dict
+    from ..weights import write_random_model
+
+    config = config_from_dict({
+        "arch": "transformer", "vocab_size": 151936, "hidden_size": 1024, "intermediate_size": 3072,
+        "num_hidden_layers": args.layers, "num_attention_heads": args.q_heads, "num_key_value_heads": args.kv_heads,
+        "head_dim": args.head_dim, "rms_norm_eps": 1e-6, "rope_theta": 1e6, "tie_word_embeddings": True,
+        "initializer_range": 0.02, "max_position_embeddings": 4096,
+    })
+    with tempfile.TemporaryDirectory(prefix="gtar_microbench_") as folder:
+        write_random_model(folder, config, seed=0)
+        model = load(folder, "bfloat16", DEV)
+    b, s = args.batch, args.context
+    engine = Engine(model, b * (s + 64), max_seqs=b, use_graphs=False)
+    gen = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, config.vocab_size, (b, s), generator=gen).tolist()
+    ids = list(range(b))
+    with torch.no_grad():
+        tokens = None
+        for start in range(0, b, 8):
+            logits = engine.step([StepEntry(i, prompts[i], [s - 1]) for i in ids[start:start + 8]])
+            part = F.argmax(logits)
+            tokens = part if tokens is None else torch.cat([tokens, part])
+        for _ in range(2):
+            tokens = F.argmax(engine.decode_on_device(ids, tokens))
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        tokens = F.argmax(engine.decode_on_device(ids, tokens))
+        end.record()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    return {"kernel": "decode step, kernel by kernel", "batch": b, "context": s, "layers": args.layers,
+            "us": round(begin.elapsed_time(end) * 1e3, 1)}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    parser.add_argument("--kernel", required=True, choices=["gemm", "attention_decode", "attention_prefill"])
+    parser.add_argument("--kernel", required=True, choices=["gemm", "attention_decode", "attention_prefill", "step"])
     parser.add_argument("--m", type=int, default=8)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=1024)
@@ -116,11 +162,12 @@ def main() -> int:
     parser.add_argument("--q-heads", type=int, default=16)
     parser.add_argument("--kv-heads", type=int, default=8)
     parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--layers", type=int, default=28)
     parser.add_argument("--iters", type=int, default=5)
     args = parser.parse_args()
     F.require_device(torch.device(DEV))
     result = {"gemm": bench_gemm, "attention_decode": bench_attention_decode,
-              "attention_prefill": bench_attention_prefill}[args.kernel](args)
+              "attention_prefill": bench_attention_prefill, "step": bench_step}[args.kernel](args)
     F.check_kernel_errors(DEV)
     print(json.dumps(result))
     return 0
