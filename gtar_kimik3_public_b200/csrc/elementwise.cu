@@ -37,7 +37,61 @@ GK_EXPORT int gk_embed_rows(const void* table, int table_dtype, const int* ids, 
 // One block per output row.  h (32-bit residual stream) gets `delta` added in place when
 // `rows` is null; with `rows`, only the listed rows are read and h is left as it is (the
 // last norm of a step, taken at the wanted positions only).
-template <typename TD, typename TW, typename TO>
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&v)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T>
+__device__ __forceinline__ void load2(const T* p, float (&v)[2]);
+template <>
+__device__ __forceinline__ void load2<float>(const float* p, float (&v)[2]) {
+    const float2 f = *reinterpret_cast<const float2*>(p);
+    v[0] = f.x; v[1] = f.y;
+}
+template <>
+__device__ __forceinline__ void load2<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[2]) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    v[0] = f.x; v[1] = f.y;
+}
+template <typename T>
+__device__ __forceinline__ void store2(T* p, const float (&v)[2]);
+template <>
+__device__ __forceinline__ void store2<float>(float* p, const float (&v)[2]) {
+    *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+}
+template <>
+__device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[2]) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+}
+
+// VEC = 4: rows are read and written four elements at a time (hidden a multiple of 4, aligned rows).
+// The sum of squares is formed element by element in the same order either way.
+template <typename TD, typename TW, typename TO, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const TW* __restrict__ w,
                                    TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float scratch[33];
@@ -45,23 +99,54 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     const int src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* hrow = h + (size_t)src * hidden;
     const bool has_delta = delta != nullptr;
-    const size_t dbase = (size_t)src * hidden;
+    const TD* drow = delta + (size_t)src * hidden;
     TO* orow = out + (size_t)blockIdx.x * hidden;
     const bool write_back = (rows == nullptr) && has_delta;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = hrow[i];
-        if (has_delta) v += to_float(delta[dbase + i]);
-        if (write_back) hrow[i] = v;
-        ss += v * v;
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float v[4], d[4];
+            load4(hrow + i, v);
+            if (has_delta) {
+                load4(drow + i, d);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] += d[j];
+            }
+            if (write_back) store4(hrow + i, v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ss += v[j] * v[j];
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = hrow[i];
+            if (has_delta) v += to_float(drow[i]);
+            if (write_back) hrow[i] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, scratch);
     pdl_launch_dependents();
     const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = hrow[i];
-        if (has_delta && !write_back) v += to_float(delta[dbase + i]);
-        orow[i] = from_float<TO>((v * inv) * to_float(w[i]));
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float v[4], d[4], wv[4];
+            load4(hrow + i, v);
+            if (has_delta && !write_back) {
+                load4(drow + i, d);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] += d[j];
+            }
+            load4(w + i, wv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = (v[j] * inv) * wv[j];
+            store4(orow + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = hrow[i];
+            if (has_delta && !write_back) v += to_float(drow[i]);
+            orow[i] = from_float<TO>((v * inv) * to_float(w[i]));
+        }
     }
 }
 
@@ -75,12 +160,18 @@ GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, const
     if (n_out_rows == 0) return GK_OK;
     // A fixed block size: the order of the sum of squares must not depend on anything but the row.
     const int threads = 256;
+    const bool vec = hidden % 4 == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)delta & 15) == 0 &&
+                     ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0;
     cudaStream_t s = (cudaStream_t)stream;
     GK_DISPATCH_DTYPE(delta_dtype, TD, {
         GK_DISPATCH_DTYPE(weight_dtype, TW, {
             GK_DISPATCH_DTYPE(out_dtype, TO, {
-                gk_launch(add_rmsnorm_kernel<TD, TW, TO>, dim3(n_out_rows), dim3(threads), 0, s, h, (const TD*)delta,
-                          (const TW*)weight, (TO*)out, rows, hidden, eps);
+                if (vec)
+                    gk_launch(add_rmsnorm_kernel<TD, TW, TO, 4>, dim3(n_out_rows), dim3(threads), 0, s, h, (const TD*)delta,
+                              (const TW*)weight, (TO*)out, rows, hidden, eps);
+                else
+                    gk_launch(add_rmsnorm_kernel<TD, TW, TO, 1>, dim3(n_out_rows), dim3(threads), 0, s, h, (const TD*)delta,
+                              (const TW*)weight, (TO*)out, rows, hidden, eps);
             })
         })
     })
@@ -170,23 +261,81 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* _
             rotate = false;
         }
     }
+    const T* in = qkv + src;
     if (!rotate) {
-        for (int i = lane; i < head_dim; i += 32) dst[i] = qkv[src + i];
+        if (head_dim % 4 == 0) {  // rows start on 8-byte boundaries (head_dim even, so offsets are multiples of it)
+            for (int i = lane * 4; i < head_dim; i += 128) {
+                float v[4];
+                load4(in + i, v);
+                store4(dst + i, v);
+            }
+        } else {
+            for (int i = lane; i < head_dim; i += 32) dst[i] = in[i];
+        }
         return;
     }
     const int half = head_dim >> 1;
+    if (half % 2 == 0) {
+        // two neighbouring pairs (p, p + half), (p + 1, p + 1 + half) per lane and iteration
+        float inv = 1.0f;
+        if (use_norm) {
+            float ss = 0.f;
+            for (int p = lane * 2; p < half; p += 64) {
+                float a[2], b[2];
+                load2(in + p, a);
+                load2(in + p + half, b);
+                ss += a[0] * a[0] + b[0] * b[0];
+                ss += a[1] * a[1] + b[1] * b[1];
+            }
+            ss = warp_sum(ss);
+            inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+        }
+        for (int p = lane * 2; p < half; p += 64) {
+            float a[2], b[2], ra[2], rb[2];
+            load2(in + p, a);
+            load2(in + p + half, b);
+            if (use_norm) {
+                float wa[2], wb[2];
+                load2(w + p, wa);
+                load2(w + p + half, wb);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    a[j] = (a[j] * inv) * wa[j];
+                    b[j] = (b[j] * inv) * wb[j];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                ra[j] = a[j];
+                rb[j] = b[j];
+            }
+            if (cos_table) {
+                float c[2], sn[2];
+                load2(cos_table + (size_t)pos * half + p, c);
+                load2(sin_table + (size_t)pos * half + p, sn);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    ra[j] = a[j] * c[j] - b[j] * sn[j];
+                    rb[j] = b[j] * c[j] + a[j] * sn[j];
+                }
+            }
+            store2(dst + p, ra);
+            store2(dst + p + half, rb);
+        }
+        return;
+    }
     float inv = 1.0f;
     if (use_norm) {
         float ss = 0.f;
         for (int p = lane; p < half; p += 32) {
-            const float a = to_float(qkv[src + p]), b = to_float(qkv[src + p + half]);
+            const float a = to_float(in[p]), b = to_float(in[p + half]);
             ss += a * a + b * b;
         }
         ss = warp_sum(ss);
         inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
     }
     for (int p = lane; p < half; p += 32) {
-        float a = to_float(qkv[src + p]), b = to_float(qkv[src + p + half]);
+        float a = to_float(in[p]), b = to_float(in[p + half]);
         if (use_norm) {
             a = (a * inv) * to_float(w[p]);
             b = (b * inv) * to_float(w[p + half]);
