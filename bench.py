@@ -81,7 +81,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -161,12 +161,12 @@ def time_decode(model, batch: int, steps: int, warmup: int, sample_clocks: bool 
             part = engine.step([StepEntry(i, prompts[i], [PROMPT_LEN - 1]) for i in ids[start:start + 8]])
             logits = part if logits is None else torch.cat([logits, part])
         tokens = F.argmax(logits)
+        sampler = ClockSampler() if sample_clocks else None
+        if sampler:  # started before the warm-up steps: nvidia-smi needs a moment to deliver its first sample
+            sampler.start()
         for _ in range(warmup):
             tokens = F.argmax(engine.decode_on_device(ids, tokens))
         torch.cuda.synchronize()
-        sampler = ClockSampler() if sample_clocks else None
-        if sampler:
-            sampler.start()
         launches_before = library.launch_count
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
@@ -257,7 +257,7 @@ def run_ours(args) -> dict:
     prefill = time_prefill(model, max(1, min(args.warmup, 3)))
     points = {}
     for b in (1, 64):
-        points[f"decode_b{b}"] = round(time_decode(model, b, args.steps, args.warmup)["tokens_per_s"], 1)
+        points[f"decode_b{b}"] = round(time_decode(model, b, min(args.steps, 64), args.warmup)["tokens_per_s"], 1)
     achieved = main["bytes_per_step"] / (main["ms_per_step"] / 1e3) / 1e9
     prefill_peak = peak["bf16_tflops"] * 1e12
     full_layers = BENCH_CONFIG["num_hidden_layers"]
@@ -299,7 +299,7 @@ def run_ours(args) -> dict:
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
