@@ -1,0 +1,489 @@
+// Prefill attention on the 5th-generation tensor cores (head size 128).
+//
+// The same computation as attention_prefill.cu — causal, grouped-query, over the paged cache,
+// flash-attention style with 32-bit running maxima and sums (reference: src/ops/flash_attention_2.py:24-60,
+// visibility rule src/layers/attention.py:116-119) — with both matrix products on tcgen05.mma:
+//
+//   S = Q K^T     A = Q tile (128 rows x 128, shared memory), B = K page (64 keys x 128, shared memory)
+//                 -> S in tensor memory, 128 lanes x 64 columns
+//   O += P V      A = P (bfloat16, written back into tensor memory by the softmax warps)
+//                 B = V page (64 keys x 128, shared memory, read with the keys as the MMA's K: "MN-major")
+//                 -> O in tensor memory, 128 lanes x 128 columns
+//
+// A block owns 128 rows = (token, query head of one kv group) pairs of one sequence and one kv head.
+// Warp 0 streams K and V pages with TMA (a 2-D map over the cache seen as [pages * heads * 64, 128]);
+// warp 1 issues the MMAs; warps 2-5 are the softmax: thread = row, so maxima and sums need no
+// shuffles.  The accumulator is rescaled only when a row's maximum has grown by more than 2^8 since
+// its last rescale (the probabilities then stay below 2^8, which bfloat16 and the 32-bit sum hold
+// with room to spare), so most pages cost no pass over O.  Two blocks share an SM (256 tensor-memory
+// columns and 97 KB of shared memory each), so one block's softmax overlaps the other's products.
+//
+// Every mbarrier wait is bounded; a wait that gives up records a code in *error_flag and the block
+// winds down (drains its copies, frees its tensor memory).
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int D = 128;
+constexpr int ROWS = 128;
+constexpr int PAGE = 64;
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr uint32_t TMEM_COLS = 256;  // two blocks share an SM's 512 columns
+constexpr uint32_t COL_S = 0, COL_P = 64, COL_O = 128;  // S: 64, P: 32 (bf16 pairs), O: 128
+constexpr float RESCALE_THRESHOLD = 8.0f;               // in log2 units
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// K-major operand, rows of 128 bytes, 128-byte swizzle, groups of eight rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// MN-major operand (V: the MMA's N runs along a row of 128 bytes = 64 head dims, its K over the rows =
+// keys): the next 64 of N are `lbo` bytes away, the next eight of K 1024 bytes.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t lbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16 instruction descriptor: f32 accumulator, bf16 inputs, A K-major, B K- or MN-major.
+__device__ __forceinline__ uint32_t idesc(int m, int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t id, bool acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a), "l"(b), "r"(id),
+        "r"((uint32_t)acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t id, bool acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(id),
+        "r"((uint32_t)acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+struct alignas(1024) Smem {
+    __nv_bfloat16 q[2][ROWS * 64];                  // two 64-wide halves of the head dim, each [128 rows][128 bytes]
+    __nv_bfloat16 k[KV_STAGES][2][PAGE * 64];       // per page: two halves, each [64 keys][128 bytes]
+    __nv_bfloat16 v[KV_STAGES][2][PAGE * 64];
+    uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES];
+    uint64_t s_full, s_empty, p_full, o_done, q_ready;
+    uint32_t tmem_base;
+};
+
+struct Params {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    const int* cu_q;
+    const int* kv_len;
+    const int* slots;
+    const int* block_table;
+    int n_q, n_kv, max_pages;
+    float sl2;
+    int window;
+    int* error_flag;
+};
+
+__global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                          const __grid_constant__ CUtensorMap map_v,
+                                                                          const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.z, hk = blockIdx.y;
+    const int group = p.n_q / p.n_kv;
+    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
+    const int n_rows = q_len * group;
+    const int n_blocks = (n_rows + ROWS - 1) / ROWS;
+    if ((int)blockIdx.x >= n_blocks) return;  // whole block, before any barrier or allocation
+    const int row0 = (n_blocks - 1 - (int)blockIdx.x) * ROWS;  // heavy blocks first
+    const int len = p.kv_len[seq], past = len - q_len;
+    const int* pages = p.block_table + (size_t)p.slots[seq] * p.max_pages;
+    const int last_row = min(row0 + ROWS, n_rows) - 1;
+    const int max_pos = past + last_row / group, min_pos = past + row0 / group;
+    const int lo_block = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
+    const int p_begin = lo_block / PAGE, p_end = max_pos / PAGE + 1;
+    const int n_iter = p_end - p_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(&sm.kv_full[s], 1);
+            mbar_init(&sm.kv_empty[s], 1);
+        }
+        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.s_empty, 128);
+        mbar_init(&sm.p_full, 128);
+        mbar_init(&sm.o_done, 1);
+        mbar_init(&sm.q_ready, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        pdl_launch_dependents();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    pdl_wait();  // queries and the new keys and values come from the kernel before
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: K and V pages, two 64-wide halves each
+            bool ok = true;
+            int issued = 0;
+            for (int i = 0; i < n_iter && ok; ++i) {
+                const int s = i % KV_STAGES;
+                if (i >= KV_STAGES) ok = mbar_wait(&sm.kv_empty[s], ((i / KV_STAGES) - 1) & 1);
+                if (!ok) break;
+                const int page = pages[p_begin + i];
+                const int y = (page * p.n_kv + hk) * PAGE;
+                mbar_expect_tx(&sm.kv_full[s], 4 * PAGE * 64 * 2);
+                tma_load_2d(sm.k[s][0], &map_k, 0, y, &sm.kv_full[s]);
+                tma_load_2d(sm.k[s][1], &map_k, 64, y, &sm.kv_full[s]);
+                tma_load_2d(sm.v[s][0], &map_v, 0, y, &sm.kv_full[s]);
+                tma_load_2d(sm.v[s][1], &map_v, 64, y, &sm.kv_full[s]);
+                issued = i + 1;
+            }
+            if (!ok) {
+                atomicExch(p.error_flag, 11);
+                for (int i = max(issued - KV_STAGES, 0); i < issued; ++i) mbar_wait(&sm.kv_full[i % KV_STAGES], (i / KV_STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            const uint32_t id_s = idesc(ROWS, PAGE, false), id_o = idesc(ROWS, D, true);
+            bool ok = mbar_wait(&sm.q_ready, 0);
+            fence_after();
+            auto issue_qk = [&](int i) {
+                const int s = i % KV_STAGES;
+                if (ok) ok = mbar_wait(&sm.kv_full[s], (i / KV_STAGES) & 1);
+                if (ok && i >= 1) ok = mbar_wait(&sm.s_empty, (i - 1) & 1);  // the softmax has taken the scores before
+                if (!ok) return;
+                fence_after();
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint64_t da = desc_k_major(smem_u32(sm.q[k >> 2]) + (k & 3) * 32);
+                    const uint64_t db = desc_k_major(smem_u32(sm.k[s][k >> 2]) + (k & 3) * 32);
+                    umma_ss(tmem + COL_S, da, db, id_s, k > 0);
+                }
+                umma_commit(&sm.s_full);
+            };
+            if (n_iter > 0) issue_qk(0);
+            for (int i = 0; i < n_iter && ok; ++i) {
+                if (i + 1 < n_iter) issue_qk(i + 1);  // the next scores while the softmax works on these
+                if (!ok) break;
+                const int s = i % KV_STAGES;
+                ok = mbar_wait(&sm.p_full, i & 1);
+                if (!ok) break;
+                fence_after();
+#pragma unroll
+                for (int j = 0; j < PAGE / 16; ++j) {
+                    // keys 16j .. 16j+15 of the page: 16 rows of 128 bytes further on in both halves
+                    const uint64_t db = desc_mn_major(smem_u32(sm.v[s][0]) + j * 16 * 128, PAGE * 128);
+                    umma_ts(tmem + COL_O, tmem + COL_P + j * 8, db, id_o, i > 0 || j > 0);
+                }
+                umma_commit(&sm.kv_empty[s]);  // the page's shared memory is free once these have read it
+                umma_commit(&sm.o_done);       // and the accumulator holds this page
+            }
+            if (!ok) atomicExch(p.error_flag, 12);
+        }
+    } else {
+        // ---- softmax warps: thread = row
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int row = row0 + r;
+        const bool row_ok = row < n_rows;
+        const int tok = row_ok ? row / group : 0;
+        const int head = hk * group + (row_ok ? row % group : 0);
+        const int pos = past + tok;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        // Q row -> swizzled shared memory (zeros for rows beyond the sequence)
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(q_begin + tok) * p.n_q + head) * D);
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) {
+                const uint4 val = row_ok ? src[c] : make_uint4(0, 0, 0, 0);
+                uint4* dst = reinterpret_cast<uint4*>(sm.q[c >> 3]) + r * 8 + ((c & 7) ^ (r & 7));
+                *dst = val;
+            }
+            fence_async_smem();
+            mbar_arrive(&sm.q_ready);
+        }
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_iter && ok; ++i) {
+            const int s = i % KV_STAGES;
+            const int key_base = (p_begin + i) * PAGE;
+            ok = mbar_wait(&sm.s_full, i & 1);
+            if (!ok) break;
+            fence_after();
+            uint32_t raw[2][32];
+            tmem_ld32(tmem + lane_base + COL_S, raw[0]);
+            tmem_ld32(tmem + lane_base + COL_S + 32, raw[1]);
+            tmem_wait_ld();
+            fence_before();
+            mbar_arrive(&sm.s_empty);  // the scores are in registers: the buffer may be overwritten
+            // the last page of the sequence may hold stale rows beyond its length: zero them in V, so that
+            // probability 0 times whatever lies there cannot make a NaN
+            const int valid = len - key_base;
+            if (valid < PAGE) {
+                ok = mbar_wait(&sm.kv_full[s], (i / KV_STAGES) & 1);
+                if (!ok) break;
+                for (int idx = r; idx < (PAGE - valid) * 16; idx += 128) {
+                    const int vr = valid + idx / 16, chunk = idx % 16;
+                    reinterpret_cast<uint4*>(sm.v[s][chunk >> 3])[vr * 8 + (chunk & 7)] = make_uint4(0, 0, 0, 0);
+                }
+                fence_async_smem();
+            }
+            float sc[64];
+            float mx = -INFINITY;
+            const bool need_mask = key_base + PAGE - 1 > pos || p.window > 0;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                float v = __uint_as_float(raw[c >> 5][c & 31]);
+                if (need_mask) {
+                    const int key = key_base + c;
+                    if (key > pos || (p.window > 0 && key <= pos - p.window)) v = -INFINITY;
+                }
+                sc[c] = v;
+                mx = fmaxf(mx, v);
+            }
+            const float m_new = fmaxf(m_used, mx * p.sl2);
+            // rescale lazily: only when the maximum has grown by more than the threshold
+            float corr = 1.0f;
+            if (m_new > m_used + RESCALE_THRESHOLD || m_used == -INFINITY) {
+                corr = m_used == -INFINITY ? 0.f : exp2f(m_used - m_new);
+                m_used = m_new;
+            }
+            const float ref = m_used == -INFINITY ? 0.f : m_used;
+            uint32_t packed[32];
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 64; c += 2) {
+                const float e0 = exp2f(fmaf(sc[c], p.sl2, -ref)), e1 = exp2f(fmaf(sc[c + 1], p.sl2, -ref));
+                sum += e0 + e1;
+                __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+                packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            l = l * corr + sum;
+            // the accumulator may be touched only when the product of the page before has landed in it
+            if (i > 0) {
+                ok = mbar_wait(&sm.o_done, (i - 1) & 1);
+                if (!ok) break;
+                fence_after();
+            }
+            if (i > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem + lane_base + COL_O + c0, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+                    tmem_st32(tmem + lane_base + COL_O + c0, o);
+                }
+            }
+            tmem_st32(tmem + lane_base + COL_P, packed);
+            tmem_wait_st();
+            fence_before();
+            mbar_arrive(&sm.p_full);
+        }
+        if (!ok && lane == 0) atomicExch(p.error_flag, 13);
+        // ---- the result: O / l
+        if (ok && n_iter > 0) ok = mbar_wait(&sm.o_done, (n_iter - 1) & 1);
+        fence_after();
+        if (ok && n_iter > 0) {
+            const float inv = 1.0f / l;
+            __nv_bfloat16* orow = p.out + ((size_t)(q_begin + tok) * p.n_q + head) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem + lane_base + COL_O + c0, o);
+                tmem_wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 w;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+                        w.x = *reinterpret_cast<uint32_t*>(&h0);
+                        w.y = *reinterpret_cast<uint32_t*>(&h1);
+                        w.z = *reinterpret_cast<uint32_t*>(&h2);
+                        w.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(orow + c0 + c) = w;
+                    }
+                }
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// The pages of one layer, [n_pages, n_kv, 64, 128], as a matrix of n_pages * n_kv * 64 rows of 128.
+int make_page_map(CUtensorMap* map, const void* base, long long rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(__nv_bfloat16)};
+    cuuint32_t box[2] = {64, (cuuint32_t)PAGE};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return GK_OK;
+}
+
+}  // namespace
+
+// Same arguments as gk_attention_prefill_bf16 plus the number of pages of the layer's storage and the
+// device error flag of the bounded waits.  head_dim must be 128.
+GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                           const int* cu_q, const int* kv_len, const int* slots, const int* block_table,
+                                           int n_seqs, int max_q_len, int n_q, int n_kv, int head_dim, int max_pages,
+                                           int page_size, long long n_pages, float scale, int window, int* error_flag,
+                                           void* stream) {
+    GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill_tc: bad head counts %d/%d", n_q, n_kv);
+    GK_REQUIRE(page_size == PAGE && head_dim == D, "attention_prefill_tc: needs page_size %d and head_dim %d", PAGE, D);
+    GK_REQUIRE(n_kv <= 65535 && n_seqs <= 65535 && window >= 0 && max_q_len >= 0 && n_pages > 0, "attention_prefill_tc: bad sizes");
+    GK_REQUIRE(((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0 && ((uintptr_t)q & 15) == 0 &&
+                   ((uintptr_t)out & 15) == 0, "attention_prefill_tc: pointers must be 16-byte aligned");
+    GK_REQUIRE(error_flag != nullptr, "attention_prefill_tc: error_flag is required");
+    if (n_seqs == 0 || max_q_len == 0) return GK_OK;
+    CUtensorMap mk, mv;
+    int status = make_page_map(&mk, k_pages, n_pages * n_kv * PAGE);
+    if (status) return status;
+    status = make_page_map(&mv, v_pages, n_pages * n_kv * PAGE);
+    if (status) return status;
+    const size_t smem = sizeof(Smem) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    Params p;
+    p.q = (const __nv_bfloat16*)q;
+    p.out = (__nv_bfloat16*)out;
+    p.cu_q = cu_q;
+    p.kv_len = kv_len;
+    p.slots = slots;
+    p.block_table = block_table;
+    p.n_q = n_q;
+    p.n_kv = n_kv;
+    p.max_pages = max_pages;
+    p.sl2 = scale * 1.4426950408889634f;
+    p.window = window;
+    p.error_flag = error_flag;
+    const int group = n_q / n_kv;
+    const long long blocks = ((long long)max_q_len * group + ROWS - 1) / ROWS;
+    GK_REQUIRE(blocks <= 2147483647LL, "attention_prefill_tc: too many rows");
+    dim3 grid((unsigned)blocks, n_kv, n_seqs);
+    gk_launch(attention_prefill_tc_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, mk, mv, p);
+    GK_CHECK_LAUNCH("attention_prefill_tc");
+    return GK_OK;
+}

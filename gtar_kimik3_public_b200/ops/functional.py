@@ -373,10 +373,12 @@ def attention_prefill(
     scale: float,
     window: int = 0,
     out: torch.Tensor | None = None,
+    tensor_cores: str = "auto",
 ) -> torch.Tensor:
     """Causal attention of the packed new tokens ``q [n_tokens, n_q, d]`` (bfloat16, ``d`` 64 or 128) of
     ``n_seqs`` sequences over the pages.  Sequence ``i`` owns tokens ``cu_q[i] .. cu_q[i+1]-1``, which
-    are its last positions: ``kv_len[i]`` counts its cached tokens including them."""
+    are its last positions: ``kv_len[i]`` counts its cached tokens including them.  ``tensor_cores``:
+    ``"tcgen05"`` (head size 128 only), ``"mma"`` (the warp-level kernel), or ``"auto"``."""
     require_device(q.device)
     _check(q, "q", torch.bfloat16, 3)
     n, n_q, d = q.shape
@@ -392,6 +394,17 @@ def attention_prefill(
         raise KernelError(f"pages have head_dim {kv.k.shape[3]}, queries {d}")
     if out is None:
         out = torch.empty_like(q)
+    if tensor_cores not in ("auto", "tcgen05", "mma"):
+        raise KernelError(f"tensor_cores must be auto, tcgen05 or mma, got {tensor_cores!r}")
+    if tensor_cores == "tcgen05" and d != 128:
+        raise KernelError("the tcgen05 prefill attention takes head size 128 only")
+    if tensor_cores == "tcgen05" or (tensor_cores == "auto" and d == 128):
+        call(
+            "gk_attention_prefill_tc_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(cu_q), ptr(kv_len), ptr(slots),
+            ptr(kv.block_table), n_seqs, int(max_q_len), n_q, n_kv, d, kv.max_pages, kv.page_size, kv.k.shape[0],
+            float(scale), int(window), ptr(error_flag(q.device)), stream_ptr(),
+        )
+        return out
     call(
         "gk_attention_prefill_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(cu_q), ptr(kv_len), ptr(slots),
         ptr(kv.block_table), n_seqs, int(max_q_len), n_q, n_kv, d, kv.max_pages, kv.page_size, float(scale), int(window),

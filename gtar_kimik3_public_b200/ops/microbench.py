@@ -95,11 +95,11 @@ def bench_attention_prefill(args) -> dict:
     slots = torch.zeros(1, dtype=torch.int32, device=DEV)
 
     def run():
-        F.attention_prefill(q, kv, cu_q, kv_len, slots, t, d**-0.5)
+        F.attention_prefill(q, kv, cu_q, kv_len, slots, t, d**-0.5, tensor_cores=args.attention_path)
 
     us = _time_graph(run, args.iters)
     flops = 4 * n_q * d * t * t / 2
-    return {"kernel": "attention_prefill", "tokens": t, "q_heads": n_q, "kv_heads": n_kv, "head_dim": d,
+    return {"kernel": "attention_prefill", "path": args.attention_path, "tokens": t, "q_heads": n_q, "kv_heads": n_kv, "head_dim": d,
             "us": round(us, 2), "tflop_s": round(flops / us / 1e6, 1)}
 
 
@@ -162,6 +162,7 @@ def main() -> int:
     parser.add_argument("--q-heads", type=int, default=16)
     parser.add_argument("--kv-heads", type=int, default=8)
     parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--attention-path", default="auto", choices=["auto", "tcgen05", "mma"])
     parser.add_argument("--layers", type=int, default=28)
     parser.add_argument("--iters", type=int, default=5)
     args = parser.parse_args()
