@@ -137,6 +137,11 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {  // 2^x, one MUFU instruction; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 struct alignas(1024) Smem {
@@ -316,18 +321,20 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const 
                 }
                 fence_async_smem();
             }
-            float sc[64];
             float mx = -INFINITY;
             const bool need_mask = key_base + PAGE - 1 > pos || p.window > 0;
+            if (need_mask) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                float v = __uint_as_float(raw[c >> 5][c & 31]);
-                if (need_mask) {
+                for (int c = 0; c < 64; ++c) {
                     const int key = key_base + c;
-                    if (key > pos || (p.window > 0 && key <= pos - p.window)) v = -INFINITY;
+                    if (key > pos || (p.window > 0 && key <= pos - p.window)) raw[c >> 5][c & 31] = 0xff800000u;  // -inf
                 }
-                sc[c] = v;
-                mx = fmaxf(mx, v);
+            }
+            {   // four independent chains keep the maximum off the critical path
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < 64; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(raw[c >> 5][c & 31]));
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
             const float m_new = fmaxf(m_used, mx * p.sl2);
             // rescale lazily: only when the maximum has grown by more than the threshold
@@ -338,14 +345,16 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const 
             }
             const float ref = m_used == -INFINITY ? 0.f : m_used;
             uint32_t packed[32];
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
-                const float e0 = exp2f(fmaf(sc[c], p.sl2, -ref)), e1 = exp2f(fmaf(sc[c + 1], p.sl2, -ref));
-                sum += e0 + e1;
+                const float e0 = ex2(fmaf(__uint_as_float(raw[c >> 5][c & 31]), p.sl2, -ref));
+                const float e1 = ex2(fmaf(__uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]), p.sl2, -ref));
+                sum4[(c >> 1) & 3] += e0 + e1;
                 __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                 packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l = l * corr + sum;
             // the accumulator may be touched only when the product of the page before has landed in it
             if (i > 0) {
