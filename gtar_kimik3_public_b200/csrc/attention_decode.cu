@@ -26,6 +26,28 @@ using namespace attn;
 constexpr int WARPS = 4;
 constexpr int STAGES = 3;
 
+// Optional fusion of the step before attention: with `qkv` set, the kernel takes the packed
+// projection row of each sequence's new token [q heads | k heads | v heads], applies the per-head
+// RMSNorm (weights `wq`, `wk`, float32 or bfloat16) and the rotation (tables [position][D/2]) itself,
+// uses the result as its queries, and — unless `write_kv` is 0 — writes the new token's key and
+// value into the page that holds it (and patches the copy of that page it has in shared memory).
+// Formulas: src/layers/rmsnorm.py:11-16, src/layers/rope.py:17-33, order src/layers/attention.py:82-89.
+struct FusedQkv {
+    const __nv_bfloat16* qkv;   // null: queries come from `q`, keys and values are in the cache already
+    const void* wq;
+    const void* wk;
+    int weights_bf16;           // dtype of wq / wk
+    int use_norm;
+    float eps;
+    const float* cos_table;     // null: no rotation
+    const float* sin_table;
+    int write_kv;
+};
+
+__device__ __forceinline__ float weight_at(const void* w, int bf16, int i) {
+    return bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]) : reinterpret_cast<const float*>(w)[i];
+}
+
 template <int D>
 struct DecodeSmem {
     __nv_bfloat16 k[STAGES][PAGE * D];
@@ -38,7 +60,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
     float* __restrict__ part_ml, const int* __restrict__ kv_len, const int* __restrict__ slots,
     const int* __restrict__ block_table, int n_q, int n_kv, int max_pages, float sl2, int window, int n_splits,
-    int cluster_merge) {
+    int cluster_merge, const FusedQkv fused) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     DecodeSmem<D>& sm = *reinterpret_cast<DecodeSmem<D>*>(smem_raw);
     const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
@@ -85,9 +107,12 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 
     // Query fragments: row r of the tile is query head hk*group + r (rows >= group are zero).
     uint32_t qf[D / 16][4];
+    const int pos_new = len - 1;
     {
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
-        const __nv_bfloat16* qbase = q + ((size_t)seq * n_q + (size_t)hk * group) * D;
+        const int n_heads = n_q + 2 * n_kv;
+        const __nv_bfloat16* qbase = fused.qkv ? fused.qkv + ((size_t)seq * n_heads + (size_t)hk * group) * D
+                                               : q + ((size_t)seq * n_q + (size_t)hk * group) * D;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
 #pragma unroll
@@ -95,6 +120,114 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
                 const int r = r0 + (i & 1) * 8, c = ks * 16 + c0 + (i >> 1) * 8;
                 qf[ks][i] = r < group ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + c) : 0u;
             }
+        }
+        if (fused.qkv) {
+            // A thread holds, of each of its two rows, the elements c0, c0+1, c0+8, c0+9 of every
+            // 16-wide step: a quad holds a whole row, and the rotation partner of column c (c + D/2)
+            // is four steps further on in the same thread.
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float x[D / 16][4];
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qf[ks][h]));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qf[ks][h + 2]));
+                    x[ks][0] = a.x; x[ks][1] = a.y; x[ks][2] = b.x; x[ks][3] = b.y;
+                }
+                if (fused.use_norm) {
+                    float ss = 0.f;
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) ss += x[ks][e] * x[ks][e];
+                    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                    const float inv = 1.0f / sqrtf(ss / (float)D + fused.eps);
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = ks * 16 + c0 + (e & 1) + (e >> 1) * 8;
+                            x[ks][e] = (x[ks][e] * inv) * weight_at(fused.wq, fused.weights_bf16, c);
+                        }
+                }
+                if (fused.cos_table) {
+#pragma unroll
+                    for (int ks = 0; ks < D / 32; ++ks)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = ks * 16 + c0 + (e & 1) + (e >> 1) * 8;  // first half of the head
+                            const float cs = fused.cos_table[(size_t)pos_new * (D / 2) + c];
+                            const float sn = fused.sin_table[(size_t)pos_new * (D / 2) + c];
+                            const float a = x[ks][e], b = x[ks + D / 32][e];
+                            x[ks][e] = a * cs - b * sn;
+                            x[ks + D / 32][e] = b * cs + a * sn;
+                        }
+                }
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    qf[ks][h] = pack_bf16(x[ks][0], x[ks][1]);
+                    qf[ks][h + 2] = pack_bf16(x[ks][2], x[ks][3]);
+                }
+            }
+        }
+    }
+    // The new token's key and value, by the block that holds its page: one warp makes them, writes them
+    // to the cache, and keeps them for patching the page's copy in shared memory once that has landed.
+    const bool owns_new = fused.qkv != nullptr && fused.write_kv && new_page >= p_begin && new_page < p_end;
+    __nv_bfloat162 k_new[D / 64], v_new[D / 64];  // lane l: elements 2l, 2l+1 of each 64-wide half
+    if (owns_new && warp == 0) {
+        const int n_heads = n_q + 2 * n_kv;
+        const __nv_bfloat16* krow = fused.qkv + ((size_t)seq * n_heads + n_q + hk) * D;
+        const __nv_bfloat16* vrow = fused.qkv + ((size_t)seq * n_heads + n_q + n_kv + hk) * D;
+        float kx[D / 64][2];
+        float ss = 0.f;
+#pragma unroll
+        for (int hf = 0; hf < D / 64; ++hf) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(krow + hf * 64 + 2 * lane));
+            kx[hf][0] = f.x;
+            kx[hf][1] = f.y;
+            ss += f.x * f.x + f.y * f.y;
+            v_new[hf] = *reinterpret_cast<const __nv_bfloat162*>(vrow + hf * 64 + 2 * lane);
+        }
+        if (fused.use_norm) {
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)D + fused.eps);
+#pragma unroll
+            for (int hf = 0; hf < D / 64; ++hf)
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                    kx[hf][e] = (kx[hf][e] * inv) * weight_at(fused.wk, fused.weights_bf16, hf * 64 + 2 * lane + e);
+        }
+        if (fused.cos_table) {
+            // partner of column c is c + D/2: for D = 128 the other half held by this lane, for D = 64 the
+            // lane 16 further on
+            if (D == 128) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int c = 2 * lane + e;
+                    const float cs = fused.cos_table[(size_t)pos_new * (D / 2) + c], sn = fused.sin_table[(size_t)pos_new * (D / 2) + c];
+                    const float a = kx[0][e], b = kx[D / 64 - 1][e];
+                    kx[0][e] = a * cs - b * sn;
+                    kx[D / 64 - 1][e] = b * cs + a * sn;
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float mine = kx[0][e];
+                    const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+                    const int c = (2 * lane + e) % (D / 2);
+                    const float cs = fused.cos_table[(size_t)pos_new * (D / 2) + c], sn = fused.sin_table[(size_t)pos_new * (D / 2) + c];
+                    kx[0][e] = lane < 16 ? mine * cs - other * sn : mine * cs + other * sn;
+                }
+            }
+        }
+        const size_t at = (((size_t)pages[new_page] * n_kv + hk) * PAGE + (pos_new % PAGE)) * D;
+#pragma unroll
+        for (int hf = 0; hf < D / 64; ++hf) {
+            k_new[hf] = __floats2bfloat162_rn(kx[hf][0], kx[hf][1]);
+            *reinterpret_cast<__nv_bfloat162*>(const_cast<__nv_bfloat16*>(k_pages) + at + hf * 64 + 2 * lane) = k_new[hf];
+            *reinterpret_cast<__nv_bfloat162*>(const_cast<__nv_bfloat16*>(v_pages) + at + hf * 64 + 2 * lane) = v_new[hf];
         }
     }
 
@@ -110,6 +243,19 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         __syncthreads();  // page `it` has landed for everyone; the stage issued next was consumed an iteration ago
         issue(it + STAGES - 1);
         const int stage = it % STAGES;
+        if (owns_new && p_begin + it == new_page) {  // block-uniform
+            if (warp == 0) {
+                const int row = pos_new % PAGE;
+#pragma unroll
+                for (int hf = 0; hf < D / 64; ++hf) {
+                    const int col = hf * 64 + 2 * lane;  // element index; its 16-byte chunk is col / 8
+                    const int word = swz<D>(row, col >> 3) * 8 + (col & 7);
+                    *reinterpret_cast<__nv_bfloat162*>(sm.k[stage] + word) = k_new[hf];
+                    *reinterpret_cast<__nv_bfloat162*>(sm.v[stage] + word) = v_new[hf];
+                }
+            }
+            __syncthreads();
+        }
         const int key0 = warp * 16;
         const int abs0 = (p_begin + it) * PAGE + key0;
         if (abs0 < len && abs0 + 16 > lo) {  // warp-uniform: skip sixteen keys that are all hidden
@@ -250,7 +396,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
 template <int D>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o, float* part_ml,
                   const int* kv_len, const int* slots, const int* block_table, int n_seqs, int n_q, int n_kv,
-                  int max_pages, float scale, int window, int n_splits, cudaStream_t stream) {
+                  int max_pages, float scale, int window, int n_splits, cudaStream_t stream, const FusedQkv& fused) {
     const size_t stage_bytes = sizeof(DecodeSmem<D>);
     const size_t merge_bytes = ((size_t)WARPS * 16 * (D + 2) + 16 * (D + 2)) * sizeof(float);
     const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
@@ -268,7 +414,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
     gk_launch_cluster(attention_decode_kernel<D>, grid, dim3(WARPS * 32), smem, stream,
         dim3(cluster_merge ? n_splits : 1, 1, 1),
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
-        part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits, cluster_merge);
+        part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits, cluster_merge, fused);
     GK_CHECK_LAUNCH("attention_decode");
     if (n_splits > 1 && !cluster_merge) {
         gk_launch(attention_decode_merge_kernel<D>, dim3(n_seqs * n_q), dim3(D <= 64 ? 64 : 128), 0, stream,
@@ -284,11 +430,10 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
 //   part_o  float [n_seqs * n_q * n_splits * head_dim],  part_ml  float [n_seqs * n_q * n_splits * 2].
 // Without scratch (null pointers; up to 8 splits): the splits of a (sequence, kv head) run as one
 // thread-block cluster and merge through distributed shared memory.
-GK_EXPORT int gk_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
-                                       float* part_o, float* part_ml, const int* kv_len, const int* slots,
-                                       const int* block_table, int n_seqs, int n_q, int n_kv, int head_dim,
-                                       int max_pages, int page_size, float scale, int window, int n_splits,
-                                       void* stream) {
+static int decode_entry(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o, float* part_ml,
+                        const int* kv_len, const int* slots, const int* block_table, int n_seqs, int n_q, int n_kv,
+                        int head_dim, int max_pages, int page_size, float scale, int window, int n_splits, void* stream,
+                        const FusedQkv& fused) {
     GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: bad head counts %d/%d", n_q, n_kv);
     GK_REQUIRE(n_q / n_kv <= 16, "attention_decode: groups of more than 16 query heads per kv head are not supported");
     GK_REQUIRE(page_size == attn::PAGE, "attention_decode: page_size must be %d, got %d", attn::PAGE, page_size);
@@ -301,9 +446,50 @@ GK_EXPORT int gk_attention_decode_bf16(const void* q, const void* k_pages, const
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64)
         return launch_decode<64>(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv,
-                                 max_pages, scale, window, n_splits, s);
+                                 max_pages, scale, window, n_splits, s, fused);
     return launch_decode<128>(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv,
-                              max_pages, scale, window, n_splits, s);
+                              max_pages, scale, window, n_splits, s, fused);
+}
+
+GK_EXPORT int gk_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                       float* part_o, float* part_ml, const int* kv_len, const int* slots,
+                                       const int* block_table, int n_seqs, int n_q, int n_kv, int head_dim,
+                                       int max_pages, int page_size, float scale, int window, int n_splits,
+                                       void* stream) {
+    FusedQkv none = {};
+    return decode_entry(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv, head_dim,
+                        max_pages, page_size, scale, window, n_splits, stream, none);
+}
+
+// Decode attention that also does the step before it: `qkv` is the packed projection of each sequence's
+// new token, [n_seqs, (n_q + 2 n_kv) * head_dim] bfloat16.  Per-head RMSNorm of q and k (`use_norm`,
+// weights of `weight_dtype`), rotation at position kv_len - 1 (tables [positions][head_dim / 2], null =
+// none) and the write of the new key and value into the pages (`write_kv`) happen inside the kernel.
+GK_EXPORT int gk_attention_decode_fused_bf16(const void* qkv, const void* wq, const void* wk, int weight_dtype,
+                                             int use_norm, float eps, const float* cos_table, const float* sin_table,
+                                             int table_positions, int max_position, int write_kv, void* k_pages,
+                                             void* v_pages, void* out, float* part_o, float* part_ml,
+                                             const int* kv_len, const int* slots, const int* block_table, int n_seqs,
+                                             int n_q, int n_kv, int head_dim, int max_pages, int page_size,
+                                             float scale, int window, int n_splits, void* stream) {
+    GK_REQUIRE(qkv != nullptr, "attention_decode_fused: qkv is required");
+    GK_REQUIRE(GK_VALID_DTYPE(weight_dtype), "attention_decode_fused: bad weight dtype");
+    GK_REQUIRE(!use_norm || (wq && wk), "attention_decode_fused: norm weights missing");
+    GK_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "attention_decode_fused: cos and sin tables go together");
+    GK_REQUIRE(cos_table == nullptr || max_position < table_positions,
+               "attention_decode_fused: position %d is beyond the rotary table (%d positions)", max_position, table_positions);
+    FusedQkv fused;
+    fused.qkv = (const __nv_bfloat16*)qkv;
+    fused.wq = wq;
+    fused.wk = wk;
+    fused.weights_bf16 = weight_dtype == GK_BF16;
+    fused.use_norm = use_norm;
+    fused.eps = eps;
+    fused.cos_table = cos_table;
+    fused.sin_table = sin_table;
+    fused.write_kv = write_kv;
+    return decode_entry(nullptr, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv,
+                        head_dim, max_pages, page_size, scale, window, n_splits, stream, fused);
 }
 
 // ---------------------------------------------------------------- the entry point that allocates nothing

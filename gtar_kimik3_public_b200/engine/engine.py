@@ -80,9 +80,9 @@ class Engine:
         for entry in entries:
             if not entry.tokens:
                 raise ValueError(f"request {entry.id!r} brings no token")
-            for token in entry.tokens:
-                if not 0 <= int(token) < vocab:
-                    raise ValueError(f"request {entry.id!r}: token id {token} is outside the vocabulary of {vocab}")
+            if min(entry.tokens) < 0 or max(entry.tokens) >= vocab:
+                bad = next(t for t in entry.tokens if not 0 <= int(t) < vocab)
+                raise ValueError(f"request {entry.id!r}: token id {bad} is outside the vocabulary of {vocab}")
         new_ids = [e.id for e in entries if e.id not in self.slot_of]
         if len(new_ids) > self.cache.slots.n_free:
             raise CacheFull(f"{len(new_ids)} new requests but only {self.cache.slots.n_free} free slots")

@@ -68,6 +68,8 @@ class Generator:
         device = self.model.device
 
         def chooser(logits, request_indices, steps):
+            if sampling.temperature == 0:  # greedy needs no keys
+                return choose(logits, sampling, None, None).cpu().tolist()
             keys = torch.tensor([request_indices, steps], dtype=torch.int32)
             if device.type == "cuda":
                 keys = keys.pin_memory()

@@ -15,6 +15,16 @@ from . import functional as F
 FAST_HEAD_DIMS = (64, 128)
 
 
+def fused_decode_ok(qkv: torch.Tensor, kv: F.PagedKV, n_q: int, n_kv: int, head_dim: int) -> bool:
+    """Whether the decode kernel that also norms, rotates and writes the new token can take the layer."""
+    return (qkv.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16 and head_dim in FAST_HEAD_DIMS
+            and kv.page_size == 64 and n_q // n_kv <= 16)
+
+
+def decode_split_count(ctx, n_kv: int, kv: F.PagedKV) -> int:
+    return ctx.extras.get("decode_splits") or F.decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len, kv.page_size)
+
+
 def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: int = 0) -> torch.Tensor:
     """Causal grouped-query attention of the step's queries ``[n_tokens, n_q, d]`` over each
     sequence's cached keys and values (the new tokens' own are already written)."""
@@ -22,7 +32,7 @@ def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: i
     n_kv = kv.k.shape[1]
     fast = q.dtype == torch.bfloat16 and d in FAST_HEAD_DIMS and kv.page_size == 64 and n_q // n_kv <= 16
     if fast and ctx.all_single:
-        splits = ctx.extras.get("decode_splits") or F.decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len, kv.page_size)
+        splits = decode_split_count(ctx, n_kv, kv)
         return F.attention_decode(q, kv, ctx.kv_len, ctx.slots, scale, window, splits)
     if fast:
         return F.attention_prefill(q, kv, ctx.cu_q, ctx.kv_len, ctx.slots, ctx.max_q_len, scale, window)

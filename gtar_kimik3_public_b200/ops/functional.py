@@ -363,6 +363,64 @@ def attention_decode(
     return out
 
 
+def attention_decode_fused(
+    qkv: torch.Tensor,
+    n_q: int,
+    n_kv: int,
+    head_dim: int,
+    q_weight: torch.Tensor | None,
+    k_weight: torch.Tensor | None,
+    eps: float,
+    cos: torch.Tensor | None,
+    sin: torch.Tensor | None,
+    kv: PagedKV,
+    kv_len: torch.Tensor,
+    slots: torch.Tensor,
+    max_position: int,
+    scale: float,
+    window: int = 0,
+    n_splits: int = 1,
+    write_kv: bool = True,
+) -> torch.Tensor:
+    """Decode attention straight from the packed projection of the new tokens: per-head q/k RMSNorm,
+    rotation, the write of the new key and value into the pages and the attention itself in one kernel
+    (bfloat16, head size 64 or 128, at most 8 splits).  Returns ``[n_seqs, n_q, head_dim]``."""
+    require_device(qkv.device)
+    _check(qkv, "qkv", torch.bfloat16, 2)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_q + 2 * n_kv) * head_dim:
+        raise KernelError(f"qkv rows are {qkv.shape[1]} wide, expected {(n_q + 2 * n_kv) * head_dim}")
+    _check(kv.k, "k pages", torch.bfloat16, 4)
+    _check(kv.v, "v pages", torch.bfloat16, 4)
+    _check(kv_len, "kv_len", torch.int32, 1)
+    _check(slots, "slots", torch.int32, 1)
+    if kv.k.shape[1] != n_kv or kv.k.shape[3] != head_dim:
+        raise KernelError(f"pages {tuple(kv.k.shape)} do not fit n_kv={n_kv}, head_dim={head_dim}")
+    if n_splits > 8:
+        raise KernelError("the fused decode attention takes at most 8 splits")
+    use_norm = q_weight is not None
+    weight_code = 0
+    if use_norm:
+        _check(q_weight, "q_weight", dims=1)
+        _check(k_weight, "k_weight", q_weight.dtype, 1)
+        weight_code = dtype_code(q_weight.dtype)
+    table_positions = 0
+    if cos is not None:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+            raise KernelError("rotary tables must be [positions, head_dim / 2]")
+        table_positions = cos.shape[0]
+    out = torch.empty((n, n_q, head_dim), dtype=torch.bfloat16, device=qkv.device)
+    call(
+        "gk_attention_decode_fused_bf16", ptr(qkv), ptr(q_weight), ptr(k_weight), weight_code, int(use_norm), float(eps),
+        ptr(cos), ptr(sin), table_positions, int(max_position), int(write_kv), ptr(kv.k), ptr(kv.v), ptr(out), None, None,
+        ptr(kv_len), ptr(slots), ptr(kv.block_table), n, n_q, n_kv, head_dim, kv.max_pages, kv.page_size, float(scale),
+        int(window), int(n_splits), stream_ptr(),
+    )
+    return out
+
+
 def attention_prefill(
     q: torch.Tensor,
     kv: PagedKV,

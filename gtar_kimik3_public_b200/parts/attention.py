@@ -67,10 +67,18 @@ class GQAAttention(Mixer):
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.cos, self.position.sin
+        write_kv = not ctx.extras.get("cache_read_only", False)
+        if ctx.all_single and attention_ops.fused_decode_ok(qkv, cache, self.n_q, self.n_kv, self.head_dim):
+            # one token per sequence: norm, rotation, cache write and attention in one kernel
+            splits = attention_ops.decode_split_count(ctx, self.n_kv, cache)
+            if splits <= 8:
+                o = F.attention_decode_fused(
+                    qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm, self.qk_norm_eps or 1.0, cos, sin,
+                    cache, ctx.kv_len, ctx.slots, ctx.max_position, self.scale, self.window or 0, splits, write_kv)
+                return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
         q = F.qk_norm_rope_write(
             qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm, self.qk_norm_eps or 1.0, cos, sin,
-            ctx.tok_pos, ctx.tok_seq, ctx.slots, cache, ctx.max_position,
-            write_kv=not ctx.extras.get("cache_read_only", False),
+            ctx.tok_pos, ctx.tok_seq, ctx.slots, cache, ctx.max_position, write_kv=write_kv,
         )
         o = attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
         return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)

@@ -27,9 +27,10 @@ class SamplingParams:
             raise ValueError("top_k must be >= 0")
 
 
-def choose(logits: torch.Tensor, params: SamplingParams, request_ids: torch.Tensor, steps: torch.Tensor,
+def choose(logits: torch.Tensor, params: SamplingParams, request_ids: torch.Tensor | None, steps: torch.Tensor | None,
            advance_steps: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
-    """One token per row of ``logits`` (float32 ``[n, vocab]``) as int32 on the device."""
+    """One token per row of ``logits`` (float32 ``[n, vocab]``) as int32 on the device.  Greedy choice
+    (temperature 0) reads neither ``request_ids`` nor ``steps``."""
     if params.temperature == 0:
         return F.argmax(logits, out)
     return F.sample(logits, params.temperature, params.top_k or 0, params.seed, request_ids, steps, advance_steps, out)

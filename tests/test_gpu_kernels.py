@@ -473,3 +473,41 @@ def test_attention_prefill_bf16_far_key_and_window(path):
     want_w = dense_attention(q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double(), 0, 100)
     assert (win - want_w).abs().max() < 2e-2
     assert (win[700:, 1] - v[5, 0].to(dtype).double()).abs().max() > 0.1  # key 5 is outside every late token's window
+
+
+# ------------------------------------------------------------------ decode attention fused with norm, rotation and cache write
+@pytest.mark.parametrize("n_q,n_kv,d,weight_dtype", [(16, 8, 128, torch.float32), (4, 1, 64, torch.float32), (6, 2, 128, torch.bfloat16)])
+@pytest.mark.parametrize("n_splits", [1, 4])
+def test_attention_decode_fused_equals_the_separate_kernels(n_q, n_kv, d, weight_dtype, n_splits):
+    dtype, eps, theta = torch.bfloat16, 1e-6, 1e6
+    lens = [1, 64, 65, 300, 1000]  # the new token is the last of each: at a page's first, last and inner places
+    width = (n_q + 2 * n_kv) * d
+    qkv = rand(len(lens), width, seed=1).to(dtype)
+    wq, wk = (1 + 0.1 * rand(d, seed=2)).to(weight_dtype), (1 + 0.1 * rand(d, seed=3)).to(weight_dtype)
+    cos, sin = plain.rotary_tables(torch.arange(1001), d, theta)
+    cos, sin = cos[:, : d // 2].contiguous().to(DEV), sin[:, : d // 2].contiguous().to(DEV)
+    kv_len = torch.tensor(lens, dtype=torch.int32).to(DEV)
+    results = []
+    for fused in (False, True):
+        kv, slots, table = scrambled_pages(len(lens), 1000, n_kv, d, dtype, seed=16)
+        for i, n in enumerate(lens):  # the cached past of each sequence (everything but the new token)
+            if n > 1:
+                fill_pages(kv, table, int(slots[i]), rand(n - 1, n_kv, d, seed=20 + i).to(dtype), rand(n - 1, n_kv, d, seed=30 + i).to(dtype))
+        pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32).to(DEV)
+        seq = torch.arange(len(lens), dtype=torch.int32).to(DEV)
+        if fused:
+            out = F().attention_decode_fused(qkv.to(DEV), n_q, n_kv, d, wq.to(DEV), wk.to(DEV), eps, cos, sin, kv, kv_len,
+                                             slots.to(DEV), max(lens) - 1, d**-0.5, 0, n_splits)
+        else:
+            q = F().qk_norm_rope_write(qkv.to(DEV), n_q, n_kv, d, wq.to(DEV), wk.to(DEV), eps, cos, sin, pos, seq, slots.to(DEV),
+                                       kv, max(lens) - 1)
+            out = F().attention_decode(q, kv, kv_len, slots.to(DEV), d**-0.5, 0, n_splits)
+        new_k = torch.stack([kv.k[int(table[slots[i], (n - 1) // 64]), :, (n - 1) % 64] for i, n in enumerate(lens)])
+        new_v = torch.stack([kv.v[int(table[slots[i], (n - 1) // 64]), :, (n - 1) % 64] for i, n in enumerate(lens)])
+        results.append((out.float().cpu(), new_k.float().cpu(), new_v.float().cpu()))
+    (out_a, k_a, v_a), (out_b, k_b, v_b) = results
+    assert torch.isfinite(out_b).all()
+    assert torch.equal(v_a, v_b)
+    # the same formulas in the same precision; the fused kernel may contract a multiply-add differently
+    assert (k_a - k_b).abs().max() <= 2.0**-7 * k_a.abs().max()
+    assert (out_a - out_b).abs().max() <= 2.0**-7 * out_a.abs().max() + 1e-3
