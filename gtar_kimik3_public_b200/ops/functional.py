@@ -255,6 +255,7 @@ SKINNY_M = 64  # up to this many tokens the weights take the MMA's 128 rows (swa
 
 
 SPLIT_TARGET_BLOCKS = 128
+SCRATCH_SPLITS_FROM = 17
 SKINNY_BN_MAX = 64
 SPLIT_MIN_K_BLOCKS = 4
 
@@ -319,7 +320,9 @@ def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_co
     per SM are busy, never more than the longest sequence has pages."""
     want = (2 * sm_count) // max(1, n_seqs * n_kv)  # rounded down: one wave of two blocks per SM
     want = max(1, min(want, -(-max_kv_len // page_size), 64))
-    return want if want > 16 else min(want, 8)  # up to eight merge in-kernel; scratch pays off only well beyond
+    # up to eight splits merge inside the kernel (and let it do the q/k preparation too); more, through
+    # scratch and a second kernel, pay off only for long sequences
+    return want if want >= SCRATCH_SPLITS_FROM and max_kv_len >= 8192 else min(want, 8)
 
 
 def attention_decode(
