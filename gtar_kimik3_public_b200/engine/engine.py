@@ -60,6 +60,14 @@ class Engine:
     def end_all(self) -> None:
         self.end(list(self.slot_of))
 
+    def check(self) -> None:
+        """Raises if a kernel of an earlier step gave up one of its bounded waits (its output is then
+        not valid).  Synchronises the device; callers use it where they wait for results anyway."""
+        if self.model.device.type == "cuda":
+            from ..ops.functional import check_kernel_errors
+
+            check_kernel_errors(self.model.device)
+
     # ------------------------------------------------------------------ the step
     def step(self, entries: list[StepEntry], keep_output: bool = True) -> torch.Tensor:
         """Runs the entries' tokens as one batch from the cache and returns float32 logits

@@ -77,7 +77,9 @@ class Generator:
             tokens = choose(logits, sampling, keys[0], keys[1])
             return tokens.cpu().tolist()
 
-        return run_generation(self.engine, prompts, params, chooser, on_step=on_step)
+        outputs = run_generation(self.engine, prompts, params, chooser, on_step=on_step)
+        self.engine.check()
+        return outputs
 
 
 def generate(model: Model, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64, temperature: float = 1.0,
