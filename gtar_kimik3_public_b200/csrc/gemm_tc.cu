@@ -456,6 +456,140 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     }
 }
 
+// ---------------------------------------------------------------- persistent variant for many tokens
+// One block per SM walks over 128 x 256 tiles (A index fastest, so the blocks working at the same time
+// share their B tiles in L2).  Two accumulators of 256 columns fill the tensor memory: while the
+// epilogue warps drain one, the MMA thread already fills the other with the next tile.  No split-K.
+template <int BN, int STAGES>
+struct alignas(1024) PersistentSmem {
+    __nv_bfloat16 a[STAGES][BM * BK];
+    __nv_bfloat16 b[STAGES][BN * BK];
+    uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                        const __grid_constant__ CUtensorMap map_b,
+                                                                        const GemmParams p) {
+    static_assert(2 * BN <= 512, "two accumulators must fit the tensor memory");
+    extern __shared__ unsigned char smem_raw[];
+    PersistentSmem<BN, STAGES>& sm =
+        *reinterpret_cast<PersistentSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t TMEM_COLS = 512;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_a = (p.rows_a + BM - 1) / BM, tiles_b = (p.rows_b + BN - 1) / BN;
+    const int n_tiles = tiles_a * tiles_b;
+    const int n_kb = p.k_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&sm.acc_full[b], 1);
+            mbar_init(&sm.acc_empty[b], 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        pdl_launch_dependents();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * sizeof(__nv_bfloat16);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: one stream of k-blocks over all the block's tiles
+            pdl_wait();
+            bool ok = true;
+            long long it = 0, issued = 0;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const int tile_a = t % tiles_a, tile_b = t / tiles_a;
+                for (int kb = 0; kb < n_kb && ok; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    if (it >= STAGES) ok = mbar_wait(&sm.empty[s], (uint32_t)((it / STAGES) - 1) & 1);
+                    if (!ok) break;
+                    mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+                    tma_load_2d(sm.a[s], &map_a, kb * BK, tile_a * BM, &sm.full[s]);
+                    tma_load_2d(sm.b[s], &map_b, kb * BK, tile_b * BN, &sm.full[s]);
+                    issued = it + 1;
+                }
+            }
+            if (!ok) {
+                atomicExch(p.error_flag, 21);
+                for (long long i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+                    mbar_wait(&sm.full[i % STAGES], (uint32_t)(i / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            const uint32_t idesc = umma_idesc(BM, BN);
+            bool ok = true;
+            long long it = 0;
+            int j = 0;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
+                const int buf = j & 1;
+                if (j >= 2) ok = mbar_wait(&sm.acc_empty[buf], (uint32_t)((j >> 1) - 1) & 1);  // the epilogue has drained it
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem + buf * BN;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    ok = mbar_wait(&sm.full[s], (uint32_t)(it / STAGES) & 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma(acc, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, kb > 0 || k > 0);
+                    umma_commit(&sm.empty[s]);
+                }
+                umma_commit(&sm.acc_full[buf]);
+            }
+            if (!ok) atomicExch(p.error_flag, 22);
+        }
+    } else {
+        // ---- epilogue warps
+        const int quarter = warp & 3;
+        pdl_wait();
+        bool ok = true;
+        int j = 0;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
+            const int tile_a = t % tiles_a, tile_b = t / tiles_a, buf = j & 1;
+            const int row_a = tile_a * BM + quarter * 32 + lane;
+            ok = mbar_wait(&sm.acc_full[buf], (uint32_t)(j >> 1) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t t_row = tmem + buf * BN + ((uint32_t)(quarter * 32) << 16);
+            const bool a_ok = row_a < p.rows_a;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                tmem_ld16(t_row + c0, v);
+                write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.acc_empty[buf])) : "memory");
+        }
+        if (!ok && lane == 0) atomicExch(p.error_flag, 23);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -503,6 +637,26 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
     return GK_OK;
 }
 
+template <int BN, int STAGES>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+    const size_t smem = sizeof(PersistentSmem<BN, STAGES>) + 1024;
+    static bool configured = false;
+    static int n_sms = 0;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int device = 0;
+        if (err == cudaSuccess) err = cudaGetDevice(&device);
+        if (err == cudaSuccess) err = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+        if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    const int n_tiles = ((p.rows_a + BM - 1) / BM) * ((p.rows_b + BN - 1) / BN);
+    dim3 grid(n_tiles < n_sms ? n_tiles : n_sms);
+    gk_launch(gemm_tc_persistent_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, ma, mb, p);
+    GK_CHECK_LAUNCH("gemm_tc_persistent");
+    return GK_OK;
+}
+
 }  // namespace
 
 // OUT[a, b] = sum_k A[a, k] B[b, k].  `bn` (16, 32, 64, 128 or 256) is the tile width along B.
@@ -544,6 +698,7 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     p.a_static = a_static;
     p.b_static = b_static;
     p.error_flag = error_flag;
+    if (bn == 256 && splits == 1) return launch_persistent<256, 4>(ma, mb, p, (cudaStream_t)stream);
     dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
     GK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;

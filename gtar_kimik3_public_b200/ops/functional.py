@@ -255,6 +255,7 @@ SKINNY_M = 64  # up to this many tokens the weights take the MMA's 128 rows (swa
 
 
 SPLIT_TARGET_BLOCKS = 128
+PREFILL_BN = 256  # 128 x 256 tiles, walked by one persistent block per SM
 SCRATCH_SPLITS_FROM = 17
 SKINNY_BN_MAX = 64
 SPLIT_MIN_K_BLOCKS = 4
@@ -309,7 +310,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
         call("gk_gemm_bf16_tc", ptr(weight), n, k, ptr(x), m, k, k, ptr(out), dtype_code(out_dtype), 1, n_out,
              EPI_SWIGLU_A if swiglu else EPI_STORE, bn, splits, 1, 0, ptr(flag), stream_ptr())
     else:
-        bn = 128 if n >= 128 else 64 if n >= 64 else 32 if n >= 32 else 16
+        wide = n >= PREFILL_BN and -(-m // 128) * -(-n // PREFILL_BN) >= 120  # enough wide tiles to fill the GPU
+        bn = PREFILL_BN if wide else 128 if n >= 128 else 64 if n >= 64 else 32 if n >= 32 else 16
         call("gk_gemm_bf16_tc", ptr(x), m, k, ptr(weight), n, k, k, ptr(out), dtype_code(out_dtype), n_out, 1,
              EPI_SWIGLU_B if swiglu else EPI_STORE, bn, splits, 0, 1, ptr(flag), stream_ptr())
     return out
