@@ -34,7 +34,29 @@ constexpr int UMMA_K = 16;  // k per tcgen05.mma for 16-bit inputs
 constexpr int THREADS = 192;
 constexpr uint32_t GK_SPIN_LIMIT = 1u << 24;
 
-enum Epilogue : int { EPI_STORE = 0, EPI_SWIGLU_A = 1, EPI_SWIGLU_B = 2 };
+enum Epilogue : int { EPI_STORE = 0, EPI_SWIGLU_A = 1, EPI_SWIGLU_B = 2, EPI_QKV = 3 };
+
+// The attention input stage done where the packed q|k|v projection leaves the tensor cores (many-token
+// orientation only: a thread owns one token's row of the tile, hence whole heads): per-head RMSNorm of
+// q and k, rotation by the token's position, queries to `q_out`, keys and values into the token's
+// place in the pages (src/layers/attention.py:82-89; src/layers/rmsnorm.py:11-16; src/layers/rope.py:17-33).
+struct QkvEpilogue {
+    int n_q, n_kv, head_dim;
+    const void* wq;
+    const void* wk;
+    int weights_bf16, use_norm;
+    float eps;
+    const float* cos_table;   // [positions][head_dim / 2]; null = no rotation
+    const float* sin_table;
+    const int* tok_pos;
+    const int* tok_seq;
+    const int* slots;
+    const int* block_table;
+    int max_pages, page_size;
+    __nv_bfloat16* q_out;     // [tokens][n_q][head_dim]
+    __nv_bfloat16* k_pages;   // null = this layer writes no keys and values
+    __nv_bfloat16* v_pages;
+};
 
 struct GemmParams {
     int rows_a, rows_b, k_blocks;      // k_blocks = ceil(K / BK)
@@ -48,6 +70,7 @@ struct GemmParams {
     int a_static, b_static;            // the operand is not written by the kernel before (weights): it may
                                        // be fetched before that kernel has finished
     int* error_flag;
+    QkvEpilogue qkv;                   // read when epilogue == EPI_QKV
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -456,6 +479,85 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     }
 }
 
+// One token's share of one head: `v` holds the head's HD projection outputs in 32-bit.
+template <int HD>
+__device__ __forceinline__ void qkv_head(const QkvEpilogue& e, float (&v)[HD], int token, int head) {
+    const bool is_q = head < e.n_q, is_k = !is_q && head < e.n_q + e.n_kv;
+    const int pos = e.tok_pos[token];
+    __nv_bfloat16* dst;
+    if (is_q) {
+        dst = e.q_out + ((size_t)token * e.n_q + head) * HD;
+    } else {
+        if (e.k_pages == nullptr) return;
+        const int hk = is_k ? head - e.n_q : head - e.n_q - e.n_kv;
+        const int page = e.block_table[(size_t)e.slots[e.tok_seq[token]] * e.max_pages + pos / e.page_size];
+        const size_t at = (((size_t)page * e.n_kv + hk) * e.page_size + (pos % e.page_size)) * HD;
+        dst = (is_k ? e.k_pages : e.v_pages) + at;
+    }
+    if (is_q || is_k) {
+        if (e.use_norm) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < HD; ++i) ss += v[i] * v[i];
+            const float inv = 1.0f / sqrtf(ss / (float)HD + e.eps);
+            const void* w = is_q ? e.wq : e.wk;
+#pragma unroll
+            for (int i = 0; i < HD; ++i) {
+                const float wi = e.weights_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i])
+                                                : reinterpret_cast<const float*>(w)[i];
+                v[i] = (v[i] * inv) * wi;
+            }
+        }
+        if (e.cos_table) {
+            const float4* c4 = reinterpret_cast<const float4*>(e.cos_table + (size_t)pos * (HD / 2));
+            const float4* s4 = reinterpret_cast<const float4*>(e.sin_table + (size_t)pos * (HD / 2));
+#pragma unroll
+            for (int i = 0; i < HD / 2; i += 4) {
+                const float4 c = c4[i >> 2], sn = s4[i >> 2];
+                const float cs[4] = {c.x, c.y, c.z, c.w}, ss4[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float a = v[i + j], b = v[i + j + HD / 2];
+                    v[i + j] = a * cs[j] - b * ss4[j];
+                    v[i + j + HD / 2] = b * cs[j] + a * ss4[j];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < HD; i += 8) {
+        uint4 w;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]), h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]), h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+        w.x = *reinterpret_cast<uint32_t*>(&h0);
+        w.y = *reinterpret_cast<uint32_t*>(&h1);
+        w.z = *reinterpret_cast<uint32_t*>(&h2);
+        w.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(dst + i) = w;
+    }
+}
+
+// The heads of one 256-wide tile for the token of this thread's row; `t_row` addresses the row's
+// accumulator.  Every lane takes part in the tensor-memory loads; rows beyond the tokens do no more.
+template <int HD, int BN>
+__device__ __forceinline__ void qkv_tile(const GemmParams& p, uint32_t t_row, int row_a, bool a_ok, int tile_b) {
+    const int n_heads = p.qkv.n_q + 2 * p.qkv.n_kv;
+#pragma unroll 1
+    for (int hh = 0; hh < BN / HD; ++hh) {
+        const int head = tile_b * (BN / HD) + hh;
+        if (head >= n_heads) break;  // uniform over the block
+        float v[HD];
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 16) {
+            float part[16];
+            tmem_ld16(t_row + hh * HD + c0, part);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[c0 + i] = part[i];
+        }
+        if (a_ok) qkv_head<HD>(p.qkv, v, row_a, head);
+    }
+}
+
 // ---------------------------------------------------------------- persistent variant for many tokens
 // One block per SM walks over 128 x 256 tiles (A index fastest, so the blocks working at the same time
 // share their B tiles in L2).  Two accumulators of 256 columns fill the tensor memory: while the
@@ -571,11 +673,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_persistent_kernel(const __
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t t_row = tmem + buf * BN + ((uint32_t)(quarter * 32) << 16);
             const bool a_ok = row_a < p.rows_a;
+            if (p.epilogue == EPI_QKV) {
+                if (p.qkv.head_dim == 128) qkv_tile<128, BN>(p, t_row, row_a, a_ok, tile_b);
+                else qkv_tile<64, BN>(p, t_row, row_a, a_ok, tile_b);
+            } else {
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float v[16];
-                tmem_ld16(t_row + c0, v);
-                write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(t_row + c0, v);
+                    write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.acc_empty[buf])) : "memory");
@@ -711,4 +818,62 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
         case 256: return launch<256, 4>(ma, mb, p, grid, s);
         default: return gk_fail(GK_BAD_ARGUMENT, "gemm_tc: bn must be 16, 32, 64, 128 or 256, got %d", bn);
     }
+}
+
+// The packed q|k|v projection of many tokens with the attention input stage in its epilogue:
+// x [n_tokens, k] times w_qkv [(n_q + 2 n_kv) * head_dim, k]^T, then per-head RMSNorm of q and k, rotation,
+// queries to q_out [n_tokens, n_q, head_dim], keys and values into the pages (null pages: not written).
+// head_dim 64 or 128; runs on the persistent 128 x 256 kernel.
+GK_EXPORT int gk_gemm_bf16_tc_qkv(const void* x, int n_tokens, const void* w_qkv, int k, int n_q, int n_kv, int head_dim,
+                                  const void* wq, const void* wk, int weight_dtype, int use_norm, float eps,
+                                  const float* cos_table, const float* sin_table, int table_positions, int max_position,
+                                  const int* tok_pos, const int* tok_seq, const int* slots, const int* block_table,
+                                  int max_pages, int page_size, void* q_out, void* k_pages, void* v_pages,
+                                  int* error_flag, void* stream) {
+    GK_REQUIRE(n_tokens > 0 && k > 0 && k % 8 == 0, "gemm_tc_qkv: bad sizes tokens=%d k=%d", n_tokens, k);
+    GK_REQUIRE(head_dim == 64 || head_dim == 128, "gemm_tc_qkv: head_dim %d is not 64 or 128", head_dim);
+    GK_REQUIRE(n_q > 0 && n_kv > 0 && page_size > 0 && max_pages > 0, "gemm_tc_qkv: bad head counts or page geometry");
+    GK_REQUIRE(GK_VALID_DTYPE(weight_dtype) && (!use_norm || (wq && wk)), "gemm_tc_qkv: bad norm weights");
+    GK_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "gemm_tc_qkv: cos and sin tables go together");
+    GK_REQUIRE(cos_table == nullptr || max_position < table_positions,
+               "gemm_tc_qkv: position %d is beyond the rotary table (%d positions)", max_position, table_positions);
+    GK_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w_qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
+                   ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0 && ((uintptr_t)cos_table & 15) == 0 &&
+                   ((uintptr_t)sin_table & 15) == 0, "gemm_tc_qkv: pointers must be 16-byte aligned");
+    GK_REQUIRE(error_flag != nullptr, "gemm_tc_qkv: error_flag is required");
+    const int n = (n_q + 2 * n_kv) * head_dim;
+    CUtensorMap ma, mb;
+    int status = make_map(&ma, x, n_tokens, k, k, BM);
+    if (status) return status;
+    status = make_map(&mb, w_qkv, n, k, k, 256);
+    if (status) return status;
+    GemmParams p = {};
+    p.rows_a = n_tokens;
+    p.rows_b = n;
+    p.k_blocks = (k + BK - 1) / BK;
+    p.k_blocks_per_split = p.k_blocks;
+    p.epilogue = EPI_QKV;
+    p.out_dtype = GK_BF16;
+    p.b_static = 1;
+    p.error_flag = error_flag;
+    p.qkv.n_q = n_q;
+    p.qkv.n_kv = n_kv;
+    p.qkv.head_dim = head_dim;
+    p.qkv.wq = wq;
+    p.qkv.wk = wk;
+    p.qkv.weights_bf16 = weight_dtype == GK_BF16;
+    p.qkv.use_norm = use_norm;
+    p.qkv.eps = eps;
+    p.qkv.cos_table = cos_table;
+    p.qkv.sin_table = sin_table;
+    p.qkv.tok_pos = tok_pos;
+    p.qkv.tok_seq = tok_seq;
+    p.qkv.slots = slots;
+    p.qkv.block_table = block_table;
+    p.qkv.max_pages = max_pages;
+    p.qkv.page_size = page_size;
+    p.qkv.q_out = (__nv_bfloat16*)q_out;
+    p.qkv.k_pages = (__nv_bfloat16*)k_pages;
+    p.qkv.v_pages = (__nv_bfloat16*)v_pages;
+    return launch_persistent<256, 4>(ma, mb, p, (cudaStream_t)stream);
 }

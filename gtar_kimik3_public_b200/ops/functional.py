@@ -181,6 +181,69 @@ def qk_norm_rope_write(
     return q_out
 
 
+def qkv_fused_ok(x: torch.Tensor, weight: torch.Tensor, head_dim: int, kv: PagedKV) -> bool:
+    """Whether the q|k|v projection of this step can do the attention input stage in its epilogue:
+    bfloat16, enough tokens for the many-token orientation and its wide tiles, head size 64 or 128."""
+    m, k = x.shape
+    n = weight.shape[0]
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16
+            and m > SKINNY_M and k % 8 == 0 and head_dim in (64, 128)
+            and n >= PREFILL_BN and -(-m // 128) * -(-n // PREFILL_BN) >= 120)
+
+
+def gemm_tc_qkv(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    n_q: int,
+    n_kv: int,
+    head_dim: int,
+    q_weight: torch.Tensor | None,
+    k_weight: torch.Tensor | None,
+    eps: float,
+    cos: torch.Tensor | None,
+    sin: torch.Tensor | None,
+    tok_pos: torch.Tensor,
+    tok_seq: torch.Tensor,
+    slots: torch.Tensor,
+    kv: PagedKV,
+    max_position: int,
+    write_kv: bool = True,
+) -> torch.Tensor:
+    """``x @ weight.T`` for the packed q|k|v weight with per-head q/k RMSNorm, rotation and the write of
+    k and v into the pages done in the product's epilogue.  Returns the queries ``[n_tokens, n_q, head_dim]``."""
+    require_device(x.device)
+    _check(x, "x", torch.bfloat16, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    n, k = x.shape
+    if weight.shape != ((n_q + 2 * n_kv) * head_dim, k):
+        raise KernelError(f"weight is {tuple(weight.shape)}, expected {((n_q + 2 * n_kv) * head_dim, k)}")
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    _check(kv.k, "k pages", torch.bfloat16, 4)
+    _check(kv.v, "v pages", torch.bfloat16, 4)
+    if kv.k.shape[1] != n_kv or kv.k.shape[3] != head_dim:
+        raise KernelError(f"pages {tuple(kv.k.shape)} do not fit n_kv={n_kv}, head_dim={head_dim}")
+    use_norm = q_weight is not None
+    weight_code = 0
+    if use_norm:
+        _check(q_weight, "q_weight", dims=1)
+        _check(k_weight, "k_weight", q_weight.dtype, 1)
+        weight_code = dtype_code(q_weight.dtype)
+    table_positions = 0
+    if cos is not None:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        table_positions = cos.shape[0]
+    q_out = torch.empty((n, n_q, head_dim), dtype=torch.bfloat16, device=x.device)
+    call(
+        "gk_gemm_bf16_tc_qkv", ptr(x), n, ptr(weight), k, n_q, n_kv, head_dim, ptr(q_weight), ptr(k_weight), weight_code,
+        int(use_norm), float(eps), ptr(cos), ptr(sin), table_positions, int(max_position), ptr(tok_pos), ptr(tok_seq),
+        ptr(slots), ptr(kv.block_table), kv.max_pages, kv.page_size, ptr(q_out), ptr(kv.k) if write_kv else None,
+        ptr(kv.v) if write_kv else None, ptr(error_flag(x.device)), stream_ptr(),
+    )
+    return q_out
+
+
 def linear_f32(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32,
                out: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight.T`` on the FP32 pipes: ``weight`` float32 ``[N, K]``, ``x`` float32 or bfloat16 ``[M, K]``."""

@@ -63,11 +63,18 @@ class GQAAttention(Mixer):
         return KVRequest(self.n_kv, self.head_dim, self.window)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: F.PagedKV) -> torch.Tensor:
-        qkv = linear(x, self.w_qkv)
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.cos, self.position.sin
         write_kv = not ctx.extras.get("cache_read_only", False)
+        if F.qkv_fused_ok(x, self.w_qkv, self.head_dim, cache):
+            # many tokens: norm, rotation and cache write happen where the projection leaves the tensor cores
+            q = F.gemm_tc_qkv(x, self.w_qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm,
+                              self.qk_norm_eps or 1.0, cos, sin, ctx.tok_pos, ctx.tok_seq, ctx.slots, cache,
+                              ctx.max_position, write_kv)
+            o = attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
+            return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
+        qkv = linear(x, self.w_qkv)
         if ctx.all_single and attention_ops.fused_decode_ok(qkv, cache, self.n_q, self.n_kv, self.head_dim):
             # one token per sequence: norm, rotation, cache write and attention in one kernel
             splits = attention_ops.decode_split_count(ctx, self.n_kv, cache)

@@ -511,3 +511,48 @@ def test_attention_decode_fused_equals_the_separate_kernels(n_q, n_kv, d, weight
     # the same formulas in the same precision; the fused kernel may contract a multiply-add differently
     assert (k_a - k_b).abs().max() <= 2.0**-7 * k_a.abs().max()
     assert (out_a - out_b).abs().max() <= 2.0**-7 * out_a.abs().max() + 1e-3
+
+
+# ------------------------------------------------------------------ q|k|v projection with the attention input stage in its epilogue
+@pytest.mark.parametrize("n_q,n_kv,d,hidden,weight_dtype", [(16, 8, 128, 1024, torch.float32), (6, 2, 64, 136, torch.bfloat16),
+                                                            (5, 1, 128, 72, torch.float32)])
+def test_gemm_tc_qkv_equals_projection_then_qk_kernel(n_q, n_kv, d, hidden, weight_dtype):
+    dtype, eps, theta = torch.bfloat16, 1e-6, 1e5
+    lens, past = [700, 1300, 60], [0, 300, 59]
+    n_tokens = sum(n - p for n, p in zip(lens, past))
+    width = (n_q + 2 * n_kv) * d
+    x = rand(n_tokens, hidden, seed=1).to(dtype)
+    w = rand(width, hidden, seed=2, scale=hidden**-0.5).to(dtype)
+    wq, wk = (1 + 0.1 * rand(d, seed=3)).to(weight_dtype), (1 + 0.1 * rand(d, seed=4)).to(weight_dtype)
+    cos, sin = plain.rotary_tables(torch.arange(1301), d, theta)
+    cos, sin = cos[:, : d // 2].contiguous().to(DEV), sin[:, : d // 2].contiguous().to(DEV)
+    pos, seq = [], []
+    for i, (n, p) in enumerate(zip(lens, past)):
+        pos += list(range(p, n))
+        seq += [i] * (n - p)
+    pos_d, seq_d = torch.tensor(pos, dtype=torch.int32).to(DEV), torch.tensor(seq, dtype=torch.int32).to(DEV)
+    results = []
+    for fused in (False, True):
+        kv, slots, table = scrambled_pages(3, 1300, n_kv, d, dtype, seed=17)
+        if fused:
+            assert F().qkv_fused_ok(x.to(DEV), w.to(DEV), d, kv) == (n_q == 16)  # the engine fuses only wide products
+            q = F().gemm_tc_qkv(x.to(DEV), w.to(DEV), n_q, n_kv, d, wq.to(DEV), wk.to(DEV), eps, cos, sin, pos_d, seq_d,
+                                slots.to(DEV), kv, max(pos))
+        else:
+            qkv = F().gemm_tc(x.to(DEV), w.to(DEV))
+            q = F().qk_norm_rope_write(qkv, n_q, n_kv, d, wq.to(DEV), wk.to(DEV), eps, cos, sin, pos_d, seq_d, slots.to(DEV), kv, max(pos))
+        F().check_kernel_errors()
+        results.append((q.float().cpu(), kv.k.float().cpu(), kv.v.float().cpu()))
+    (q_a, k_a, v_a), (q_b, k_b, v_b) = results
+    assert torch.isfinite(q_b).all()
+    written = ~torch.isnan(k_a)
+    assert torch.equal(written, ~torch.isnan(k_b)) and torch.equal(~torch.isnan(v_a), ~torch.isnan(v_b))  # the same places
+    # the unfused path rounds the projection to bfloat16 before the norm, the fused one does not
+    assert (q_a - q_b).abs().max() <= 2.0**-6 * q_a.abs().max()
+    assert (k_a[written] - k_b[written]).abs().max() <= 2.0**-6 * k_a[written].abs().max()
+    assert (v_a[written] - v_b[written]).abs().max() <= 2.0**-7 * v_a[written].abs().max()
+    # and against the plain formulas
+    xq = (x.double() @ w.double().T).view(n_tokens, n_q + 2 * n_kv, d)
+    c, s = plain.rotary_tables(torch.tensor(pos), d, theta)
+    want_q = plain.apply_rotary(plain.rms_norm(xq[:, :n_q], wq.double(), eps), c.double(), s.double())
+    assert (q_b.double() - want_q).abs().max() <= 2.0**-7 * want_q.abs().max() + 1e-3
