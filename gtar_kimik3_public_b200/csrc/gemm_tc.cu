@@ -537,15 +537,16 @@ __device__ __forceinline__ void qkv_head(const QkvEpilogue& e, float (&v)[HD], i
     }
 }
 
-// The heads of one 256-wide tile for the token of this thread's row; `t_row` addresses the row's
-// accumulator.  Every lane takes part in the tensor-memory loads; rows beyond the tokens do no more.
+// The heads of one half (`half` = 0, 1) of a 256-wide tile for the token of this thread's row; `t_row`
+// addresses the row's accumulator.  Every lane takes part in the tensor-memory loads; rows beyond the tokens do no more.
 template <int HD, int BN>
-__device__ __forceinline__ void qkv_tile(const GemmParams& p, uint32_t t_row, int row_a, bool a_ok, int tile_b) {
+__device__ __forceinline__ void qkv_tile(const GemmParams& p, uint32_t t_row, int row_a, bool a_ok, int tile_b, int half) {
     const int n_heads = p.qkv.n_q + 2 * p.qkv.n_kv;
+    constexpr int PER_HALF = BN / HD / 2;  // heads of the tile this warp takes
 #pragma unroll 1
-    for (int hh = 0; hh < BN / HD; ++hh) {
+    for (int hh = half * PER_HALF; hh < (half + 1) * PER_HALF; ++hh) {
         const int head = tile_b * (BN / HD) + hh;
-        if (head >= n_heads) break;  // uniform over the block
+        if (head >= n_heads) break;  // uniform over the warp
         float v[HD];
 #pragma unroll
         for (int c0 = 0; c0 < HD; c0 += 16) {
@@ -570,8 +571,10 @@ struct alignas(1024) PersistentSmem {
     uint32_t tmem_base;
 };
 
+constexpr int PERSISTENT_THREADS = 320;  // TMA warp, MMA warp, eight epilogue warps (two per lane quarter)
+
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(THREADS, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(PERSISTENT_THREADS, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                         const __grid_constant__ CUtensorMap map_b,
                                                                         const GemmParams p) {
     static_assert(2 * BN <= 512, "two accumulators must fit the tensor memory");
@@ -591,7 +594,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_persistent_kernel(const __
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&sm.acc_full[b], 1);
-            mbar_init(&sm.acc_empty[b], 128);
+            mbar_init(&sm.acc_empty[b], PERSISTENT_THREADS - 64);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         pdl_launch_dependents();
@@ -660,8 +663,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_persistent_kernel(const __
             if (!ok) atomicExch(p.error_flag, 22);
         }
     } else {
-        // ---- epilogue warps
-        const int quarter = warp & 3;
+        // ---- epilogue warps: warp w reads the lanes of quarter w % 4; the two warps of a quarter take
+        // one half of the tile's columns each
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         pdl_wait();
         bool ok = true;
         int j = 0;
@@ -674,11 +678,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_persistent_kernel(const __
             const uint32_t t_row = tmem + buf * BN + ((uint32_t)(quarter * 32) << 16);
             const bool a_ok = row_a < p.rows_a;
             if (p.epilogue == EPI_QKV) {
-                if (p.qkv.head_dim == 128) qkv_tile<128, BN>(p, t_row, row_a, a_ok, tile_b);
-                else qkv_tile<64, BN>(p, t_row, row_a, a_ok, tile_b);
+                if (p.qkv.head_dim == 128) qkv_tile<128, BN>(p, t_row, row_a, a_ok, tile_b, half);
+                else qkv_tile<64, BN>(p, t_row, row_a, a_ok, tile_b, half);
             } else {
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 16) {
                     float v[16];
                     tmem_ld16(t_row + c0, v);
                     write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
@@ -759,7 +763,7 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
     }
     const int n_tiles = ((p.rows_a + BM - 1) / BM) * ((p.rows_b + BN - 1) / BN);
     dim3 grid(n_tiles < n_sms ? n_tiles : n_sms);
-    gk_launch(gemm_tc_persistent_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, ma, mb, p);
+    gk_launch(gemm_tc_persistent_kernel<BN, STAGES>, grid, dim3(PERSISTENT_THREADS), smem, stream, ma, mb, p);
     GK_CHECK_LAUNCH("gemm_tc_persistent");
     return GK_OK;
 }
