@@ -58,6 +58,20 @@ struct QkvEpilogue {
     __nv_bfloat16* v_pages;
 };
 
+// The B operand of a skinny product made inside the kernel from the residual stream: x = RMSNorm(h + delta)
+// (src/layers/rmsnorm.py:11-16, src/models/transformer.py:47-48), for up to 16 tokens.  Every block reads
+// the tokens' whole rows (a few tens of kilobytes from L2) to get the row's mean square, normalises the
+// K range it works on straight into shared memory in the MMA's layout, and the blocks of the first tile
+// write h + delta back (to `h_out`, another buffer than `h`: other blocks still read `h`).
+struct NormInput {
+    const float* h;                 // [rows_b][k]; null = B comes through TMA as usual
+    const __nv_bfloat16* delta;     // [rows_b][k] or null
+    const void* weight;             // norm weight [k]
+    int weight_bf16;
+    float eps;
+    float* h_out;                   // [rows_b][k]
+};
+
 struct GemmParams {
     int rows_a, rows_b, k_blocks;      // k_blocks = ceil(K / BK)
     int k_blocks_per_split;
@@ -71,6 +85,8 @@ struct GemmParams {
                                        // be fetched before that kernel has finished
     int* error_flag;
     QkvEpilogue qkv;                   // read when epilogue == EPI_QKV
+    NormInput norm;                    // read when norm.h != null (BN = 16 only)
+    int k_total;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -231,7 +247,7 @@ template <int BN, int STAGES>
 struct alignas(1024) GemmSmem {
     __nv_bfloat16 a[STAGES][BM * BK];
     __nv_bfloat16 b[STAGES][BN * BK];
-    uint64_t full[STAGES], empty[STAGES], acc_ready;
+    uint64_t full[STAGES], empty[STAGES], acc_ready, b_ready;
     uint32_t tmem_base;
 };
 
@@ -256,6 +272,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             mbar_init(&sm.empty[s], 1);
         }
         mbar_init(&sm.acc_ready, 1);
+        mbar_init(&sm.b_ready, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         pdl_launch_dependents();
     }
@@ -268,7 +285,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_acc = sm.tmem_base;
-    constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * sizeof(__nv_bfloat16);
+    const bool b_normed = p.norm.h != nullptr;  // B is made here from the residual stream; TMA brings A only
+    // the normalised B tiles of this block's K range, one [BN rows][128 bytes] tile per k-block, after the stages
+    __nv_bfloat16* b_tiles = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(&sm) + sizeof(GemmSmem<BN, STAGES>));
+    const uint32_t STAGE_BYTES = (b_normed ? BM : BM + BN) * BK * sizeof(__nv_bfloat16);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -282,13 +302,13 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 mbar_expect_tx(&sm.full[i], STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
                 if (p.a_static) tma_load_2d(sm.a[i], &map_a, k, tile_a * BM, &sm.full[i]);
-                if (p.b_static) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
+                if (p.b_static && !b_normed) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
             }
             pdl_wait();
             for (int i = 0; i < pre; ++i) {
                 const int k = (kb_begin + i) * BK;
                 if (!p.a_static) tma_load_2d(sm.a[i], &map_a, k, tile_a * BM, &sm.full[i]);
-                if (!p.b_static) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
+                if (!p.b_static && !b_normed) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
             }
             issued = pre;
             for (int i = pre; i < n_kb && ok; ++i) {
@@ -298,7 +318,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 mbar_expect_tx(&sm.full[s], STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
                 tma_load_2d(sm.a[s], &map_a, k, tile_a * BM, &sm.full[s]);
-                tma_load_2d(sm.b[s], &map_b, k, tile_b * BN, &sm.full[s]);
+                if (!b_normed) tma_load_2d(sm.b[s], &map_b, k, tile_b * BN, &sm.full[s]);
                 issued = i + 1;
             }
             if (!ok) {
@@ -312,12 +332,14 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             // ---- MMA issuer
             const uint32_t idesc = umma_idesc(BM, BN);
             bool ok = true;
-            for (int i = 0; i < n_kb; ++i) {
+            if (b_normed && n_kb > 0) ok = mbar_wait(&sm.b_ready, 0);  // the epilogue warps have made the B tiles
+            for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % STAGES;
                 ok = mbar_wait(&sm.full[s], (i / STAGES) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+                const uint32_t a_addr = smem_u32(sm.a[s]);
+                const uint32_t b_addr = b_normed ? smem_u32(b_tiles + (size_t)i * BN * BK) : smem_u32(sm.b[s]);
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k) {
                     const uint64_t da = umma_desc(a_addr + k * UMMA_K * 2), db = umma_desc(b_addr + k * UMMA_K * 2);
@@ -333,6 +355,66 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         const int quarter = warp & 3;
         const int row_a = tile_a * BM + quarter * 32 + lane;
         bool ok = true;
+        if (b_normed) {
+            // x = RMSNorm(h + delta) for this block's K range, straight into the MMA's shared-memory layout.
+            // Eight threads a token: first the whole row's sum of squares, then the range.
+            pdl_wait();
+            const int e = (warp - 2) * 32 + lane, m = e >> 3, part = e & 7;
+            const int K = p.k_total;
+            const bool row_ok = m < p.rows_b;
+            const float* hrow = p.norm.h + (size_t)m * K;
+            const __nv_bfloat16* drow = p.norm.delta ? p.norm.delta + (size_t)m * K : nullptr;
+            float ss = 0.f;
+            if (row_ok) {
+                for (int c = part * 4; c < K; c += 32) {
+                    const float4 hv = *reinterpret_cast<const float4*>(hrow + c);
+                    float v[4] = {hv.x, hv.y, hv.z, hv.w};
+                    if (drow) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(drow + c);
+                        const float2 d0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                        const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                        v[0] += d0.x; v[1] += d0.y; v[2] += d1.x; v[3] += d1.y;
+                    }
+                    ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+                }
+            }
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+            const float inv = 1.0f / sqrtf(ss / (float)K + p.norm.eps);
+            const int k_lo = kb_begin * BK, k_hi = min(kb_end * BK, K);
+            const bool write_h = tile_a == 0 && tile_b == 0 && p.norm.h_out != nullptr;
+            for (int c = k_lo + part * 4; c < kb_end * BK; c += 32) {
+                float x[4] = {0.f, 0.f, 0.f, 0.f};
+                if (row_ok && c < k_hi) {
+                    const float4 hv = *reinterpret_cast<const float4*>(hrow + c);
+                    float v[4] = {hv.x, hv.y, hv.z, hv.w};
+                    if (drow) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(drow + c);
+                        const float2 d0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                        const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                        v[0] += d0.x; v[1] += d0.y; v[2] += d1.x; v[3] += d1.y;
+                    }
+                    if (write_h) *reinterpret_cast<float4*>(p.norm.h_out + (size_t)m * K + c) = make_float4(v[0], v[1], v[2], v[3]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float wj = p.norm.weight_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.norm.weight)[c + j])
+                                                            : reinterpret_cast<const float*>(p.norm.weight)[c + j];
+                        x[j] = (v[j] * inv) * wj;
+                    }
+                }
+                // element (row m, column col) of k-block kb: 128-byte rows, 16-byte chunks XOR-swizzled with the row
+                const int kb = (c - k_lo) / BK, col = (c - k_lo) % BK;
+                __nv_bfloat16* tile = b_tiles + (size_t)kb * BN * BK;
+                __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(tile + m * BK + (((col >> 3) ^ (m & 7)) << 3) + (col & 7)) = packed;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.b_ready)) : "memory");
+        }
         if (n_kb > 0) {
             ok = mbar_wait(&sm.acc_ready, 0);
             if (!ok && lane == 0) atomicExch(p.error_flag, 3);
@@ -733,13 +815,17 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, 
     return GK_OK;
 }
 
+constexpr int NORMED_MAX_K_BLOCKS = 16;  // k-blocks of normalised B a block keeps in shared memory
+
 template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     static_assert(STAGES * (BM + BN) * BK * 2 >= BM * BN * 4, "the partial tile must fit in the pipeline stages");
-    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+    const size_t base = sizeof(GemmSmem<BN, STAGES>) + 1024;
+    const size_t smem_max = base + (BN == 16 ? (size_t)NORMED_MAX_K_BLOCKS * BN * BK * 2 : 0);
+    const size_t smem = base + (p.norm.h ? (size_t)p.k_blocks_per_split * BN * BK * 2 : 0);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
         if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
         configured = true;
     }
@@ -794,7 +880,8 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     if (status) return status;
     status = make_map(&mb, b, rows_b, k, ldb, bn);
     if (status) return status;
-    GemmParams p;
+    GemmParams p = {};
+    p.k_total = k;
     p.rows_a = rows_a;
     p.rows_b = rows_b;
     p.k_blocks = (k + BK - 1) / BK;
@@ -880,4 +967,51 @@ GK_EXPORT int gk_gemm_bf16_tc_qkv(const void* x, int n_tokens, const void* w_qkv
     p.qkv.k_pages = (__nv_bfloat16*)k_pages;
     p.qkv.v_pages = (__nv_bfloat16*)v_pages;
     return launch_persistent<256, 4>(ma, mb, p, (cudaStream_t)stream);
+}
+
+// A skinny product whose activations come straight from the residual stream:
+//   OUT[m, :] = RMSNorm(h[m] + delta[m]; norm_weight, eps) @ w^T     for m < n_tokens <= 16,
+// and h_out = h + delta.  `w` is [n, k] bfloat16 (rows alternate gate, up with the SwiGLU epilogue);
+// `delta` may be null; `h_out` must not alias `h`.  The K range of a tile may be shared by 1, 2, 4 or 8
+// blocks (one cluster), each keeping at most 16 k-blocks of 64 of the normalised activations.
+GK_EXPORT int gk_gemm_bf16_tc_normed(const void* w, int n, int k, const float* h, const void* delta, int n_tokens,
+                                     const void* norm_weight, int norm_weight_dtype, float eps, float* h_out, void* out,
+                                     int swiglu, int splits, int* error_flag, void* stream) {
+    GK_REQUIRE(n > 0 && k > 0 && k % 8 == 0, "gemm_tc_normed: bad sizes n=%d k=%d", n, k);
+    GK_REQUIRE(n_tokens > 0 && n_tokens <= 16, "gemm_tc_normed: takes 1 to 16 tokens, got %d", n_tokens);
+    GK_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "gemm_tc_normed: splits must be 1, 2, 4 or 8");
+    GK_REQUIRE(GK_VALID_DTYPE(norm_weight_dtype) && norm_weight && h && h_out && h != h_out, "gemm_tc_normed: bad norm inputs");
+    GK_REQUIRE(eps > 0.f, "gemm_tc_normed: eps must be positive");
+    GK_REQUIRE(((uintptr_t)w & 15) == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)delta & 15) == 0 &&
+                   ((uintptr_t)h_out & 15) == 0 && ((uintptr_t)out & 15) == 0, "gemm_tc_normed: pointers must be 16-byte aligned");
+    GK_REQUIRE(!swiglu || n % 2 == 0, "gemm_tc_normed: the SwiGLU epilogue needs an even number of weight rows");
+    GK_REQUIRE(error_flag != nullptr, "gemm_tc_normed: error_flag is required");
+    CUtensorMap ma;
+    int status = make_map(&ma, w, n, k, k, BM);
+    if (status) return status;
+    GemmParams p = {};
+    p.k_total = k;
+    p.rows_a = n;
+    p.rows_b = n_tokens;
+    p.k_blocks = (k + BK - 1) / BK;
+    p.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
+    GK_REQUIRE(p.k_blocks_per_split <= NORMED_MAX_K_BLOCKS,
+               "gemm_tc_normed: %d k-blocks a block exceed the %d it can keep; use more splits", p.k_blocks_per_split,
+               NORMED_MAX_K_BLOCKS);
+    p.out = out;
+    p.stride_a = 1;
+    p.stride_b = swiglu ? n / 2 : n;
+    p.out_dtype = GK_BF16;
+    p.epilogue = swiglu ? EPI_SWIGLU_A : EPI_STORE;
+    p.a_static = 1;
+    p.b_static = 0;
+    p.error_flag = error_flag;
+    p.norm.h = h;
+    p.norm.delta = (const __nv_bfloat16*)delta;
+    p.norm.weight = norm_weight;
+    p.norm.weight_bf16 = norm_weight_dtype == GK_BF16;
+    p.norm.eps = eps;
+    p.norm.h_out = h_out;
+    dim3 grid((n + BM - 1) / BM, 1, splits);
+    return launch<16, 5>(ma, ma, p, grid, (cudaStream_t)stream);
 }

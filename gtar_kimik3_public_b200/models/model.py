@@ -104,7 +104,7 @@ class Model:
         pending = None
         for index, entry in enumerate(plan.run_list):
             ctx.extras["cache_read_only"] = cache.is_shared(index)
-            pending = plan.layers[entry.layer].forward(h, pending, ctx, cache.view(index))
+            h, pending = plan.layers[entry.layer].forward(h, pending, ctx, cache.view(index))
         if ctx.want_rows.numel() == 0:
             # nothing asked for: still fold the last branch into the stream so the step is whole
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)

@@ -181,6 +181,48 @@ def qk_norm_rope_write(
     return q_out
 
 
+NORMED_MAX_TOKENS = 16
+
+
+def normed_splits(n: int, k: int) -> int | None:
+    """Split count for a skinny product that normalises its own input, or None if it cannot take the
+    shape (a block keeps at most 16 k-blocks of its K range)."""
+    splits = split_k_for(1, n, k)
+    while -(-(-(-k // 64)) // splits) > 16 and splits < 8:
+        splits *= 2
+    return splits if -(-(-(-k // 64)) // splits) <= 16 else None
+
+
+def gemm_tc_normed(h: torch.Tensor, delta: torch.Tensor | None, norm_weight: torch.Tensor, eps: float,
+                   weight: torch.Tensor, swiglu: bool = False, splits: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """``RMSNorm(h + delta) @ weight.T`` for up to 16 tokens in one kernel: every block normalises the
+    part of the rows it needs itself.  Returns the product (bfloat16; ``silu(gate) * up`` with ``swiglu``)
+    and the new residual stream ``h + delta`` (a new tensor; ``h`` is left as it is)."""
+    require_device(h.device)
+    _check(h, "h", torch.float32, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    _check(norm_weight, "norm_weight", dims=1)
+    m, k = h.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or norm_weight.shape[0] != k:
+        raise KernelError(f"h is {tuple(h.shape)}, weight {tuple(weight.shape)}, norm weight {tuple(norm_weight.shape)}")
+    if delta is not None:
+        _check(delta, "delta", torch.bfloat16, 2)
+        if delta.shape != h.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
+    if m > NORMED_MAX_TOKENS:
+        raise KernelError(f"the self-normalising product takes up to {NORMED_MAX_TOKENS} tokens, got {m}")
+    if splits is None:
+        splits = normed_splits(n, k)
+        if splits is None:
+            raise KernelError(f"k = {k} is too long for the self-normalising product")
+    out = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=h.device)
+    h_out = torch.empty_like(h)
+    call("gk_gemm_bf16_tc_normed", ptr(weight), n, k, ptr(h), ptr(delta), m, ptr(norm_weight), dtype_code(norm_weight.dtype),
+         float(eps), ptr(h_out), ptr(out), int(swiglu), int(splits), ptr(error_flag(h.device)), stream_ptr())
+    return out, h_out
+
+
 def qkv_fused_ok(x: torch.Tensor, weight: torch.Tensor, head_dim: int, kv: PagedKV) -> bool:
     """Whether the q|k|v projection of this step can do the attention input stage in its epilogue:
     bfloat16, enough tokens for the many-token orientation and its wide tiles, head size 64 or 128."""

@@ -19,6 +19,21 @@ def _tc_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
 
 
+def linear_after_norm(pending, weight: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+    """``linear(norm(h + delta), weight)`` for a ``PendingNorm``: in one kernel where that is possible (an
+    RMSNorm, bfloat16 weights, at most 16 tokens), otherwise the norm kernel and then the product."""
+    from ..parts.norms import RMSNorm
+
+    h, norm = pending.h, pending.norm
+    if (isinstance(norm, RMSNorm) and pending.h_new is None and weight.dtype == torch.bfloat16
+            and pending.out_dtype == torch.bfloat16 and h.shape[0] <= F.NORMED_MAX_TOKENS and h.shape[1] % 8 == 0
+            and (pending.delta is None or pending.delta.dtype == torch.bfloat16)
+            and F.normed_splits(weight.shape[0], h.shape[1]) is not None):
+        y, pending.h_new = F.gemm_tc_normed(h, pending.delta, norm.weight, norm.eps, weight, swiglu=swiglu)
+        return y
+    return linear(pending.materialize(), weight, swiglu=swiglu)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
            swiglu: bool = False) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T -> [M, N]`` in ``out_dtype`` (default: ``x.dtype``).

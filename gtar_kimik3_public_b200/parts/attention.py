@@ -13,12 +13,13 @@ import torch
 
 from ..ops import attention as attention_ops
 from ..ops import functional as F
-from ..ops.linear import linear
-from .base import KVRequest, Mixer, PositionEncoding, StepContext, TensorSpec, register_part
+from ..ops.linear import linear, linear_after_norm
+from .base import KVRequest, Mixer, PendingNorm, PositionEncoding, StepContext, TensorSpec, register_part
 
 
 class GQAAttention(Mixer):
     graph_safe = True  # all per-step numbers are read from device memory by the kernels
+    accepts_pending_norm = True  # the q|k|v projection can do the add and the norm of its input itself
 
     def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int, qk_norm_eps: float | None,
                  position: PositionEncoding | None, window: int | None = None):
@@ -67,6 +68,11 @@ class GQAAttention(Mixer):
         if self.position is not None:
             cos, sin = self.position.cos, self.position.sin
         write_kv = not ctx.extras.get("cache_read_only", False)
+        if isinstance(x, PendingNorm):
+            if ctx.all_single:  # few tokens: the projection normalises its own input
+                qkv = linear_after_norm(x, self.w_qkv)
+                return self._attend(qkv, ctx, cache, cos, sin, write_kv)
+            x = x.materialize()
         if F.qkv_fused_ok(x, self.w_qkv, self.head_dim, cache):
             # many tokens: norm, rotation and cache write happen where the projection leaves the tensor cores
             q = F.gemm_tc_qkv(x, self.w_qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm,
@@ -74,7 +80,9 @@ class GQAAttention(Mixer):
                               ctx.max_position, write_kv)
             o = attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
             return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
-        qkv = linear(x, self.w_qkv)
+        return self._attend(linear(x, self.w_qkv), ctx, cache, cos, sin, write_kv)
+
+    def _attend(self, qkv: torch.Tensor, ctx: StepContext, cache: F.PagedKV, cos, sin, write_kv: bool) -> torch.Tensor:
         if ctx.all_single and attention_ops.fused_decode_ok(qkv, cache, self.n_q, self.n_kv, self.head_dim):
             # one token per sequence: norm, rotation, cache write and attention in one kernel
             splits = attention_ops.decode_split_count(ctx, self.n_kv, cache)

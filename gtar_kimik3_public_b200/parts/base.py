@@ -82,6 +82,28 @@ class StepContext:
     extras: dict[str, Any] = field(default_factory=dict)
 
 
+@dataclass
+class PendingNorm:
+    """A norm that has not run yet: ``norm(h + delta)``.  A block hands this to a mixer or feed-forward
+    that declares ``accepts_pending_norm`` instead of the normalised activations, so that the part's
+    first projection can do the add and the norm itself.  Whoever consumes it either calls
+    ``materialize()`` (runs the norm kernel; ``h`` is updated in place) or computes the same thing
+    another way and stores the new residual stream in ``h_new``."""
+
+    h: torch.Tensor
+    delta: torch.Tensor | None
+    norm: "Norm"
+    out_dtype: torch.dtype
+    h_new: torch.Tensor | None = None
+
+    def materialize(self) -> torch.Tensor:
+        return self.norm.forward(self.h, self.delta, self.out_dtype)
+
+    def stream(self) -> torch.Tensor:
+        """The residual stream after the add."""
+        return self.h if self.h_new is None else self.h_new
+
+
 class Part:
     """Common face of every part."""
 
@@ -110,6 +132,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    accepts_pending_norm = False  # forward() can take a PendingNorm in place of the normalised activations
+
     def cache_request(self) -> KVRequest | StateRequest | None:
         return None
 
@@ -119,6 +143,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_pending_norm = False
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
@@ -128,9 +154,11 @@ class Block(Part):
 
     mixer: Mixer
 
-    def forward(self, h: torch.Tensor, pending: torch.Tensor | None, ctx: StepContext, cache: Any) -> torch.Tensor | None:
+    def forward(self, h: torch.Tensor, pending: torch.Tensor | None, ctx: StepContext,
+                cache: Any) -> tuple[torch.Tensor, torch.Tensor | None]:
         """Runs the layer.  ``h`` is the 32-bit residual stream, ``pending`` a branch output not yet
-        added to it (so that the add can be fused with the next norm).  Returns the new pending."""
+        added to it (so that the add can be fused with the next norm).  Returns the stream (the same
+        tensor updated in place, or a new one) and the new pending."""
         raise NotImplementedError
 
 

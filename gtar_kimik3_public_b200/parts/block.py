@@ -4,7 +4,7 @@ block hands its last branch output on as ``pending`` instead of adding it itself
 
 from __future__ import annotations
 
-from .base import Block, FeedForward, Mixer, Norm, StepContext, register_part
+from .base import Block, FeedForward, Mixer, Norm, PendingNorm, StepContext, register_part
 
 
 class PreNormBlock(Block):
@@ -33,10 +33,21 @@ class PreNormBlock(Block):
         return sum(part.weight_bytes() for _, part in self.children())
 
     def forward(self, h, pending, ctx: StepContext, cache):
-        x = self.input_norm.forward(h, pending, ctx.dtype)
+        x = self._normed(self.input_norm, h, pending, ctx, self.mixer)
         branch = self.mixer.forward(x, ctx, cache)
-        x = self.post_norm.forward(h, branch, ctx.dtype)
-        return self.feed_forward.forward(x, ctx)
+        h = x.stream() if isinstance(x, PendingNorm) else h
+        x = self._normed(self.post_norm, h, branch, ctx, self.feed_forward)
+        out = self.feed_forward.forward(x, ctx)
+        h = x.stream() if isinstance(x, PendingNorm) else h
+        return h, out
+
+    @staticmethod
+    def _normed(norm: Norm, h, delta, ctx: StepContext, consumer):
+        """The consumer's input: normalised activations, or the norm still to be done if the consumer
+        can fold it into its first projection."""
+        if getattr(consumer, "accepts_pending_norm", False):
+            return PendingNorm(h, delta, norm, ctx.dtype)
+        return norm.forward(h, delta, ctx.dtype)
 
 
 register_part("block", "pre_norm", PreNormBlock)

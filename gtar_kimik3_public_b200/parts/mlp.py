@@ -8,11 +8,13 @@ from __future__ import annotations
 import torch
 
 from ..ops import functional as F
-from ..ops.linear import linear
-from .base import FeedForward, StepContext, TensorSpec, register_part
+from ..ops.linear import linear, linear_after_norm
+from .base import FeedForward, PendingNorm, StepContext, TensorSpec, register_part
 
 
 class SwiGLUFeedForward(FeedForward):
+    accepts_pending_norm = True  # the gate/up projection can do the add and the norm of its input itself
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.w_gate_up = self.w_down = None
@@ -36,7 +38,10 @@ class SwiGLUFeedForward(FeedForward):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        act = linear(x, self.w_gate_up, swiglu=True)
+        if isinstance(x, PendingNorm):
+            act = linear_after_norm(x, self.w_gate_up, swiglu=True)
+        else:
+            act = linear(x, self.w_gate_up, swiglu=True)
         return linear(act, self.w_down)
 
 

@@ -556,3 +556,33 @@ def test_gemm_tc_qkv_equals_projection_then_qk_kernel(n_q, n_kv, d, hidden, weig
     c, s = plain.rotary_tables(torch.tensor(pos), d, theta)
     want_q = plain.apply_rotary(plain.rms_norm(xq[:, :n_q], wq.double(), eps), c.double(), s.double())
     assert (q_b.double() - want_q).abs().max() <= 2.0**-7 * want_q.abs().max() + 1e-3
+
+
+# ------------------------------------------------------------------ skinny product that normalises its own input
+@pytest.mark.parametrize("m,n,k,swiglu,with_delta,weight_dtype", [
+    (8, 4096, 1024, False, True, torch.float32), (8, 6144, 1024, True, True, torch.float32), (1, 384, 96, False, False, torch.float32),
+    (16, 1000, 200, False, True, torch.bfloat16), (3, 448, 2560, True, True, torch.float32)])
+def test_gemm_tc_normed_equals_norm_then_product(m, n, k, swiglu, with_delta, weight_dtype):
+    eps = 1e-6
+    h = rand(m, k, seed=1, scale=2.0).float()
+    delta = rand(m, k, seed=2).to(torch.bfloat16) if with_delta else None
+    nw = (1 + 0.1 * rand(k, seed=3)).to(weight_dtype)
+    w = rand(n, k, seed=4, scale=k**-0.5).to(torch.bfloat16)
+    hd = h.to(DEV)
+    got, h_new = F().gemm_tc_normed(hd, None if delta is None else delta.to(DEV), nw.to(DEV), eps, w.to(DEV), swiglu=swiglu)
+    F().check_kernel_errors()
+    assert torch.equal(hd.cpu(), h)  # the input stream is left alone
+    total = h.double() + (0 if delta is None else delta.double())
+    assert (h_new.double().cpu() - total).abs().max() < 1e-6
+    # the two-kernel path on the same inputs
+    h2 = h.to(DEV)
+    x = F().add_rmsnorm(h2, None if delta is None else delta.to(DEV), nw.to(DEV), eps, torch.bfloat16)
+    want = F().gemm_tc(x, w.to(DEV), swiglu=swiglu)
+    scale = want.float().abs().max().item()
+    assert (got.float() - want.float()).abs().max().item() <= 2.0**-7 * scale + 1e-3
+    # and the plain formulas
+    y = plain.rms_norm(total, nw.double(), eps) @ w.double().T
+    if swiglu:
+        g, u = y[:, 0::2], y[:, 1::2]
+        y = g * torch.sigmoid(g) * u
+    assert (got.double().cpu() - y).abs().max().item() <= 2.0**-6 * y.abs().max().item() + 2e-3

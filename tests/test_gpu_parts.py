@@ -139,8 +139,8 @@ def test_pre_norm_block_and_pending_add(dtype):
     cache, ctx = one_sequence_ctx(n, dtype, n_kv, d)
     rope.prepare(n, torch.device(DEV))
     hd = h.to(DEV)
-    pending = block.forward(hd, None, ctx, cache.view(0))
-    got = hd.double().cpu() + pending.double().cpu()  # the stream after the layer = stream + pending
+    stream, pending = block.forward(hd, None, ctx, cache.view(0))
+    got = stream.double().cpu() + pending.double().cpu()  # the stream after the layer = stream + pending
     cfg = {"num_attention_heads": n_q, "num_key_value_heads": n_kv, "head_dim": d, "rms_norm_eps": eps, "rope_theta": theta}
     want = plain.block(h.double(), {"model.layers.0." + k: v for k, v in w.items()}, 0, cfg)
     assert (got - want).abs().max() < tol(dtype, want.abs().max().item())
