@@ -251,7 +251,7 @@ struct alignas(1024) GemmSmem {
     uint32_t tmem_base;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool NORMED>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                              const __grid_constant__ CUtensorMap map_b,
                                                              const GemmParams p) {
@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             mbar_init(&sm.empty[s], 1);
         }
         mbar_init(&sm.acc_ready, 1);
-        mbar_init(&sm.b_ready, 128);
+        if (NORMED) mbar_init(&sm.b_ready, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         pdl_launch_dependents();
     }
@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_acc = sm.tmem_base;
-    const bool b_normed = p.norm.h != nullptr;  // B is made here from the residual stream; TMA brings A only
+    constexpr bool b_normed = NORMED;  // B is made here from the residual stream; TMA brings A only
     // the normalised B tiles of this block's K range, one [BN rows][128 bytes] tile per k-block, after the stages
     __nv_bfloat16* b_tiles = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(&sm) + sizeof(GemmSmem<BN, STAGES>));
     const uint32_t STAGE_BYTES = (b_normed ? BM : BM + BN) * BK * sizeof(__nv_bfloat16);
@@ -355,62 +355,100 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         const int quarter = warp & 3;
         const int row_a = tile_a * BM + quarter * 32 + lane;
         bool ok = true;
-        if (b_normed) {
+        if constexpr (NORMED) {
             // x = RMSNorm(h + delta) for this block's K range, straight into the MMA's shared-memory layout.
             // Eight threads a token: first the whole row's sum of squares, then the range.
             pdl_wait();
-            const int e = (warp - 2) * 32 + lane, m = e >> 3, part = e & 7;
+            // `tpr` threads a token (a power of two, at most a warp), so that all 128 threads are busy for
+            // 4 to 16 tokens; a thread's loads are issued eight chunks of four at a time
+            const int e = (warp - 2) * 32 + lane;
+            const int rows_pad = p.rows_b <= 4 ? 4 : p.rows_b <= 8 ? 8 : 16;
+            const int tpr = 128 / rows_pad;           // 32, 16 or 8
+            const int m = e / tpr, part = e % tpr;
             const int K = p.k_total;
             const bool row_ok = m < p.rows_b;
             const float* hrow = p.norm.h + (size_t)m * K;
             const __nv_bfloat16* drow = p.norm.delta ? p.norm.delta + (size_t)m * K : nullptr;
+            auto load_sum = [&](int c, float (&v)[4]) {  // h + delta at columns c .. c+3
+                const float4 hv = *reinterpret_cast<const float4*>(hrow + c);
+                v[0] = hv.x; v[1] = hv.y; v[2] = hv.z; v[3] = hv.w;
+                if (drow) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(drow + c);
+                    const float2 d0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                    const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                    v[0] += d0.x; v[1] += d0.y; v[2] += d1.x; v[3] += d1.y;
+                }
+            };
             float ss = 0.f;
             if (row_ok) {
-                for (int c = part * 4; c < K; c += 32) {
-                    const float4 hv = *reinterpret_cast<const float4*>(hrow + c);
-                    float v[4] = {hv.x, hv.y, hv.z, hv.w};
-                    if (drow) {
-                        const uint2 raw = *reinterpret_cast<const uint2*>(drow + c);
-                        const float2 d0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                        const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-                        v[0] += d0.x; v[1] += d0.y; v[2] += d1.x; v[3] += d1.y;
+                const int step = tpr * 4;
+                for (int c0 = part * 4; c0 < K; c0 += 8 * step) {
+                    float v[8][4];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int c = c0 + u * step;
+                        if (c < K) load_sum(c, v[u]);
+                        else v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0.f;
                     }
-                    ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) ss += v[u][0] * v[u][0] + v[u][1] * v[u][1] + v[u][2] * v[u][2] + v[u][3] * v[u][3];
                 }
             }
-            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+            for (int o = 1; o < tpr; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const float inv = 1.0f / sqrtf(ss / (float)K + p.norm.eps);
             const int k_lo = kb_begin * BK, k_hi = min(kb_end * BK, K);
             const bool write_h = tile_a == 0 && tile_b == 0 && p.norm.h_out != nullptr;
-            for (int c = k_lo + part * 4; c < kb_end * BK; c += 32) {
-                float x[4] = {0.f, 0.f, 0.f, 0.f};
-                if (row_ok && c < k_hi) {
-                    const float4 hv = *reinterpret_cast<const float4*>(hrow + c);
-                    float v[4] = {hv.x, hv.y, hv.z, hv.w};
-                    if (drow) {
-                        const uint2 raw = *reinterpret_cast<const uint2*>(drow + c);
-                        const float2 d0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                        const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-                        v[0] += d0.x; v[1] += d0.y; v[2] += d1.x; v[3] += d1.y;
-                    }
-                    if (write_h) *reinterpret_cast<float4*>(p.norm.h_out + (size_t)m * K + c) = make_float4(v[0], v[1], v[2], v[3]);
+            if (m < BN) {
+                // the block's own K range, again eight chunks at a time (the values are in L1 from the pass
+                // above): all loads of a batch are issued before the first is used
+                const int step = tpr * 4;
+                for (int c0 = k_lo + part * 4; c0 < kb_end * BK; c0 += 8 * step) {
+                    float v[8][4], wv[8][4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float wj = p.norm.weight_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.norm.weight)[c + j])
-                                                            : reinterpret_cast<const float*>(p.norm.weight)[c + j];
-                        x[j] = (v[j] * inv) * wj;
+                    for (int u = 0; u < 8; ++u) {
+                        const int c = c0 + u * step;
+                        if (row_ok && c < k_hi) {
+                            load_sum(c, v[u]);
+                            if (p.norm.weight_bf16) {
+                                const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.norm.weight) + c);
+                                const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                                const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                                wv[u][0] = w0.x; wv[u][1] = w0.y; wv[u][2] = w1.x; wv[u][3] = w1.y;
+                            } else {
+                                const float4 w4 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm.weight) + c);
+                                wv[u][0] = w4.x; wv[u][1] = w4.y; wv[u][2] = w4.z; wv[u][3] = w4.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) v[u][j] = wv[u][j] = 0.f;
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int c = c0 + u * step;
+                        if (c >= kb_end * BK) continue;
+                        if (write_h && row_ok && c < k_hi)
+                            *reinterpret_cast<float4*>(p.norm.h_out + (size_t)m * K + c) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+                        float x[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) x[j] = (v[u][j] * inv) * wv[u][j];
+                        // element (row m, column col) of k-block kb: 128-byte rows, 16-byte chunks XOR-swizzled with the row
+                        const int kb = (c - k_lo) / BK, col = (c - k_lo) % BK;
+                        __nv_bfloat16* tile = b_tiles + (size_t)kb * BN * BK;
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(tile + m * BK + (((col >> 3) ^ (m & 7)) << 3) + (col & 7)) = packed;
                     }
                 }
-                // element (row m, column col) of k-block kb: 128-byte rows, 16-byte chunks XOR-swizzled with the row
-                const int kb = (c - k_lo) / BK, col = (c - k_lo) % BK;
-                __nv_bfloat16* tile = b_tiles + (size_t)kb * BN * BK;
-                __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
-                uint2 packed;
-                packed.x = *reinterpret_cast<uint32_t*>(&lo);
-                packed.y = *reinterpret_cast<uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(tile + m * BK + (((col >> 3) ^ (m & 7)) << 3) + (col & 7)) = packed;
+            }
+            // rows of the tile beyond the padded token count (tokens <= 8 leave rows 8..15, <= 4 rows 4..15)
+            for (int idx = e; idx < (BN - rows_pad) * (kb_end - kb_begin) * (BK / 8); idx += 128) {
+                const int chunks_per_kb = (BN - rows_pad) * (BK / 8);
+                const int kb = idx / chunks_per_kb, rest = idx % chunks_per_kb;
+                const int r = rows_pad + rest / (BK / 8), ch = rest % (BK / 8);
+                *reinterpret_cast<uint4*>(b_tiles + (size_t)kb * BN * BK + r * BK + (ch << 3)) = make_uint4(0, 0, 0, 0);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.b_ready)) : "memory");
@@ -817,19 +855,19 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, 
 
 constexpr int NORMED_MAX_K_BLOCKS = 16;  // k-blocks of normalised B a block keeps in shared memory
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool NORMED = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     static_assert(STAGES * (BM + BN) * BK * 2 >= BM * BN * 4, "the partial tile must fit in the pipeline stages");
     const size_t base = sizeof(GemmSmem<BN, STAGES>) + 1024;
-    const size_t smem_max = base + (BN == 16 ? (size_t)NORMED_MAX_K_BLOCKS * BN * BK * 2 : 0);
-    const size_t smem = base + (p.norm.h ? (size_t)p.k_blocks_per_split * BN * BK * 2 : 0);
+    const size_t smem_max = base + (NORMED ? (size_t)NORMED_MAX_K_BLOCKS * BN * BK * 2 : 0);
+    const size_t smem = base + (NORMED ? (size_t)p.k_blocks_per_split * BN * BK * 2 : 0);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, NORMED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
         if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
         configured = true;
     }
-    gk_launch_cluster(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, dim3(1, 1, grid.z), ma, mb, p);
+    gk_launch_cluster(gemm_tc_kernel<BN, STAGES, NORMED>, grid, dim3(THREADS), smem, stream, dim3(1, 1, grid.z), ma, mb, p);
     GK_CHECK_LAUNCH("gemm_tc");
     return GK_OK;
 }
@@ -1013,5 +1051,5 @@ GK_EXPORT int gk_gemm_bf16_tc_normed(const void* w, int n, int k, const float* h
     p.norm.eps = eps;
     p.norm.h_out = h_out;
     dim3 grid((n + BM - 1) / BM, 1, splits);
-    return launch<16, 5>(ma, ma, p, grid, (cudaStream_t)stream);
+    return launch<16, 5, true>(ma, ma, p, grid, (cudaStream_t)stream);
 }
