@@ -72,6 +72,27 @@ struct NormInput {
     float* h_out;                   // [rows_b][k]
 };
 
+// The residual add and the first half of the next RMSNorm done where a skinny product (A = weights) is
+// written (src/models/transformer.py:47-48, src/layers/rmsnorm.py:11-16):  h += OUT (32-bit, in place),
+// xw = bfloat16(h * weight) and, per token, this block's share of sum(h^2) in `ss[token][partial]`.  The next
+// product reads xw and multiplies its own output rows by rsqrt(sum(ss) / size + eps) (RowScale).
+struct ResidualOutput {
+    float* h;                       // [rows_b][rows_a]
+    const void* weight;             // the next norm's weight [rows_a]
+    int weight_bf16;
+    __nv_bfloat16* xw;              // [rows_b][rows_a]
+    float* ss;                      // [rows_b][n_partials], n_partials = tiles along A * splits
+    int n_partials;
+};
+
+struct RowScale {
+    const float* ss;                // [rows_b][n_partials]
+    int n_partials;
+    float eps, inv_size;            // 1 / (width of the normalised rows)
+};
+
+enum Mode : int { MODE_PLAIN = 0, MODE_NORMED = 1, MODE_RESIDUAL = 2, MODE_SCALED = 3 };
+
 struct GemmParams {
     int rows_a, rows_b, k_blocks;      // k_blocks = ceil(K / BK)
     int k_blocks_per_split;
@@ -85,7 +106,9 @@ struct GemmParams {
                                        // be fetched before that kernel has finished
     int* error_flag;
     QkvEpilogue qkv;                   // read when epilogue == EPI_QKV
-    NormInput norm;                    // read when norm.h != null (BN = 16 only)
+    NormInput norm;                    // MODE_NORMED (BN = 16 only)
+    ResidualOutput residual;           // MODE_RESIDUAL
+    RowScale scale;                    // MODE_SCALED
     int k_total;
 };
 
@@ -161,6 +184,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float weight_at(const void* w, int is_bf16, int i) {
+    return is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]) : reinterpret_cast<const float*>(w)[i];
 }
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
@@ -251,7 +278,7 @@ struct alignas(1024) GemmSmem {
     uint32_t tmem_base;
 };
 
-template <int BN, int STAGES, bool NORMED>
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                              const __grid_constant__ CUtensorMap map_b,
                                                              const GemmParams p) {
@@ -260,6 +287,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     GemmSmem<BN, STAGES>& sm =
         *reinterpret_cast<GemmSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;  // a power of two >= 32 (BN is 16, 32, 64, 128 or 256)
+    constexpr bool NORMED = MODE == MODE_NORMED;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
     const int kb_begin = split * p.k_blocks_per_split;
@@ -288,6 +316,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     constexpr bool b_normed = NORMED;  // B is made here from the residual stream; TMA brings A only
     // the normalised B tiles of this block's K range, one [BN rows][128 bytes] tile per k-block, after the stages
     __nv_bfloat16* b_tiles = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(&sm) + sizeof(GemmSmem<BN, STAGES>));
+    // the same place in the other modes: per-token scales (MODE_SCALED), shares of the sums of squares (MODE_RESIDUAL)
+    float* extra = reinterpret_cast<float*>(b_tiles);
     const uint32_t STAGE_BYTES = (b_normed ? BM : BM + BN) * BK * sizeof(__nv_bfloat16);
 
     if (warp == 0) {
@@ -453,6 +483,26 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.b_ready)) : "memory");
         }
+        if constexpr (MODE == MODE_SCALED) {
+            // 1 / rms of each token of this tile from the shares the product before left, while the MMAs run:
+            // 128 / BN threads a token, each adding every (128 / BN)-th share, then a tree over those threads
+            pdl_wait();
+            constexpr int TPT = BN >= 128 ? 1 : 128 / BN;
+            const int e = (warp - 2) * 32 + lane;
+            for (int t0 = 0; t0 < BN; t0 += 128 / TPT) {
+                const int local = t0 + e / TPT, part = e % TPT, token = tile_b * BN + local;
+                float sum = 0.f;
+                if (local < BN && token < p.rows_b) {
+                    const float* shares = p.scale.ss + (size_t)token * p.scale.n_partials;
+#pragma unroll 4
+                    for (int j = part; j < p.scale.n_partials; j += TPT) sum += shares[j];
+                }
+#pragma unroll
+                for (int o = 1; o < TPT; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (part == 0 && local < BN) extra[local] = 1.0f / sqrtf(sum * p.scale.inv_size + p.scale.eps);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         if (n_kb > 0) {
             ok = mbar_wait(&sm.acc_ready, 0);
             if (!ok && lane == 0) atomicExch(p.error_flag, 3);
@@ -472,7 +522,38 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;
                 }
-                write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
+                if constexpr (MODE == MODE_SCALED) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] *= extra[c0 + i];
+                }
+                if constexpr (MODE == MODE_RESIDUAL) {
+                    // h += v; xw = h * weight; the warp's 32 rows of every token's square go to extra[col][quarter]
+                    const float w = a_ok ? weight_at(p.residual.weight, p.residual.weight_bf16, row_a) : 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int rb = tile_b * BN + c0 + i;
+                        float sq = 0.f;
+                        if (a_ok && rb < p.rows_b) {
+                            const size_t at = (size_t)rb * p.rows_a + row_a;
+                            const float hn = p.residual.h[at] + v[i];
+                            p.residual.h[at] = hn;
+                            p.residual.xw[at] = __float2bfloat16(hn * w);
+                            sq = hn * hn;
+                        }
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                        if (lane == 0) extra[(c0 + i) * 4 + quarter] = sq;
+                    }
+                } else {
+                    write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
+                }
+            }
+            if constexpr (MODE == MODE_RESIDUAL) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int e = (warp - 2) * 32 + lane, token = tile_b * BN + e;
+                if (e < BN && token < p.rows_b)
+                    p.residual.ss[(size_t)token * p.residual.n_partials + tile_a] =
+                        ((extra[e * 4] + extra[e * 4 + 1]) + extra[e * 4 + 2]) + extra[e * 4 + 3];
             }
         } else {
             // split-K: this block's partial tile goes to its own shared memory, [column][row] float32,
@@ -490,6 +571,31 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) stage[(c0 + i) * BM + row_in_tile] = v[i];
+            }
+        }
+    }
+    // MODE_RESIDUAL: the stream and norm weights of the first two groups this thread will finish, fetched while
+    // the cluster gathers (they do not depend on the partial tiles)
+    float4 pre_h[2], pre_w[2];
+    if constexpr (MODE == MODE_RESIDUAL) {
+        if (gridDim.z > 1 && warp >= 2 && (p.rows_a & 3) == 0) {
+            const int rows_per = BM / (int)gridDim.z, quads = rows_per / 4, count = quads * BN;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int idx = (warp - 2) * 32 + lane + u * 128;
+                const int row_a = tile_a * BM + (int)blockIdx.z * rows_per + 4 * (idx % quads), rb = tile_b * BN + idx / quads;
+                pre_h[u] = pre_w[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (idx < count && row_a + 3 < p.rows_a && rb < p.rows_b) {
+                    pre_h[u] = *reinterpret_cast<const float4*>(p.residual.h + (size_t)rb * p.rows_a + row_a);
+                    if (p.residual.weight_bf16) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.residual.weight) + row_a);
+                        const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                        const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                        pre_w[u] = make_float4(w0.x, w0.y, w1.x, w1.y);
+                    } else {
+                        pre_w[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.residual.weight) + row_a);
+                    }
+                }
             }
         }
     }
@@ -552,10 +658,57 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     const int idx = base + u * 128;
                     if (idx >= count) continue;
                     const int row_a = tile_a * BM + rank * rows_per + 4 * (idx % quads), rb = tile_b * BN + idx / quads;
-                    if (row_a >= p.rows_a || rb >= p.rows_b) continue;
-                    const float4 v = add_up(part[u]);
+                    if (row_a >= p.rows_a || rb >= p.rows_b) {
+                        if constexpr (MODE == MODE_RESIDUAL) extra[(idx / quads) * 16 + idx % quads] = 0.f;
+                        continue;
+                    }
+                    float4 v = add_up(part[u]);
+                    if constexpr (MODE == MODE_SCALED) {
+                        const float inv = extra[idx / quads];
+                        v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
+                    }
                     const float vs[4] = {v.x, v.y, v.z, v.w};
-                    if (swiglu) {
+                    if constexpr (MODE == MODE_RESIDUAL) {
+                        // h += v over four consecutive features of one token; the quad's squares go to extra[col][quad]
+                        const size_t at = (size_t)rb * p.rows_a + row_a;
+                        float hn[4], sq = 0.f;
+                        if (row_a + 3 < p.rows_a && (p.rows_a & 3) == 0) {
+                            float4 h4, w4;
+                            if (base == e) {
+                                h4 = pre_h[u];
+                                w4 = pre_w[u];
+                            } else {
+                                h4 = *reinterpret_cast<const float4*>(p.residual.h + at);
+                                w4 = make_float4(weight_at(p.residual.weight, p.residual.weight_bf16, row_a),
+                                                 weight_at(p.residual.weight, p.residual.weight_bf16, row_a + 1),
+                                                 weight_at(p.residual.weight, p.residual.weight_bf16, row_a + 2),
+                                                 weight_at(p.residual.weight, p.residual.weight_bf16, row_a + 3));
+                            }
+                            hn[0] = h4.x + vs[0]; hn[1] = h4.y + vs[1]; hn[2] = h4.z + vs[2]; hn[3] = h4.w + vs[3];
+                            *reinterpret_cast<float4*>(p.residual.h + at) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+                            const float w[4] = {w4.x, w4.y, w4.z, w4.w};
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(hn[0] * w[0], hn[1] * w[1]);
+                            __nv_bfloat162 hi = __floats2bfloat162_rn(hn[2] * w[2], hn[3] * w[3]);
+                            uint2 packed;
+                            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                            *reinterpret_cast<uint2*>(p.residual.xw + at) = packed;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) sq += hn[i] * hn[i];
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                if (row_a + i < p.rows_a) {
+                                    hn[i] = p.residual.h[at + i] + vs[i];
+                                    p.residual.h[at + i] = hn[i];
+                                    p.residual.xw[at + i] =
+                                        __float2bfloat16(hn[i] * weight_at(p.residual.weight, p.residual.weight_bf16, row_a + i));
+                                    sq += hn[i] * hn[i];
+                                }
+                            }
+                        }
+                        extra[(idx / quads) * 16 + idx % quads] = sq;
+                    } else if (swiglu) {
 #pragma unroll
                         for (int i = 0; i < 4; i += 2) {
                             if (row_a + i + 1 < p.rows_a) {
@@ -584,6 +737,19 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                             }
                         }
                     }
+                }
+            }
+        }
+        if constexpr (MODE == MODE_RESIDUAL) {
+            if (warp >= 2) {
+                // this block's share of each token's sum of squares: its quads in order
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int e = (warp - 2) * 32 + lane, token = tile_b * BN + e;
+                const int quads = BM / (int)gridDim.z / 4;
+                if (e < BN && token < p.rows_b) {
+                    float sum = 0.f;
+                    for (int q = 0; q < quads; ++q) sum += extra[e * 16 + q];
+                    p.residual.ss[(size_t)token * p.residual.n_partials + tile_a * gridDim.z + blockIdx.z] = sum;
                 }
             }
         }
@@ -855,19 +1021,20 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, 
 
 constexpr int NORMED_MAX_K_BLOCKS = 16;  // k-blocks of normalised B a block keeps in shared memory
 
-template <int BN, int STAGES, bool NORMED = false>
+template <int BN, int STAGES, int MODE = MODE_PLAIN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     static_assert(STAGES * (BM + BN) * BK * 2 >= BM * BN * 4, "the partial tile must fit in the pipeline stages");
     const size_t base = sizeof(GemmSmem<BN, STAGES>) + 1024;
-    const size_t smem_max = base + (NORMED ? (size_t)NORMED_MAX_K_BLOCKS * BN * BK * 2 : 0);
-    const size_t smem = base + (NORMED ? (size_t)p.k_blocks_per_split * BN * BK * 2 : 0);
+    constexpr size_t EXTRA = MODE == MODE_RESIDUAL ? (size_t)BN * 16 * 4 : MODE == MODE_SCALED ? (size_t)BN * 4 : 0;
+    const size_t smem_max = base + (MODE == MODE_NORMED ? (size_t)NORMED_MAX_K_BLOCKS * BN * BK * 2 : EXTRA);
+    const size_t smem = base + (MODE == MODE_NORMED ? (size_t)p.k_blocks_per_split * BN * BK * 2 : EXTRA);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, NORMED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
         if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
         configured = true;
     }
-    gk_launch_cluster(gemm_tc_kernel<BN, STAGES, NORMED>, grid, dim3(THREADS), smem, stream, dim3(1, 1, grid.z), ma, mb, p);
+    gk_launch_cluster(gemm_tc_kernel<BN, STAGES, MODE>, grid, dim3(THREADS), smem, stream, dim3(1, 1, grid.z), ma, mb, p);
     GK_CHECK_LAUNCH("gemm_tc");
     return GK_OK;
 }
@@ -1051,5 +1218,97 @@ GK_EXPORT int gk_gemm_bf16_tc_normed(const void* w, int n, int k, const float* h
     p.norm.eps = eps;
     p.norm.h_out = h_out;
     dim3 grid((n + BM - 1) / BM, 1, splits);
-    return launch<16, 5, true>(ma, ma, p, grid, (cudaStream_t)stream);
+    return launch<16, 5, MODE_NORMED>(ma, ma, p, grid, (cudaStream_t)stream);
+}
+
+namespace {
+
+template <int MODE>
+int launch_skinny(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t s) {
+    switch (bn) {
+        case 16: return launch<16, 5, MODE>(ma, mb, p, grid, s);
+        case 32: return launch<32, 9, MODE>(ma, mb, p, grid, s);
+        case 64: return launch<64, 8, MODE>(ma, mb, p, grid, s);
+        default: return gk_fail(GK_BAD_ARGUMENT, "gemm_tc: the token tile of a skinny product is 16, 32 or 64, got %d", bn);
+    }
+}
+
+int skinny_params(GemmParams& p, CUtensorMap& ma, CUtensorMap& mb, const void* w, int n, int k, const void* x, int n_tokens,
+                  long long ldx, int bn, int splits, int* error_flag, const char* who) {
+    GK_REQUIRE(n > 0 && k > 0 && k % 8 == 0 && ldx % 8 == 0, "%s: bad sizes n=%d k=%d ldx=%lld (k and ldx in steps of 8)", who, n, k, ldx);
+    GK_REQUIRE(n_tokens > 0 && n_tokens <= 64, "%s: takes 1 to 64 tokens, got %d", who, n_tokens);
+    GK_REQUIRE((bn == 16 || bn == 32 || bn == 64) && n_tokens <= bn, "%s: token tile %d does not hold %d tokens", who, bn, n_tokens);
+    GK_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "%s: splits must be 1, 2, 4 or 8, got %d", who, splits);
+    GK_REQUIRE(((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0, "%s: operands must be 16-byte aligned", who);
+    GK_REQUIRE(error_flag != nullptr, "%s: error_flag is required", who);
+    int status = make_map(&ma, w, n, k, k, BM);
+    if (status) return status;
+    status = make_map(&mb, x, n_tokens, k, ldx, bn);
+    if (status) return status;
+    p.k_total = k;
+    p.rows_a = n;
+    p.rows_b = n_tokens;
+    p.k_blocks = (k + BK - 1) / BK;
+    p.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
+    p.stride_a = 1;
+    p.a_static = 1;
+    p.b_static = 0;
+    p.error_flag = error_flag;
+    return GK_OK;
+}
+
+}  // namespace
+
+// A skinny product that ends a branch of a pre-norm block and starts the next norm
+// (src/models/transformer.py:47-48, src/layers/rmsnorm.py:11-16), for up to 64 tokens:
+//   h[m, :] += x[m, :] @ w^T            (float32, in place)
+//   xw[m, :] = bfloat16(h[m, :] * next_weight)
+//   ss[m, j] = block j's share of sum(h[m, :]^2),   j < n_partials = ceil(n / 128) * splits.
+// The product that follows takes xw and `ss` (gk_gemm_bf16_tc_scaled).
+GK_EXPORT int gk_gemm_bf16_tc_residual(const void* w, int n, int k, const void* x, int n_tokens, long long ldx, float* h,
+                                       const void* next_weight, int next_weight_dtype, void* xw, float* ss, int n_partials,
+                                       int bn, int splits, int* error_flag, void* stream) {
+    GemmParams p = {};
+    CUtensorMap ma, mb;
+    int status = skinny_params(p, ma, mb, w, n, k, x, n_tokens, ldx, bn, splits, error_flag, "gemm_tc_residual");
+    if (status) return status;
+    GK_REQUIRE(h && next_weight && xw && ss && GK_VALID_DTYPE(next_weight_dtype), "gemm_tc_residual: bad outputs or norm weight");
+    GK_REQUIRE(((uintptr_t)h & 15) == 0 && ((uintptr_t)xw & 15) == 0, "gemm_tc_residual: h and xw must be 16-byte aligned");
+    dim3 grid((n + BM - 1) / BM, 1, splits);
+    GK_REQUIRE(n_partials == (int)grid.x * splits, "gemm_tc_residual: %d shares expected, got room for %d", (int)grid.x * splits,
+               n_partials);
+    p.stride_b = n;
+    p.out_dtype = GK_BF16;
+    p.epilogue = EPI_STORE;
+    p.residual.h = h;
+    p.residual.weight = next_weight;
+    p.residual.weight_bf16 = next_weight_dtype == GK_BF16;
+    p.residual.xw = (__nv_bfloat16*)xw;
+    p.residual.ss = ss;
+    p.residual.n_partials = n_partials;
+    return launch_skinny<MODE_RESIDUAL>(bn, ma, mb, p, grid, (cudaStream_t)stream);
+}
+
+// The product after gk_gemm_bf16_tc_residual:  OUT[m, :] = (xw[m, :] @ w^T) * rsqrt(sum_j ss[m, j] / k + eps),
+// which is RMSNorm(h) @ w^T up to the rounding of xw.  `w` is [n, k] bfloat16 (rows alternate gate, up with
+// the SwiGLU epilogue, and OUT is [n_tokens, n / 2]); OUT is bfloat16.
+GK_EXPORT int gk_gemm_bf16_tc_scaled(const void* w, int n, int k, const void* xw, int n_tokens, long long ldx, const float* ss,
+                                     int n_partials, float eps, void* out, int swiglu, int bn, int splits, int* error_flag,
+                                     void* stream) {
+    GemmParams p = {};
+    CUtensorMap ma, mb;
+    int status = skinny_params(p, ma, mb, w, n, k, xw, n_tokens, ldx, bn, splits, error_flag, "gemm_tc_scaled");
+    if (status) return status;
+    GK_REQUIRE(ss && n_partials > 0 && eps > 0.f && out, "gemm_tc_scaled: bad scale inputs");
+    GK_REQUIRE(!swiglu || n % 2 == 0, "gemm_tc_scaled: the SwiGLU epilogue needs an even number of weight rows");
+    p.out = out;
+    p.stride_b = swiglu ? n / 2 : n;
+    p.out_dtype = GK_BF16;
+    p.epilogue = swiglu ? EPI_SWIGLU_A : EPI_STORE;
+    p.scale.ss = ss;
+    p.scale.n_partials = n_partials;
+    p.scale.eps = eps;
+    p.scale.inv_size = 1.0f / (float)k;
+    dim3 grid((n + BM - 1) / BM, 1, splits);
+    return launch_skinny<MODE_SCALED>(bn, ma, mb, p, grid, (cudaStream_t)stream);
 }

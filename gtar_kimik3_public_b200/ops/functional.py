@@ -422,6 +422,76 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
     return out
 
 
+def _skinny_bn(m: int) -> int:
+    return min(16 if m <= 16 else 32 if m <= 32 else 64, SKINNY_BN_MAX)
+
+
+@dataclass
+class Prescaled:
+    """Rows that still lack their RMSNorm's division: ``xw = h * weight`` in bfloat16 and, per row, shares
+    of ``sum(h^2)``.  ``gemm_tc_scaled`` multiplies a product of ``xw`` by ``rsqrt(sum(shares) / width + eps)``;
+    ``materialize()`` gives the normalised rows themselves."""
+
+    xw: torch.Tensor      # [m, width] bfloat16
+    shares: torch.Tensor  # [m, n_shares] float32
+    eps: float
+
+    def materialize(self) -> torch.Tensor:
+        inv = torch.rsqrt(self.shares.sum(dim=1, keepdim=True) / self.xw.shape[1] + self.eps)
+        return (self.xw.float() * inv).to(self.xw.dtype)
+
+
+def gemm_tc_residual(x: torch.Tensor, weight: torch.Tensor, h: torch.Tensor, next_norm_weight: torch.Tensor, eps: float,
+                     splits: int | None = None) -> Prescaled:
+    """``h += x @ weight.T`` (in place, float32) for up to 64 tokens, and the first half of the RMSNorm that
+    follows: returns ``h * next_norm_weight`` in bfloat16 with every row's shares of ``sum(h^2)``."""
+    require_device(x.device)
+    _check(x, "x", torch.bfloat16, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    _check(h, "h", torch.float32, 2)
+    _check(next_norm_weight, "next_norm_weight", dims=1)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or tuple(h.shape) != (m, n) or next_norm_weight.shape[0] != n:
+        raise KernelError(f"x {tuple(x.shape)}, weight {tuple(weight.shape)}, h {tuple(h.shape)} and norm weight "
+                          f"{tuple(next_norm_weight.shape)} do not fit together")
+    if m > SKINNY_M:
+        raise KernelError(f"the product with the residual epilogue takes up to {SKINNY_M} tokens, got {m}")
+    if splits is None:
+        splits = split_k_for(m, n, k)
+    n_shares = -(-n // 128) * splits
+    xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    shares = torch.empty((m, n_shares), dtype=torch.float32, device=x.device)
+    call("gk_gemm_bf16_tc_residual", ptr(weight), n, k, ptr(x), m, k, ptr(h), ptr(next_norm_weight),
+         dtype_code(next_norm_weight.dtype), ptr(xw), ptr(shares), n_shares, _skinny_bn(m), int(splits),
+         ptr(error_flag(x.device)), stream_ptr())
+    return Prescaled(xw, shares, float(eps))
+
+
+def gemm_tc_scaled(pre: Prescaled, weight: torch.Tensor, swiglu: bool = False, splits: int | None = None) -> torch.Tensor:
+    """``RMSNorm(h) @ weight.T`` from the two halves ``gemm_tc_residual`` left (bfloat16 out; ``silu(gate) * up``
+    with ``swiglu``): the product of ``xw``, its rows multiplied by ``rsqrt(mean(h^2) + eps)`` where it is written."""
+    xw, shares = pre.xw, pre.shares
+    require_device(xw.device)
+    _check(xw, "xw", torch.bfloat16, 2)
+    _check(shares, "shares", torch.float32, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    m, k = xw.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or shares.shape[0] != m:
+        raise KernelError(f"xw {tuple(xw.shape)}, shares {tuple(shares.shape)} and weight {tuple(weight.shape)} do not fit together")
+    if m > SKINNY_M:
+        raise KernelError(f"the row-scaled product takes up to {SKINNY_M} tokens, got {m}")
+    if swiglu and n % 2:
+        raise KernelError("the SwiGLU epilogue needs an even number of weight rows")
+    if splits is None:
+        splits = split_k_for(m, n, k)
+    out = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=xw.device)
+    call("gk_gemm_bf16_tc_scaled", ptr(weight), n, k, ptr(xw), m, k, ptr(shares), shares.shape[1], float(pre.eps), ptr(out),
+         int(swiglu), _skinny_bn(m), int(splits), ptr(error_flag(xw.device)), stream_ptr())
+    return out
+
+
 def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_count: int = 148) -> int:
     """How many blocks share a sequence's pages in decode attention: enough that about two blocks
     per SM are busy, never more than the longest sequence has pages."""

@@ -46,8 +46,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     """``x [M, K] @ weight[N, K].T -> [M, N]`` in ``out_dtype`` (default: ``x.dtype``).
 
     ``swiglu``: ``weight`` holds gate and up rows alternately and the result is ``silu(gate) * up``
-    of width ``N / 2``.
+    of width ``N / 2``.  ``x`` may be a ``Prescaled`` (rows of an RMSNorm before their division): the
+    division is then done where the product is written.
     """
+    if isinstance(x, F.Prescaled):
+        if weight.dtype == torch.bfloat16 and out_dtype in (None, torch.bfloat16) and weight.data_ptr() % 16 == 0:
+            return F.gemm_tc_scaled(x, weight, swiglu=swiglu)
+        x = x.materialize()
     require_device(x.device)
     out_dtype = out_dtype or x.dtype
     if weight.dtype == torch.float32:

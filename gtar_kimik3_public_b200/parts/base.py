@@ -104,6 +104,28 @@ class PendingNorm:
         return self.h if self.h_new is None else self.h_new
 
 
+@dataclass
+class DeferredProjection:
+    """A branch output that has not been computed yet: ``x @ weight.T``, the last projection of a mixer or
+    feed-forward.  A part returns it only when asked to (``forward(..., defer=True)``, which a block passes to
+    parts that declare ``can_defer_output``); a norm that declares ``takes_deferred`` may then do the product,
+    the add into the residual stream and the start of its own work in one kernel.  ``materialize()`` is the
+    plain product."""
+
+    x: torch.Tensor
+    weight: torch.Tensor
+
+    def materialize(self) -> torch.Tensor:
+        from ..ops.linear import linear
+
+        return linear(self.x, self.weight)
+
+
+def resolve(branch):
+    """The branch output as a tensor, whatever form it came in."""
+    return branch.materialize() if isinstance(branch, DeferredProjection) else branch
+
+
 class Part:
     """Common face of every part."""
 
@@ -120,9 +142,15 @@ class Part:
 
 
 class Norm(Part):
+    takes_deferred = False  # forward() takes a DeferredProjection as ``delta`` and understands ``prescaled_ok``
+
     def forward(self, h: torch.Tensor, delta: torch.Tensor | None, out_dtype: torch.dtype,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
-        """Adds ``delta`` into the 32-bit stream ``h`` (in place) and returns the normalised rows."""
+        """Adds ``delta`` into the 32-bit stream ``h`` (in place) and returns the normalised rows.
+
+        A norm with ``takes_deferred`` has one more parameter, ``prescaled_ok``: with it the caller says that
+        the consumer of the result ``accepts_prescaled``, and the norm may return an
+        ``ops.functional.Prescaled`` (rows still to be divided by their root mean square) instead."""
         raise NotImplementedError
 
 
@@ -133,6 +161,8 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     accepts_pending_norm = False  # forward() can take a PendingNorm in place of the normalised activations
+    accepts_prescaled = False     # forward() can take an ops.functional.Prescaled in place of the activations
+    can_defer_output = False      # forward(..., defer=True) may return a DeferredProjection
 
     def cache_request(self) -> KVRequest | StateRequest | None:
         return None
@@ -144,6 +174,8 @@ class Mixer(Part):
 
 class FeedForward(Part):
     accepts_pending_norm = False
+    accepts_prescaled = False
+    can_defer_output = False
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
@@ -153,6 +185,7 @@ class Block(Part):
     """Arrangement of the parts of one layer around the residual stream."""
 
     mixer: Mixer
+    takes_deferred = False  # ``pending`` may be a DeferredProjection (else the model computes it first)
 
     def forward(self, h: torch.Tensor, pending: torch.Tensor | None, ctx: StepContext,
                 cache: Any) -> tuple[torch.Tensor, torch.Tensor | None]:

@@ -9,7 +9,7 @@ import torch
 
 from ..ops import functional as F
 from ..ops.linear import linear, linear_after_norm
-from .base import FeedForward, PendingNorm, StepContext, TensorSpec, register_part
+from .base import DeferredProjection, FeedForward, PendingNorm, StepContext, TensorSpec, register_part
 
 
 class SwiGLUFeedForward(FeedForward):
@@ -37,11 +37,16 @@ class SwiGLUFeedForward(FeedForward):
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    accepts_prescaled = True
+    can_defer_output = True
+
+    def forward(self, x, ctx: StepContext, defer: bool = False):
         if isinstance(x, PendingNorm):
             act = linear_after_norm(x, self.w_gate_up, swiglu=True)
         else:
-            act = linear(x, self.w_gate_up, swiglu=True)
+            act = linear(x, self.w_gate_up, swiglu=True)  # x: activations or Prescaled
+        if defer and ctx.n_tokens <= F.SKINNY_M:
+            return DeferredProjection(act, self.w_down)
         return linear(act, self.w_down)
 
 

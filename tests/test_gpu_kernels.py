@@ -586,3 +586,57 @@ def test_gemm_tc_normed_equals_norm_then_product(m, n, k, swiglu, with_delta, we
         g, u = y[:, 0::2], y[:, 1::2]
         y = g * torch.sigmoid(g) * u
     assert (got.double().cpu() - y).abs().max().item() <= 2.0**-6 * y.abs().max().item() + 2e-3
+
+
+# ------------------------------------------------------------------ residual epilogue + row-scaled product
+@pytest.mark.parametrize("m,n,k,splits,weight_dtype", [
+    (8, 1024, 2048, None, torch.float32), (8, 1024, 3072, 8, torch.float32), (1, 1024, 2048, 4, torch.bfloat16),
+    (5, 1000, 512, 2, torch.float32), (16, 1002, 200, 1, torch.float32), (33, 264, 1024, 4, torch.bfloat16),
+    (64, 1024, 3072, None, torch.float32), (20, 72, 64, 1, torch.float32)])
+def test_gemm_tc_residual_adds_and_prepares_the_next_norm(m, n, k, splits, weight_dtype):
+    eps = 1e-6
+    h = rand(m, n, seed=1, scale=2.0).float()
+    x = rand(m, k, seed=2).to(torch.bfloat16)
+    w = rand(n, k, seed=4, scale=k**-0.5).to(torch.bfloat16)
+    nw = (1 + 0.1 * rand(n, seed=3)).to(weight_dtype)
+    hd = h.to(DEV)
+    pre = F().gemm_tc_residual(x.to(DEV), w.to(DEV), hd, nw.to(DEV), eps, splits=splits)
+    F().check_kernel_errors()
+    want_h = h.double() + x.double() @ w.double().T
+    assert (hd.double().cpu() - want_h).abs().max().item() < 1e-4 * max(1.0, want_h.abs().max().item())
+    # the shares add up to the rows' sums of squares; xw is the stream times the weight
+    ss = pre.shares.double().sum(dim=1).cpu()
+    assert torch.allclose(ss, (want_h**2).sum(dim=1), rtol=1e-5)
+    assert (pre.xw.double().cpu() - want_h * nw.double()).abs().max().item() <= 2.0**-8 * (want_h * nw.double()).abs().max().item() + 1e-6
+    normed = plain.rms_norm(want_h, nw.double(), eps)
+    assert (pre.materialize().double().cpu() - normed).abs().max().item() <= 2.0**-7 * normed.abs().max().item()
+
+
+@pytest.mark.parametrize("m,hidden,k,n2,swiglu,splits", [
+    (8, 1024, 2048, 4096, False, None), (8, 1024, 3072, 6144, True, None), (1, 1024, 2048, 6144, True, 4),
+    (13, 200, 320, 136, False, 1), (40, 264, 512, 1000, True, 2), (64, 1024, 1024, 512, False, 8)])
+def test_gemm_tc_scaled_after_residual_equals_norm_then_product(m, hidden, k, n2, swiglu, splits):
+    eps = 1e-5
+    h = rand(m, hidden, seed=1, scale=2.0).float()
+    x = rand(m, k, seed=2).to(torch.bfloat16)
+    w1 = rand(hidden, k, seed=4, scale=k**-0.5).to(torch.bfloat16)
+    nw = (1 + 0.1 * rand(hidden, seed=3)).float()
+    w2 = rand(n2, hidden, seed=5, scale=hidden**-0.5).to(torch.bfloat16)
+    hd = h.to(DEV)
+    pre = F().gemm_tc_residual(x.to(DEV), w1.to(DEV), hd, nw.to(DEV), eps)
+    got = F().gemm_tc_scaled(pre, w2.to(DEV), swiglu=swiglu, splits=splits)
+    F().check_kernel_errors()
+    # the three-kernel path on the same inputs
+    h2 = h.to(DEV)
+    branch = F().gemm_tc(x.to(DEV), w1.to(DEV), splits=F().split_k_for(m, hidden, k))
+    xn = F().add_rmsnorm(h2, branch, nw.to(DEV), eps, torch.bfloat16)
+    want = F().gemm_tc(xn, w2.to(DEV), swiglu=swiglu)
+    scale = want.float().abs().max().item()
+    assert (got.float() - want.float()).abs().max().item() <= 2.0**-6 * scale + 1e-3
+    # and the plain formulas
+    total = h.double() + x.double() @ w1.double().T
+    y = plain.rms_norm(total, nw.double(), eps) @ w2.double().T
+    if swiglu:
+        g, u = y[:, 0::2], y[:, 1::2]
+        y = g * torch.sigmoid(g) * u
+    assert (got.double().cpu() - y).abs().max().item() <= 2.0**-6 * y.abs().max().item() + 2e-3
