@@ -376,8 +376,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               __nv_bfloat16* __restrict__ out, int n_splits) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const size_t row = blockIdx.x;  // seq * n_q + head
     const float* ml = part_ml + row * n_splits * 2;
     float mm = -INFINITY;

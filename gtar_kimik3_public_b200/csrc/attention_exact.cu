@@ -61,8 +61,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_exact_kernel(
     const int* __restrict__ block_table, int n_tokens, int n_q, int n_kv, int head_dim, int max_pages, int page_size,
     float scale, int window) {
     extern __shared__ float q_smem[];  // WARPS * head_dim
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * WARPS + warp;
     if (wid >= (long long)n_tokens * n_q) return;  // whole warp leaves together; no block-wide sync below

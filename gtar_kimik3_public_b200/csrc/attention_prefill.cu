@@ -35,8 +35,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(
     int n_kv, int max_pages, float sl2, int window) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     PrefillSmem<D>& sm = *reinterpret_cast<PrefillSmem<D>*>(smem_raw);
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int seq = blockIdx.z, hk = blockIdx.y;
     const int group = n_q / n_kv;
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;

@@ -37,12 +37,14 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 extern int g_gk_pdl;  // set through gk_set_pdl(): launch kernels with programmatic stream serialization
+void gk_prepare_kernel(const void* kernel);  // once per kernel: its preferred L1 / shared-memory split
 
 // Launches `kernel` on `stream`, with the programmatic-dependent-launch attribute when it is switched
 // on, and as thread-block clusters of `cluster` blocks when that is more than one block.
 template <typename... KArgs, typename... Args>
 inline cudaError_t gk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                      dim3 cluster, Args... args) {
+    gk_prepare_kernel(reinterpret_cast<const void*>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

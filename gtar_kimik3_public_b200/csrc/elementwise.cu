@@ -12,6 +12,7 @@
 template <typename TT>
 __global__ void embed_rows_kernel(const TT* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                                   int hidden) {
+    pdl_launch_dependents();  // the next kernel may take its place on the SMs and fetch what does not depend on this one
     pdl_wait();
     const int t = blockIdx.x;
     const TT* row = table + (size_t)ids[t] * hidden;
@@ -95,6 +96,7 @@ template <typename TD, typename TW, typename TO, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const TW* __restrict__ w,
                                    TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();  // the next kernel may take its place on the SMs and fetch what does not depend on this one
     pdl_wait();
     const int src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* hrow = h + (size_t)src * hidden;
@@ -125,7 +127,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
         }
     }
     ss = block_sum(ss, scratch);
-    pdl_launch_dependents();
     const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
     if (VEC == 4) {
         for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
@@ -184,6 +185,7 @@ GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, const
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, long long total,
                               int interleaved) {
+    pdl_launch_dependents();  // the next kernel may take its place on the SMs and fetch what does not depend on this one
     pdl_wait();
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
@@ -231,6 +233,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, const TW* _
                                           T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                           int n_tokens, int n_q, int n_kv, int head_dim, int max_pages, int page_size,
                                           float eps, int use_norm) {
+    pdl_launch_dependents();  // the next kernel may take its place on the SMs and fetch what does not depend on this one
     pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);

@@ -20,8 +20,8 @@ __global__ void __launch_bounds__(THREADS) gemm_f32_kernel(const TA* __restrict_
                                                            long long ldw, long long ldc) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int ty = tid / (BN / TN), tx = tid % (BN / TN);

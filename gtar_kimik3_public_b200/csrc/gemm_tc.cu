@@ -58,41 +58,6 @@ struct QkvEpilogue {
     __nv_bfloat16* v_pages;
 };
 
-// The B operand of a skinny product made inside the kernel from the residual stream: x = RMSNorm(h + delta)
-// (src/layers/rmsnorm.py:11-16, src/models/transformer.py:47-48), for up to 16 tokens.  Every block reads
-// the tokens' whole rows (a few tens of kilobytes from L2) to get the row's mean square, normalises the
-// K range it works on straight into shared memory in the MMA's layout, and the blocks of the first tile
-// write h + delta back (to `h_out`, another buffer than `h`: other blocks still read `h`).
-struct NormInput {
-    const float* h;                 // [rows_b][k]; null = B comes through TMA as usual
-    const __nv_bfloat16* delta;     // [rows_b][k] or null
-    const void* weight;             // norm weight [k]
-    int weight_bf16;
-    float eps;
-    float* h_out;                   // [rows_b][k]
-};
-
-// The residual add and the first half of the next RMSNorm done where a skinny product (A = weights) is
-// written (src/models/transformer.py:47-48, src/layers/rmsnorm.py:11-16):  h += OUT (32-bit, in place),
-// xw = bfloat16(h * weight) and, per token, this block's share of sum(h^2) in `ss[token][partial]`.  The next
-// product reads xw and multiplies its own output rows by rsqrt(sum(ss) / size + eps) (RowScale).
-struct ResidualOutput {
-    float* h;                       // [rows_b][rows_a]
-    const void* weight;             // the next norm's weight [rows_a]
-    int weight_bf16;
-    __nv_bfloat16* xw;              // [rows_b][rows_a]
-    float* ss;                      // [rows_b][n_partials], n_partials = tiles along A * splits
-    int n_partials;
-};
-
-struct RowScale {
-    const float* ss;                // [rows_b][n_partials]
-    int n_partials;
-    float eps, inv_size;            // 1 / (width of the normalised rows)
-};
-
-enum Mode : int { MODE_PLAIN = 0, MODE_NORMED = 1, MODE_RESIDUAL = 2, MODE_SCALED = 3 };
-
 struct GemmParams {
     int rows_a, rows_b, k_blocks;      // k_blocks = ceil(K / BK)
     int k_blocks_per_split;
@@ -106,10 +71,6 @@ struct GemmParams {
                                        // be fetched before that kernel has finished
     int* error_flag;
     QkvEpilogue qkv;                   // read when epilogue == EPI_QKV
-    NormInput norm;                    // MODE_NORMED (BN = 16 only)
-    ResidualOutput residual;           // MODE_RESIDUAL
-    RowScale scale;                    // MODE_SCALED
-    int k_total;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -184,10 +145,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-__device__ __forceinline__ float weight_at(const void* w, int is_bf16, int i) {
-    return is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]) : reinterpret_cast<const float*>(w)[i];
 }
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
@@ -274,11 +231,11 @@ template <int BN, int STAGES>
 struct alignas(1024) GemmSmem {
     __nv_bfloat16 a[STAGES][BM * BK];
     __nv_bfloat16 b[STAGES][BN * BK];
-    uint64_t full[STAGES], empty[STAGES], acc_ready, b_ready;
+    uint64_t full[STAGES], empty[STAGES], acc_ready;
     uint32_t tmem_base;
 };
 
-template <int BN, int STAGES, int MODE>
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                              const __grid_constant__ CUtensorMap map_b,
                                                              const GemmParams p) {
@@ -287,7 +244,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     GemmSmem<BN, STAGES>& sm =
         *reinterpret_cast<GemmSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;  // a power of two >= 32 (BN is 16, 32, 64, 128 or 256)
-    constexpr bool NORMED = MODE == MODE_NORMED;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
     const int kb_begin = split * p.k_blocks_per_split;
@@ -300,7 +256,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             mbar_init(&sm.empty[s], 1);
         }
         mbar_init(&sm.acc_ready, 1);
-        if (NORMED) mbar_init(&sm.b_ready, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         pdl_launch_dependents();
     }
@@ -313,12 +268,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_acc = sm.tmem_base;
-    constexpr bool b_normed = NORMED;  // B is made here from the residual stream; TMA brings A only
-    // the normalised B tiles of this block's K range, one [BN rows][128 bytes] tile per k-block, after the stages
-    __nv_bfloat16* b_tiles = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(&sm) + sizeof(GemmSmem<BN, STAGES>));
-    // the same place in the other modes: per-token scales (MODE_SCALED), shares of the sums of squares (MODE_RESIDUAL)
-    float* extra = reinterpret_cast<float*>(b_tiles);
-    const uint32_t STAGE_BYTES = (b_normed ? BM : BM + BN) * BK * sizeof(__nv_bfloat16);
+    constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * sizeof(__nv_bfloat16);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -332,13 +282,13 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 mbar_expect_tx(&sm.full[i], STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
                 if (p.a_static) tma_load_2d(sm.a[i], &map_a, k, tile_a * BM, &sm.full[i]);
-                if (p.b_static && !b_normed) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
+                if (p.b_static) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
             }
             pdl_wait();
             for (int i = 0; i < pre; ++i) {
                 const int k = (kb_begin + i) * BK;
                 if (!p.a_static) tma_load_2d(sm.a[i], &map_a, k, tile_a * BM, &sm.full[i]);
-                if (!p.b_static && !b_normed) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
+                if (!p.b_static) tma_load_2d(sm.b[i], &map_b, k, tile_b * BN, &sm.full[i]);
             }
             issued = pre;
             for (int i = pre; i < n_kb && ok; ++i) {
@@ -348,7 +298,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 mbar_expect_tx(&sm.full[s], STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
                 tma_load_2d(sm.a[s], &map_a, k, tile_a * BM, &sm.full[s]);
-                if (!b_normed) tma_load_2d(sm.b[s], &map_b, k, tile_b * BN, &sm.full[s]);
+                tma_load_2d(sm.b[s], &map_b, k, tile_b * BN, &sm.full[s]);
                 issued = i + 1;
             }
             if (!ok) {
@@ -362,14 +312,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             // ---- MMA issuer
             const uint32_t idesc = umma_idesc(BM, BN);
             bool ok = true;
-            if (b_normed && n_kb > 0) ok = mbar_wait(&sm.b_ready, 0);  // the epilogue warps have made the B tiles
-            for (int i = 0; i < n_kb && ok; ++i) {
+            for (int i = 0; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 ok = mbar_wait(&sm.full[s], (i / STAGES) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(sm.a[s]);
-                const uint32_t b_addr = b_normed ? smem_u32(b_tiles + (size_t)i * BN * BK) : smem_u32(sm.b[s]);
+                const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k) {
                     const uint64_t da = umma_desc(a_addr + k * UMMA_K * 2), db = umma_desc(b_addr + k * UMMA_K * 2);
@@ -385,124 +333,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         const int quarter = warp & 3;
         const int row_a = tile_a * BM + quarter * 32 + lane;
         bool ok = true;
-        if constexpr (NORMED) {
-            // x = RMSNorm(h + delta) for this block's K range, straight into the MMA's shared-memory layout.
-            // Eight threads a token: first the whole row's sum of squares, then the range.
-            pdl_wait();
-            // `tpr` threads a token (a power of two, at most a warp), so that all 128 threads are busy for
-            // 4 to 16 tokens; a thread's loads are issued eight chunks of four at a time
-            const int e = (warp - 2) * 32 + lane;
-            const int rows_pad = p.rows_b <= 4 ? 4 : p.rows_b <= 8 ? 8 : 16;
-            const int tpr = 128 / rows_pad;           // 32, 16 or 8
-            const int m = e / tpr, part = e % tpr;
-            const int K = p.k_total;
-            const bool row_ok = m < p.rows_b;
-            const float* hrow = p.norm.h + (size_t)m * K;
-            const __nv_bfloat16* drow = p.norm.delta ? p.norm.delta + (size_t)m * K : nullptr;
-            auto load_sum = [&](int c, float (&v)[4]) {  // h + delta at columns c .. c+3
-                const float4 hv = *reinterpret_cast<const float4*>(hrow + c);
-                v[0] = hv.x; v[1] = hv.y; v[2] = hv.z; v[3] = hv.w;
-                if (drow) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(drow + c);
-                    const float2 d0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                    const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-                    v[0] += d0.x; v[1] += d0.y; v[2] += d1.x; v[3] += d1.y;
-                }
-            };
-            float ss = 0.f;
-            if (row_ok) {
-                const int step = tpr * 4;
-                for (int c0 = part * 4; c0 < K; c0 += 8 * step) {
-                    float v[8][4];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int c = c0 + u * step;
-                        if (c < K) load_sum(c, v[u]);
-                        else v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0.f;
-                    }
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) ss += v[u][0] * v[u][0] + v[u][1] * v[u][1] + v[u][2] * v[u][2] + v[u][3] * v[u][3];
-                }
-            }
-            for (int o = 1; o < tpr; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            const float inv = 1.0f / sqrtf(ss / (float)K + p.norm.eps);
-            const int k_lo = kb_begin * BK, k_hi = min(kb_end * BK, K);
-            const bool write_h = tile_a == 0 && tile_b == 0 && p.norm.h_out != nullptr;
-            if (m < BN) {
-                // the block's own K range, again eight chunks at a time (the values are in L1 from the pass
-                // above): all loads of a batch are issued before the first is used
-                const int step = tpr * 4;
-                for (int c0 = k_lo + part * 4; c0 < kb_end * BK; c0 += 8 * step) {
-                    float v[8][4], wv[8][4];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int c = c0 + u * step;
-                        if (row_ok && c < k_hi) {
-                            load_sum(c, v[u]);
-                            if (p.norm.weight_bf16) {
-                                const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.norm.weight) + c);
-                                const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                                const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-                                wv[u][0] = w0.x; wv[u][1] = w0.y; wv[u][2] = w1.x; wv[u][3] = w1.y;
-                            } else {
-                                const float4 w4 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm.weight) + c);
-                                wv[u][0] = w4.x; wv[u][1] = w4.y; wv[u][2] = w4.z; wv[u][3] = w4.w;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) v[u][j] = wv[u][j] = 0.f;
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int c = c0 + u * step;
-                        if (c >= kb_end * BK) continue;
-                        if (write_h && row_ok && c < k_hi)
-                            *reinterpret_cast<float4*>(p.norm.h_out + (size_t)m * K + c) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
-                        float x[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) x[j] = (v[u][j] * inv) * wv[u][j];
-                        // element (row m, column col) of k-block kb: 128-byte rows, 16-byte chunks XOR-swizzled with the row
-                        const int kb = (c - k_lo) / BK, col = (c - k_lo) % BK;
-                        __nv_bfloat16* tile = b_tiles + (size_t)kb * BN * BK;
-                        __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
-                        uint2 packed;
-                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
-                        packed.y = *reinterpret_cast<uint32_t*>(&hi);
-                        *reinterpret_cast<uint2*>(tile + m * BK + (((col >> 3) ^ (m & 7)) << 3) + (col & 7)) = packed;
-                    }
-                }
-            }
-            // rows of the tile beyond the padded token count (tokens <= 8 leave rows 8..15, <= 4 rows 4..15)
-            for (int idx = e; idx < (BN - rows_pad) * (kb_end - kb_begin) * (BK / 8); idx += 128) {
-                const int chunks_per_kb = (BN - rows_pad) * (BK / 8);
-                const int kb = idx / chunks_per_kb, rest = idx % chunks_per_kb;
-                const int r = rows_pad + rest / (BK / 8), ch = rest % (BK / 8);
-                *reinterpret_cast<uint4*>(b_tiles + (size_t)kb * BN * BK + r * BK + (ch << 3)) = make_uint4(0, 0, 0, 0);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.b_ready)) : "memory");
-        }
-        if constexpr (MODE == MODE_SCALED) {
-            // 1 / rms of each token of this tile from the shares the product before left, while the MMAs run:
-            // 128 / BN threads a token, each adding every (128 / BN)-th share, then a tree over those threads
-            pdl_wait();
-            constexpr int TPT = BN >= 128 ? 1 : 128 / BN;
-            const int e = (warp - 2) * 32 + lane;
-            for (int t0 = 0; t0 < BN; t0 += 128 / TPT) {
-                const int local = t0 + e / TPT, part = e % TPT, token = tile_b * BN + local;
-                float sum = 0.f;
-                if (local < BN && token < p.rows_b) {
-                    const float* shares = p.scale.ss + (size_t)token * p.scale.n_partials;
-#pragma unroll 4
-                    for (int j = part; j < p.scale.n_partials; j += TPT) sum += shares[j];
-                }
-#pragma unroll
-                for (int o = 1; o < TPT; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                if (part == 0 && local < BN) extra[local] = 1.0f / sqrtf(sum * p.scale.inv_size + p.scale.eps);
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
         if (n_kb > 0) {
             ok = mbar_wait(&sm.acc_ready, 0);
             if (!ok && lane == 0) atomicExch(p.error_flag, 3);
@@ -522,38 +352,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;
                 }
-                if constexpr (MODE == MODE_SCALED) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] *= extra[c0 + i];
-                }
-                if constexpr (MODE == MODE_RESIDUAL) {
-                    // h += v; xw = h * weight; the warp's 32 rows of every token's square go to extra[col][quarter]
-                    const float w = a_ok ? weight_at(p.residual.weight, p.residual.weight_bf16, row_a) : 0.f;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int rb = tile_b * BN + c0 + i;
-                        float sq = 0.f;
-                        if (a_ok && rb < p.rows_b) {
-                            const size_t at = (size_t)rb * p.rows_a + row_a;
-                            const float hn = p.residual.h[at] + v[i];
-                            p.residual.h[at] = hn;
-                            p.residual.xw[at] = __float2bfloat16(hn * w);
-                            sq = hn * hn;
-                        }
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                        if (lane == 0) extra[(c0 + i) * 4 + quarter] = sq;
-                    }
-                } else {
-                    write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
-                }
-            }
-            if constexpr (MODE == MODE_RESIDUAL) {
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                const int e = (warp - 2) * 32 + lane, token = tile_b * BN + e;
-                if (e < BN && token < p.rows_b)
-                    p.residual.ss[(size_t)token * p.residual.n_partials + tile_a] =
-                        ((extra[e * 4] + extra[e * 4 + 1]) + extra[e * 4 + 2]) + extra[e * 4 + 3];
+                write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
             }
         } else {
             // split-K: this block's partial tile goes to its own shared memory, [column][row] float32,
@@ -571,31 +370,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) stage[(c0 + i) * BM + row_in_tile] = v[i];
-            }
-        }
-    }
-    // MODE_RESIDUAL: the stream and norm weights of the first two groups this thread will finish, fetched while
-    // the cluster gathers (they do not depend on the partial tiles)
-    float4 pre_h[2], pre_w[2];
-    if constexpr (MODE == MODE_RESIDUAL) {
-        if (gridDim.z > 1 && warp >= 2 && (p.rows_a & 3) == 0) {
-            const int rows_per = BM / (int)gridDim.z, quads = rows_per / 4, count = quads * BN;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int idx = (warp - 2) * 32 + lane + u * 128;
-                const int row_a = tile_a * BM + (int)blockIdx.z * rows_per + 4 * (idx % quads), rb = tile_b * BN + idx / quads;
-                pre_h[u] = pre_w[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (idx < count && row_a + 3 < p.rows_a && rb < p.rows_b) {
-                    pre_h[u] = *reinterpret_cast<const float4*>(p.residual.h + (size_t)rb * p.rows_a + row_a);
-                    if (p.residual.weight_bf16) {
-                        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.residual.weight) + row_a);
-                        const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                        const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-                        pre_w[u] = make_float4(w0.x, w0.y, w1.x, w1.y);
-                    } else {
-                        pre_w[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.residual.weight) + row_a);
-                    }
-                }
             }
         }
     }
@@ -658,57 +432,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     const int idx = base + u * 128;
                     if (idx >= count) continue;
                     const int row_a = tile_a * BM + rank * rows_per + 4 * (idx % quads), rb = tile_b * BN + idx / quads;
-                    if (row_a >= p.rows_a || rb >= p.rows_b) {
-                        if constexpr (MODE == MODE_RESIDUAL) extra[(idx / quads) * 16 + idx % quads] = 0.f;
-                        continue;
-                    }
-                    float4 v = add_up(part[u]);
-                    if constexpr (MODE == MODE_SCALED) {
-                        const float inv = extra[idx / quads];
-                        v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
-                    }
+                    if (row_a >= p.rows_a || rb >= p.rows_b) continue;
+                    const float4 v = add_up(part[u]);
                     const float vs[4] = {v.x, v.y, v.z, v.w};
-                    if constexpr (MODE == MODE_RESIDUAL) {
-                        // h += v over four consecutive features of one token; the quad's squares go to extra[col][quad]
-                        const size_t at = (size_t)rb * p.rows_a + row_a;
-                        float hn[4], sq = 0.f;
-                        if (row_a + 3 < p.rows_a && (p.rows_a & 3) == 0) {
-                            float4 h4, w4;
-                            if (base == e) {
-                                h4 = pre_h[u];
-                                w4 = pre_w[u];
-                            } else {
-                                h4 = *reinterpret_cast<const float4*>(p.residual.h + at);
-                                w4 = make_float4(weight_at(p.residual.weight, p.residual.weight_bf16, row_a),
-                                                 weight_at(p.residual.weight, p.residual.weight_bf16, row_a + 1),
-                                                 weight_at(p.residual.weight, p.residual.weight_bf16, row_a + 2),
-                                                 weight_at(p.residual.weight, p.residual.weight_bf16, row_a + 3));
-                            }
-                            hn[0] = h4.x + vs[0]; hn[1] = h4.y + vs[1]; hn[2] = h4.z + vs[2]; hn[3] = h4.w + vs[3];
-                            *reinterpret_cast<float4*>(p.residual.h + at) = make_float4(hn[0], hn[1], hn[2], hn[3]);
-                            const float w[4] = {w4.x, w4.y, w4.z, w4.w};
-                            __nv_bfloat162 lo = __floats2bfloat162_rn(hn[0] * w[0], hn[1] * w[1]);
-                            __nv_bfloat162 hi = __floats2bfloat162_rn(hn[2] * w[2], hn[3] * w[3]);
-                            uint2 packed;
-                            packed.x = *reinterpret_cast<uint32_t*>(&lo);
-                            packed.y = *reinterpret_cast<uint32_t*>(&hi);
-                            *reinterpret_cast<uint2*>(p.residual.xw + at) = packed;
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) sq += hn[i] * hn[i];
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                if (row_a + i < p.rows_a) {
-                                    hn[i] = p.residual.h[at + i] + vs[i];
-                                    p.residual.h[at + i] = hn[i];
-                                    p.residual.xw[at + i] =
-                                        __float2bfloat16(hn[i] * weight_at(p.residual.weight, p.residual.weight_bf16, row_a + i));
-                                    sq += hn[i] * hn[i];
-                                }
-                            }
-                        }
-                        extra[(idx / quads) * 16 + idx % quads] = sq;
-                    } else if (swiglu) {
+                    if (swiglu) {
 #pragma unroll
                         for (int i = 0; i < 4; i += 2) {
                             if (row_a + i + 1 < p.rows_a) {
@@ -737,19 +464,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                             }
                         }
                     }
-                }
-            }
-        }
-        if constexpr (MODE == MODE_RESIDUAL) {
-            if (warp >= 2) {
-                // this block's share of each token's sum of squares: its quads in order
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                const int e = (warp - 2) * 32 + lane, token = tile_b * BN + e;
-                const int quads = BM / (int)gridDim.z / 4;
-                if (e < BN && token < p.rows_b) {
-                    float sum = 0.f;
-                    for (int q = 0; q < quads; ++q) sum += extra[e * 16 + q];
-                    p.residual.ss[(size_t)token * p.residual.n_partials + tile_a * gridDim.z + blockIdx.z] = sum;
                 }
             }
         }
@@ -1019,22 +733,17 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, 
     return GK_OK;
 }
 
-constexpr int NORMED_MAX_K_BLOCKS = 16;  // k-blocks of normalised B a block keeps in shared memory
-
-template <int BN, int STAGES, int MODE = MODE_PLAIN>
+template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     static_assert(STAGES * (BM + BN) * BK * 2 >= BM * BN * 4, "the partial tile must fit in the pipeline stages");
-    const size_t base = sizeof(GemmSmem<BN, STAGES>) + 1024;
-    constexpr size_t EXTRA = MODE == MODE_RESIDUAL ? (size_t)BN * 16 * 4 : MODE == MODE_SCALED ? (size_t)BN * 4 : 0;
-    const size_t smem_max = base + (MODE == MODE_NORMED ? (size_t)NORMED_MAX_K_BLOCKS * BN * BK * 2 : EXTRA);
-    const size_t smem = base + (MODE == MODE_NORMED ? (size_t)p.k_blocks_per_split * BN * BK * 2 : EXTRA);
+    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
         configured = true;
     }
-    gk_launch_cluster(gemm_tc_kernel<BN, STAGES, MODE>, grid, dim3(THREADS), smem, stream, dim3(1, 1, grid.z), ma, mb, p);
+    gk_launch_cluster(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, dim3(1, 1, grid.z), ma, mb, p);
     GK_CHECK_LAUNCH("gemm_tc");
     return GK_OK;
 }
@@ -1085,8 +794,7 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     if (status) return status;
     status = make_map(&mb, b, rows_b, k, ldb, bn);
     if (status) return status;
-    GemmParams p = {};
-    p.k_total = k;
+    GemmParams p;
     p.rows_a = rows_a;
     p.rows_b = rows_b;
     p.k_blocks = (k + BK - 1) / BK;
@@ -1172,143 +880,4 @@ GK_EXPORT int gk_gemm_bf16_tc_qkv(const void* x, int n_tokens, const void* w_qkv
     p.qkv.k_pages = (__nv_bfloat16*)k_pages;
     p.qkv.v_pages = (__nv_bfloat16*)v_pages;
     return launch_persistent<256, 4>(ma, mb, p, (cudaStream_t)stream);
-}
-
-// A skinny product whose activations come straight from the residual stream:
-//   OUT[m, :] = RMSNorm(h[m] + delta[m]; norm_weight, eps) @ w^T     for m < n_tokens <= 16,
-// and h_out = h + delta.  `w` is [n, k] bfloat16 (rows alternate gate, up with the SwiGLU epilogue);
-// `delta` may be null; `h_out` must not alias `h`.  The K range of a tile may be shared by 1, 2, 4 or 8
-// blocks (one cluster), each keeping at most 16 k-blocks of 64 of the normalised activations.
-GK_EXPORT int gk_gemm_bf16_tc_normed(const void* w, int n, int k, const float* h, const void* delta, int n_tokens,
-                                     const void* norm_weight, int norm_weight_dtype, float eps, float* h_out, void* out,
-                                     int swiglu, int splits, int* error_flag, void* stream) {
-    GK_REQUIRE(n > 0 && k > 0 && k % 8 == 0, "gemm_tc_normed: bad sizes n=%d k=%d", n, k);
-    GK_REQUIRE(n_tokens > 0 && n_tokens <= 16, "gemm_tc_normed: takes 1 to 16 tokens, got %d", n_tokens);
-    GK_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "gemm_tc_normed: splits must be 1, 2, 4 or 8");
-    GK_REQUIRE(GK_VALID_DTYPE(norm_weight_dtype) && norm_weight && h && h_out && h != h_out, "gemm_tc_normed: bad norm inputs");
-    GK_REQUIRE(eps > 0.f, "gemm_tc_normed: eps must be positive");
-    GK_REQUIRE(((uintptr_t)w & 15) == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)delta & 15) == 0 &&
-                   ((uintptr_t)h_out & 15) == 0 && ((uintptr_t)out & 15) == 0, "gemm_tc_normed: pointers must be 16-byte aligned");
-    GK_REQUIRE(!swiglu || n % 2 == 0, "gemm_tc_normed: the SwiGLU epilogue needs an even number of weight rows");
-    GK_REQUIRE(error_flag != nullptr, "gemm_tc_normed: error_flag is required");
-    CUtensorMap ma;
-    int status = make_map(&ma, w, n, k, k, BM);
-    if (status) return status;
-    GemmParams p = {};
-    p.k_total = k;
-    p.rows_a = n;
-    p.rows_b = n_tokens;
-    p.k_blocks = (k + BK - 1) / BK;
-    p.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
-    GK_REQUIRE(p.k_blocks_per_split <= NORMED_MAX_K_BLOCKS,
-               "gemm_tc_normed: %d k-blocks a block exceed the %d it can keep; use more splits", p.k_blocks_per_split,
-               NORMED_MAX_K_BLOCKS);
-    p.out = out;
-    p.stride_a = 1;
-    p.stride_b = swiglu ? n / 2 : n;
-    p.out_dtype = GK_BF16;
-    p.epilogue = swiglu ? EPI_SWIGLU_A : EPI_STORE;
-    p.a_static = 1;
-    p.b_static = 0;
-    p.error_flag = error_flag;
-    p.norm.h = h;
-    p.norm.delta = (const __nv_bfloat16*)delta;
-    p.norm.weight = norm_weight;
-    p.norm.weight_bf16 = norm_weight_dtype == GK_BF16;
-    p.norm.eps = eps;
-    p.norm.h_out = h_out;
-    dim3 grid((n + BM - 1) / BM, 1, splits);
-    return launch<16, 5, MODE_NORMED>(ma, ma, p, grid, (cudaStream_t)stream);
-}
-
-namespace {
-
-template <int MODE>
-int launch_skinny(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t s) {
-    switch (bn) {
-        case 16: return launch<16, 5, MODE>(ma, mb, p, grid, s);
-        case 32: return launch<32, 9, MODE>(ma, mb, p, grid, s);
-        case 64: return launch<64, 8, MODE>(ma, mb, p, grid, s);
-        default: return gk_fail(GK_BAD_ARGUMENT, "gemm_tc: the token tile of a skinny product is 16, 32 or 64, got %d", bn);
-    }
-}
-
-int skinny_params(GemmParams& p, CUtensorMap& ma, CUtensorMap& mb, const void* w, int n, int k, const void* x, int n_tokens,
-                  long long ldx, int bn, int splits, int* error_flag, const char* who) {
-    GK_REQUIRE(n > 0 && k > 0 && k % 8 == 0 && ldx % 8 == 0, "%s: bad sizes n=%d k=%d ldx=%lld (k and ldx in steps of 8)", who, n, k, ldx);
-    GK_REQUIRE(n_tokens > 0 && n_tokens <= 64, "%s: takes 1 to 64 tokens, got %d", who, n_tokens);
-    GK_REQUIRE((bn == 16 || bn == 32 || bn == 64) && n_tokens <= bn, "%s: token tile %d does not hold %d tokens", who, bn, n_tokens);
-    GK_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "%s: splits must be 1, 2, 4 or 8, got %d", who, splits);
-    GK_REQUIRE(((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0, "%s: operands must be 16-byte aligned", who);
-    GK_REQUIRE(error_flag != nullptr, "%s: error_flag is required", who);
-    int status = make_map(&ma, w, n, k, k, BM);
-    if (status) return status;
-    status = make_map(&mb, x, n_tokens, k, ldx, bn);
-    if (status) return status;
-    p.k_total = k;
-    p.rows_a = n;
-    p.rows_b = n_tokens;
-    p.k_blocks = (k + BK - 1) / BK;
-    p.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
-    p.stride_a = 1;
-    p.a_static = 1;
-    p.b_static = 0;
-    p.error_flag = error_flag;
-    return GK_OK;
-}
-
-}  // namespace
-
-// A skinny product that ends a branch of a pre-norm block and starts the next norm
-// (src/models/transformer.py:47-48, src/layers/rmsnorm.py:11-16), for up to 64 tokens:
-//   h[m, :] += x[m, :] @ w^T            (float32, in place)
-//   xw[m, :] = bfloat16(h[m, :] * next_weight)
-//   ss[m, j] = block j's share of sum(h[m, :]^2),   j < n_partials = ceil(n / 128) * splits.
-// The product that follows takes xw and `ss` (gk_gemm_bf16_tc_scaled).
-GK_EXPORT int gk_gemm_bf16_tc_residual(const void* w, int n, int k, const void* x, int n_tokens, long long ldx, float* h,
-                                       const void* next_weight, int next_weight_dtype, void* xw, float* ss, int n_partials,
-                                       int bn, int splits, int* error_flag, void* stream) {
-    GemmParams p = {};
-    CUtensorMap ma, mb;
-    int status = skinny_params(p, ma, mb, w, n, k, x, n_tokens, ldx, bn, splits, error_flag, "gemm_tc_residual");
-    if (status) return status;
-    GK_REQUIRE(h && next_weight && xw && ss && GK_VALID_DTYPE(next_weight_dtype), "gemm_tc_residual: bad outputs or norm weight");
-    GK_REQUIRE(((uintptr_t)h & 15) == 0 && ((uintptr_t)xw & 15) == 0, "gemm_tc_residual: h and xw must be 16-byte aligned");
-    dim3 grid((n + BM - 1) / BM, 1, splits);
-    GK_REQUIRE(n_partials == (int)grid.x * splits, "gemm_tc_residual: %d shares expected, got room for %d", (int)grid.x * splits,
-               n_partials);
-    p.stride_b = n;
-    p.out_dtype = GK_BF16;
-    p.epilogue = EPI_STORE;
-    p.residual.h = h;
-    p.residual.weight = next_weight;
-    p.residual.weight_bf16 = next_weight_dtype == GK_BF16;
-    p.residual.xw = (__nv_bfloat16*)xw;
-    p.residual.ss = ss;
-    p.residual.n_partials = n_partials;
-    return launch_skinny<MODE_RESIDUAL>(bn, ma, mb, p, grid, (cudaStream_t)stream);
-}
-
-// The product after gk_gemm_bf16_tc_residual:  OUT[m, :] = (xw[m, :] @ w^T) * rsqrt(sum_j ss[m, j] / k + eps),
-// which is RMSNorm(h) @ w^T up to the rounding of xw.  `w` is [n, k] bfloat16 (rows alternate gate, up with
-// the SwiGLU epilogue, and OUT is [n_tokens, n / 2]); OUT is bfloat16.
-GK_EXPORT int gk_gemm_bf16_tc_scaled(const void* w, int n, int k, const void* xw, int n_tokens, long long ldx, const float* ss,
-                                     int n_partials, float eps, void* out, int swiglu, int bn, int splits, int* error_flag,
-                                     void* stream) {
-    GemmParams p = {};
-    CUtensorMap ma, mb;
-    int status = skinny_params(p, ma, mb, w, n, k, xw, n_tokens, ldx, bn, splits, error_flag, "gemm_tc_scaled");
-    if (status) return status;
-    GK_REQUIRE(ss && n_partials > 0 && eps > 0.f && out, "gemm_tc_scaled: bad scale inputs");
-    GK_REQUIRE(!swiglu || n % 2 == 0, "gemm_tc_scaled: the SwiGLU epilogue needs an even number of weight rows");
-    p.out = out;
-    p.stride_b = swiglu ? n / 2 : n;
-    p.out_dtype = GK_BF16;
-    p.epilogue = swiglu ? EPI_SWIGLU_A : EPI_STORE;
-    p.scale.ss = ss;
-    p.scale.n_partials = n_partials;
-    p.scale.eps = eps;
-    p.scale.inv_size = 1.0f / (float)k;
-    dim3 grid((n + BM - 1) / BM, 1, splits);
-    return launch_skinny<MODE_SCALED>(bn, ma, mb, p, grid, (cudaStream_t)stream);
 }

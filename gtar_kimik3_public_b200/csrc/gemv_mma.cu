@@ -1,0 +1,260 @@
+// Product of a few tokens with a weight matrix,  OUT[t, n] = sum_k X[t, k] * W[n, k]  for up to 16 tokens
+// (every projection of a decode step: src/layers/attention.py:62-65, src/layers/swiglu.py:9-14), built for
+// latency rather than arithmetic: with so few tokens the time goes to getting the weights in, not to the
+// multiplications.
+//
+// The weight rows are taken in groups of eight.  There is one block of eight warps per SM at most, and it is
+// small in registers and threads, so that the blocks of the next kernel in the stream are resident beside it
+// (programmatic dependent launch).  A block takes every grid-th group; within a group its warps take the
+// 32-wide k-chunks in turn.  A thread is responsible for 16 bytes of one weight row per chunk, and it asks for
+// all of them, for all its chunks, with cp.async into shared memory before the kernel has waited for the
+// kernel in front of it: weights do not depend on that kernel, so by the time that kernel has finished the
+// block's whole share of the matrix is in shared memory or on its way.  Once it has waited, the block copies
+// the tokens' activations into shared memory (one trip to L2 for all of them), and per chunk a thread takes
+// its own 16 bytes of weights back out of shared memory (nobody else reads them) and the matching 16 bytes of
+// a token's activations, and two mma.sync.m16n8k16 (tokens on the 16 rows, the eight weight rows on the 8
+// columns, 32-bit accumulation) finish the chunk.  Which k goes to which slot of the instruction
+// is the same for both operands and otherwise of no consequence for a sum, so both are read as plain
+// contiguous 16-byte pieces.  The warps' partial sums of a group meet in shared memory (in the place of a
+// weight piece the thread has used up) and are added in the order of the warps by one warp, which writes the
+// group's result.
+//
+// Output stages: plain store (bfloat16 or float32) and SwiGLU over row pairs (gate and up rows interleaved,
+// even = gate, odd = up: both of a channel end up in the same thread).
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int ROWS = 8;          // weight rows of a group = the N of the MMA
+constexpr int CHUNK = 32;        // k of one 16-byte piece per thread and row: 4 threads x 8 elements
+constexpr int MAX_GROUPS = 8;    // groups a block can take (its partial sums stay in shared memory)
+constexpr int ROUND_ITEMS = 24;  // chunks per thread whose weights fit in shared memory at once (96 KB a block)
+
+struct GemvParams {
+    const __nv_bfloat16* w;   // [n][ldw]
+    const __nv_bfloat16* x;   // [tokens][ldx]
+    void* out;                // [tokens][n] (or [tokens][n / 2] with SwiGLU)
+    int n, k, tokens;
+    long long ldw, ldx, ldo;
+    int out_f32, swiglu;
+};
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 16 bytes from global to shared memory without passing through registers; `bytes` = 0 writes zeros
+__device__ __forceinline__ void copy16_async(void* smem_dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+
+// TWO_ROWS: more than eight tokens (the MMA's rows 8..15 are tokens 8..15, else zero).
+// Shared memory: [item of the round][thread] 16-byte weight pieces; the tokens' activations, a row every
+// `x_stride` bytes (the rows of two tokens a quarter-warp reads together lie in different banks); and, when the
+// weights come in more than one round, [group of the block][thread] partial sums (with one round a thread
+// leaves its partial sum where the group's first weight piece was).
+template <bool TWO_ROWS>
+__global__ void __launch_bounds__(THREADS, TWO_ROWS ? 3 : 4) gemv_mma_kernel(const GemvParams p, int round_items, int x_stride) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int X_ROWS = TWO_ROWS ? 16 : 8;
+    uint4* pieces = reinterpret_cast<uint4*>(smem);
+    unsigned char* xs = smem + (size_t)round_items * THREADS * 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = lane >> 2, piece = lane & 3;  // group: weight row (B) and token (A); piece: 8 of the chunk's 32 k
+    if (threadIdx.x == 0) pdl_launch_dependents();
+
+    const int n_groups = (p.n + ROWS - 1) / ROWS;
+    const int my_groups = ((int)blockIdx.x < n_groups) ? (n_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int n_chunks = (p.k + CHUNK - 1) / CHUNK;
+    const int cpw = (n_chunks + WARPS - 1) / WARPS;  // chunks of a group per warp: warp, warp + 8, ...
+    const int n_items = my_groups * cpw;             // item i: group i / cpw of the block, chunk warp + (i % cpw) * 8
+    const bool one_round = n_items <= round_items;
+    float4* partial = one_round ? reinterpret_cast<float4*>(pieces) : reinterpret_cast<float4*>(xs + (size_t)X_ROWS * x_stride);
+    const int partial_step = one_round ? cpw * THREADS : THREADS;  // from one group's partial sums to the next group's
+
+    // The weights of items first .. first + round_items - 1 (item = group of the block * cpw + chunk of the warp),
+    // on their way to shared memory.
+    auto request = [&](int first) {
+        int g = first / cpw, j = first % cpw;
+        uint4* dst = pieces + threadIdx.x;
+        for (int item = first; item < first + round_items && item < n_items; ++item) {
+            const int row = ((int)blockIdx.x + g * (int)gridDim.x) * ROWS + group;
+            const int k = (warp + j * WARPS) * CHUNK + piece * 8;
+            const bool in = row < p.n && k < p.k;
+            copy16_async(dst, in ? p.w + (size_t)row * p.ldw + k : p.w, in ? 16 : 0);
+            dst += THREADS;
+            if (++j == cpw) {
+                j = 0;
+                ++g;
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    request(0);  // before the kernel in front has finished
+    pdl_wait();
+    // the activations of all tokens; zeros for the rows that are no token and from K up to the end of the last
+    // chunk any warp looks at
+    const int x_pieces = cpw * WARPS * 4;  // 16-byte pieces of a row
+    for (int i = threadIdx.x; i < X_ROWS * x_pieces; i += THREADS) {
+        const int row = i / x_pieces, at = (i % x_pieces) * 8;
+        const bool in = row < p.tokens && at < p.k;
+        copy16_async(xs + (size_t)row * x_stride + at * 2, in ? p.x + (size_t)row * p.ldx + at : p.x, in ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    const unsigned char* xa_first = xs + (size_t)group * x_stride + (warp * CHUNK + piece * 8) * 2;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    // one chunk: the thread's weights, the token's activations (zeros beyond K, see above), two MMAs into two
+    // accumulators that do not wait for one another
+    auto chunk = [&](const uint4 wv, const unsigned char* xa_at, float (&acc0)[4], float (&acc1)[4]) {
+        const uint4 xa = *reinterpret_cast<const uint4*>(xa_at);
+        const uint4 xb = TWO_ROWS ? *reinterpret_cast<const uint4*>(xa_at + 8 * (size_t)x_stride) : zero;
+        mma_bf16(acc0, xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
+        mma_bf16(acc1, xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
+    };
+    const uint4* wp = pieces + threadIdx.x;
+    if (one_round) {
+        for (int g = 0; g < my_groups; ++g) {
+            float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+            const unsigned char* xa_at = xa_first;
+#pragma unroll 4
+            for (int j = 0; j < cpw; ++j) {
+                chunk(*wp, xa_at, acc0, acc1);
+                wp += THREADS;
+                xa_at += WARPS * CHUNK * 2;
+            }
+            partial[(size_t)g * partial_step + threadIdx.x] =
+                make_float4(acc0[0] + acc1[0], acc0[1] + acc1[1], acc0[2] + acc1[2], acc0[3] + acc1[3]);
+        }
+    } else {
+        // a block's share exceeds shared memory: the weights come in rounds
+        int in_round = 0;
+        for (int g = 0; g < my_groups; ++g) {
+            float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+            const unsigned char* xa_at = xa_first;
+            for (int j = 0; j < cpw; ++j) {
+                if (in_round == round_items) {
+                    request(g * cpw + j);
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    wp = pieces + threadIdx.x;
+                    in_round = 0;
+                }
+                chunk(*wp, xa_at, acc0, acc1);
+                wp += THREADS;
+                xa_at += WARPS * CHUNK * 2;
+                ++in_round;
+            }
+            partial[(size_t)g * partial_step + threadIdx.x] =
+                make_float4(acc0[0] + acc1[0], acc0[1] + acc1[1], acc0[2] + acc1[2], acc0[3] + acc1[3]);
+        }
+    }
+    __syncthreads();
+    if (warp >= my_groups) return;
+    // warp g of the block finishes the block's g-th group: the warps' sums in their order
+    const float4* slots = partial + (size_t)warp * partial_step + lane;
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+        const float4 v = slots[w * 32];
+        sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+    }
+    // sum[0], sum[1]: token `group`, weight rows col and col + 1;  sum[2], sum[3]: token group + 8
+    const int col = ((int)blockIdx.x + warp * (int)gridDim.x) * ROWS + 2 * piece;
+#pragma unroll
+    for (int half = 0; half < (TWO_ROWS ? 2 : 1); ++half) {
+        const int token = group + 8 * half;
+        if (token >= p.tokens) continue;
+        const float a = sum[2 * half], b = sum[2 * half + 1];
+        if (p.swiglu) {
+            if (col + 1 < p.n)
+                reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)token * p.ldo + (col >> 1)] = __float2bfloat16(silu(a) * b);
+        } else if (p.out_f32) {
+            float* o = reinterpret_cast<float*>(p.out) + (size_t)token * p.ldo + col;
+            if (col < p.n) o[0] = a;
+            if (col + 1 < p.n) o[1] = b;
+        } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)token * p.ldo + col;
+            if (col + 1 < p.n && ((p.ldo & 1) == 0)) {
+                *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(a, b);
+            } else {
+                if (col < p.n) o[0] = __float2bfloat16(a);
+                if (col + 1 < p.n) o[1] = __float2bfloat16(b);
+            }
+        }
+    }
+}
+
+}  // namespace
+
+namespace {
+
+int launch_gemv(GemvParams& p, cudaStream_t stream) {
+    static int n_sms = 0;
+    constexpr size_t SMEM_MAX = 200 * 1024;
+    if (n_sms == 0) {
+        int device = 0;
+        cudaError_t err = cudaGetDevice(&device);
+        if (err == cudaSuccess) err = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (err != cudaSuccess) { n_sms = 0; return gk_fail(GK_CUDA_ERROR, "gemv: %s", cudaGetErrorString(err)); }
+    }
+    const int n_groups = (p.n + ROWS - 1) / ROWS;
+    GK_REQUIRE(n_groups <= n_sms * MAX_GROUPS, "gemv: takes up to %d weight rows on this device, got %d", n_sms * MAX_GROUPS * ROWS, p.n);
+    dim3 grid(n_groups < n_sms ? n_groups : n_sms);
+    const int groups_per_block = (n_groups + grid.x - 1) / grid.x;
+    const int n_chunks = (p.k + CHUNK - 1) / CHUNK;
+    const int items = groups_per_block * ((n_chunks + WARPS - 1) / WARPS);
+    const int round_items = items < ROUND_ITEMS ? items : ROUND_ITEMS;
+    // rows of the activations in shared memory: the same number of chunks for every warp, and an odd multiple
+    // of 64 bytes apart
+    int x_stride = ((n_chunks + WARPS - 1) / WARPS) * WARPS * CHUNK * 2;
+    if (x_stride % 128 == 0) x_stride += 64;
+    const int x_rows = p.tokens > 8 ? 16 : 8;
+    const size_t smem = (size_t)round_items * THREADS * 16 + (size_t)x_rows * x_stride +
+                        (items > round_items ? (size_t)groups_per_block * THREADS * 16 : 0);
+    GK_REQUIRE(smem <= SMEM_MAX, "gemv: k = %d with %d tokens needs %zu bytes of shared memory, more than %zu", p.k, p.tokens, smem, SMEM_MAX);
+    if (p.tokens > 8) gk_launch(gemv_mma_kernel<true>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
+    else gk_launch(gemv_mma_kernel<false>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
+    GK_CHECK_LAUNCH("gemv");
+    return GK_OK;
+}
+
+}  // namespace
+
+// OUT[t, :] = x[t, :] @ w^T for 1 to 16 tokens and up to 64 weight rows per SM; `w` [n, k] and `x` [tokens, k]
+// bfloat16 with rows in steps of 8 elements (16 bytes); OUT bfloat16 or float32, [tokens, n], or with `swiglu`
+// [tokens, n / 2] bfloat16 = silu(even rows) * odd rows.
+GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const void* x, int tokens, long long ldx, void* out,
+                           int out_dtype, int swiglu, void* stream) {
+    GK_REQUIRE(n > 0 && k > 0 && tokens > 0 && tokens <= 16, "gemv: takes 1 to 16 tokens and positive sizes; got %d tokens, n=%d k=%d",
+               tokens, n, k);
+    GK_REQUIRE(k % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0, "gemv: k and the row strides must be multiples of 8 elements; got k=%d ldw=%lld ldx=%lld",
+               k, ldw, ldx);
+    GK_REQUIRE(((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 3) == 0, "gemv: operands must be 16-byte aligned");
+    GK_REQUIRE(GK_VALID_DTYPE(out_dtype), "gemv: bad output dtype");
+    GK_REQUIRE(!swiglu || (n % 2 == 0 && out_dtype == GK_BF16), "gemv: the SwiGLU output stage needs an even number of rows and writes bfloat16");
+    GemvParams p = {};
+    p.w = (const __nv_bfloat16*)w;
+    p.x = (const __nv_bfloat16*)x;
+    p.out = out;
+    p.n = n;
+    p.k = k;
+    p.tokens = tokens;
+    p.ldw = ldw;
+    p.ldx = ldx;
+    p.ldo = swiglu ? n / 2 : n;
+    p.out_f32 = out_dtype == GK_F32;
+    p.swiglu = swiglu;
+    return launch_gemv(p, (cudaStream_t)stream);
+}

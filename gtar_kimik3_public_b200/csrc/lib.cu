@@ -3,6 +3,9 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <mutex>
+#include <unordered_set>
+
 #include "common.cuh"
 
 static thread_local char g_last_error[512] = "";
@@ -16,6 +19,18 @@ int gk_fail(int status, const char* fmt, ...) {
 }
 
 int g_gk_pdl = 0;
+
+// Every kernel asks for the largest shared-memory share of the SM's L1/shared-memory array.  An SM changes
+// that split only when it is idle, so kernels that prefer different splits cannot be resident side by side,
+// and a kernel launched early (programmatic dependent launch) would wait for the SMs to drain instead of
+// fetching its weights next to the kernel in front of it.
+void gk_prepare_kernel(const void* kernel) {
+    static std::mutex lock;
+    static std::unordered_set<const void*> seen;
+    std::lock_guard<std::mutex> guard(lock);
+    if (seen.insert(kernel).second)
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
 
 // Switches programmatic dependent launch on (1) or off (0) for every later kernel launch of the
 // library; returns the previous setting.

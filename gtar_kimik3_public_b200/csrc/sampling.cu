@@ -79,8 +79,8 @@ __device__ __forceinline__ Best block_best(Best mine, Best* scratch) {
 __global__ void argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
                               int* __restrict__ out, Best* __restrict__ partial) {
     __shared__ Best scratch[32];
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int parts = gridDim.x, part = blockIdx.x, r = blockIdx.y;
     const float* row = logits + (size_t)r * row_stride;
     const int per = (vocab + parts - 1) / parts;
@@ -95,8 +95,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, long long row_st
 }
 
 __global__ void argmax_merge_kernel(const Best* __restrict__ partial, int parts, int* __restrict__ out) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     Best mine{-INFINITY, 0x7fffffff};
     for (int p = threadIdx.x; p < parts; p += 32) mine = better(mine, partial[(size_t)r * parts + p]);
@@ -116,8 +116,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long row_st
     __shared__ Best scratch[32];
     __shared__ unsigned int hist[256];
     __shared__ unsigned int sel_prefix, sel_remaining;
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * row_stride;
 
     unsigned int threshold_key = 0;  // keep everything

@@ -14,7 +14,7 @@ from dataclasses import dataclass, field
 import torch
 
 from ..cache import Cache, CacheLayout
-from ..parts.base import Block, Norm, Part, PositionEncoding, StepContext, TensorSpec, resolve
+from ..parts.base import Block, Norm, Part, PositionEncoding, StepContext, TensorSpec
 from ..parts.embedding import OutputHead, TokenEmbedding
 
 
@@ -104,12 +104,9 @@ class Model:
         pending = None
         for index, entry in enumerate(plan.run_list):
             ctx.extras["cache_read_only"] = cache.is_shared(index)
-            layer = plan.layers[entry.layer]
-            if not getattr(layer, "takes_deferred", False):
-                pending = resolve(pending)
-            h, pending = layer.forward(h, pending, ctx, cache.view(index))
+            h, pending = plan.layers[entry.layer].forward(h, pending, ctx, cache.view(index))
         if ctx.want_rows.numel() == 0:
             # nothing asked for: still fold the last branch into the stream so the step is whole
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        z = plan.final_norm.forward(h, resolve(pending), ctx.dtype, rows=ctx.want_rows)
+        z = plan.final_norm.forward(h, pending, ctx.dtype, rows=ctx.want_rows)
         return plan.head.forward(z)

@@ -181,48 +181,6 @@ def qk_norm_rope_write(
     return q_out
 
 
-NORMED_MAX_TOKENS = 16
-
-
-def normed_splits(n: int, k: int) -> int | None:
-    """Split count for a skinny product that normalises its own input, or None if it cannot take the
-    shape (a block keeps at most 16 k-blocks of its K range)."""
-    splits = split_k_for(1, n, k)
-    while -(-(-(-k // 64)) // splits) > 16 and splits < 8:
-        splits *= 2
-    return splits if -(-(-(-k // 64)) // splits) <= 16 else None
-
-
-def gemm_tc_normed(h: torch.Tensor, delta: torch.Tensor | None, norm_weight: torch.Tensor, eps: float,
-                   weight: torch.Tensor, swiglu: bool = False, splits: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
-    """``RMSNorm(h + delta) @ weight.T`` for up to 16 tokens in one kernel: every block normalises the
-    part of the rows it needs itself.  Returns the product (bfloat16; ``silu(gate) * up`` with ``swiglu``)
-    and the new residual stream ``h + delta`` (a new tensor; ``h`` is left as it is)."""
-    require_device(h.device)
-    _check(h, "h", torch.float32, 2)
-    _check(weight, "weight", torch.bfloat16, 2)
-    _check(norm_weight, "norm_weight", dims=1)
-    m, k = h.shape
-    n = weight.shape[0]
-    if weight.shape[1] != k or norm_weight.shape[0] != k:
-        raise KernelError(f"h is {tuple(h.shape)}, weight {tuple(weight.shape)}, norm weight {tuple(norm_weight.shape)}")
-    if delta is not None:
-        _check(delta, "delta", torch.bfloat16, 2)
-        if delta.shape != h.shape:
-            raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
-    if m > NORMED_MAX_TOKENS:
-        raise KernelError(f"the self-normalising product takes up to {NORMED_MAX_TOKENS} tokens, got {m}")
-    if splits is None:
-        splits = normed_splits(n, k)
-        if splits is None:
-            raise KernelError(f"k = {k} is too long for the self-normalising product")
-    out = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=h.device)
-    h_out = torch.empty_like(h)
-    call("gk_gemm_bf16_tc_normed", ptr(weight), n, k, ptr(h), ptr(delta), m, ptr(norm_weight), dtype_code(norm_weight.dtype),
-         float(eps), ptr(h_out), ptr(out), int(swiglu), int(splits), ptr(error_flag(h.device)), stream_ptr())
-    return out, h_out
-
-
 def qkv_fused_ok(x: torch.Tensor, weight: torch.Tensor, head_dim: int, kv: PagedKV) -> bool:
     """Whether the q|k|v projection of this step can do the attention input stage in its epilogue:
     bfloat16, enough tokens for the many-token orientation and its wide tiles, head size 64 or 128."""
@@ -384,6 +342,45 @@ def set_pdl(on: bool) -> bool:
     return bool(library().gk_set_pdl(int(on)))
 
 
+GEMV_MAX_TOKENS = 16
+_sm_counts: dict[int, int] = {}
+
+
+def gemv_max_rows(device: torch.device) -> int:
+    """Most weight rows ``gemv`` takes: one block per SM, each with up to eight groups of eight rows."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index] * 64
+
+
+
+def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x [M, K] @ weight[N, K].T`` for up to 16 tokens: weights go from memory straight into registers and
+    through ``mma.sync`` with 32-bit accumulation; made for the latency of a decode step, where a projection
+    is a few megabytes of weights and next to no arithmetic.  ``swiglu`` as in ``gemm_tc``."""
+    require_device(x.device)
+    _check(x, "x", torch.bfloat16, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"x is {tuple(x.shape)} but weight is {tuple(weight.shape)}")
+    if m > GEMV_MAX_TOKENS:
+        raise KernelError(f"gemv takes up to {GEMV_MAX_TOKENS} tokens, got {m}")
+    if swiglu and n % 2:
+        raise KernelError("the SwiGLU epilogue needs an even number of weight rows")
+    n_out = n // 2 if swiglu else n
+    if out is None:
+        out = torch.empty((m, n_out), dtype=out_dtype, device=x.device)
+    _check(out, "out", out_dtype, 2)
+    if tuple(out.shape) != (m, n_out):
+        raise KernelError(f"out has shape {tuple(out.shape)}, expected {(m, n_out)}")
+    call("gk_gemv_bf16", ptr(weight), n, k, k, ptr(x), m, k, ptr(out), dtype_code(out_dtype), int(swiglu), stream_ptr())
+    return out
+
+
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
             splits: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` in bfloat16 on the tcgen05 tensor cores, float32 accumulation.
@@ -419,76 +416,6 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
         bn = PREFILL_BN if wide else 128 if n >= 128 else 64 if n >= 64 else 32 if n >= 32 else 16
         call("gk_gemm_bf16_tc", ptr(x), m, k, ptr(weight), n, k, k, ptr(out), dtype_code(out_dtype), n_out, 1,
              EPI_SWIGLU_B if swiglu else EPI_STORE, bn, splits, 0, 1, ptr(flag), stream_ptr())
-    return out
-
-
-def _skinny_bn(m: int) -> int:
-    return min(16 if m <= 16 else 32 if m <= 32 else 64, SKINNY_BN_MAX)
-
-
-@dataclass
-class Prescaled:
-    """Rows that still lack their RMSNorm's division: ``xw = h * weight`` in bfloat16 and, per row, shares
-    of ``sum(h^2)``.  ``gemm_tc_scaled`` multiplies a product of ``xw`` by ``rsqrt(sum(shares) / width + eps)``;
-    ``materialize()`` gives the normalised rows themselves."""
-
-    xw: torch.Tensor      # [m, width] bfloat16
-    shares: torch.Tensor  # [m, n_shares] float32
-    eps: float
-
-    def materialize(self) -> torch.Tensor:
-        inv = torch.rsqrt(self.shares.sum(dim=1, keepdim=True) / self.xw.shape[1] + self.eps)
-        return (self.xw.float() * inv).to(self.xw.dtype)
-
-
-def gemm_tc_residual(x: torch.Tensor, weight: torch.Tensor, h: torch.Tensor, next_norm_weight: torch.Tensor, eps: float,
-                     splits: int | None = None) -> Prescaled:
-    """``h += x @ weight.T`` (in place, float32) for up to 64 tokens, and the first half of the RMSNorm that
-    follows: returns ``h * next_norm_weight`` in bfloat16 with every row's shares of ``sum(h^2)``."""
-    require_device(x.device)
-    _check(x, "x", torch.bfloat16, 2)
-    _check(weight, "weight", torch.bfloat16, 2)
-    _check(h, "h", torch.float32, 2)
-    _check(next_norm_weight, "next_norm_weight", dims=1)
-    m, k = x.shape
-    n = weight.shape[0]
-    if weight.shape[1] != k or tuple(h.shape) != (m, n) or next_norm_weight.shape[0] != n:
-        raise KernelError(f"x {tuple(x.shape)}, weight {tuple(weight.shape)}, h {tuple(h.shape)} and norm weight "
-                          f"{tuple(next_norm_weight.shape)} do not fit together")
-    if m > SKINNY_M:
-        raise KernelError(f"the product with the residual epilogue takes up to {SKINNY_M} tokens, got {m}")
-    if splits is None:
-        splits = split_k_for(m, n, k)
-    n_shares = -(-n // 128) * splits
-    xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-    shares = torch.empty((m, n_shares), dtype=torch.float32, device=x.device)
-    call("gk_gemm_bf16_tc_residual", ptr(weight), n, k, ptr(x), m, k, ptr(h), ptr(next_norm_weight),
-         dtype_code(next_norm_weight.dtype), ptr(xw), ptr(shares), n_shares, _skinny_bn(m), int(splits),
-         ptr(error_flag(x.device)), stream_ptr())
-    return Prescaled(xw, shares, float(eps))
-
-
-def gemm_tc_scaled(pre: Prescaled, weight: torch.Tensor, swiglu: bool = False, splits: int | None = None) -> torch.Tensor:
-    """``RMSNorm(h) @ weight.T`` from the two halves ``gemm_tc_residual`` left (bfloat16 out; ``silu(gate) * up``
-    with ``swiglu``): the product of ``xw``, its rows multiplied by ``rsqrt(mean(h^2) + eps)`` where it is written."""
-    xw, shares = pre.xw, pre.shares
-    require_device(xw.device)
-    _check(xw, "xw", torch.bfloat16, 2)
-    _check(shares, "shares", torch.float32, 2)
-    _check(weight, "weight", torch.bfloat16, 2)
-    m, k = xw.shape
-    n = weight.shape[0]
-    if weight.shape[1] != k or shares.shape[0] != m:
-        raise KernelError(f"xw {tuple(xw.shape)}, shares {tuple(shares.shape)} and weight {tuple(weight.shape)} do not fit together")
-    if m > SKINNY_M:
-        raise KernelError(f"the row-scaled product takes up to {SKINNY_M} tokens, got {m}")
-    if swiglu and n % 2:
-        raise KernelError("the SwiGLU epilogue needs an even number of weight rows")
-    if splits is None:
-        splits = split_k_for(m, n, k)
-    out = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=xw.device)
-    call("gk_gemm_bf16_tc_scaled", ptr(weight), n, k, ptr(xw), m, k, ptr(shares), shares.shape[1], float(pre.eps), ptr(out),
-         int(swiglu), _skinny_bn(m), int(splits), ptr(error_flag(xw.device)), stream_ptr())
     return out
 
 

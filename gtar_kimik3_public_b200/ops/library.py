@@ -38,9 +38,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_attention_decode_bf16": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_gemm_bf16_tc": [P, I, L, P, I, L, I, P, I, L, L, I, I, I, I, I, P, P],
     "gk_gemm_bf16_tc_qkv": [P, I, P, I, I, I, I, P, P, I, I, F, P, P, I, I, P, P, P, P, I, I, P, P, P, P, P],
-    "gk_gemm_bf16_tc_normed": [P, I, I, P, P, I, P, I, F, P, P, I, I, P, P],
-    "gk_gemm_bf16_tc_residual": [P, I, I, P, I, L, P, P, I, P, P, I, I, I, P, P],
-    "gk_gemm_bf16_tc_scaled": [P, I, I, P, I, L, P, I, F, P, I, I, I, P, P],
+    "gk_gemv_bf16": [P, I, I, L, P, I, L, P, I, I, P],
     "gk_set_pdl": [I],
     "gk_attention_decode_fused_bf16": [P, P, P, I, I, F, P, P, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_decode_bf16_no_alloc": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],

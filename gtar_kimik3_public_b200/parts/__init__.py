@@ -3,6 +3,6 @@ Importing the package registers the built-in parts."""
 
 from . import attention, block, embedding, mlp, norms, rope  # noqa: F401
 from .base import (  # noqa: F401
-    Block, FeedForward, KVRequest, Mixer, Norm, Part, PendingNorm, PositionEncoding, StateRequest, StepContext, TensorSpec,
+    Block, FeedForward, KVRequest, Mixer, Norm, Part, PositionEncoding, StateRequest, StepContext, TensorSpec,
     build_part, known_parts, register_part,
 )

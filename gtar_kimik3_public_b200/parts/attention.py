@@ -13,13 +13,12 @@ import torch
 
 from ..ops import attention as attention_ops
 from ..ops import functional as F
-from ..ops.linear import linear, linear_after_norm
-from .base import DeferredProjection, KVRequest, Mixer, PendingNorm, PositionEncoding, StepContext, TensorSpec, register_part
+from ..ops.linear import linear
+from .base import KVRequest, Mixer, PositionEncoding, StepContext, TensorSpec, register_part
 
 
 class GQAAttention(Mixer):
     graph_safe = True  # all per-step numbers are read from device memory by the kernels
-    accepts_pending_norm = True  # the q|k|v projection can do the add and the norm of its input itself
 
     def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int, qk_norm_eps: float | None,
                  position: PositionEncoding | None, window: int | None = None):
@@ -63,34 +62,18 @@ class GQAAttention(Mixer):
     def cache_request(self):
         return KVRequest(self.n_kv, self.head_dim, self.window)
 
-    accepts_prescaled = True
-    can_defer_output = True
-
-    def forward(self, x, ctx: StepContext, cache: F.PagedKV, defer: bool = False):
-        o = self._attention(x, ctx, cache)
-        w_o = self.w_o
-        if defer and ctx.n_tokens <= F.SKINNY_M:
-            return DeferredProjection(o, w_o)
-        return linear(o, w_o)
-
-    def _attention(self, x, ctx: StepContext, cache: F.PagedKV) -> torch.Tensor:
-        """The heads' outputs side by side, ``[n_tokens, n_q * head_dim]``, before the output projection."""
+    def forward(self, x, ctx: StepContext, cache: F.PagedKV) -> torch.Tensor:
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.cos, self.position.sin
         write_kv = not ctx.extras.get("cache_read_only", False)
-        if isinstance(x, PendingNorm):
-            if ctx.all_single:  # few tokens: the projection normalises its own input
-                qkv = linear_after_norm(x, self.w_qkv)
-                return self._attend(qkv, ctx, cache, cos, sin, write_kv)
-            x = x.materialize()
-        if not isinstance(x, F.Prescaled) and F.qkv_fused_ok(x, self.w_qkv, self.head_dim, cache):
+        if F.qkv_fused_ok(x, self.w_qkv, self.head_dim, cache):
             # many tokens: norm, rotation and cache write happen where the projection leaves the tensor cores
             q = F.gemm_tc_qkv(x, self.w_qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm,
                               self.qk_norm_eps or 1.0, cos, sin, ctx.tok_pos, ctx.tok_seq, ctx.slots, cache,
                               ctx.max_position, write_kv)
             o = attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
-            return o.view(ctx.n_tokens, self.n_q * self.head_dim)
+            return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
         return self._attend(linear(x, self.w_qkv), ctx, cache, cos, sin, write_kv)
 
     def _attend(self, qkv: torch.Tensor, ctx: StepContext, cache: F.PagedKV, cos, sin, write_kv: bool) -> torch.Tensor:
@@ -101,13 +84,13 @@ class GQAAttention(Mixer):
                 o = F.attention_decode_fused(
                     qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm, self.qk_norm_eps or 1.0, cos, sin,
                     cache, ctx.kv_len, ctx.slots, ctx.max_position, self.scale, self.window or 0, splits, write_kv)
-                return o.view(ctx.n_tokens, self.n_q * self.head_dim)
+                return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
         q = F.qk_norm_rope_write(
             qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm, self.qk_norm_eps or 1.0, cos, sin,
             ctx.tok_pos, ctx.tok_seq, ctx.slots, cache, ctx.max_position, write_kv=write_kv,
         )
         o = attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
-        return o.view(ctx.n_tokens, self.n_q * self.head_dim)
+        return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -82,50 +82,6 @@ class StepContext:
     extras: dict[str, Any] = field(default_factory=dict)
 
 
-@dataclass
-class PendingNorm:
-    """A norm that has not run yet: ``norm(h + delta)``.  A block hands this to a mixer or feed-forward
-    that declares ``accepts_pending_norm`` instead of the normalised activations, so that the part's
-    first projection can do the add and the norm itself.  Whoever consumes it either calls
-    ``materialize()`` (runs the norm kernel; ``h`` is updated in place) or computes the same thing
-    another way and stores the new residual stream in ``h_new``."""
-
-    h: torch.Tensor
-    delta: torch.Tensor | None
-    norm: "Norm"
-    out_dtype: torch.dtype
-    h_new: torch.Tensor | None = None
-
-    def materialize(self) -> torch.Tensor:
-        return self.norm.forward(self.h, self.delta, self.out_dtype)
-
-    def stream(self) -> torch.Tensor:
-        """The residual stream after the add."""
-        return self.h if self.h_new is None else self.h_new
-
-
-@dataclass
-class DeferredProjection:
-    """A branch output that has not been computed yet: ``x @ weight.T``, the last projection of a mixer or
-    feed-forward.  A part returns it only when asked to (``forward(..., defer=True)``, which a block passes to
-    parts that declare ``can_defer_output``); a norm that declares ``takes_deferred`` may then do the product,
-    the add into the residual stream and the start of its own work in one kernel.  ``materialize()`` is the
-    plain product."""
-
-    x: torch.Tensor
-    weight: torch.Tensor
-
-    def materialize(self) -> torch.Tensor:
-        from ..ops.linear import linear
-
-        return linear(self.x, self.weight)
-
-
-def resolve(branch):
-    """The branch output as a tensor, whatever form it came in."""
-    return branch.materialize() if isinstance(branch, DeferredProjection) else branch
-
-
 class Part:
     """Common face of every part."""
 
@@ -142,15 +98,9 @@ class Part:
 
 
 class Norm(Part):
-    takes_deferred = False  # forward() takes a DeferredProjection as ``delta`` and understands ``prescaled_ok``
-
     def forward(self, h: torch.Tensor, delta: torch.Tensor | None, out_dtype: torch.dtype,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
-        """Adds ``delta`` into the 32-bit stream ``h`` (in place) and returns the normalised rows.
-
-        A norm with ``takes_deferred`` has one more parameter, ``prescaled_ok``: with it the caller says that
-        the consumer of the result ``accepts_prescaled``, and the norm may return an
-        ``ops.functional.Prescaled`` (rows still to be divided by their root mean square) instead."""
+        """Adds ``delta`` into the 32-bit stream ``h`` (in place) and returns the normalised rows."""
         raise NotImplementedError
 
 
@@ -160,9 +110,6 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    accepts_pending_norm = False  # forward() can take a PendingNorm in place of the normalised activations
-    accepts_prescaled = False     # forward() can take an ops.functional.Prescaled in place of the activations
-    can_defer_output = False      # forward(..., defer=True) may return a DeferredProjection
 
     def cache_request(self) -> KVRequest | StateRequest | None:
         return None
@@ -173,9 +120,6 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    accepts_pending_norm = False
-    accepts_prescaled = False
-    can_defer_output = False
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
@@ -185,7 +129,6 @@ class Block(Part):
     """Arrangement of the parts of one layer around the residual stream."""
 
     mixer: Mixer
-    takes_deferred = False  # ``pending`` may be a DeferredProjection (else the model computes it first)
 
     def forward(self, h: torch.Tensor, pending: torch.Tensor | None, ctx: StepContext,
                 cache: Any) -> tuple[torch.Tensor, torch.Tensor | None]:

@@ -4,12 +4,10 @@ block hands its last branch output on as ``pending`` instead of adding it itself
 
 from __future__ import annotations
 
-from .base import Block, FeedForward, Mixer, Norm, PendingNorm, StepContext, register_part, resolve
+from .base import Block, FeedForward, Mixer, Norm, StepContext, register_part
 
 
 class PreNormBlock(Block):
-    takes_deferred = True  # ``pending`` may be a DeferredProjection
-
     def __init__(self, input_norm: Norm, mixer: Mixer, post_norm: Norm, feed_forward: FeedForward,
                  names: dict[str, str] | None = None):
         self.input_norm, self.mixer, self.post_norm, self.feed_forward = input_norm, mixer, post_norm, feed_forward
@@ -35,31 +33,10 @@ class PreNormBlock(Block):
         return sum(part.weight_bytes() for _, part in self.children())
 
     def forward(self, h, pending, ctx: StepContext, cache):
-        # a part that can leaves its last projection to the norm after it (of this layer or the next)
-        x = self._normed(self.input_norm, h, pending, ctx, self.mixer)
-        if getattr(self.mixer, "can_defer_output", False) and getattr(self.post_norm, "takes_deferred", False):
-            branch = self.mixer.forward(x, ctx, cache, defer=True)
-        else:
-            branch = self.mixer.forward(x, ctx, cache)
-        h = x.stream() if isinstance(x, PendingNorm) else h
-        x = self._normed(self.post_norm, h, branch, ctx, self.feed_forward)
-        if getattr(self.feed_forward, "can_defer_output", False):
-            out = self.feed_forward.forward(x, ctx, defer=True)
-        else:
-            out = self.feed_forward.forward(x, ctx)
-        h = x.stream() if isinstance(x, PendingNorm) else h
-        return h, out
-
-    @staticmethod
-    def _normed(norm: Norm, h, delta, ctx: StepContext, consumer):
-        """The consumer's input: normalised activations, or, where norm and consumer can, rows that the
-        consumer's first projection still has to divide by their root mean square."""
-        if getattr(norm, "takes_deferred", False):
-            return norm.forward(h, delta, ctx.dtype, prescaled_ok=getattr(consumer, "accepts_prescaled", False))
-        delta = resolve(delta)
-        if getattr(consumer, "accepts_pending_norm", False):
-            return PendingNorm(h, delta, norm, ctx.dtype)
-        return norm.forward(h, delta, ctx.dtype)
+        x = self.input_norm.forward(h, pending, ctx.dtype)
+        branch = self.mixer.forward(x, ctx, cache)
+        x = self.post_norm.forward(h, branch, ctx.dtype)
+        return h, self.feed_forward.forward(x, ctx)
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -8,13 +8,11 @@ from __future__ import annotations
 import torch
 
 from ..ops import functional as F
-from ..ops.linear import linear, linear_after_norm
-from .base import DeferredProjection, FeedForward, PendingNorm, StepContext, TensorSpec, register_part
+from ..ops.linear import linear
+from .base import FeedForward, StepContext, TensorSpec, register_part
 
 
 class SwiGLUFeedForward(FeedForward):
-    accepts_pending_norm = True  # the gate/up projection can do the add and the norm of its input itself
-
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.w_gate_up = self.w_down = None
@@ -37,17 +35,8 @@ class SwiGLUFeedForward(FeedForward):
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
-    accepts_prescaled = True
-    can_defer_output = True
-
-    def forward(self, x, ctx: StepContext, defer: bool = False):
-        if isinstance(x, PendingNorm):
-            act = linear_after_norm(x, self.w_gate_up, swiglu=True)
-        else:
-            act = linear(x, self.w_gate_up, swiglu=True)  # x: activations or Prescaled
-        if defer and ctx.n_tokens <= F.SKINNY_M:
-            return DeferredProjection(act, self.w_down)
-        return linear(act, self.w_down)
+    def forward(self, x, ctx: StepContext) -> torch.Tensor:
+        return linear(linear(x, self.w_gate_up, swiglu=True), self.w_down)
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import functional as F
-from .base import DeferredProjection, Norm, TensorSpec, register_part
+from .base import Norm, TensorSpec, register_part
 
 
 class RMSNorm(Norm):
@@ -24,18 +24,7 @@ class RMSNorm(Norm):
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
-    takes_deferred = True
-
-    def forward(self, h, delta, out_dtype, rows=None, prescaled_ok=False):
-        if isinstance(delta, DeferredProjection):
-            x, w = delta.x, delta.weight
-            if (prescaled_ok and rows is None and out_dtype == torch.bfloat16 and h.dtype == torch.float32
-                    and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= F.SKINNY_M
-                    and x.shape[1] % 8 == 0 and h.shape[1] % 8 == 0):
-                # few tokens: the projection adds into the stream and leaves the rows times this norm's weight;
-                # the division by the root mean square happens where the next product is written
-                return F.gemm_tc_residual(x, w, h, self.weight, self.eps)
-            delta = delta.materialize()
+    def forward(self, h, delta, out_dtype, rows=None):
         return F.add_rmsnorm(h, delta, self.weight, self.eps, out_dtype, rows)
 
 

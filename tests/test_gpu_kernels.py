@@ -558,85 +558,31 @@ def test_gemm_tc_qkv_equals_projection_then_qk_kernel(n_q, n_kv, d, hidden, weig
     assert (q_b.double() - want_q).abs().max() <= 2.0**-7 * want_q.abs().max() + 1e-3
 
 
-# ------------------------------------------------------------------ skinny product that normalises its own input
-@pytest.mark.parametrize("m,n,k,swiglu,with_delta,weight_dtype", [
-    (8, 4096, 1024, False, True, torch.float32), (8, 6144, 1024, True, True, torch.float32), (1, 384, 96, False, False, torch.float32),
-    (16, 1000, 200, False, True, torch.bfloat16), (3, 448, 2560, True, True, torch.float32)])
-def test_gemm_tc_normed_equals_norm_then_product(m, n, k, swiglu, with_delta, weight_dtype):
-    eps = 1e-6
-    h = rand(m, k, seed=1, scale=2.0).float()
-    delta = rand(m, k, seed=2).to(torch.bfloat16) if with_delta else None
-    nw = (1 + 0.1 * rand(k, seed=3)).to(weight_dtype)
-    w = rand(n, k, seed=4, scale=k**-0.5).to(torch.bfloat16)
-    hd = h.to(DEV)
-    got, h_new = F().gemm_tc_normed(hd, None if delta is None else delta.to(DEV), nw.to(DEV), eps, w.to(DEV), swiglu=swiglu)
-    F().check_kernel_errors()
-    assert torch.equal(hd.cpu(), h)  # the input stream is left alone
-    total = h.double() + (0 if delta is None else delta.double())
-    assert (h_new.double().cpu() - total).abs().max() < 1e-6
-    # the two-kernel path on the same inputs
-    h2 = h.to(DEV)
-    x = F().add_rmsnorm(h2, None if delta is None else delta.to(DEV), nw.to(DEV), eps, torch.bfloat16)
-    want = F().gemm_tc(x, w.to(DEV), swiglu=swiglu)
-    scale = want.float().abs().max().item()
-    assert (got.float() - want.float()).abs().max().item() <= 2.0**-7 * scale + 1e-3
-    # and the plain formulas
-    y = plain.rms_norm(total, nw.double(), eps) @ w.double().T
+# ------------------------------------------------------------------ few-token product (weights prefetched into shared memory)
+@pytest.mark.parametrize("m,n,k,swiglu,out_dtype", [
+    (8, 4096, 1024, False, torch.bfloat16), (8, 6144, 1024, True, torch.bfloat16), (1, 1024, 3072, False, torch.bfloat16),
+    (16, 1024, 2048, False, torch.float32), (9, 1000, 200, False, torch.bfloat16), (3, 446, 72, True, torch.bfloat16),
+    (5, 77, 8, False, torch.float32), (12, 9472, 64, False, torch.float32), (2, 7, 4104, False, torch.bfloat16),
+    (16, 6144, 1024, True, torch.bfloat16), (11, 1176, 520, False, torch.bfloat16)])
+def test_gemv_against_plain_product(m, n, k, swiglu, out_dtype):
+    x = rand(m, k, seed=1).to(torch.bfloat16)
+    w = rand(n, k, seed=2, scale=k**-0.5).to(torch.bfloat16)
+    got = F().gemv(x.to(DEV), w.to(DEV), out_dtype, swiglu=swiglu)
+    y = x.double() @ w.double().T
     if swiglu:
         g, u = y[:, 0::2], y[:, 1::2]
         y = g * torch.sigmoid(g) * u
-    assert (got.double().cpu() - y).abs().max().item() <= 2.0**-6 * y.abs().max().item() + 2e-3
+    assert got.dtype == out_dtype and tuple(got.shape) == tuple(y.shape)
+    tol = 2.0**-8 * y.abs().max().item() + 1e-5 if out_dtype == torch.bfloat16 else 1e-5 * max(1.0, y.abs().max().item())
+    assert (got.double().cpu() - y).abs().max().item() <= tol
 
 
-# ------------------------------------------------------------------ residual epilogue + row-scaled product
-@pytest.mark.parametrize("m,n,k,splits,weight_dtype", [
-    (8, 1024, 2048, None, torch.float32), (8, 1024, 3072, 8, torch.float32), (1, 1024, 2048, 4, torch.bfloat16),
-    (5, 1000, 512, 2, torch.float32), (16, 1002, 200, 1, torch.float32), (33, 264, 1024, 4, torch.bfloat16),
-    (64, 1024, 3072, None, torch.float32), (20, 72, 64, 1, torch.float32)])
-def test_gemm_tc_residual_adds_and_prepares_the_next_norm(m, n, k, splits, weight_dtype):
-    eps = 1e-6
-    h = rand(m, n, seed=1, scale=2.0).float()
-    x = rand(m, k, seed=2).to(torch.bfloat16)
-    w = rand(n, k, seed=4, scale=k**-0.5).to(torch.bfloat16)
-    nw = (1 + 0.1 * rand(n, seed=3)).to(weight_dtype)
-    hd = h.to(DEV)
-    pre = F().gemm_tc_residual(x.to(DEV), w.to(DEV), hd, nw.to(DEV), eps, splits=splits)
-    F().check_kernel_errors()
-    want_h = h.double() + x.double() @ w.double().T
-    assert (hd.double().cpu() - want_h).abs().max().item() < 1e-4 * max(1.0, want_h.abs().max().item())
-    # the shares add up to the rows' sums of squares; xw is the stream times the weight
-    ss = pre.shares.double().sum(dim=1).cpu()
-    assert torch.allclose(ss, (want_h**2).sum(dim=1), rtol=1e-5)
-    assert (pre.xw.double().cpu() - want_h * nw.double()).abs().max().item() <= 2.0**-8 * (want_h * nw.double()).abs().max().item() + 1e-6
-    normed = plain.rms_norm(want_h, nw.double(), eps)
-    assert (pre.materialize().double().cpu() - normed).abs().max().item() <= 2.0**-7 * normed.abs().max().item()
-
-
-@pytest.mark.parametrize("m,hidden,k,n2,swiglu,splits", [
-    (8, 1024, 2048, 4096, False, None), (8, 1024, 3072, 6144, True, None), (1, 1024, 2048, 6144, True, 4),
-    (13, 200, 320, 136, False, 1), (40, 264, 512, 1000, True, 2), (64, 1024, 1024, 512, False, 8)])
-def test_gemm_tc_scaled_after_residual_equals_norm_then_product(m, hidden, k, n2, swiglu, splits):
-    eps = 1e-5
-    h = rand(m, hidden, seed=1, scale=2.0).float()
-    x = rand(m, k, seed=2).to(torch.bfloat16)
-    w1 = rand(hidden, k, seed=4, scale=k**-0.5).to(torch.bfloat16)
-    nw = (1 + 0.1 * rand(hidden, seed=3)).float()
-    w2 = rand(n2, hidden, seed=5, scale=hidden**-0.5).to(torch.bfloat16)
-    hd = h.to(DEV)
-    pre = F().gemm_tc_residual(x.to(DEV), w1.to(DEV), hd, nw.to(DEV), eps)
-    got = F().gemm_tc_scaled(pre, w2.to(DEV), swiglu=swiglu, splits=splits)
-    F().check_kernel_errors()
-    # the three-kernel path on the same inputs
-    h2 = h.to(DEV)
-    branch = F().gemm_tc(x.to(DEV), w1.to(DEV), splits=F().split_k_for(m, hidden, k))
-    xn = F().add_rmsnorm(h2, branch, nw.to(DEV), eps, torch.bfloat16)
-    want = F().gemm_tc(xn, w2.to(DEV), swiglu=swiglu)
-    scale = want.float().abs().max().item()
-    assert (got.float() - want.float()).abs().max().item() <= 2.0**-6 * scale + 1e-3
-    # and the plain formulas
-    total = h.double() + x.double() @ w1.double().T
-    y = plain.rms_norm(total, nw.double(), eps) @ w2.double().T
-    if swiglu:
-        g, u = y[:, 0::2], y[:, 1::2]
-        y = g * torch.sigmoid(g) * u
-    assert (got.double().cpu() - y).abs().max().item() <= 2.0**-6 * y.abs().max().item() + 2e-3
+def test_gemv_refuses_what_it_cannot_take():
+    x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(Exception, match="16 tokens"):
+        F().gemv(x, w)
+    with pytest.raises(Exception, match="weight rows"):
+        F().gemv(x[:2], torch.zeros(F().gemv_max_rows(torch.device(DEV)) + 8, 64, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(Exception, match="multiples of 8"):
+        F().gemv(torch.zeros(2, 12, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV))

@@ -138,30 +138,3 @@ def test_replayed_graph_steps_equal_plain_launches(tag, dtype):
             live = [r for r in live if r not in done]
         results.append(torch.cat(rows))
     assert torch.equal(results[0], results[1])
-
-
-@pytest.mark.parametrize("tag", ["tiny_a", "tiny_b"])
-def test_decode_with_norm_folded_into_projection(tag, monkeypatch):
-    """The projections that add the pending branch and normalise their own input are off by default;
-    switched on, one-token steps still give the plain logits."""
-    from gtar_kimik3_public_b200.ops import functional as F
-    from gtar_kimik3_public_b200.ops import linear as linear_ops
-
-    monkeypatch.setattr(linear_ops, "FOLD_NORM_MAX_TOKENS", F.NORMED_MAX_TOKENS)
-    engine = load_engine(tag, "bfloat16", max_tokens=512)
-    poison(engine)
-    requests = requests_for(tag, [70, 41, 9])
-    heads = [len(t) - 6 for t in requests]
-    outs = [[] for _ in requests]
-    first = engine.step([_entry(r, t[:h], list(range(h))) for r, (t, h) in enumerate(zip(requests, heads))])
-    offset = 0
-    for r, h in enumerate(heads):
-        outs[r].append(first[offset:offset + h])
-        offset += h
-    for i in range(6):
-        got = engine.step([_entry(r, [t[h + i]], [0]) for r, (t, h) in enumerate(zip(requests, heads))])
-        for r in range(len(requests)):
-            outs[r].append(got[r:r + 1])
-    engine.end(list(range(len(requests))))
-    for r, tokens in enumerate(requests):
-        check_against_plain(tag, "bfloat16", tokens, list(range(len(tokens))), torch.cat(outs[r]), f"{tag} folded norm request {r}")
