@@ -9,11 +9,13 @@
 // 32-wide k-chunks in turn.  A thread is responsible for 16 bytes of one weight row per chunk, and it asks for
 // all of them, for all its chunks, with cp.async into shared memory before the kernel has waited for the
 // kernel in front of it: weights do not depend on that kernel, so by the time that kernel has finished the
-// block's whole share of the matrix is in shared memory or on its way.  Once it has waited, the block copies
-// the tokens' activations into shared memory (one trip to L2 for all of them), and per chunk a thread takes
-// its own 16 bytes of weights back out of shared memory (nobody else reads them) and the matching 16 bytes of
-// a token's activations, and two mma.sync.m16n8k16 (tokens on the 16 rows, the eight weight rows on the 8
-// columns, 32-bit accumulation) finish the chunk.  Which k goes to which slot of the instruction
+// block's whole share of the matrix is in shared memory or on its way.  Once it has waited, it fetches the
+// tokens' activations (one trip to L2): for K up to 1024 a warp sees the same four chunks in every group, so a
+// thread keeps its 16 bytes of each in registers; for longer K the block copies all of them into shared
+// memory.  Per chunk a thread then takes its own 16 bytes of weights back out of shared memory (nobody else
+// reads them), and two mma.sync.m16n8k16 (tokens on the 16 rows, the eight weight rows on the 8 columns,
+// 32-bit accumulation) finish the chunk.  Shared-memory bandwidth is what this part costs: every weight byte
+// is read from it once, and nothing else.  Which k goes to which slot of the instruction
 // is the same for both operands and otherwise of no consequence for a sum, so both are read as plain
 // contiguous 16-byte pieces.  The warps' partial sums of a group meet in shared memory (in the place of a
 // weight piece the thread has used up) and are added in the order of the warps by one warp, which writes the
@@ -31,6 +33,7 @@ constexpr int THREADS = WARPS * 32;
 constexpr int ROWS = 8;          // weight rows of a group = the N of the MMA
 constexpr int CHUNK = 32;        // k of one 16-byte piece per thread and row: 4 threads x 8 elements
 constexpr int MAX_GROUPS = 8;    // groups a block can take (its partial sums stay in shared memory)
+constexpr int X_REGS = 4;        // chunks per warp and group up to which the activations stay in registers
 constexpr int ROUND_ITEMS = 24;  // chunks per thread whose weights fit in shared memory at once (96 KB a block)
 
 struct GemvParams {
@@ -98,10 +101,78 @@ __global__ void __launch_bounds__(THREADS, TWO_ROWS ? 3 : 4) gemv_mma_kernel(con
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
+    // after the block's barrier: warp g of the block finishes the block's g-th group
+    auto finish = [&]() {
+        if (warp >= my_groups) return;
+        // the warps' sums in their order
+        const float4* slots = partial + (size_t)warp * partial_step + lane;
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float4 v = slots[w * 32];
+            sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+        }
+        // sum[0], sum[1]: token `group`, weight rows col and col + 1;  sum[2], sum[3]: token group + 8
+        const int col = ((int)blockIdx.x + warp * (int)gridDim.x) * ROWS + 2 * piece;
+#pragma unroll
+        for (int half = 0; half < (TWO_ROWS ? 2 : 1); ++half) {
+            const int token = group + 8 * half;
+            if (token >= p.tokens) continue;
+            const float a = sum[2 * half], b = sum[2 * half + 1];
+            if (p.swiglu) {
+                if (col + 1 < p.n)
+                    reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)token * p.ldo + (col >> 1)] = __float2bfloat16(silu(a) * b);
+            } else if (p.out_f32) {
+                float* o = reinterpret_cast<float*>(p.out) + (size_t)token * p.ldo + col;
+                if (col < p.n) o[0] = a;
+                if (col + 1 < p.n) o[1] = b;
+            } else {
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)token * p.ldo + col;
+                if (col + 1 < p.n && ((p.ldo & 1) == 0)) {
+                    *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(a, b);
+                } else {
+                    if (col < p.n) o[0] = __float2bfloat16(a);
+                    if (col + 1 < p.n) o[1] = __float2bfloat16(b);
+                }
+            }
+        }
+    };
+
     request(0);  // before the kernel in front has finished
     pdl_wait();
-    // the activations of all tokens; zeros for the rows that are no token and from K up to the end of the last
-    // chunk any warp looks at
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const uint4* wp = pieces + threadIdx.x;
+    if (cpw <= X_REGS && one_round) {
+        // short K: the thread's pieces of the activations straight from memory into registers, no staging
+        uint4 xr[X_REGS], xr2[X_REGS];
+#pragma unroll
+        for (int j = 0; j < X_REGS; ++j) {
+            const int k = (warp + j * WARPS) * CHUNK + piece * 8;
+            const bool in = j < cpw && k < p.k;
+            xr[j] = in && group < p.tokens ? *reinterpret_cast<const uint4*>(p.x + (size_t)group * p.ldx + k) : zero;
+            xr2[j] = TWO_ROWS && in && group + 8 < p.tokens ? *reinterpret_cast<const uint4*>(p.x + (size_t)(group + 8) * p.ldx + k) : zero;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        for (int g = 0; g < my_groups; ++g) {
+            float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < X_REGS; ++j) {
+                if (j < cpw) {
+                    const uint4 wv = *wp;
+                    wp += THREADS;
+                    mma_bf16(acc0, xr[j].x, xr2[j].x, xr[j].y, xr2[j].y, wv.x, wv.y);
+                    mma_bf16(acc1, xr[j].z, xr2[j].z, xr[j].w, xr2[j].w, wv.z, wv.w);
+                }
+            }
+            partial[(size_t)g * partial_step + threadIdx.x] =
+                make_float4(acc0[0] + acc1[0], acc0[1] + acc1[1], acc0[2] + acc1[2], acc0[3] + acc1[3]);
+        }
+        __syncthreads();
+        finish();
+        return;
+    }
+    // the activations of all tokens into shared memory; zeros for the rows that are no token and from K up to
+    // the end of the last chunk any warp looks at
     const int x_pieces = cpw * WARPS * 4;  // 16-byte pieces of a row
     for (int i = threadIdx.x; i < X_ROWS * x_pieces; i += THREADS) {
         const int row = i / x_pieces, at = (i % x_pieces) * 8;
@@ -113,7 +184,6 @@ __global__ void __launch_bounds__(THREADS, TWO_ROWS ? 3 : 4) gemv_mma_kernel(con
     __syncthreads();
 
     const unsigned char* xa_first = xs + (size_t)group * x_stride + (warp * CHUNK + piece * 8) * 2;
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     // one chunk: the thread's weights, the token's activations (zeros beyond K, see above), two MMAs into two
     // accumulators that do not wait for one another
     auto chunk = [&](const uint4 wv, const unsigned char* xa_at, float (&acc0)[4], float (&acc1)[4]) {
@@ -122,7 +192,6 @@ __global__ void __launch_bounds__(THREADS, TWO_ROWS ? 3 : 4) gemv_mma_kernel(con
         mma_bf16(acc0, xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
         mma_bf16(acc1, xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
     };
-    const uint4* wp = pieces + threadIdx.x;
     if (one_round) {
         for (int g = 0; g < my_groups; ++g) {
             float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -159,39 +228,7 @@ __global__ void __launch_bounds__(THREADS, TWO_ROWS ? 3 : 4) gemv_mma_kernel(con
         }
     }
     __syncthreads();
-    if (warp >= my_groups) return;
-    // warp g of the block finishes the block's g-th group: the warps' sums in their order
-    const float4* slots = partial + (size_t)warp * partial_step + lane;
-    float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int w = 0; w < WARPS; ++w) {
-        const float4 v = slots[w * 32];
-        sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
-    }
-    // sum[0], sum[1]: token `group`, weight rows col and col + 1;  sum[2], sum[3]: token group + 8
-    const int col = ((int)blockIdx.x + warp * (int)gridDim.x) * ROWS + 2 * piece;
-#pragma unroll
-    for (int half = 0; half < (TWO_ROWS ? 2 : 1); ++half) {
-        const int token = group + 8 * half;
-        if (token >= p.tokens) continue;
-        const float a = sum[2 * half], b = sum[2 * half + 1];
-        if (p.swiglu) {
-            if (col + 1 < p.n)
-                reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)token * p.ldo + (col >> 1)] = __float2bfloat16(silu(a) * b);
-        } else if (p.out_f32) {
-            float* o = reinterpret_cast<float*>(p.out) + (size_t)token * p.ldo + col;
-            if (col < p.n) o[0] = a;
-            if (col + 1 < p.n) o[1] = b;
-        } else {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)token * p.ldo + col;
-            if (col + 1 < p.n && ((p.ldo & 1) == 0)) {
-                *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(a, b);
-            } else {
-                if (col < p.n) o[0] = __float2bfloat16(a);
-                if (col + 1 < p.n) o[1] = __float2bfloat16(b);
-            }
-        }
-    }
+    finish();
 }
 
 }  // namespace
@@ -211,16 +248,27 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
     }
     const int n_groups = (p.n + ROWS - 1) / ROWS;
     GK_REQUIRE(n_groups <= n_sms * MAX_GROUPS, "gemv: takes up to %d weight rows on this device, got %d", n_sms * MAX_GROUPS * ROWS, p.n);
-    dim3 grid(n_groups < n_sms ? n_groups : n_sms);
-    const int groups_per_block = (n_groups + grid.x - 1) / grid.x;
     const int n_chunks = (p.k + CHUNK - 1) / CHUNK;
+    int blocks = n_groups < n_sms ? n_groups : n_sms;
+    if ((n_chunks + WARPS - 1) / WARPS > X_REGS) {
+        // long K: every block copies all activations from L2, so fewer blocks with more groups each (as many
+        // as fit in one round of weights) cost less there than they lose in the multiplications
+        const int fit = ROUND_ITEMS / ((n_chunks + WARPS - 1) / WARPS);
+        const int per_block = fit < 1 ? 1 : fit > MAX_GROUPS ? MAX_GROUPS : fit;
+        const int fewer = (n_groups + per_block - 1) / per_block;
+        if (fewer < blocks) blocks = fewer;
+    }
+    dim3 grid(blocks);
+    const int groups_per_block = (n_groups + grid.x - 1) / grid.x;
     const int items = groups_per_block * ((n_chunks + WARPS - 1) / WARPS);
     const int round_items = items < ROUND_ITEMS ? items : ROUND_ITEMS;
     // rows of the activations in shared memory: the same number of chunks for every warp, and an odd multiple
     // of 64 bytes apart
     int x_stride = ((n_chunks + WARPS - 1) / WARPS) * WARPS * CHUNK * 2;
     if (x_stride % 128 == 0) x_stride += 64;
-    const int x_rows = p.tokens > 8 ? 16 : 8;
+    // (no copy of the activations in shared memory when they stay in registers)
+    const int cpw = (n_chunks + WARPS - 1) / WARPS;
+    const int x_rows = (cpw <= X_REGS && items <= round_items) ? 0 : p.tokens > 8 ? 16 : 8;
     const size_t smem = (size_t)round_items * THREADS * 16 + (size_t)x_rows * x_stride +
                         (items > round_items ? (size_t)groups_per_block * THREADS * 16 : 0);
     GK_REQUIRE(smem <= SMEM_MAX, "gemv: k = %d with %d tokens needs %zu bytes of shared memory, more than %zu", p.k, p.tokens, smem, SMEM_MAX);
