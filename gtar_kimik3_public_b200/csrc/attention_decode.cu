@@ -52,6 +52,9 @@ template <int D>
 struct DecodeSmem {
     __nv_bfloat16 k[STAGES][PAGE * D];
     __nv_bfloat16 v[STAGES][PAGE * D];
+    // what the fused input stage needs and no kernel of the step writes: the q and k norm weights and the
+    // rotation of the new token's position, fetched while the kernel in front still runs
+    float wq[D], wk[D], cos[D / 2], sin[D / 2];
 };
 
 template <int D>
@@ -100,7 +103,18 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
             issue(s);
             early = s + 1;
         }
+    if (fused.qkv) {
+        for (int c = tid; c < D; c += WARPS * 32) {
+            sm.wq[c] = fused.use_norm ? weight_at(fused.wq, fused.weights_bf16, c) : 1.f;
+            sm.wk[c] = fused.use_norm ? weight_at(fused.wk, fused.weights_bf16, c) : 1.f;
+            if (c < D / 2) {
+                sm.cos[c] = fused.cos_table ? fused.cos_table[(size_t)(len - 1) * (D / 2) + c] : 1.f;
+                sm.sin[c] = fused.cos_table ? fused.sin_table[(size_t)(len - 1) * (D / 2) + c] : 0.f;
+            }
+        }
+    }
     pdl_wait();
+    if (fused.qkv) __syncthreads();  // the constants above, for every warp
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s)
         if (s >= early) issue(s);
@@ -148,7 +162,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int c = ks * 16 + c0 + (e & 1) + (e >> 1) * 8;
-                            x[ks][e] = (x[ks][e] * inv) * weight_at(fused.wq, fused.weights_bf16, c);
+                            x[ks][e] = (x[ks][e] * inv) * sm.wq[c];
                         }
                 }
                 if (fused.cos_table) {
@@ -157,8 +171,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int c = ks * 16 + c0 + (e & 1) + (e >> 1) * 8;  // first half of the head
-                            const float cs = fused.cos_table[(size_t)pos_new * (D / 2) + c];
-                            const float sn = fused.sin_table[(size_t)pos_new * (D / 2) + c];
+                            const float cs = sm.cos[c], sn = sm.sin[c];
                             const float a = x[ks][e], b = x[ks + D / 32][e];
                             x[ks][e] = a * cs - b * sn;
                             x[ks + D / 32][e] = b * cs + a * sn;
@@ -197,7 +210,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
             for (int hf = 0; hf < D / 64; ++hf)
 #pragma unroll
                 for (int e = 0; e < 2; ++e)
-                    kx[hf][e] = (kx[hf][e] * inv) * weight_at(fused.wk, fused.weights_bf16, hf * 64 + 2 * lane + e);
+                    kx[hf][e] = (kx[hf][e] * inv) * sm.wk[hf * 64 + 2 * lane + e];
         }
         if (fused.cos_table) {
             // partner of column c is c + D/2: for D = 128 the other half held by this lane, for D = 64 the
@@ -206,7 +219,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int c = 2 * lane + e;
-                    const float cs = fused.cos_table[(size_t)pos_new * (D / 2) + c], sn = fused.sin_table[(size_t)pos_new * (D / 2) + c];
+                    const float cs = sm.cos[c], sn = sm.sin[c];
                     const float a = kx[0][e], b = kx[D / 64 - 1][e];
                     kx[0][e] = a * cs - b * sn;
                     kx[D / 64 - 1][e] = b * cs + a * sn;
@@ -217,7 +230,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
                     const float mine = kx[0][e];
                     const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
                     const int c = (2 * lane + e) % (D / 2);
-                    const float cs = fused.cos_table[(size_t)pos_new * (D / 2) + c], sn = fused.sin_table[(size_t)pos_new * (D / 2) + c];
+                    const float cs = sm.cos[c], sn = sm.sin[c];
                     kx[0][e] = lane < 16 ? mine * cs - other * sn : mine * cs + other * sn;
                 }
             }
@@ -284,6 +297,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = r0 + 8 * h;
+            if (r >= group) continue;  // rows of the tile beyond the heads of this group hold nothing
             if ((lane & 3) == 0) {
                 red_ml[(warp * 16 + r) * 2] = m[h];
                 red_ml[(warp * 16 + r) * 2 + 1] = l[h];
@@ -331,13 +345,17 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         }
     }
     if (n_splits > 1 && cluster_merge) {
-        // The splits of one (sequence, kv head) are one cluster: block 0 merges the partial results of
-        // all of them through distributed shared memory, in split order; no scratch, no second kernel.
+        // The splits of one (sequence, kv head) are one cluster: the partial results of all of them are
+        // merged through distributed shared memory, in split order; no scratch, no second kernel.
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (split == 0) {
+        {
+            // every block merges its own share of the group's outputs: elements split, split + n_splits, ...
+            // in units of 32 (a warp reads consecutive words of every block's result)
             const uint32_t o_addr = smem_u32(cl_o), ml_addr = smem_u32(cl_ml);
-            for (int idx = tid; idx < group * D; idx += WARPS * 32) {
+            for (int unit = split + warp * n_splits; unit * 32 < group * D; unit += WARPS * n_splits) {
+                const int idx = unit * 32 + lane;
+                if (idx >= group * D) break;
                 const int r = idx / D;
                 float ms[8], ls[8], os[8];
 #pragma unroll
