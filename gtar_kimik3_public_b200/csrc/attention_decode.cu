@@ -119,6 +119,20 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     for (int s = 0; s < STAGES - 1; ++s)
         if (s >= early) issue(s);
 
+    // The new token's raw key and value are asked for first (by the warp of the block that will write them), so
+    // that they are on their way while the queries are prepared.
+    const bool owns_new = fused.qkv != nullptr && fused.write_kv && new_page >= p_begin && new_page < p_end;
+    __nv_bfloat162 k_raw[D / 64], k_new[D / 64], v_new[D / 64];  // lane l: elements 2l, 2l+1 of each 64-wide half
+    if (owns_new && warp == 0) {
+        const int n_heads = n_q + 2 * n_kv;
+        const __nv_bfloat16* krow = fused.qkv + ((size_t)seq * n_heads + n_q + hk) * D;
+        const __nv_bfloat16* vrow = fused.qkv + ((size_t)seq * n_heads + n_q + n_kv + hk) * D;
+#pragma unroll
+        for (int hf = 0; hf < D / 64; ++hf) {
+            k_raw[hf] = *reinterpret_cast<const __nv_bfloat162*>(krow + hf * 64 + 2 * lane);
+            v_new[hf] = *reinterpret_cast<const __nv_bfloat162*>(vrow + hf * 64 + 2 * lane);
+        }
+    }
     // Query fragments: row r of the tile is query head hk*group + r (rows >= group are zero).
     uint32_t qf[D / 16][4];
     const int pos_new = len - 1;
@@ -187,21 +201,15 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     }
     // The new token's key and value, by the block that holds its page: one warp makes them, writes them
     // to the cache, and keeps them for patching the page's copy in shared memory once that has landed.
-    const bool owns_new = fused.qkv != nullptr && fused.write_kv && new_page >= p_begin && new_page < p_end;
-    __nv_bfloat162 k_new[D / 64], v_new[D / 64];  // lane l: elements 2l, 2l+1 of each 64-wide half
     if (owns_new && warp == 0) {
-        const int n_heads = n_q + 2 * n_kv;
-        const __nv_bfloat16* krow = fused.qkv + ((size_t)seq * n_heads + n_q + hk) * D;
-        const __nv_bfloat16* vrow = fused.qkv + ((size_t)seq * n_heads + n_q + n_kv + hk) * D;
         float kx[D / 64][2];
         float ss = 0.f;
 #pragma unroll
         for (int hf = 0; hf < D / 64; ++hf) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(krow + hf * 64 + 2 * lane));
+            const float2 f = __bfloat1622float2(k_raw[hf]);
             kx[hf][0] = f.x;
             kx[hf][1] = f.y;
             ss += f.x * f.x + f.y * f.y;
-            v_new[hf] = *reinterpret_cast<const __nv_bfloat162*>(vrow + hf * 64 + 2 * lane);
         }
         if (fused.use_norm) {
             ss = warp_sum(ss);
