@@ -1,6 +1,7 @@
 """Micro-benchmarks of single kernels at the shapes of a model's step.
 
     python -m gtar_kimik3_public_b200.ops.microbench --kernel gemm --m 8 --n 4096 --k 1024
+    python -m gtar_kimik3_public_b200.ops.microbench --kernel gemv --m 8 --n 4096 --k 1024
     python -m gtar_kimik3_public_b200.ops.microbench --kernel attention_decode --batch 8 --context 2048
     python -m gtar_kimik3_public_b200.ops.microbench --kernel attention_prefill --tokens 2048
     python -m gtar_kimik3_public_b200.ops.microbench --kernel step --batch 8 --context 2048
@@ -56,6 +57,25 @@ def bench_gemm(args) -> dict:
     us = _time_graph(run, args.iters) / ring
     return {"kernel": "gemm_tc", "m": m, "n": n, "k": k, "splits": splits, "swiglu": args.swiglu, "us": round(us, 2),
             "weight_gb_s": round(n * k * 2 / us / 1e3, 1), "tflop_s": round(2 * m * n * k / us / 1e6, 1)}
+
+
+def bench_gemv(args) -> dict:
+    m, n, k = args.m, args.n, args.k
+    ring = max(2, min(64, (256 << 20) // (n * k * 2) + 1))
+    weights = [torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(ring)]
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    before = F.set_pdl(args.pdl)
+
+    def run():
+        for w in weights:
+            F.gemv(x, w, torch.bfloat16, swiglu=args.swiglu)
+
+    try:
+        us = _time_graph(run, args.iters) / ring
+    finally:
+        F.set_pdl(before)
+    return {"kernel": "gemv", "m": m, "n": n, "k": k, "swiglu": args.swiglu, "pdl": args.pdl, "us": round(us, 2),
+            "weight_gb_s": round(n * k * 2 / us / 1e3, 1)}
 
 
 def _paged(batch: int, context: int, n_kv: int, d: int):
@@ -150,7 +170,7 @@ def bench_step(args) -> dict:
 
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    parser.add_argument("--kernel", required=True, choices=["gemm", "attention_decode", "attention_prefill", "step"])
+    parser.add_argument("--kernel", required=True, choices=["gemm", "gemv", "attention_decode", "attention_prefill", "step"])
     parser.add_argument("--m", type=int, default=8)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=1024)
@@ -165,9 +185,10 @@ def main() -> int:
     parser.add_argument("--attention-path", default="auto", choices=["auto", "tcgen05", "mma"])
     parser.add_argument("--layers", type=int, default=28)
     parser.add_argument("--iters", type=int, default=5)
+    parser.add_argument("--pdl", action="store_true", help="gemv: launch with programmatic dependent launch, as a model step does")
     args = parser.parse_args()
     F.require_device(torch.device(DEV))
-    result = {"gemm": bench_gemm, "attention_decode": bench_attention_decode,
+    result = {"gemm": bench_gemm, "gemv": bench_gemv, "attention_decode": bench_attention_decode,
               "attention_prefill": bench_attention_prefill, "step": bench_step}[args.kernel](args)
     F.check_kernel_errors(DEV)
     print(json.dumps(result))
