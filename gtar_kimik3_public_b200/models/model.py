@@ -86,9 +86,11 @@ class Model:
         return Cache(self.cache_layout(), max_tokens, self.dtype, self.device, max_seqs=max_seqs, max_seq_len=max_len)
 
     def graph_safe(self) -> bool:
-        """Whether a decode step may be captured in a CUDA graph: every mixer must say so (a part
+        """Whether a decode step may be captured in a CUDA graph: every part of the plan must say so (a part
         that does host work per step, as test fixtures may, keeps the step out of graphs)."""
-        return all(getattr(self.plan.layers[e.layer].mixer, "graph_safe", False) for e in self.plan.run_list)
+        plan = self.plan
+        parts = [plan.embedding, plan.final_norm, plan.head, *plan.positions, *(plan.layers[e.layer] for e in plan.run_list)]
+        return all(getattr(part, "graph_safe", False) for part in parts)
 
     # ------------------------------------------------------------------ the forward pass of one step
     def prepare(self, max_position: int) -> None:

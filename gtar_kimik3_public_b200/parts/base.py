@@ -85,6 +85,12 @@ class StepContext:
 class Part:
     """Common face of every part."""
 
+    # Whether the part's forward() may be captured in a CUDA graph: it launches kernels only, and every
+    # number that changes from step to step is read from device memory.  A part that looks at host copies
+    # of lengths, loops over sequences on the host or waits for the device says False (the default), and a
+    # model with such a part runs its steps launch by launch.
+    graph_safe = False
+
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {}
 
@@ -127,6 +133,15 @@ class FeedForward(Part):
 
 class Block(Part):
     """Arrangement of the parts of one layer around the residual stream."""
+
+    def children(self) -> list[tuple[str, Part]]:
+        """(tensor-name prefix, part) of everything inside the block."""
+        return []
+
+    @property
+    def graph_safe(self) -> bool:
+        parts = self.children()
+        return bool(parts) and all(part.graph_safe for _, part in parts)
 
     mixer: Mixer
 

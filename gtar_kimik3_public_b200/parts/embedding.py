@@ -11,6 +11,8 @@ from .base import Part, TensorSpec
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.weight: torch.Tensor | None = None
@@ -26,6 +28,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
+    graph_safe = True
+
     """Logits in float32.  ``tied_to`` names an embedding whose table is used instead of an own matrix."""
 
     def __init__(self, hidden_size: int, vocab_size: int, tied_to: TokenEmbedding | None = None):

@@ -13,6 +13,8 @@ from .base import FeedForward, StepContext, TensorSpec, register_part
 
 
 class SwiGLUFeedForward(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.w_gate_up = self.w_down = None

@@ -10,6 +10,8 @@ from .base import Norm, TensorSpec, register_part
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, size: int, eps: float):
         self.size = int(size)
         self.eps = float(eps)

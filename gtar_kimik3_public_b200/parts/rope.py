@@ -14,6 +14,8 @@ from .base import PositionEncoding, register_part
 
 
 class RotaryEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, dim: int, base: float):
         if dim % 2:
             raise ValueError(f"rotary dimension must be even, got {dim}")
