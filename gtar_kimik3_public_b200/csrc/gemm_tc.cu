@@ -701,6 +701,185 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS, 1) gemm_tc_persistent_kern
     }
 }
 
+// ---------------------------------------------------------------- two blocks on one 256 x 256 tile
+// The same walk over tiles by pairs of blocks on neighbouring SMs (a cluster of two).  Each block of a pair
+// loads its own 128 rows of A and HALF of the tile's 256 rows of B; one thread of the first block issues
+// tcgen05.mma.cta_group::2, which multiplies in both SMs at once (M = 256: each block's 128 rows of A against
+// all 256 rows of B, read from both blocks' shared memory) and leaves each block's 128 x 256 accumulator in its
+// own tensor memory.  A block thus brings in 32 KB per k-block instead of 48 KB for the same 128 x 256 x 64
+// product, and six stages instead of four fit in its shared memory: the k-blocks in flight cover the 1.3 us a
+// TMA load takes from L2, which four stages of the one-block kernel do not (its MMA thread waits for data half
+// of the time).  Loads carry no multicast.  Barriers: `full` lives in the first block and counts both blocks'
+// loads; tcgen05.commit arrives on `empty` and `acc_full` in both blocks; the output warps of both blocks
+// arrive on the first block's `acc_empty`.
+template <int STAGES>
+struct alignas(1024) PairSmem {
+    __nv_bfloat16 a[STAGES][BM * BK];
+    __nv_bfloat16 b[STAGES][BM * BK];  // this block's 128 of the tile's 256 rows of B
+    uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+};
+
+__device__ __forceinline__ uint32_t cluster_address(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster)
+        : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+// arrives on the barrier at this offset in both blocks of the pair once the MMAs issued so far have finished
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(PERSISTENT_THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                           const __grid_constant__ CUtensorMap map_b,
+                                                                           const GemmParams p) {
+    constexpr int BN = 256;
+    extern __shared__ unsigned char smem_raw[];
+    PairSmem<STAGES>& sm = *reinterpret_cast<PairSmem<STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t TMEM_COLS = 512;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int tiles_a = (p.rows_a + 2 * BM - 1) / (2 * BM), tiles_b = (p.rows_b + BN - 1) / BN;  // tiles of 256 x 256
+    const int n_tiles = tiles_a * tiles_b;
+    const int n_kb = p.k_blocks;
+    constexpr int OUTPUT_WARPS = (PERSISTENT_THREADS - 64) / 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.full[s], 2);   // one arrival (with its byte count) from each block's producer
+            mbar_init(&sm.empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&sm.acc_full[b], 1);
+            mbar_init(&sm.acc_empty[b], 2 * OUTPUT_WARPS);  // one arrival per output warp of both blocks
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        pdl_launch_dependents();
+    }
+    if (warp == 1) {  // in both blocks: the allocation spans the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync_all();  // both blocks' barriers are initialised before either signals the other
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    constexpr uint32_t STAGE_BYTES = 2 * BM * BK * sizeof(__nv_bfloat16);  // what ONE block loads per k-block
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer (both blocks): this block's rows of A and its half of B, signalled to the first block
+            pdl_wait();
+            bool ok = true;
+            long long it = 0;
+            for (int t = pair; t < n_tiles && ok; t += n_pairs) {
+                const int tile_a = t % tiles_a, tile_b = t / tiles_a;
+                for (int kb = 0; kb < n_kb && ok; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    if (it >= STAGES) ok = mbar_wait(&sm.empty[s], (uint32_t)((it / STAGES) - 1) & 1);
+                    if (!ok) break;
+                    const uint32_t full = cluster_address(smem_u32(&sm.full[s]), 0);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(full), "r"(STAGE_BYTES) : "memory");
+                    tma_load_2d_pair(sm.a[s], &map_a, kb * BK, (tile_a * 2 + (int)rank) * BM, full);
+                    tma_load_2d_pair(sm.b[s], &map_b, kb * BK, tile_b * BN + (int)rank * BM, full);
+                }
+            }
+            if (!ok) atomicExch(p.error_flag, 31);
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---- MMA issuer (first block only)
+            const uint32_t idesc = umma_idesc(2 * BM, BN);
+            bool ok = true;
+            long long it = 0;
+            int j = 0;
+            for (int t = pair; t < n_tiles && ok; t += n_pairs, ++j) {
+                const int buf = j & 1;
+                if (j >= 2) ok = mbar_wait(&sm.acc_empty[buf], (uint32_t)((j >> 1) - 1) & 1);  // both blocks have drained it
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem + buf * BN;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    ok = mbar_wait(&sm.full[s], (uint32_t)(it / STAGES) & 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_pair(acc, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, kb > 0 || k > 0);
+                    umma_commit_pair(&sm.empty[s]);
+                }
+                umma_commit_pair(&sm.acc_full[buf]);
+            }
+            if (!ok) atomicExch(p.error_flag, 32);
+        }
+    } else {
+        // ---- output warps (both blocks), as in the one-block kernel: this block's 128 rows of the tile
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        pdl_wait();
+        bool ok = true;
+        int j = 0;
+        for (int t = pair; t < n_tiles && ok; t += n_pairs, ++j) {
+            const int tile_a = t % tiles_a, tile_b = t / tiles_a, buf = j & 1;
+            const int row_a = (tile_a * 2 + (int)rank) * BM + quarter * 32 + lane;
+            ok = mbar_wait(&sm.acc_full[buf], (uint32_t)(j >> 1) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t t_row = tmem + buf * BN + ((uint32_t)(quarter * 32) << 16);
+            const bool a_ok = row_a < p.rows_a;
+            if (p.epilogue == EPI_QKV) {
+                if (p.qkv.head_dim == 128) qkv_tile<128, BN>(p, t_row, row_a, a_ok, tile_b, half);
+                else qkv_tile<64, BN>(p, t_row, row_a, a_ok, tile_b, half);
+            } else {
+#pragma unroll 1
+                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 16) {
+                    float v[16];
+                    tmem_ld16(t_row + c0, v);
+                    write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t drained = cluster_address(smem_u32(&sm.acc_empty[buf]), 0);
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(drained) : "memory");
+            }
+        }
+        if (!ok && lane == 0) atomicExch(p.error_flag, 33);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync_all();  // nobody leaves while the other block may still signal it or read its shared memory
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -768,7 +947,51 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
     return GK_OK;
 }
 
+int g_gemm_pairs = 2;  // 0: never, 1: always, 2: where it is the faster one (large products)
+
+// `mb` must have boxes of 128 rows (each block loads half of a 256-row B tile).
+bool use_pairs(int rows_a, int rows_b);
+
+template <int STAGES>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+    const size_t smem = sizeof(PairSmem<STAGES>) + 1024;
+    static bool configured = false;
+    static int n_sms = 0;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_pair_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int device = 0;
+        if (err == cudaSuccess) err = cudaGetDevice(&device);
+        if (err == cudaSuccess) err = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+        if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    const int n_tiles = ((p.rows_a + 2 * BM - 1) / (2 * BM)) * ((p.rows_b + 255) / 256);
+    const int pairs = n_tiles < n_sms / 2 ? n_tiles : n_sms / 2;
+    gk_launch_cluster(gemm_tc_pair_kernel<STAGES>, dim3(2 * pairs), dim3(PERSISTENT_THREADS), smem, stream, dim3(2, 1, 1), ma, mb, p);
+    GK_CHECK_LAUNCH("gemm_tc_pair");
+    return GK_OK;
+}
+
+bool use_pairs(int rows_a, int rows_b) {
+    if (g_gemm_pairs != 2) return g_gemm_pairs == 1;
+    int device = 0, n_sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+    const long long tiles = (long long)((rows_a + 255) / 256) * ((rows_b + 255) / 256);
+    return tiles >= 3LL * (n_sms / 2);
+}
+
 }  // namespace
+
+// Whether many-token products with wide tiles run as pairs of blocks (tcgen05 cta_group::2): 0 never, 1 always,
+// 2 (the default) where there are at least three 256 x 256 tiles per pair of SMs.  Measured on a B200: 1.35
+// against 1.33 PFLOP/s at 8192^3, 1.36 against 1.32 at 4096^3, but 840 against 937 TFLOP/s on the gate|up
+// product of a 2,048-token prompt (1.7 tiles per SM: start-up and the last tile's output stage dominate, and
+// pairs make both a little longer).  Returns the old setting.
+GK_EXPORT int gk_set_gemm_pairs(int mode) {
+    const int before = g_gemm_pairs;
+    g_gemm_pairs = mode < 0 ? 0 : mode > 2 ? 2 : mode;
+    return before;
+}
 
 // OUT[a, b] = sum_k A[a, k] B[b, k].  `bn` (16, 32, 64, 128 or 256) is the tile width along B.
 // With `splits` = 2, 4 or 8 the K range of a tile is shared by that many blocks (one cluster).  `a_static` / `b_static` mark an operand that no
@@ -794,7 +1017,7 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     if (status) return status;
     status = make_map(&mb, b, rows_b, k, ldb, bn);
     if (status) return status;
-    GemmParams p;
+    GemmParams p = {};
     p.rows_a = rows_a;
     p.rows_b = rows_b;
     p.k_blocks = (k + BK - 1) / BK;
@@ -809,7 +1032,13 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     p.a_static = a_static;
     p.b_static = b_static;
     p.error_flag = error_flag;
-    if (bn == 256 && splits == 1) return launch_persistent<256, 4>(ma, mb, p, (cudaStream_t)stream);
+    if (bn == 256 && splits == 1) {
+        if (!use_pairs(rows_a, rows_b)) return launch_persistent<256, 4>(ma, mb, p, (cudaStream_t)stream);
+        CUtensorMap mb_half;  // boxes of 128 rows: each block of a pair loads half of a B tile
+        status = make_map(&mb_half, b, rows_b, k, ldb, BM);
+        if (status) return status;
+        return launch_pair<6>(ma, mb_half, p, (cudaStream_t)stream);
+    }
     dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
     GK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;
@@ -879,5 +1108,9 @@ GK_EXPORT int gk_gemm_bf16_tc_qkv(const void* x, int n_tokens, const void* w_qkv
     p.qkv.q_out = (__nv_bfloat16*)q_out;
     p.qkv.k_pages = (__nv_bfloat16*)k_pages;
     p.qkv.v_pages = (__nv_bfloat16*)v_pages;
-    return launch_persistent<256, 4>(ma, mb, p, (cudaStream_t)stream);
+    if (!use_pairs(n_tokens, n)) return launch_persistent<256, 4>(ma, mb, p, (cudaStream_t)stream);
+    CUtensorMap mb_half;
+    status = make_map(&mb_half, w_qkv, n, k, k, BM);
+    if (status) return status;
+    return launch_pair<6>(ma, mb_half, p, (cudaStream_t)stream);
 }

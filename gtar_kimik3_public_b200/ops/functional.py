@@ -355,6 +355,15 @@ def gemv_max_rows(device: torch.device) -> int:
 
 
 
+def set_gemm_pairs(mode: int) -> int:
+    """How many-token products with wide tiles are run: 1 as pairs of blocks on one 256 x 256 tile (tcgen05
+    cta_group::2), 0 as single blocks on 128 x 256 tiles, 2 (the default) pairs where the product is large
+    enough for them to be the faster choice.  Returns the old setting."""
+    from .library import library
+
+    return int(library().gk_set_gemm_pairs(int(mode)))
+
+
 def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
          out: torch.Tensor | None = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` for up to 16 tokens: weights go from memory straight into registers and

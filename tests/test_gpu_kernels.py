@@ -586,3 +586,55 @@ def test_gemv_refuses_what_it_cannot_take():
         F().gemv(x[:2], torch.zeros(F().gemv_max_rows(torch.device(DEV)) + 8, 64, dtype=torch.bfloat16, device=DEV))
     with pytest.raises(Exception, match="multiples of 8"):
         F().gemv(torch.zeros(2, 12, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV))
+
+
+# ------------------------------------------------------------------ pairs of blocks on one tile (tcgen05 cta_group::2)
+@pytest.fixture
+def gemm_pairs_forced():
+    before = F().set_gemm_pairs(1)
+    yield
+    F().set_gemm_pairs(before)
+
+
+@pytest.mark.parametrize("m,n,k,swiglu", [(2048, 4096, 1024, False), (2048, 6144, 1024, True), (1000, 31000, 200, False),
+                                          (4097, 8200, 72, True), (16384, 1024, 64, False)])
+def test_gemm_tc_pairs_against_plain_product(gemm_pairs_forced, m, n, k, swiglu):
+    x = rand(m, k, seed=1).to(torch.bfloat16)
+    w = rand(n, k, seed=2, scale=k**-0.5).to(torch.bfloat16)
+    got = F().gemm_tc(x.to(DEV), w.to(DEV), swiglu=swiglu)
+    F().check_kernel_errors()
+    rows = torch.cat([torch.arange(0, 260), torch.arange(m - 260, m), torch.arange(m // 2, m // 2 + 130)])
+    y = x.double()[rows] @ w.double().T
+    if swiglu:
+        g, u = y[:, 0::2], y[:, 1::2]
+        y = g * torch.sigmoid(g) * u
+    assert (got.cpu().double()[rows] - y).abs().max().item() <= BF16_ULP * y.abs().max().item() + 1e-4
+    # and bit for bit what single blocks on 128 x 256 tiles give (the same products added in the same order)
+    F().set_gemm_pairs(0)
+    assert torch.equal(got, F().gemm_tc(x.to(DEV), w.to(DEV), swiglu=swiglu))
+
+
+def test_gemm_tc_qkv_in_pairs_equals_single_blocks():
+    n_q, n_kv, d, hidden, dtype = 16, 8, 128, 1024, torch.bfloat16
+    lens = [900, 1100]
+    n_tokens, width = sum(lens), (n_q + 2 * n_kv) * d
+    x = rand(n_tokens, hidden, seed=1).to(dtype).to(DEV)
+    w = rand(width, hidden, seed=2, scale=hidden**-0.5).to(dtype).to(DEV)
+    wq, wk = (1 + 0.1 * rand(d, seed=3)).float().to(DEV), (1 + 0.1 * rand(d, seed=4)).float().to(DEV)
+    cos, sin = plain.rotary_tables(torch.arange(max(lens)), d, 1e5)
+    cos, sin = cos[:, : d // 2].contiguous().to(DEV), sin[:, : d // 2].contiguous().to(DEV)
+    pos = torch.tensor([p for n in lens for p in range(n)], dtype=torch.int32).to(DEV)
+    seq = torch.tensor([i for i, n in enumerate(lens) for _ in range(n)], dtype=torch.int32).to(DEV)
+    results = []
+    before = F().set_gemm_pairs(0)
+    try:
+        for mode in (0, 1):
+            F().set_gemm_pairs(mode)
+            kv, slots, table = scrambled_pages(2, max(lens), n_kv, d, dtype, seed=17)
+            q = F().gemm_tc_qkv(x, w, n_q, n_kv, d, wq, wk, 1e-6, cos, sin, pos, seq, slots.to(DEV), kv, max(lens) - 1)
+            F().check_kernel_errors()
+            results.append((q.clone(), kv.k.clone(), kv.v.clone()))
+    finally:
+        F().set_gemm_pairs(before)
+    for a, b in zip(*results):
+        assert torch.equal(torch.nan_to_num(a.float(), nan=-7.0), torch.nan_to_num(b.float(), nan=-7.0))
