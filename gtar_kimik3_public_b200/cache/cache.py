@@ -23,6 +23,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..ops.functional import PagedKV
@@ -51,20 +52,24 @@ class _KVGroup:
         self.v = torch.empty(shape, dtype=dtype, device=device)
         self.pages = PageAllocator(n_pages)
         self.max_pages_per_seq = max_pages_per_seq
-        self.table_host = torch.zeros((n_slots, max_pages_per_seq), dtype=torch.int32)
+        self.table_host = np.zeros((n_slots, max_pages_per_seq), dtype=np.int32)
         self.table = torch.zeros((n_slots, max_pages_per_seq), dtype=torch.int32, device=device)
         self.owned: dict[int, dict[int, int]] = {}  # slot -> {page index in sequence: page}
+        self.upto: dict[int, int] = {}  # slot -> one past the highest page index the sequence ever had
         self.dirty: set[int] = set()
 
     def open_slot(self, slot: int) -> None:
         self.owned[slot] = {}
+        self.upto[slot] = 0
 
     def close_slot(self, slot: int) -> None:
         self.pages.free(self.owned.pop(slot).values())
+        del self.upto[slot]
 
     def pages_needed(self, slot: int, old_len: int, new_len: int) -> int:
+        # a sequence only grows, so the pages it lacks are those from `upto` on (a window may have skipped some)
         first, last = self._span(old_len, new_len)
-        return sum(1 for i in range(first, last + 1) if i not in self.owned[slot])
+        return max(0, last + 1 - max(first, self.upto[slot]))
 
     def _span(self, old_len: int, new_len: int) -> tuple[int, int]:
         """Page indices that hold positions a step from old_len to new_len reads or writes."""
@@ -85,11 +90,13 @@ class _KVGroup:
             gone = [i for i in owned if i < first]
             if gone:
                 self.pages.free([owned.pop(i) for i in gone])
-        missing = [i for i in range(first, last + 1) if i not in owned]
-        if missing:
-            for i, page in zip(missing, self.pages.alloc(len(missing))):
-                owned[i] = page
-                self.table_host[slot, i] = page
+        begin = max(first, self.upto[slot])
+        if begin <= last:
+            missing = list(range(begin, last + 1))
+            pages = self.pages.alloc(len(missing))
+            owned.update(zip(missing, pages))
+            self.table_host[slot, begin:last + 1] = pages
+            self.upto[slot] = last + 1
             self.dirty.add(slot)
 
     def sync(self) -> None:
@@ -100,7 +107,7 @@ class _KVGroup:
         if not self.dirty:
             return
         slots = sorted(self.dirty)
-        staged = self.table_host[slots]
+        staged = torch.from_numpy(self.table_host[slots])  # fancy indexing copies
         if self.table.is_cuda:
             staged = staged.pin_memory()
         for i, slot in enumerate(slots):

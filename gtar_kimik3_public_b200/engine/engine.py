@@ -12,6 +12,7 @@ from __future__ import annotations
 import os
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..cache import Cache, CacheFull
@@ -85,12 +86,17 @@ class Engine:
         if len(set(ids)) != len(ids):
             raise ValueError("a request appears twice in one step")
         vocab = self.model.vocab_size
+        token_arrays = []  # a prompt of thousands of tokens is checked and packed as an array, not token by token
         for entry in entries:
-            if not entry.tokens:
+            if len(entry.tokens) == 0:
                 raise ValueError(f"request {entry.id!r} brings no token")
-            if min(entry.tokens) < 0 or max(entry.tokens) >= vocab:
-                bad = next(t for t in entry.tokens if not 0 <= int(t) < vocab)
+            tokens = np.asarray(entry.tokens, dtype=np.int64)
+            if tokens.ndim != 1:
+                raise ValueError(f"request {entry.id!r}: tokens must be a flat list of ids")
+            if tokens.min() < 0 or tokens.max() >= vocab:
+                bad = int(tokens[(tokens < 0) | (tokens >= vocab)][0])
                 raise ValueError(f"request {entry.id!r}: token id {bad} is outside the vocabulary of {vocab}")
+            token_arrays.append(tokens)
         new_ids = [e.id for e in entries if e.id not in self.slot_of]
         if len(new_ids) > self.cache.slots.n_free:
             raise CacheFull(f"{len(new_ids)} new requests but only {self.cache.slots.n_free} free slots")
@@ -111,10 +117,10 @@ class Engine:
                 self.cache.close(self.slot_of.pop(request_id))
             raise
         sequences = []
-        for entry in entries:
+        for entry, tokens in zip(entries, token_arrays):
             slot = self.slot_of[entry.id]
-            past = self.cache.grow(slot, len(entry.tokens))
-            sequences.append(SequenceStep(slot, past, [int(t) for t in entry.tokens], [int(w) for w in entry.want]))
+            past = self.cache.grow(slot, len(tokens))
+            sequences.append(SequenceStep(slot, past, tokens, [int(w) for w in entry.want]))
         self.cache.sync()
         self.steps_run += 1
         if self.graphs is not None:

@@ -11,6 +11,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+from typing import Sequence
+
 import numpy as np
 import torch
 
@@ -23,7 +25,7 @@ class SequenceStep:
 
     slot: int
     past_len: int
-    tokens: list[int]
+    tokens: Sequence[int]  # a list or a numpy array of ids
     want: list[int]  # places among ``tokens`` whose logits are asked for
 
 
@@ -71,7 +73,7 @@ def pack_step(sequences: list[SequenceStep], vocab_size: int, check_tokens: bool
     past = [s.past_len for s in sequences]
     starts = np.zeros(len(sequences) + 1, dtype=np.int32)
     np.cumsum(q_lens, out=starts[1:])
-    tokens = np.fromiter((t for s in sequences for t in s.tokens), dtype=np.int64, count=int(starts[-1]))
+    tokens = np.concatenate([np.asarray(s.tokens, dtype=np.int64) for s in sequences])
     if check_tokens and tokens.size and (tokens.min() < 0 or tokens.max() >= vocab_size):
         bad = int(tokens[(tokens < 0) | (tokens >= vocab_size)][0])
         raise ValueError(f"token id {bad} is outside the vocabulary of {vocab_size}")
