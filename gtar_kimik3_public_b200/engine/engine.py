@@ -86,17 +86,23 @@ class Engine:
         if len(set(ids)) != len(ids):
             raise ValueError("a request appears twice in one step")
         vocab = self.model.vocab_size
-        token_arrays = []  # a prompt of thousands of tokens is checked and packed as an array, not token by token
-        for entry in entries:
-            if len(entry.tokens) == 0:
-                raise ValueError(f"request {entry.id!r} brings no token")
-            tokens = np.asarray(entry.tokens, dtype=np.int64)
-            if tokens.ndim != 1:
-                raise ValueError(f"request {entry.id!r}: tokens must be a flat list of ids")
-            if tokens.min() < 0 or tokens.max() >= vocab:
-                bad = int(tokens[(tokens < 0) | (tokens >= vocab)][0])
-                raise ValueError(f"request {entry.id!r}: token id {bad} is outside the vocabulary of {vocab}")
-            token_arrays.append(tokens)
+        # all tokens of the step as one array: checked once, and packed from it
+        q_lens = [len(e.tokens) for e in entries]
+        if min(q_lens) == 0:
+            raise ValueError(f"request {entries[q_lens.index(0)].id!r} brings no token")
+        parts = [np.asarray(e.tokens, dtype=np.int64) for e in entries]
+        if any(part.ndim != 1 for part in parts):
+            raise ValueError("tokens must be a flat list of ids")
+        flat = parts[0] if len(parts) == 1 else np.concatenate(parts)
+        if flat.min() < 0 or flat.max() >= vocab:
+            for entry, part in zip(entries, parts):
+                wrong = part[(part < 0) | (part >= vocab)]
+                if wrong.size:
+                    raise ValueError(f"request {entry.id!r}: token id {int(wrong[0])} is outside the vocabulary of {vocab}")
+        for entry, n in zip(entries, q_lens):
+            for place in entry.want:
+                if not 0 <= int(place) < n:
+                    raise ValueError(f"request {entry.id!r}: wanted place {place} is outside the {n} tokens it brings")
         new_ids = [e.id for e in entries if e.id not in self.slot_of]
         if len(new_ids) > self.cache.slots.n_free:
             raise CacheFull(f"{len(new_ids)} new requests but only {self.cache.slots.n_free} free slots")
@@ -117,7 +123,7 @@ class Engine:
                 self.cache.close(self.slot_of.pop(request_id))
             raise
         sequences = []
-        for entry, tokens in zip(entries, token_arrays):
+        for entry, tokens in zip(entries, parts):
             slot = self.slot_of[entry.id]
             past = self.cache.grow(slot, len(tokens))
             sequences.append(SequenceStep(slot, past, tokens, [int(w) for w in entry.want]))

@@ -71,14 +71,21 @@ def pack_step(sequences: list[SequenceStep], vocab_size: int, check_tokens: bool
     if min(q_lens) == 0:
         raise ValueError(f"sequence {q_lens.index(0)} of the step brings no token")
     past = [s.past_len for s in sequences]
-    starts = np.zeros(len(sequences) + 1, dtype=np.int32)
-    np.cumsum(q_lens, out=starts[1:])
-    tokens = np.concatenate([np.asarray(s.tokens, dtype=np.int64) for s in sequences])
+    n_seqs = len(sequences)
+    past_np = np.asarray(past, dtype=np.int32)
+    if max(q_lens) == 1:  # a decode step: one token each
+        starts = np.arange(n_seqs + 1, dtype=np.int32)
+        tokens = np.asarray([s.tokens[0] for s in sequences], dtype=np.int64)
+        tok_seq, tok_pos = starts[:-1], past_np
+    else:
+        starts = np.zeros(n_seqs + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=starts[1:])
+        tokens = np.concatenate([np.asarray(s.tokens, dtype=np.int64) for s in sequences])
+        tok_seq = np.repeat(np.arange(n_seqs, dtype=np.int32), q_lens)
+        tok_pos = np.arange(int(starts[-1]), dtype=np.int32) - starts[:-1][tok_seq] + past_np[tok_seq]
     if check_tokens and tokens.size and (tokens.min() < 0 or tokens.max() >= vocab_size):
         bad = int(tokens[(tokens < 0) | (tokens >= vocab_size)][0])
         raise ValueError(f"token id {bad} is outside the vocabulary of {vocab_size}")
-    tok_seq = np.repeat(np.arange(len(sequences), dtype=np.int32), q_lens)
-    tok_pos = np.arange(int(starts[-1]), dtype=np.int32) - starts[:-1][tok_seq] + np.asarray(past, dtype=np.int32)[tok_seq]
     want_rows = []
     for index, seq in enumerate(sequences):
         for place in seq.want:
@@ -88,7 +95,7 @@ def pack_step(sequences: list[SequenceStep], vocab_size: int, check_tokens: bool
     slots = [s.slot for s in sequences]
     fields = [
         tokens.astype(np.int32), tok_pos.astype(np.int32), tok_seq, starts, np.asarray(slots, dtype=np.int32),
-        np.asarray([p + n for p, n in zip(past, q_lens)], dtype=np.int32), np.asarray(want_rows, dtype=np.int32),
+        past_np + np.asarray(q_lens, dtype=np.int32), np.asarray(want_rows, dtype=np.int32),
     ]
     return PackedStep(fields, q_lens, past, slots)
 
