@@ -1047,7 +1047,14 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
         case 16: return launch<16, 5>(ma, mb, p, grid, s);
         case 32: return launch<32, 9>(ma, mb, p, grid, s);
         case 64: return launch<64, 8>(ma, mb, p, grid, s);
-        case 128: return launch<128, 3>(ma, mb, p, grid, s);
+        case 128: {
+            // one block per SM at most: a deeper ring instead of a second resident block (the k-blocks in flight
+            // have to cover the 1.3 us a TMA load takes, and 3 stages of 32 KB cover 0.5 us of MMAs)
+            int device = 0, n_sms = 148;
+            if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+            if ((long long)grid.x * grid.y * grid.z <= n_sms) return launch<128, 6>(ma, mb, p, grid, s);
+            return launch<128, 3>(ma, mb, p, grid, s);
+        }
         case 256: return launch<256, 4>(ma, mb, p, grid, s);
         default: return gk_fail(GK_BAD_ARGUMENT, "gemm_tc: bn must be 16, 32, 64, 128 or 256, got %d", bn);
     }
