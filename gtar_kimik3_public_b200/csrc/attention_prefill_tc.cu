@@ -323,11 +323,13 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const 
             }
             float mx = -INFINITY;
             const bool need_mask = key_base + PAGE - 1 > pos || p.window > 0;
+            const int hidden_upto = p.window > 0 ? pos - p.window : -1;  // keys up to here are behind the window
             if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
+                for (int c = 0; c < 64; ++c) {  // selects, not branches: the rows of a warp differ in what they see
                     const int key = key_base + c;
-                    if (key > pos || (p.window > 0 && key <= pos - p.window)) raw[c >> 5][c & 31] = 0xff800000u;  // -inf
+                    const bool hidden = (key > pos) | (key <= hidden_upto);
+                    raw[c >> 5][c & 31] = hidden ? 0xff800000u : raw[c >> 5][c & 31];  // -inf
                 }
             }
             {   // four independent chains keep the maximum off the critical path
@@ -416,6 +418,321 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const 
     }
 }
 
+// ---------------------------------------------------------------- the same with 128 keys per step
+// One block per SM with all 512 tensor-memory columns: two score buffers of 128 keys (two pages) each, so the
+// MMA warp forms the next scores while the softmax warps work on these; P (64 columns) and O (128) beside
+// them.  Eight softmax warps, two threads a row (the exponentials are what a step waits for longest).  A step of 128 keys costs as many tcgen05.mma as a step of 64 (an instruction costs about 84 cycles
+// whether its N is 64 or 128), and the chain of dependent steps of a query tile is half as long.  A block
+// takes two query tiles one after the other, the c-th from the end and the c-th from the start: under the
+// causal mask their work adds up to the same for every block, so one wave of blocks ends together.
+constexpr int KEYS2 = 2 * PAGE;
+constexpr uint32_t COL2_S = 0, COL2_P = 256, COL2_O = 320;  // S: 2 x 128, P: 64 (bf16 pairs), O: 128
+
+struct alignas(1024) Smem2 {
+    __nv_bfloat16 q[2][ROWS * 64];                      // two 64-wide halves of the head dim
+    __nv_bfloat16 k[KV_STAGES][2][2][PAGE * 64];        // [stage][half of the head dim][page of the step][64 keys x 128 bytes]
+    __nv_bfloat16 v[KV_STAGES][2][2][PAGE * 64];        // [stage][page of the step][half of the head dim][64 keys x 128 bytes]
+    uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES];
+    uint64_t s_full[2], s_empty[2], p_full, o_done, q_ready;
+    uint64_t max_ready[2], sum_ready;  // the two halves of the rows have left their maxima / sums
+    float row_max[2][2][ROWS];  // [step parity][half of the keys][row]
+    float row_sum[2][ROWS];
+    uint32_t tmem_base;
+};
+
+constexpr int THREADS2 = 320;  // TMA warp, MMA warp, eight softmax warps
+
+__global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                           const __grid_constant__ CUtensorMap map_v,
+                                                                           const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    Smem2& sm = *reinterpret_cast<Smem2*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.z, hk = blockIdx.y;
+    const int group = p.n_q / p.n_kv;
+    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
+    const int n_rows = q_len * group;
+    const int n_blocks = (n_rows + ROWS - 1) / ROWS;
+    if (2 * (int)blockIdx.x >= n_blocks) return;  // whole block, before any barrier or allocation
+    // the block's query tiles: the heavy one first
+    const int tile_of[2] = {n_blocks - 1 - (int)blockIdx.x, (int)blockIdx.x};
+    const int n_tiles = tile_of[0] > tile_of[1] ? 2 : 1;
+    const int len = p.kv_len[seq], past = len - q_len;
+    const int* pages = p.block_table + (size_t)p.slots[seq] * p.max_pages;
+    // pages [p_begin, p_end) of query tile u, in steps of two
+    auto span = [&](int u, int& p_begin, int& p_end) {
+        const int row0 = tile_of[u] * ROWS;
+        const int last_row = min(row0 + ROWS, n_rows) - 1;
+        const int max_pos = past + last_row / group, min_pos = past + row0 / group;
+        const int lo = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
+        p_begin = lo / PAGE;
+        p_end = max_pos / PAGE + 1;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(&sm.kv_full[s], 1);
+            mbar_init(&sm.kv_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&sm.s_full[b], 1);
+            mbar_init(&sm.s_empty[b], 256);
+            mbar_init(&sm.max_ready[b], 256);
+        }
+        mbar_init(&sm.p_full, 256);
+        mbar_init(&sm.o_done, 1);
+        mbar_init(&sm.q_ready, 256);
+        mbar_init(&sm.sum_ready, 256);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        pdl_launch_dependents();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512u));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    pdl_wait();  // queries and the new keys and values come from the kernel before
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: per step two pages of K and of V, each in two 64-wide halves
+            bool ok = true;
+            int g = 0;
+            for (int u = 0; u < n_tiles && ok; ++u) {
+                int p_begin, p_end;
+                span(u, p_begin, p_end);
+                for (int pg = p_begin; pg < p_end && ok; pg += 2, ++g) {
+                    const int s = g % KV_STAGES;
+                    if (g >= KV_STAGES) ok = mbar_wait(&sm.kv_empty[s], ((g / KV_STAGES) - 1) & 1);
+                    if (!ok) break;
+                    const int n_pages = min(2, p_end - pg);
+                    mbar_expect_tx(&sm.kv_full[s], (uint32_t)n_pages * 4 * PAGE * 64 * 2);
+                    for (int j = 0; j < n_pages; ++j) {
+                        const int y = (pages[pg + j] * p.n_kv + hk) * PAGE;
+                        tma_load_2d(sm.k[s][0][j], &map_k, 0, y, &sm.kv_full[s]);
+                        tma_load_2d(sm.k[s][1][j], &map_k, 64, y, &sm.kv_full[s]);
+                        tma_load_2d(sm.v[s][j][0], &map_v, 0, y, &sm.kv_full[s]);
+                        tma_load_2d(sm.v[s][j][1], &map_v, 64, y, &sm.kv_full[s]);
+                    }
+                }
+            }
+            if (!ok) atomicExch(p.error_flag, 41);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            const uint32_t id_s = idesc(ROWS, KEYS2, false), id_o = idesc(ROWS, D, true);
+            bool ok = true;
+            auto issue_qk = [&](int g) {  // the scores of step g into buffer g & 1
+                const int s = g % KV_STAGES, b = g & 1;
+                if (ok) ok = mbar_wait(&sm.kv_full[s], (g / KV_STAGES) & 1);
+                if (ok && g >= 2) ok = mbar_wait(&sm.s_empty[b], ((g >> 1) - 1) & 1);  // the softmax has taken what was there
+                if (!ok) return;
+                fence_after();
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint64_t da = desc_k_major(smem_u32(sm.q[k >> 2]) + (k & 3) * 32);
+                    const uint64_t db = desc_k_major(smem_u32(sm.k[s][k >> 2][0]) + (k & 3) * 32);
+                    umma_ss(tmem + COL2_S + b * KEYS2, da, db, id_s, k > 0);
+                }
+                umma_commit(&sm.s_full[b]);
+            };
+            int g = 0;
+            for (int u = 0; u < n_tiles && ok; ++u) {
+                int p_begin, p_end;
+                span(u, p_begin, p_end);
+                const int n_iter = (p_end - p_begin + 1) / 2;
+                ok = mbar_wait(&sm.q_ready, u & 1);
+                if (!ok) break;
+                fence_after();
+                issue_qk(g);
+                for (int i = 0; i < n_iter && ok; ++i, ++g) {
+                    if (i + 1 < n_iter) issue_qk(g + 1);  // the next scores while the softmax works on these
+                    if (!ok) break;
+                    const int s = g % KV_STAGES;
+                    ok = mbar_wait(&sm.p_full, g & 1);
+                    if (!ok) break;
+                    fence_after();
+#pragma unroll
+                    for (int j = 0; j < KEYS2 / 16; ++j) {
+                        // keys 16j .. 16j+15 of the step: page j / 4, 16 rows of 128 bytes further on per j in both halves
+                        const uint64_t db = desc_mn_major(smem_u32(sm.v[s][j >> 2][0]) + (j & 3) * 16 * 128, PAGE * 128);
+                        umma_ts(tmem + COL2_O, tmem + COL2_P + j * 8, db, id_o, i > 0 || j > 0);
+                    }
+                    umma_commit(&sm.kv_empty[s]);  // the pages' shared memory is free once these have read it
+                    umma_commit(&sm.o_done);       // and the accumulator holds this step
+                }
+            }
+            if (!ok) atomicExch(p.error_flag, 42);
+        }
+    } else {
+        // ---- softmax warps: two threads a row.  Warps 2-5 take keys 0..63 of a step, warps 6-9 keys 64..127 (a
+        // warp reaches the tensor-memory lanes of its quarter, warp % 4, whatever its columns); the halves of a
+        // row exchange their maxima through shared memory, keep a sum each and add the two at the end.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        bool ok = true;
+        int g = 0;
+        for (int u = 0; u < n_tiles && ok; ++u) {
+            int p_begin, p_end;
+            span(u, p_begin, p_end);
+            const int n_iter = (p_end - p_begin + 1) / 2;
+            const int row = tile_of[u] * ROWS + r;
+            const bool row_ok = row < n_rows;
+            const int tok = row_ok ? row / group : 0;
+            const int head = hk * group + (row_ok ? row % group : 0);
+            const int pos = past + tok;
+            // this thread's half of the Q row -> swizzled shared memory (zeros for rows beyond the sequence); the
+            // MMAs that read the tile before have finished (its last o_done was waited for below)
+            {
+                const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(q_begin + tok) * p.n_q + head) * D) + half * 8;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 val = row_ok ? src[c] : make_uint4(0, 0, 0, 0);
+                    uint4* dst = reinterpret_cast<uint4*>(sm.q[half]) + r * 8 + (c ^ (r & 7));
+                    *dst = val;
+                }
+                fence_async_smem();
+                mbar_arrive(&sm.q_ready);
+            }
+            float m_used = -INFINITY, l = 0.f;
+            for (int i = 0; i < n_iter && ok; ++i, ++g) {
+                const int s = g % KV_STAGES, b = g & 1;
+                const int key_base = (p_begin + 2 * i) * PAGE + half * 64;  // the first key this thread looks at
+                const uint32_t s_cols = tmem + lane_base + COL2_S + b * KEYS2 + half * 64;
+                ok = mbar_wait(&sm.s_full[b], (g >> 1) & 1);
+                if (!ok) break;
+                fence_after();
+                uint32_t raw[2][32];
+                tmem_ld32(s_cols, raw[0]);
+                tmem_ld32(s_cols + 32, raw[1]);
+                tmem_wait_ld();
+                fence_before();
+                mbar_arrive(&sm.s_empty[b]);  // the scores are in registers: the buffer may be overwritten
+                // rows of V beyond the sequence's length or beyond the pages this step loaded (a stale page end, no
+                // second page): zero them, so that probability 0 times whatever lies there cannot make a NaN
+                const int step_base = (p_begin + 2 * i) * PAGE;
+                const int valid = min(len - step_base, min(2, p_end - (p_begin + 2 * i)) * PAGE);
+                if (valid < KEYS2) {
+                    ok = mbar_wait(&sm.kv_full[s], (g / KV_STAGES) & 1);
+                    if (!ok) break;
+                    for (int idx = half * 128 + r; idx < (KEYS2 - valid) * 16; idx += 256) {
+                        const int vr = valid + idx / 16, chunk = idx % 16;
+                        reinterpret_cast<uint4*>(sm.v[s][vr >> 6][chunk >> 3])[(vr & 63) * 8 + (chunk & 7)] = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_async_smem();
+                }
+                // scores of keys the row must not see become -inf (whatever they were: stale keys may hold anything);
+                // only the steps on the diagonal, or with a window, come here
+                if (key_base + 63 > pos || p.window > 0) {
+                    const int hidden_upto = p.window > 0 ? pos - p.window : -1;  // keys up to here are behind the window
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {  // selects, not branches: the rows of a warp differ in what they see
+                        const int key = key_base + c;
+                        const bool hidden = (key > pos) | (key <= hidden_upto);
+                        raw[c >> 5][c & 31] = hidden ? 0xff800000u : raw[c >> 5][c & 31];
+                    }
+                }
+                float mx;
+                {   // four independent chains keep the maximum off the critical path
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(raw[c >> 5][c & 31]));
+                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                }
+                // the row's maximum over both halves
+                sm.row_max[g & 1][half][r] = mx;
+                mbar_arrive(&sm.max_ready[g & 1]);  // (release: the store above is visible to who sees the phase end)
+                ok = mbar_wait(&sm.max_ready[g & 1], (g >> 1) & 1);
+                if (!ok) break;
+                mx = fmaxf(mx, sm.row_max[g & 1][half ^ 1][r]);
+                const float m_new = fmaxf(m_used, mx * p.sl2);
+                float corr = 1.0f;  // rescale lazily: only when the maximum has grown by more than the threshold
+                if (m_new > m_used + RESCALE_THRESHOLD || m_used == -INFINITY) {
+                    corr = m_used == -INFINITY ? 0.f : exp2f(m_used - m_new);
+                    m_used = m_new;
+                }
+                const float ref = m_used == -INFINITY ? 0.f : m_used;
+                uint32_t packed[32];
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < 64; c += 2) {
+                    const float e0 = ex2(fmaf(__uint_as_float(raw[c >> 5][c & 31]), p.sl2, -ref));
+                    const float e1 = ex2(fmaf(__uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]), p.sl2, -ref));
+                    sum4[(c >> 1) & 3] += e0 + e1;
+                    __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
+                    packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+                }
+                l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+                // P and the accumulator may be touched only when the product of the step before has finished
+                if (g > 0) {
+                    ok = mbar_wait(&sm.o_done, (g - 1) & 1);
+                    if (!ok) break;
+                    fence_after();
+                }
+                if (i > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {  // this thread's half of the accumulator's columns
+#pragma unroll 1
+                    for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem + lane_base + COL2_O + c0, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+                        tmem_st32(tmem + lane_base + COL2_O + c0, o);
+                    }
+                }
+                tmem_st32(tmem + lane_base + COL2_P + half * 32, packed);
+                tmem_wait_st();
+                fence_before();
+                mbar_arrive(&sm.p_full);
+            }
+            if (!ok) break;
+            // ---- the tile's result: O / l, this thread's half of the columns; l is the sum of both halves' sums
+            sm.row_sum[half][r] = l;
+            mbar_arrive(&sm.sum_ready);
+            ok = mbar_wait(&sm.o_done, (g - 1) & 1);
+            if (ok) ok = mbar_wait(&sm.sum_ready, u & 1);
+            if (!ok) break;
+            fence_after();
+            const float inv = 1.0f / (sm.row_sum[0][r] + sm.row_sum[1][r]);
+            __nv_bfloat16* orow = p.out + ((size_t)(q_begin + tok) * p.n_q + head) * D;
+#pragma unroll 1
+            for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem + lane_base + COL2_O + c0, o);
+                tmem_wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 w;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+                        w.x = *reinterpret_cast<uint32_t*>(&h0);
+                        w.y = *reinterpret_cast<uint32_t*>(&h1);
+                        w.z = *reinterpret_cast<uint32_t*>(&h2);
+                        w.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(orow + c0 + c) = w;
+                    }
+                }
+            }
+            fence_before();  // (row_sum is written again only after the next tile's steps, each a barrier of all rows' threads)
+        }
+        if (!ok && lane == 0) atomicExch(p.error_flag, 43);
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -446,6 +763,8 @@ int make_page_map(CUtensorMap* map, const void* base, long long rows) {
     if (r != CUDA_SUCCESS) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
     return GK_OK;
 }
+
+int g_attention_prefill_keys = 0;  // 0: chosen by the size of the step, else 64 or 128
 
 }  // namespace
 
@@ -491,8 +810,37 @@ GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     const int group = n_q / n_kv;
     const long long blocks = ((long long)max_q_len * group + ROWS - 1) / ROWS;
     GK_REQUIRE(blocks <= 2147483647LL, "attention_prefill_tc: too many rows");
+    // 128 keys per step while its blocks (half as many, each with two query tiles) fit the GPU in one wave: the
+    // chain of dependent steps of the longest tile is then what the kernel takes, and it is half as long.  With
+    // more work than that the two resident blocks per SM of the 64-key kernel keep the SMs busier
+    // (measured: 46 against 58 us at 2,048 tokens, 495 against 437 us at 8,192).
+    int device = 0, n_sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+    const bool one_wave = ((blocks + 1) / 2) * n_kv * n_seqs <= n_sms;
+    if (g_attention_prefill_keys == KEYS2 || (g_attention_prefill_keys == 0 && one_wave)) {
+        const size_t smem2 = sizeof(Smem2) + 1024;
+        static bool configured2 = false;
+        if (!configured2) {
+            cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+            if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: %s", cudaGetErrorString(err));
+            configured2 = true;
+        }
+        dim3 grid2((unsigned)((blocks + 1) / 2), n_kv, n_seqs);
+        gk_launch(attention_prefill_tc2_kernel, grid2, dim3(THREADS2), smem2, (cudaStream_t)stream, mk, mv, p);
+        GK_CHECK_LAUNCH("attention_prefill_tc2");
+        return GK_OK;
+    }
     dim3 grid((unsigned)blocks, n_kv, n_seqs);
     gk_launch(attention_prefill_tc_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, mk, mv, p);
     GK_CHECK_LAUNCH("attention_prefill_tc");
     return GK_OK;
+}
+
+// Keys per step of the tcgen05 prefill attention: 128 (one block per SM, two score buffers, eight softmax warps,
+// pairs of query tiles), 64 (two blocks per SM, one query tile each), or 0 = chosen by the size of the step (the
+// default).  Returns the old setting.
+GK_EXPORT int gk_set_attention_prefill_keys(int keys) {
+    const int before = g_attention_prefill_keys;
+    g_attention_prefill_keys = keys == PAGE ? PAGE : keys == KEYS2 ? KEYS2 : 0;
+    return before;
 }

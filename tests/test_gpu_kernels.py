@@ -428,8 +428,20 @@ def test_swiglu_interleaved():
 
 
 # ------------------------------------------------------------------ bfloat16 flash prefill attention
+def prefill_attention(path, *args, **kwargs):
+    """``path``: "mma", "tcgen05_128" or "tcgen05_64" (the tcgen05 kernels with 128 or 64 keys per step)."""
+    if not path.startswith("tcgen05_"):
+        return F().attention_prefill(*args, tensor_cores=path, **kwargs)
+    before = F().set_attention_prefill_keys(int(path[8:]))
+    try:
+        return F().attention_prefill(*args, tensor_cores="tcgen05", **kwargs)
+    finally:
+        F().set_attention_prefill_keys(before)
+
+
 @pytest.mark.parametrize("n_q,n_kv,d,path", [(4, 4, 64, "mma"), (16, 8, 128, "mma"), (6, 2, 128, "mma"), (3, 1, 64, "mma"),
-                                              (16, 8, 128, "tcgen05"), (6, 2, 128, "tcgen05"), (4, 4, 128, "tcgen05")])
+                                              (16, 8, 128, "tcgen05_128"), (6, 2, 128, "tcgen05_128"), (4, 4, 128, "tcgen05_128"),
+                                              (16, 8, 128, "tcgen05_64"), (6, 2, 128, "tcgen05_64"), (4, 4, 128, "tcgen05_64")])
 def test_attention_prefill_bf16_varlen(n_q, n_kv, d, path):
     dtype = torch.bfloat16
     lens, past = [1, 777, 1000, 64, 130], [0, 700, 0, 0, 129]  # whole prompts, a continuation, a single token
@@ -443,16 +455,16 @@ def test_attention_prefill_bf16_varlen(n_q, n_kv, d, path):
         qs.append(q)
         cu.append(cu[-1] + n - p)
         wants.append(dense_attention(q.double(), k.double(), v.double(), p))
-    out = F().attention_prefill(torch.cat(qs).to(DEV), kv, torch.tensor(cu, dtype=torch.int32).to(DEV),
-                                torch.tensor(lens, dtype=torch.int32).to(DEV), slots.to(DEV),
-                                max(n - p for n, p in zip(lens, past)), d**-0.5, tensor_cores=path)
+    out = prefill_attention(path, torch.cat(qs).to(DEV), kv, torch.tensor(cu, dtype=torch.int32).to(DEV),
+                            torch.tensor(lens, dtype=torch.int32).to(DEV), slots.to(DEV),
+                            max(n - p for n, p in zip(lens, past)), d**-0.5)
     F().check_kernel_errors()
     got, want = out.double().cpu(), torch.cat(wants)
     assert torch.isfinite(got).all()
     assert (got - want).abs().max().item() < 1.5 * BF16_ULP * want.abs().max().item() + 2e-3
 
 
-@pytest.mark.parametrize("path", ["mma", "tcgen05"])
+@pytest.mark.parametrize("path", ["mma", "tcgen05_128", "tcgen05_64"])
 def test_attention_prefill_bf16_far_key_and_window(path):
     dtype, n_q, n_kv, d, n = torch.bfloat16, 4, 2, 128, 900
     kv, slots, table = scrambled_pages(1, n, n_kv, d, dtype, seed=15)
@@ -464,12 +476,12 @@ def test_attention_prefill_bf16_far_key_and_window(path):
     fill_pages(kv, table, int(slots[0]), k.to(dtype), v.to(dtype))
     args = (q.to(dtype).to(DEV), kv, torch.tensor([0, n], dtype=torch.int32).to(DEV), torch.tensor([n], dtype=torch.int32).to(DEV),
             slots.to(DEV), n, d**-0.5)
-    out = F().attention_prefill(*args, tensor_cores=path).double().cpu()
+    out = prefill_attention(path, *args).double().cpu()
     F().check_kernel_errors()
     assert (out[700:, 1] - v[5, 0].to(dtype).double()).abs().max() < 1e-2
     want = dense_attention(q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double(), 0)
     assert (out - want).abs().max() < 2e-2
-    win = F().attention_prefill(*args, window=100, tensor_cores=path).double().cpu()
+    win = prefill_attention(path, *args, window=100).double().cpu()
     want_w = dense_attention(q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double(), 0, 100)
     assert (win - want_w).abs().max() < 2e-2
     assert (win[700:, 1] - v[5, 0].to(dtype).double()).abs().max() > 0.1  # key 5 is outside every late token's window
