@@ -426,13 +426,17 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const 
 // takes two query tiles one after the other, the c-th from the end and the c-th from the start: under the
 // causal mask their work adds up to the same for every block, so one wave of blocks ends together.
 constexpr int KEYS2 = 2 * PAGE;
+constexpr int K_STAGES2 = 3;
 constexpr uint32_t COL2_S = 0, COL2_P = 256, COL2_O = 320;  // S: 2 x 128, P: 64 (bf16 pairs), O: 128
 
 struct alignas(1024) Smem2 {
     __nv_bfloat16 q[2][ROWS * 64];                      // two 64-wide halves of the head dim
-    __nv_bfloat16 k[KV_STAGES][2][2][PAGE * 64];        // [stage][half of the head dim][page of the step][64 keys x 128 bytes]
+    // K and V have rings of their own: the keys of a step are wanted a whole step before its values (the scores
+    // are formed ahead), and are free again as soon as the scores are, so three stages of keys and two of values
+    // keep a TMA load's 1.3 us off the chain of steps
+    __nv_bfloat16 k[K_STAGES2][2][2][PAGE * 64];        // [stage][half of the head dim][page of the step][64 keys x 128 bytes]
     __nv_bfloat16 v[KV_STAGES][2][2][PAGE * 64];        // [stage][page of the step][half of the head dim][64 keys x 128 bytes]
-    uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES];
+    uint64_t k_full[K_STAGES2], k_empty[K_STAGES2], v_full[KV_STAGES], v_empty[KV_STAGES];
     uint64_t s_full[2], s_empty[2], p_full, o_done, q_ready;
     uint64_t max_ready[2], sum_ready;  // the two halves of the rows have left their maxima / sums
     float row_max[2][2][ROWS];  // [step parity][half of the keys][row]
@@ -470,9 +474,13 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
     };
 
     if (threadIdx.x == 0) {
+        for (int s = 0; s < K_STAGES2; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+        }
         for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(&sm.kv_full[s], 1);
-            mbar_init(&sm.kv_empty[s], 1);
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&sm.s_full[b], 1);
@@ -498,25 +506,49 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- producer: per step two pages of K and of V, each in two 64-wide halves
+            // ---- producer: per step two pages of K and of V, each in two 64-wide halves; the keys run one step
+            // ahead of the values
             bool ok = true;
-            int g = 0;
-            for (int u = 0; u < n_tiles && ok; ++u) {
-                int p_begin, p_end;
-                span(u, p_begin, p_end);
-                for (int pg = p_begin; pg < p_end && ok; pg += 2, ++g) {
-                    const int s = g % KV_STAGES;
-                    if (g >= KV_STAGES) ok = mbar_wait(&sm.kv_empty[s], ((g / KV_STAGES) - 1) & 1);
-                    if (!ok) break;
-                    const int n_pages = min(2, p_end - pg);
-                    mbar_expect_tx(&sm.kv_full[s], (uint32_t)n_pages * 4 * PAGE * 64 * 2);
+            auto load = [&](int g, int pg, int p_end, bool keys) {
+                const int n_pages = min(2, p_end - pg);
+                if (keys) {
+                    const int s = g % K_STAGES2;
+                    if (g >= K_STAGES2) ok = mbar_wait(&sm.k_empty[s], ((g / K_STAGES2) - 1) & 1);
+                    if (!ok) return;
+                    mbar_expect_tx(&sm.k_full[s], (uint32_t)n_pages * 2 * PAGE * 64 * 2);
                     for (int j = 0; j < n_pages; ++j) {
                         const int y = (pages[pg + j] * p.n_kv + hk) * PAGE;
-                        tma_load_2d(sm.k[s][0][j], &map_k, 0, y, &sm.kv_full[s]);
-                        tma_load_2d(sm.k[s][1][j], &map_k, 64, y, &sm.kv_full[s]);
-                        tma_load_2d(sm.v[s][j][0], &map_v, 0, y, &sm.kv_full[s]);
-                        tma_load_2d(sm.v[s][j][1], &map_v, 64, y, &sm.kv_full[s]);
+                        tma_load_2d(sm.k[s][0][j], &map_k, 0, y, &sm.k_full[s]);
+                        tma_load_2d(sm.k[s][1][j], &map_k, 64, y, &sm.k_full[s]);
                     }
+                } else {
+                    const int s = g % KV_STAGES;
+                    if (g >= KV_STAGES) ok = mbar_wait(&sm.v_empty[s], ((g / KV_STAGES) - 1) & 1);
+                    if (!ok) return;
+                    mbar_expect_tx(&sm.v_full[s], (uint32_t)n_pages * 2 * PAGE * 64 * 2);
+                    for (int j = 0; j < n_pages; ++j) {
+                        const int y = (pages[pg + j] * p.n_kv + hk) * PAGE;
+                        tma_load_2d(sm.v[s][j][0], &map_v, 0, y, &sm.v_full[s]);
+                        tma_load_2d(sm.v[s][j][1], &map_v, 64, y, &sm.v_full[s]);
+                    }
+                }
+            };
+            // the steps of the block's tiles in one list: (first page, end page of the tile)
+            int g_k = 0, g_v = 0;          // steps whose keys / values have been asked for
+            int uk = 0, pk = 0, ek = 0;    // where the keys are: tile, next page, end page
+            int uv = 0, pv = 0, ev = 0;    // where the values are
+            if (n_tiles > 0) { span(0, pk, ek); pv = pk; ev = ek; }
+            auto advance = [&](int& u, int& pg, int& pe) {
+                pg += 2;
+                if (pg >= pe && ++u < n_tiles) span(u, pg, pe);
+            };
+            while (ok && (uk < n_tiles || uv < n_tiles)) {
+                if (uk < n_tiles && g_k <= g_v + 1) {  // keys at most two steps ahead of the values
+                    load(g_k++, pk, ek, true);
+                    advance(uk, pk, ek);
+                } else {
+                    load(g_v++, pv, ev, false);
+                    advance(uv, pv, ev);
                 }
             }
             if (!ok) atomicExch(p.error_flag, 41);
@@ -527,8 +559,8 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
             const uint32_t id_s = idesc(ROWS, KEYS2, false), id_o = idesc(ROWS, D, true);
             bool ok = true;
             auto issue_qk = [&](int g) {  // the scores of step g into buffer g & 1
-                const int s = g % KV_STAGES, b = g & 1;
-                if (ok) ok = mbar_wait(&sm.kv_full[s], (g / KV_STAGES) & 1);
+                const int s = g % K_STAGES2, b = g & 1;
+                if (ok) ok = mbar_wait(&sm.k_full[s], (g / K_STAGES2) & 1);
                 if (ok && g >= 2) ok = mbar_wait(&sm.s_empty[b], ((g >> 1) - 1) & 1);  // the softmax has taken what was there
                 if (!ok) return;
                 fence_after();
@@ -538,6 +570,7 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
                     const uint64_t db = desc_k_major(smem_u32(sm.k[s][k >> 2][0]) + (k & 3) * 32);
                     umma_ss(tmem + COL2_S + b * KEYS2, da, db, id_s, k > 0);
                 }
+                umma_commit(&sm.k_empty[s]);  // the keys' shared memory is free once the scores are formed
                 umma_commit(&sm.s_full[b]);
             };
             int g = 0;
@@ -554,6 +587,7 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
                     if (!ok) break;
                     const int s = g % KV_STAGES;
                     ok = mbar_wait(&sm.p_full, g & 1);
+                    if (ok) ok = mbar_wait(&sm.v_full[s], (g / KV_STAGES) & 1);
                     if (!ok) break;
                     fence_after();
 #pragma unroll
@@ -562,7 +596,7 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
                         const uint64_t db = desc_mn_major(smem_u32(sm.v[s][j >> 2][0]) + (j & 3) * 16 * 128, PAGE * 128);
                         umma_ts(tmem + COL2_O, tmem + COL2_P + j * 8, db, id_o, i > 0 || j > 0);
                     }
-                    umma_commit(&sm.kv_empty[s]);  // the pages' shared memory is free once these have read it
+                    umma_commit(&sm.v_empty[s]);  // the values' shared memory is free once these have read it
                     umma_commit(&sm.o_done);       // and the accumulator holds this step
                 }
             }
@@ -618,7 +652,7 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
                 const int step_base = (p_begin + 2 * i) * PAGE;
                 const int valid = min(len - step_base, min(2, p_end - (p_begin + 2 * i)) * PAGE);
                 if (valid < KEYS2) {
-                    ok = mbar_wait(&sm.kv_full[s], (g / KV_STAGES) & 1);
+                    ok = mbar_wait(&sm.v_full[s], (g / KV_STAGES) & 1);
                     if (!ok) break;
                     for (int idx = half * 128 + r; idx < (KEYS2 - valid) * 16; idx += 256) {
                         const int vr = valid + idx / 16, chunk = idx % 16;
@@ -764,7 +798,7 @@ int make_page_map(CUtensorMap* map, const void* base, long long rows) {
     return GK_OK;
 }
 
-int g_attention_prefill_keys = 0;  // 0: chosen by the size of the step, else 64 or 128
+int g_attention_prefill_keys = KEYS2;  // 128 (the default) or 64
 
 }  // namespace
 
@@ -810,14 +844,8 @@ GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     const int group = n_q / n_kv;
     const long long blocks = ((long long)max_q_len * group + ROWS - 1) / ROWS;
     GK_REQUIRE(blocks <= 2147483647LL, "attention_prefill_tc: too many rows");
-    // 128 keys per step while its blocks (half as many, each with two query tiles) fit the GPU in one wave: the
-    // chain of dependent steps of the longest tile is then what the kernel takes, and it is half as long.  With
-    // more work than that the two resident blocks per SM of the 64-key kernel keep the SMs busier
-    // (measured: 46 against 58 us at 2,048 tokens, 495 against 437 us at 8,192).
-    int device = 0, n_sms = 148;
-    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
-    const bool one_wave = ((blocks + 1) / 2) * n_kv * n_seqs <= n_sms;
-    if (g_attention_prefill_keys == KEYS2 || (g_attention_prefill_keys == 0 && one_wave)) {
+    // measured for one prompt: 42 against 58 us at 2,048 tokens, 396 against 442 us at 8,192
+    if (g_attention_prefill_keys == KEYS2) {
         const size_t smem2 = sizeof(Smem2) + 1024;
         static bool configured2 = false;
         if (!configured2) {
@@ -836,11 +864,10 @@ GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     return GK_OK;
 }
 
-// Keys per step of the tcgen05 prefill attention: 128 (one block per SM, two score buffers, eight softmax warps,
-// pairs of query tiles), 64 (two blocks per SM, one query tile each), or 0 = chosen by the size of the step (the
-// default).  Returns the old setting.
+// Keys per step of the tcgen05 prefill attention: 128 (the default: one block per SM, two score buffers, eight
+// softmax warps, pairs of query tiles) or 64 (two blocks per SM, one query tile each).  Returns the old setting.
 GK_EXPORT int gk_set_attention_prefill_keys(int keys) {
     const int before = g_attention_prefill_keys;
-    g_attention_prefill_keys = keys == PAGE ? PAGE : keys == KEYS2 ? KEYS2 : 0;
+    g_attention_prefill_keys = keys == PAGE ? PAGE : KEYS2;
     return before;
 }

@@ -588,9 +588,9 @@ def attention_prefill(
 
 
 def set_attention_prefill_keys(keys: int) -> int:
-    """Keys per step of the tcgen05 prefill attention: 128 (one block per SM, two score buffers, two threads a
-    row, a heavy and a light query tile per block), 64 (two blocks per SM, one query tile each) or 0 (the
-    default: 128 while its blocks fit the GPU in one wave, else 64).  Returns the old setting."""
+    """Keys per step of the tcgen05 prefill attention: 128 (the default: one block per SM, two score buffers,
+    two threads a row, a heavy and a light query tile per block) or 64 (two blocks per SM, one query tile
+    each).  Returns the old setting."""
     from .library import library
 
     return int(library().gk_set_attention_prefill_keys(int(keys)))
