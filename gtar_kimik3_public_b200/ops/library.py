@@ -104,17 +104,29 @@ def ptr(tensor: torch.Tensor | None) -> int | None:
     return None if tensor is None else tensor.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr() -> int:
+    """The current CUDA stream of the current device as a raw handle.  Asked for at every launch (a graph
+    capture switches streams), so through the one C call that does nothing else where torch has it: building
+    a ``torch.cuda.Stream`` object costs more than launching the kernel."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
 launch_count = 0  # entries into the kernel library since import (each is one or more kernel launches)
 
 
+_entries: dict[str, object] = {}  # name -> the library's function, looked up once
+
+
 def call(name: str, *args) -> None:
     global launch_count
     launch_count += 1
-    lib = library()
-    status = getattr(lib, name)(*args)
-    if status != 0:
-        raise KernelError(f"{name}: {lib.gk_last_error().decode(errors='replace')}")
+    entry = _entries.get(name)
+    if entry is None:
+        entry = _entries[name] = getattr(library(), name)
+    if entry(*args) != 0:
+        raise KernelError(f"{name}: {library().gk_last_error().decode(errors='replace')}")
