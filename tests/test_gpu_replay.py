@@ -138,3 +138,38 @@ def test_replayed_graph_steps_equal_plain_launches(tag, dtype):
             live = [r for r in live if r not in done]
         results.append(torch.cat(rows))
     assert torch.equal(results[0], results[1])
+
+
+@pytest.mark.parametrize("tag,dtype,n_requests", [("tiny_a", "bfloat16", 13), ("tiny_b", "bfloat16", 16), ("tiny_c", "bfloat16", 20),
+                                                  ("tiny_b", "float32", 13)])
+def test_decode_in_batches_of_more_than_eight(tag, dtype, n_requests):
+    """Nine to sixteen sequences take other kernel variants than a handful (two row blocks in the few-token
+    product), seventeen and more the many-token product: prompts of unequal lengths in one step, then eight
+    tokens each, the shorter requests ending earlier."""
+    lengths = [10 + (7 * i) % 60 for i in range(n_requests)]
+    requests = requests_for(tag, lengths, seed=23)
+    engine = load_engine(tag, dtype, max_tokens=n_requests * 128, max_seqs=n_requests)
+    poison(engine)
+    batch = list(range(n_requests))
+    prompt_len = {r: max(1, len(requests[r]) - 8 + (r % 3)) for r in batch}  # 6 to 8 tokens left to decode
+    got = {r: [] for r in batch}
+    logits = engine.step([_entry(r, requests[r][:prompt_len[r]], list(range(prompt_len[r]))) for r in batch])
+    offset = 0
+    for r in batch:
+        got[r].append(logits[offset:offset + prompt_len[r]])
+        offset += prompt_len[r]
+    fed = dict(prompt_len)
+    live = list(batch)
+    while live:
+        logits = engine.step([_entry(r, [requests[r][fed[r]]], [0]) for r in live])
+        for i, r in enumerate(live):
+            got[r].append(logits[i:i + 1])
+            fed[r] += 1
+        done = [r for r in live if fed[r] == len(requests[r])]
+        if done:
+            engine.end(done)
+        live = [r for r in live if r not in done]
+    for r in batch:
+        tokens = requests[r]
+        check_against_plain(tag, dtype, tokens, list(range(len(tokens))), torch.cat(got[r]), f"{tag} {dtype} request {r} of {n_requests}")
+    assert engine.cache.slots.n_used == 0
