@@ -190,7 +190,7 @@ def time_decode(model, batch: int, steps: int, warmup: int, sample_clocks: bool 
 
 def time_e2e(model, batch: int, steps: int, warmup: int) -> dict:
     """The same decode through the Python entry point: host token lists in, host token lists out,
-    every step a pinned host-to-device copy of its inputs and a device-to-host read of its tokens."""
+    every step a pinned host-to-device copy of its numbers and a device-to-host read of its tokens."""
     import torch
 
     from gtar_kimik3_public_b200.generate import Generator
@@ -207,8 +207,10 @@ def time_e2e(model, batch: int, steps: int, warmup: int) -> dict:
     torch.cuda.synchronize()
     timed = stamps[warmup:warmup + steps + 1]
     seconds = timed[-1] - timed[0]
-    # per step: tokens + positions + sequence index + starts + slots + lengths + wanted rows in, tokens out
-    h2d = 4 * (6 * batch + 1)
+    # per step: positions + sequence index + starts + slots + lengths + wanted rows in (the token ids a step
+    # chose stay on the device for the next step: the loop runs the device one step ahead of the host),
+    # tokens out; a sequence's page-table row follows every 64 steps and is not counted
+    h2d = 4 * (5 * batch + 1)
     return {"value": batch * steps / seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
 
 

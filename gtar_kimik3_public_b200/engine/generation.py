@@ -78,8 +78,23 @@ def form_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_batch: int
 Chooser = Callable[[object, list[int], list[int]], list[int]]  # (logits, request indices, steps) -> token ids
 
 
+@dataclass
+class DeviceChooser:
+    """The chooser in two halves, for an engine that can take a step's tokens from device memory:
+    ``choose(logits, request indices, steps)`` returns the token ids as a device tensor (int32 ``[n]``),
+    ``fetch(tokens)`` starts their copy to the host and returns a callable that waits for it and gives the
+    list.  With both, the next step is launched on the device's copy of the tokens before the host has
+    seen them, and the host's work on a step (stop tokens, bookkeeping, the next step's numbers) happens
+    while the device computes."""
+
+    choose: Callable
+    fetch: Callable
+    take: Callable  # (tokens on the device, row indices) -> those rows, on the device
+
+
 def run_generation(engine, prompts: Sequence[Sequence[int]], params: GenerationParams, choose: Chooser,
-                   request_offset: int = 0, on_step: Callable | None = None) -> list[list[int]]:
+                   request_offset: int = 0, on_step: Callable | None = None,
+                   device_chooser: DeviceChooser | None = None) -> list[list[int]]:
     """Generates for every prompt; returns the new tokens of each (the stop token included).
 
     ``engine`` offers ``step(entries) -> logits`` and ``end(ids)``, and a ``cache`` with
@@ -91,6 +106,10 @@ def run_generation(engine, prompts: Sequence[Sequence[int]], params: GenerationP
     cache = engine.cache
     batches = form_batches([len(p) for p in prompts], params.max_new_tokens, params.max_batch,
                            cache.n_pages * cache.page_size, cache.page_size, cache.max_seq_len, cache.max_seqs)
+    if device_chooser is not None and hasattr(engine, "decode_on_device"):
+        for batch in batches:
+            _run_batch_ahead(engine, prompts, params, device_chooser, request_offset, on_step, batch, outputs)
+        return outputs
     for batch in batches:
         live = [_Live(i, ("gen", request_offset + i)) for i in batch]
         entries = [StepEntry(s.request_id, list(prompts[s.index]), [len(prompts[s.index]) - 1]) for s in live]
@@ -126,3 +145,74 @@ def run_generation(engine, prompts: Sequence[Sequence[int]], params: GenerationP
                 engine.end(leftover)
             raise
     return outputs
+
+
+def _run_batch_ahead(engine, prompts, params: GenerationParams, chooser: DeviceChooser, request_offset: int,
+                     on_step: Callable | None, batch: list[int], outputs: list[list[int]]) -> None:
+    """One batch with the device one step ahead of the host.
+
+    The tokens a step chose stay on the device and are fed to the next step at once, for every sequence
+    that may go on (one that has reached ``max_new_tokens`` or the longest sequence certainly does not);
+    only then does the host wait for the step's tokens.  A sequence that turns out to have chosen a stop
+    token has been fed one step too many: that step's token for it is dropped, and its storage is given
+    back like any other's.  The tokens a sequence gets are the same as in the loop above.
+    """
+    cache = engine.cache
+    live = [_Live(i, ("gen", request_offset + i)) for i in batch]
+    try:
+        entries = [StepEntry(s.request_id, list(prompts[s.index]), [len(prompts[s.index]) - 1]) for s in live]
+        logits = engine.step(entries, keep_output=False)
+        rows = list(live)  # rows[i]: the sequence row i of the pending step's tokens belongs to
+        tokens_dev = chooser.choose(logits, [request_offset + s.index for s in rows], [0] * len(rows))
+        wait = chooser.fetch(tokens_dev)
+        while rows:
+            # --- the next step, on the device's copy of the pending tokens
+            def may_go_on(seq: _Live) -> bool:  # after the pending token
+                n = len(seq.produced) + 1
+                fed_length = len(prompts[seq.index]) + n
+                return n < params.max_new_tokens and not (cache.max_seq_len is not None and fed_length > cache.max_seq_len)
+            keep = [i for i, seq in enumerate(rows) if may_go_on(seq)]
+            next_rows, next_tokens_dev, next_wait = [], None, None
+            if keep:
+                next_rows = [rows[i] for i in keep]
+                fed = tokens_dev if len(keep) == len(rows) else chooser.take(tokens_dev, keep)
+                logits = engine.decode_on_device([s.request_id for s in next_rows], fed)
+                next_tokens_dev = chooser.choose(logits, [request_offset + s.index for s in next_rows],
+                                                 [len(s.produced) + 1 for s in next_rows])
+                next_wait = chooser.fetch(next_tokens_dev)
+            # --- the pending step's tokens on the host
+            tokens = wait()
+            if on_step is not None:
+                on_step(rows, tokens)
+            ended = []
+            for seq, token in zip(rows, tokens):
+                token = int(token)
+                seq.produced.append(token)
+                length_after = len(prompts[seq.index]) + len(seq.produced)
+                if (token in params.stop_ids or len(seq.produced) >= params.max_new_tokens
+                        or (cache.max_seq_len is not None and length_after > cache.max_seq_len)):
+                    ended.append(seq)
+                    outputs[seq.index] = seq.produced
+            if ended:
+                engine.end([s.request_id for s in ended])
+                live = [s for s in live if s not in ended]
+                gone = set(id(s) for s in ended)
+                if any(id(s) in gone for s in next_rows):  # fed one step too many: their rows of the next step are dropped
+                    still = [i for i, s in enumerate(next_rows) if id(s) not in gone]
+                    next_rows = [next_rows[i] for i in still]
+                    if next_rows:
+                        next_wait = _subset(next_wait, still)
+                        next_tokens_dev = chooser.take(next_tokens_dev, still)
+            rows, tokens_dev, wait = next_rows, next_tokens_dev, next_wait
+    except Exception:
+        leftover = [s.request_id for s in live if s.request_id in getattr(engine, "slot_of", {})]
+        if leftover:
+            engine.end(leftover)
+        raise
+
+
+def _subset(wait: Callable, keep: list[int]) -> Callable:
+    def waited():
+        tokens = wait()
+        return [tokens[i] for i in keep]
+    return waited

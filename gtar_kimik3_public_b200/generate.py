@@ -15,7 +15,7 @@ from typing import Sequence
 import torch
 
 from .engine.engine import Engine
-from .engine.generation import GenerationParams, run_generation
+from .engine.generation import DeviceChooser, GenerationParams, run_generation
 from .models.model import Model
 from .registry import architecture, config_from_file
 from .sampling.sampler import SamplingParams, choose
@@ -77,7 +77,28 @@ class Generator:
             tokens = choose(logits, sampling, keys[0], keys[1])
             return tokens.cpu().tolist()
 
-        outputs = run_generation(self.engine, prompts, params, chooser, on_step=on_step)
+        def choose_on_device(logits, request_indices, steps):
+            if sampling.temperature == 0:
+                return choose(logits, sampling, None, None)
+            keys = torch.tensor([request_indices, steps], dtype=torch.int32).pin_memory().to(device, non_blocking=True)
+            return choose(logits, sampling, keys[0], keys[1])
+
+        def fetch(tokens):
+            host = torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True)
+            host.copy_(tokens, non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record()
+
+            def wait():
+                arrived.synchronize()
+                return host.tolist()
+            return wait
+
+        def take(tokens, rows):
+            return tokens[torch.tensor(rows, dtype=torch.int64, device=tokens.device)]
+
+        ahead = DeviceChooser(choose_on_device, fetch, take) if device.type == "cuda" else None
+        outputs = run_generation(self.engine, prompts, params, chooser, on_step=on_step, device_chooser=ahead)
         self.engine.check()
         return outputs
 

@@ -124,3 +124,74 @@ def test_storage_is_given_back_when_a_step_fails():
     with pytest.raises(RuntimeError):
         run_generation(engine, [[1], [2]], GenerationParams(max_new_tokens=5), choose)
     assert engine.slot_of == {}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# the loop that runs the device one step ahead of the host
+class AheadEngine(ScriptedEngine):
+    """Also takes a step's tokens "from the device" (here: a list the loop has not looked into)."""
+
+    def __init__(self, **kwargs):
+        super().__init__(**kwargs)
+        self.device_steps = []
+
+    def decode_on_device(self, request_ids, tokens):
+        assert len(request_ids) == len(tokens) and all(i in self.slot_of for i in request_ids)
+        for i, t in zip(request_ids, tokens):
+            self.fed[i].append(t)
+        self.steps.append(list(request_ids))
+        self.device_steps.append(list(request_ids))
+        return [(i, list(self.fed[i])) for i in request_ids]
+
+
+def ahead_chooser_from(plan, log):
+    from gtar_kimik3_public_b200.engine.generation import DeviceChooser
+
+    def choose(logits, request_indices, steps):
+        return [plan[r][s] if s < len(plan[r]) else -1 for r, s in zip(request_indices, steps)]
+
+    def fetch(tokens):
+        log.append(("fetch", list(tokens)))
+        return lambda: list(tokens)
+
+    def take(tokens, rows):
+        return [tokens[i] for i in rows]
+
+    return DeviceChooser(choose, fetch, take)
+
+
+@pytest.mark.parametrize("prompts,plan,max_new,stops", [
+    ([[1, 2, 3], [4], [5, 6, 7, 8, 9]], {0: [10, 11, 99, 12], 1: [20, 21, 22, 23, 24], 2: [99]}, 4, {99}),
+    ([[1], [2, 3]], {0: [5, 6, 7], 1: [99, 1, 1]}, 3, {99}),
+    ([[1, 2]], {0: [7, 8, 9, 10, 11]}, 1, set()),
+    ([[1] * 10, [2] * 70, [3] * 30, [4] * 64, [5] * 5], {i: [7, 8, 99, 9, 9, 9, 9, 9] for i in range(5)}, 8, {99}),
+])
+def test_loop_one_step_ahead_gives_the_same_tokens(prompts, plan, max_new, stops):
+    params = GenerationParams(max_new_tokens=max_new, stop_ids=frozenset(stops), max_batch=3)
+    plain_engine = ScriptedEngine(n_pages=6, max_seqs=3)
+    want = run_generation(plain_engine, prompts, params, chooser_from(plan))
+    log = []
+    engine = AheadEngine(n_pages=6, max_seqs=3)
+    got = run_generation(engine, prompts, params, chooser_from(plan), device_chooser=ahead_chooser_from(plan, log))
+    assert got == want
+    assert engine.slot_of == {} and sorted(map(str, engine.ended)) == sorted(map(str, plain_engine.ended))
+    for request, fed in plain_engine.fed.items():
+        # the same tokens were fed, except that a sequence that chose a stop token was fed it once more
+        extra = engine.fed[request][len(fed):]
+        assert engine.fed[request][:len(fed)] == fed and len(extra) <= 1
+        if extra:
+            assert extra[0] in stops
+    # no step is launched for a sequence that has reached max_new_tokens
+    for request, fed in engine.fed.items():
+        assert len(fed) <= len(prompts[request[1]]) + max_new - 1
+
+
+def test_loop_one_step_ahead_respects_the_longest_sequence():
+    prompts = [[1] * 5, [2] * 3]
+    plan = {0: [7] * 20, 1: [8] * 20}
+    params = GenerationParams(max_new_tokens=20)
+    want = run_generation(ScriptedEngine(max_seq_len=8), prompts, params, chooser_from(plan))
+    engine = AheadEngine(max_seq_len=8)
+    got = run_generation(engine, prompts, params, chooser_from(plan), device_chooser=ahead_chooser_from(plan, []))
+    assert got == want and [len(o) for o in got] == [4, 6]
+    assert max(len(f) for f in engine.fed.values()) <= 8
