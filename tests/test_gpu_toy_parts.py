@@ -247,6 +247,6 @@ def test_toy_parts_run_in_bfloat16_too(tmp_path):
         engine = Engine(load(folder, dtype), max_tokens=128, max_seqs=1)
         outs[dtype] = engine.step([StepEntry(0, tokens, list(range(len(tokens))))]).float().cpu()
         engine.end([0])
-    # a token near a routing tie may go to another expert in bfloat16: judge the bulk, not the worst place
+    # a token near a routing tie may go to another expert in bfloat16: look at the bulk, not the worst place
     err = (outs["bfloat16"] - outs["float32"]).abs().amax(dim=-1)
     assert err.median() < 0.05 * outs["float32"].abs().max()
