@@ -260,18 +260,25 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
     }
     dim3 grid(blocks);
     const int groups_per_block = (n_groups + grid.x - 1) / grid.x;
-    const int items = groups_per_block * ((n_chunks + WARPS - 1) / WARPS);
-    const int round_items = items < ROUND_ITEMS ? items : ROUND_ITEMS;
-    // rows of the activations in shared memory: the same number of chunks for every warp, and an odd multiple
-    // of 64 bytes apart
-    int x_stride = ((n_chunks + WARPS - 1) / WARPS) * WARPS * CHUNK * 2;
-    if (x_stride % 128 == 0) x_stride += 64;
-    // (no copy of the activations in shared memory when they stay in registers)
     const int cpw = (n_chunks + WARPS - 1) / WARPS;
-    const int x_rows = (cpw <= X_REGS && items <= round_items) ? 0 : p.tokens > 8 ? 16 : 8;
-    const size_t smem = (size_t)round_items * THREADS * 16 + (size_t)x_rows * x_stride +
-                        (items > round_items ? (size_t)groups_per_block * THREADS * 16 : 0);
-    GK_REQUIRE(smem <= SMEM_MAX, "gemv: k = %d with %d tokens needs %zu bytes of shared memory, more than %zu", p.k, p.tokens, smem, SMEM_MAX);
+    const int items = groups_per_block * cpw;
+    // rows of the activations in shared memory: the same number of chunks for every warp, and an odd multiple
+    // of 64 bytes apart (none when they stay in registers: short K and all weights in one round)
+    int x_stride = cpw * WARPS * CHUNK * 2;
+    if (x_stride % 128 == 0) x_stride += 64;
+    const bool x_in_registers = cpw <= X_REGS && items <= ROUND_ITEMS;
+    const size_t x_bytes = x_in_registers ? 0 : (size_t)(p.tokens > 8 ? 16 : 8) * x_stride;
+    // weight pieces of as many chunks as fit beside them (a block whose share does not fit takes it in rounds and
+    // keeps its partial sums in a buffer of their own)
+    int round_items = items < ROUND_ITEMS ? items : ROUND_ITEMS;
+    const size_t partial_bytes = (size_t)groups_per_block * THREADS * 16;
+    if ((size_t)round_items * THREADS * 16 + x_bytes + (items > round_items ? partial_bytes : 0) > SMEM_MAX) {
+        const size_t fixed = x_bytes + partial_bytes;
+        GK_REQUIRE(fixed + THREADS * 16 <= SMEM_MAX, "gemv: k = %d with %d tokens needs %zu bytes of shared memory for the activations alone, more than %zu",
+                   p.k, p.tokens, fixed, SMEM_MAX);
+        round_items = (int)((SMEM_MAX - fixed) / (THREADS * 16));
+    }
+    const size_t smem = (size_t)round_items * THREADS * 16 + x_bytes + (items > round_items ? partial_bytes : 0);
     if (p.tokens > 8) gk_launch(gemv_mma_kernel<true>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
     else gk_launch(gemv_mma_kernel<false>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
     GK_CHECK_LAUNCH("gemv");

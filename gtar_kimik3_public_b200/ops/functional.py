@@ -364,6 +364,14 @@ def set_gemm_pairs(mode: int) -> int:
     return int(library().gk_set_gemm_pairs(int(mode)))
 
 
+def gemv_suits(m: int, n: int, k: int, device: torch.device) -> bool:
+    """Whether ``gemv`` is the kernel for ``[m, k] @ [n, k].T``: few tokens, few enough weight rows, and
+    activations that fit in shared memory beside a block's weights (it takes longer K too, in rounds, but
+    there the tensor-memory product is the better choice)."""
+    rows = 8 if m <= 8 else 16
+    return m <= GEMV_MAX_TOKENS and n <= gemv_max_rows(device) and (k <= 1024 or rows * k * 2 <= 96 * 1024)
+
+
 def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
          out: torch.Tensor | None = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` for up to 16 tokens: weights go from memory straight into registers and

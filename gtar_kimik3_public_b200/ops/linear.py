@@ -38,7 +38,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if not _tc_ok(x, weight):
         y = F.linear_bf16(x, weight, torch.bfloat16 if swiglu else out_dtype)
         return F.swiglu(y, interleaved=True) if swiglu else y
-    if x.shape[0] <= F.GEMV_MAX_TOKENS and weight.shape[0] <= F.gemv_max_rows(x.device):
+    if F.gemv_suits(x.shape[0], weight.shape[0], x.shape[1], x.device):
         return F.gemv(x, weight, torch.bfloat16 if swiglu else out_dtype, swiglu=swiglu)
     splits = F.split_k_for(x.shape[0], weight.shape[0], x.shape[1])
     return F.gemm_tc(x, weight, torch.bfloat16 if swiglu else out_dtype, swiglu=swiglu, splits=splits)

@@ -575,7 +575,9 @@ def test_gemm_tc_qkv_equals_projection_then_qk_kernel(n_q, n_kv, d, hidden, weig
     (8, 4096, 1024, False, torch.bfloat16), (8, 6144, 1024, True, torch.bfloat16), (1, 1024, 3072, False, torch.bfloat16),
     (16, 1024, 2048, False, torch.float32), (9, 1000, 200, False, torch.bfloat16), (3, 446, 72, True, torch.bfloat16),
     (5, 77, 8, False, torch.float32), (12, 9472, 64, False, torch.float32), (2, 7, 4104, False, torch.bfloat16),
-    (16, 6144, 1024, True, torch.bfloat16), (11, 1176, 520, False, torch.bfloat16)])
+    (16, 6144, 1024, True, torch.bfloat16), (11, 1176, 520, False, torch.bfloat16),
+    # a block's share of the weights exceeds shared memory: several rounds
+    (16, 4096, 4104, False, torch.bfloat16), (5, 9472, 520, True, torch.bfloat16), (8, 2048, 8192, False, torch.float32)])
 def test_gemv_against_plain_product(m, n, k, swiglu, out_dtype):
     x = rand(m, k, seed=1).to(torch.bfloat16)
     w = rand(n, k, seed=2, scale=k**-0.5).to(torch.bfloat16)
