@@ -67,6 +67,7 @@ struct GemmParams {
     int epilogue;
     int vector_ok;                     // rows of OUT start on 16-byte boundaries (stride_b == 1 case)
     int swiglu_vector_ok;              // rows of the SwiGLU output start on 16-byte boundaries
+    int rows32_ok;                     // rows of a row-major bfloat16 output (plain or SwiGLU) start on 32-byte boundaries
     int a_static, b_static;            // the operand is not written by the kernel before (weights): it may
                                        // be fetched before that kernel has finished
     int* error_flag;
@@ -147,7 +148,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+// x * sigmoid(x) with the fast division (two units in the last place of the 32-bit quotient, which is then rounded
+// to bfloat16): the exact one is a subroutine of a dozen instructions, and a 2,048-token gate|up product calls
+// it 6 million times in its output stage
+__device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 template <typename T>
 __device__ __forceinline__ void store_out(void* out, long long index, float v) {
@@ -223,6 +227,107 @@ __device__ __forceinline__ void write_chunk(const GemmParams& p, float (&v)[16],
                 const long long at = (long long)row_a * p.stride_a + (long long)(rb >> 1) * p.stride_b;
                 store_out<__nv_bfloat16>(out, at, silu(v[i]) * v[i + 1]);
             }
+        }
+    }
+}
+
+// ---- whole lines to memory.  A thread of the output stage owns one row of the tile, so a store instruction of
+// its warp touches 32 different lines with 16 bytes each, and the memory pipeline takes such requests at about
+// one in two cycles: the stores of a 128 x 256 tile then cost as much as its multiplications (measured: 650 to
+// 1,100 cycles for sixteen columns, against 28 for reading them out of tensor memory).  Shared memory is no
+// way round it, for the MMAs need its bandwidth.  So four lanes with four consecutive rows swap, by shuffles,
+// the four 32-byte pieces of 128 bytes of their rows: lane 4j + m ends up with piece m of the rows 4j .. 4j + 3,
+// and each of four 32-byte stores of the warp fills eight whole lines.
+__device__ __forceinline__ void pack8(const float* v, uint32_t* r) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        r[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+}
+
+// in: r[P m .. P m + P - 1] = piece m of this lane's row;  out: r[P i .. P i + P - 1] = piece (lane % 4) of row (lane - lane % 4) + i
+template <typename T, int P>
+__device__ __forceinline__ void swap_pieces(T* r, int lane) {
+#pragma unroll
+    for (int bit = 0; bit < 2; ++bit) {
+        const int step = 1 << bit;           // partner lane ^ step; slots s and s + step with (s & step) == 0
+        const bool upper = (lane & step) != 0;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            if (s & step) continue;
+#pragma unroll
+            for (int e = 0; e < P; ++e) {
+                T& lo = r[s * P + e];
+                T& hi = r[(s + step) * P + e];
+                const T got = __shfl_xor_sync(0xffffffffu, upper ? lo : hi, step);
+                if (upper) lo = got;
+                else hi = got;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void load32(const float* src, float (&v)[8]) {
+    asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(src));
+}
+__device__ __forceinline__ void store32(void* dst, const uint32_t* r) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]),
+                 "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+
+// The output stage for the accumulator columns c_begin .. c_end - 1 of this thread's row (`tile_col0` = B index of
+// the tile's first column): whole lines as above where the output is row-major bfloat16 (plain, or SwiGLU over
+// neighbouring columns) with aligned rows and the columns are whole, else sixteen at a time, each lane its row.
+__device__ __forceinline__ void write_columns(const GemmParams& p, uint32_t t_row, bool have_acc, int row_a, bool a_ok,
+                                              int tile_col0, int c_begin, int c_end, int lane) {
+    const bool plain = p.epilogue == EPI_STORE && p.stride_b == 1 && p.out_dtype == GK_BF16 && p.rows32_ok;
+    const bool swiglu = p.epilogue == EPI_SWIGLU_B && p.stride_b == 1 && p.rows32_ok;
+    const int span = plain ? 64 : 128;  // accumulator columns that make 128 bytes of output
+    auto load16 = [&](int c, float (&v)[16]) {
+        if (have_acc) {
+            tmem_ld16(t_row + c, v);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+    };
+#pragma unroll 1
+    for (int c0 = c_begin; c0 < c_end;) {
+        if ((plain || swiglu) && c0 + span <= c_end && tile_col0 + c0 + span <= p.rows_b) {
+            uint32_t r[32];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                float v[16];
+                if (plain) {
+                    load16(c0 + 16 * m, v);
+                    pack8(v, r + 8 * m);
+                    pack8(v + 8, r + 8 * m + 4);
+                } else {
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        load16(c0 + 32 * m + 16 * half, v);
+                        float o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = silu(v[2 * i]) * v[2 * i + 1];
+                        pack8(o, r + 8 * m + 4 * half);
+                    }
+                }
+            }
+            swap_pieces<uint32_t, 8>(r, lane);
+            const int first_row = row_a - (lane & 3);
+            __nv_bfloat16* at = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)first_row * p.stride_a +
+                                (plain ? tile_col0 + c0 : (tile_col0 + c0) >> 1) + (lane & 3) * 16;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (first_row + i < p.rows_a) store32(at + (long long)i * p.stride_a, r + 8 * i);
+            c0 += span;
+        } else {
+            float v[16];
+            load16(c0, v);
+            write_chunk(p, v, row_a, a_ok, tile_col0 + c0, lane);
+            c0 += 16;
         }
     }
 }
@@ -343,17 +448,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         const bool have_acc = n_kb > 0 && ok;
         const uint32_t t_row = tmem_acc + ((uint32_t)(quarter * 32) << 16);
         if (gridDim.z == 1) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float v[16];
-                if (have_acc) {
-                    tmem_ld16(t_row + c0, v);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                }
-                write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
-            }
+            write_columns(p, t_row, have_acc, row_a, a_ok, tile_b * BN, 0, BN, lane);
         } else {
             // split-K: this block's partial tile goes to its own shared memory, [column][row] float32,
             // over the pipeline stages (every copy has landed and every MMA has read them by now)
@@ -479,36 +574,111 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     }
 }
 
-// One token's share of one head: `v` holds the head's HD projection outputs in 32-bit.
+// One head of the 32 tokens of a warp: `v` holds the HD projection outputs of this lane's token in 32-bit.
+// Every lane of the warp calls it (the lanes work on one another's rows); `token_ok` = the lane's row is a token.
+// For a head size of 128 the lanes of a quad swap their rows' 16-column pieces first, so that lane 4j + m holds
+// the columns 16m .. 16m + 15 and 64 + 16m .. 64 + 16m + 15 (the two partners of the rotation) of the four
+// tokens 4j .. 4j + 3: a quad then reads a token's row of the cos and sin tables as whole lines and writes the
+// token's head as whole lines, where with a row per lane every load and store of the warp touched 32 lines.
 template <int HD>
-__device__ __forceinline__ void qkv_head(const QkvEpilogue& e, float (&v)[HD], int token, int head) {
+__device__ __forceinline__ void qkv_head(const QkvEpilogue& e, float (&v)[HD], int token, bool token_ok, int head, int lane) {
     const bool is_q = head < e.n_q, is_k = !is_q && head < e.n_q + e.n_kv;
-    const int pos = e.tok_pos[token];
-    __nv_bfloat16* dst;
-    if (is_q) {
+    if (!is_q && e.k_pages == nullptr) return;  // the same for the whole warp
+    const int pos = token_ok ? e.tok_pos[token] : 0;
+    __nv_bfloat16* dst = nullptr;
+    if (!token_ok) {
+    } else if (is_q) {
         dst = e.q_out + ((size_t)token * e.n_q + head) * HD;
     } else {
-        if (e.k_pages == nullptr) return;
         const int hk = is_k ? head - e.n_q : head - e.n_q - e.n_kv;
         const int page = e.block_table[(size_t)e.slots[e.tok_seq[token]] * e.max_pages + pos / e.page_size];
         const size_t at = (((size_t)page * e.n_kv + hk) * e.page_size + (pos % e.page_size)) * HD;
         dst = (is_k ? e.k_pages : e.v_pages) + at;
     }
-    if (is_q || is_k) {
-        if (e.use_norm) {
-            float ss = 0.f;
+    const bool normed = (is_q || is_k) && e.use_norm, rotated = (is_q || is_k) && e.cos_table != nullptr;
+    float inv = 1.0f;
+    if (normed) {
+        float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < HD; ++i) ss += v[i] * v[i];
-            const float inv = 1.0f / sqrtf(ss / (float)HD + e.eps);
-            const void* w = is_q ? e.wq : e.wk;
+        for (int i = 0; i < HD; ++i) ss += v[i] * v[i];
+        inv = 1.0f / sqrtf(ss / (float)HD + e.eps);
+    }
+    const void* w = is_q ? e.wq : e.wk;
+    auto weight = [&](int i) {
+        return e.weights_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]) : reinterpret_cast<const float*>(w)[i];
+    };
+    const unsigned long long dst_bits = reinterpret_cast<unsigned long long>(dst);
+    const int quad = lane & ~3, m = lane & 3;
+    if constexpr (HD == 128) {
+        swap_pieces<float, 16>(&v[0], lane);
+        swap_pieces<float, 16>(&v[64], lane);
+        // eight consecutive norm weights from index i (a multiple of 8)
+        auto weights8 = [&](int i, float (&out)[8]) {
+            if (e.weights_bf16) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w) + i);
+                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-            for (int i = 0; i < HD; ++i) {
-                const float wi = e.weights_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i])
-                                                : reinterpret_cast<const float*>(w)[i];
-                v[i] = (v[i] * inv) * wi;
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[j]));
+                    out[2 * j] = f.x;
+                    out[2 * j + 1] = f.y;
+                }
+            } else {
+                const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i);
+                const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i + 4);
+                out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+                out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
             }
+        };
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // token quad + i
+            float* lo = &v[16 * i];
+            float* hi = &v[64 + 16 * i];
+            const float inv_i = __shfl_sync(0xffffffffu, inv, quad + i);
+            const int pos_i = __shfl_sync(0xffffffffu, pos, quad + i);
+            const unsigned long long to = __shfl_sync(0xffffffffu, dst_bits, quad + i);
+            const float* cs = e.cos_table + (size_t)pos_i * (HD / 2) + 16 * m;
+            const float* sn = e.sin_table + (size_t)pos_i * (HD / 2) + 16 * m;
+#pragma unroll
+            for (int j0 = 0; j0 < 16; j0 += 8) {
+                if (normed) {
+                    float wl[8], wh[8];
+                    weights8(16 * m + j0, wl);
+                    weights8(64 + 16 * m + j0, wh);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        lo[j0 + j] = (lo[j0 + j] * inv_i) * wl[j];
+                        hi[j0 + j] = (hi[j0 + j] * inv_i) * wh[j];
+                    }
+                }
+                if (rotated) {
+                    float c[8], sv[8];
+                    load32(cs + j0, c);
+                    load32(sn + j0, sv);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float a = lo[j0 + j], b = hi[j0 + j];
+                        lo[j0 + j] = a * c[j] - b * sv[j];
+                        hi[j0 + j] = b * c[j] + a * sv[j];
+                    }
+                }
+            }
+            uint32_t r[8];
+            pack8(lo, r);
+            pack8(lo + 8, r + 4);
+            if (to) store32(reinterpret_cast<__nv_bfloat16*>(to) + 16 * m, r);
+            pack8(hi, r);
+            pack8(hi + 8, r + 4);
+            if (to) store32(reinterpret_cast<__nv_bfloat16*>(to) + 64 + 16 * m, r);
         }
-        if (e.cos_table) {
+    } else {
+        // a head of 64: the partners of the rotation are 32 apart, within a row's 64 columns, so the row is
+        // finished by its own lane and only its stores go through the swap
+        if (normed) {
+#pragma unroll
+            for (int i = 0; i < HD; ++i) v[i] = (v[i] * inv) * weight(i);
+        }
+        if (rotated) {
             const float4* c4 = reinterpret_cast<const float4*>(e.cos_table + (size_t)pos * (HD / 2));
             const float4* s4 = reinterpret_cast<const float4*>(e.sin_table + (size_t)pos * (HD / 2));
 #pragma unroll
@@ -523,24 +693,22 @@ __device__ __forceinline__ void qkv_head(const QkvEpilogue& e, float (&v)[HD], i
                 }
             }
         }
-    }
+        uint32_t r[32];
 #pragma unroll
-    for (int i = 0; i < HD; i += 8) {
-        uint4 w;
-        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]), h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]), h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
-        w.x = *reinterpret_cast<uint32_t*>(&h0);
-        w.y = *reinterpret_cast<uint32_t*>(&h1);
-        w.z = *reinterpret_cast<uint32_t*>(&h2);
-        w.w = *reinterpret_cast<uint32_t*>(&h3);
-        *reinterpret_cast<uint4*>(dst + i) = w;
+        for (int i = 0; i < HD / 8; ++i) pack8(&v[8 * i], r + 4 * i);
+        swap_pieces<uint32_t, 8>(r, lane);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const unsigned long long to = __shfl_sync(0xffffffffu, dst_bits, quad + i);
+            if (to) store32(reinterpret_cast<__nv_bfloat16*>(to) + 16 * m, r + 8 * i);
+        }
     }
 }
 
 // The heads of one half (`half` = 0, 1) of a 256-wide tile for the token of this thread's row; `t_row`
 // addresses the row's accumulator.  Every lane takes part in the tensor-memory loads; rows beyond the tokens do no more.
 template <int HD, int BN>
-__device__ __forceinline__ void qkv_tile(const GemmParams& p, uint32_t t_row, int row_a, bool a_ok, int tile_b, int half) {
+__device__ __forceinline__ void qkv_tile(const GemmParams& p, uint32_t t_row, int row_a, bool a_ok, int tile_b, int half, int lane) {
     const int n_heads = p.qkv.n_q + 2 * p.qkv.n_kv;
     constexpr int PER_HALF = BN / HD / 2;  // heads of the tile this warp takes
 #pragma unroll 1
@@ -555,7 +723,7 @@ __device__ __forceinline__ void qkv_tile(const GemmParams& p, uint32_t t_row, in
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[c0 + i] = part[i];
         }
-        if (a_ok) qkv_head<HD>(p.qkv, v, row_a, head);
+        qkv_head<HD>(p.qkv, v, row_a, a_ok, head, lane);
     }
 }
 
@@ -678,15 +846,10 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS, 1) gemm_tc_persistent_kern
             const uint32_t t_row = tmem + buf * BN + ((uint32_t)(quarter * 32) << 16);
             const bool a_ok = row_a < p.rows_a;
             if (p.epilogue == EPI_QKV) {
-                if (p.qkv.head_dim == 128) qkv_tile<128, BN>(p, t_row, row_a, a_ok, tile_b, half);
-                else qkv_tile<64, BN>(p, t_row, row_a, a_ok, tile_b, half);
+                if (p.qkv.head_dim == 128) qkv_tile<128, BN>(p, t_row, row_a, a_ok, tile_b, half, lane);
+                else qkv_tile<64, BN>(p, t_row, row_a, a_ok, tile_b, half, lane);
             } else {
-#pragma unroll 1
-                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 16) {
-                    float v[16];
-                    tmem_ld16(t_row + c0, v);
-                    write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
-                }
+                write_columns(p, t_row, true, row_a, a_ok, tile_b * BN, half * (BN / 2), (half + 1) * (BN / 2), lane);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.acc_empty[buf])) : "memory");
@@ -853,15 +1016,10 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS, 1) gemm_tc_pair_kernel(con
             const uint32_t t_row = tmem + buf * BN + ((uint32_t)(quarter * 32) << 16);
             const bool a_ok = row_a < p.rows_a;
             if (p.epilogue == EPI_QKV) {
-                if (p.qkv.head_dim == 128) qkv_tile<128, BN>(p, t_row, row_a, a_ok, tile_b, half);
-                else qkv_tile<64, BN>(p, t_row, row_a, a_ok, tile_b, half);
+                if (p.qkv.head_dim == 128) qkv_tile<128, BN>(p, t_row, row_a, a_ok, tile_b, half, lane);
+                else qkv_tile<64, BN>(p, t_row, row_a, a_ok, tile_b, half, lane);
             } else {
-#pragma unroll 1
-                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 16) {
-                    float v[16];
-                    tmem_ld16(t_row + c0, v);
-                    write_chunk(p, v, row_a, a_ok, tile_b * BN + c0, lane);
-                }
+                write_columns(p, t_row, true, row_a, a_ok, tile_b * BN, half * (BN / 2), (half + 1) * (BN / 2), lane);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -1029,6 +1187,7 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     p.epilogue = epilogue;
     p.vector_ok = stride_b == 1 && ((uintptr_t)out & 15) == 0 && (stride_a * (out_dtype == GK_F32 ? 4 : 2)) % 16 == 0;
     p.swiglu_vector_ok = ((uintptr_t)out & 15) == 0 && (stride_a * 2) % 16 == 0;
+    p.rows32_ok = ((uintptr_t)out & 31) == 0 && (stride_a * 2) % 32 == 0;
     p.a_static = a_static;
     p.b_static = b_static;
     p.error_flag = error_flag;
@@ -1077,9 +1236,11 @@ GK_EXPORT int gk_gemm_bf16_tc_qkv(const void* x, int n_tokens, const void* w_qkv
     GK_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "gemm_tc_qkv: cos and sin tables go together");
     GK_REQUIRE(cos_table == nullptr || max_position < table_positions,
                "gemm_tc_qkv: position %d is beyond the rotary table (%d positions)", max_position, table_positions);
-    GK_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w_qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
-                   ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0 && ((uintptr_t)cos_table & 15) == 0 &&
-                   ((uintptr_t)sin_table & 15) == 0, "gemm_tc_qkv: pointers must be 16-byte aligned");
+    GK_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w_qkv & 15) == 0 && ((uintptr_t)wq & 15) == 0 && ((uintptr_t)wk & 15) == 0,
+               "gemm_tc_qkv: operands and norm weights must be 16-byte aligned");
+    GK_REQUIRE(((uintptr_t)q_out & 31) == 0 && ((uintptr_t)k_pages & 31) == 0 && ((uintptr_t)v_pages & 31) == 0 &&
+                   ((uintptr_t)cos_table & 31) == 0 && ((uintptr_t)sin_table & 31) == 0,
+               "gemm_tc_qkv: queries, pages and rotary tables must be 32-byte aligned (they are read and written 32 bytes at a time)");
     GK_REQUIRE(error_flag != nullptr, "gemm_tc_qkv: error_flag is required");
     const int n = (n_q + 2 * n_kv) * head_dim;
     CUtensorMap ma, mb;
