@@ -618,17 +618,28 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
             const int row = tile_of[u] * ROWS + r;
             const bool row_ok = row < n_rows;
             const int tok = row_ok ? row / group : 0;
-            const int head = hk * group + (row_ok ? row % group : 0);
             const int pos = past + tok;
-            // this thread's half of the Q row -> swizzled shared memory (zeros for rows beyond the sequence); the
+            // Where this warp's half of the row `rr` of the tile lies in the queries or the output (null: no such row).
+            // The four lanes of a quad work on the rows of the quad together, 32 bytes of a row's 128 each, so that
+            // a load or store of the warp touches eight whole lines instead of 32 partly.
+            const int quad_row = quarter * 32 + (lane & ~3), piece = lane & 3;
+            auto row_at = [&](__nv_bfloat16* base, int rr) -> __nv_bfloat16* {
+                const int row_i = tile_of[u] * ROWS + rr;
+                if (row_i >= n_rows) return nullptr;
+                return base + ((size_t)(q_begin + row_i / group) * p.n_q + hk * group + row_i % group) * D + half * 64 + piece * 16;
+            };
+            // this warp's halves of its Q rows -> swizzled shared memory (zeros for rows beyond the sequence); the
             // MMAs that read the tile before have finished (its last o_done was waited for below)
             {
-                const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(q_begin + tok) * p.n_q + head) * D) + half * 8;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 val = row_ok ? src[c] : make_uint4(0, 0, 0, 0);
-                    uint4* dst = reinterpret_cast<uint4*>(sm.q[half]) + r * 8 + (c ^ (r & 7));
-                    *dst = val;
+                for (int i = 0; i < 4; ++i) {
+                    const int rr = quad_row + i;
+                    const __nv_bfloat16* src = row_at(const_cast<__nv_bfloat16*>(p.q), rr);
+                    uint32_t val[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    if (src) load32(src, val);
+                    uint4* dst = reinterpret_cast<uint4*>(sm.q[half]) + rr * 8;
+                    dst[(2 * piece) ^ (rr & 7)] = make_uint4(val[0], val[1], val[2], val[3]);
+                    dst[(2 * piece + 1) ^ (rr & 7)] = make_uint4(val[4], val[5], val[6], val[7]);
                 }
                 fence_async_smem();
                 mbar_arrive(&sm.q_ready);
@@ -733,27 +744,23 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
             if (!ok) break;
             fence_after();
             const float inv = 1.0f / (sm.row_sum[0][r] + sm.row_sum[1][r]);
-            __nv_bfloat16* orow = p.out + ((size_t)(q_begin + tok) * p.n_q + head) * D;
-#pragma unroll 1
-            for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
-                uint32_t o[32];
-                tmem_ld32(tmem + lane_base + COL2_O + c0, o);
-                tmem_wait_ld();
-                if (row_ok) {
+            uint32_t packed[32];  // this thread's 64 columns of its row, then 16 columns of each row of the quad
 #pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
-                        uint4 w;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-                        w.x = *reinterpret_cast<uint32_t*>(&h0);
-                        w.y = *reinterpret_cast<uint32_t*>(&h1);
-                        w.z = *reinterpret_cast<uint32_t*>(&h2);
-                        w.w = *reinterpret_cast<uint32_t*>(&h3);
-                        *reinterpret_cast<uint4*>(orow + c0 + c) = w;
-                    }
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem + lane_base + COL2_O + half * 64 + c0, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+                    packed[(c0 + c) >> 1] = *reinterpret_cast<uint32_t*>(&h);
                 }
+            }
+            swap_pieces<uint32_t, 8>(packed, lane);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __nv_bfloat16* dst = row_at(p.out, quad_row + i);
+                if (dst) store32(dst, packed + 8 * i);
             }
             fence_before();  // (row_sum is written again only after the next tile's steps, each a barrier of all rows' threads)
         }
@@ -812,8 +819,8 @@ GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill_tc: bad head counts %d/%d", n_q, n_kv);
     GK_REQUIRE(page_size == PAGE && head_dim == D, "attention_prefill_tc: needs page_size %d and head_dim %d", PAGE, D);
     GK_REQUIRE(n_kv <= 65535 && n_seqs <= 65535 && window >= 0 && max_q_len >= 0 && n_pages > 0, "attention_prefill_tc: bad sizes");
-    GK_REQUIRE(((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0 && ((uintptr_t)q & 15) == 0 &&
-                   ((uintptr_t)out & 15) == 0, "attention_prefill_tc: pointers must be 16-byte aligned");
+    GK_REQUIRE(((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0 && ((uintptr_t)q & 31) == 0 &&
+                   ((uintptr_t)out & 31) == 0, "attention_prefill_tc: pages must be 16-byte, queries and output 32-byte aligned");
     GK_REQUIRE(error_flag != nullptr, "attention_prefill_tc: error_flag is required");
     if (n_seqs == 0 || max_q_len == 0) return GK_OK;
     CUtensorMap mk, mv;

@@ -114,6 +114,58 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return scratch[32];
 }
 
+// ---- whole lines to memory.  A thread of the output stage owns one row of the tile, so a store instruction of
+// its warp touches 32 different lines with 16 bytes each, and the memory pipeline takes such requests at about
+// one in two cycles: the stores of a 128 x 256 tile then cost as much as its multiplications (measured: 650 to
+// 1,100 cycles for sixteen columns, against 28 for reading them out of tensor memory).  Shared memory is no
+// way round it, for the MMAs need its bandwidth.  So four lanes with four consecutive rows swap, by shuffles,
+// the four 32-byte pieces of 128 bytes of their rows: lane 4j + m ends up with piece m of the rows 4j .. 4j + 3,
+// and each of four 32-byte stores of the warp fills eight whole lines.
+__device__ __forceinline__ void pack8(const float* v, uint32_t* r) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        r[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+}
+
+// in: r[P m .. P m + P - 1] = piece m of this lane's row;  out: r[P i .. P i + P - 1] = piece (lane % 4) of row (lane - lane % 4) + i
+template <typename T, int P>
+__device__ __forceinline__ void swap_pieces(T* r, int lane) {
+#pragma unroll
+    for (int bit = 0; bit < 2; ++bit) {
+        const int step = 1 << bit;           // partner lane ^ step; slots s and s + step with (s & step) == 0
+        const bool upper = (lane & step) != 0;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            if (s & step) continue;
+#pragma unroll
+            for (int e = 0; e < P; ++e) {
+                T& lo = r[s * P + e];
+                T& hi = r[(s + step) * P + e];
+                const T got = __shfl_xor_sync(0xffffffffu, upper ? lo : hi, step);
+                if (upper) lo = got;
+                else hi = got;
+            }
+        }
+    }
+}
+
+// 32 bytes of a table that no kernel in flight writes
+__device__ __forceinline__ void load32(const float* src, float (&v)[8]) {
+    asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(src));
+}
+// 32 bytes that an earlier kernel may have written
+__device__ __forceinline__ void load32(const void* src, uint32_t (&v)[8]) {
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "l"(src) : "memory");
+}
+__device__ __forceinline__ void store32(void* dst, const uint32_t* r) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]),
+                 "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+
 // Dispatch on a dtype code: binds `T` in the body.
 #define GK_DISPATCH_DTYPE(code, T, ...)                  \
     if ((code) == GK_F32) {                              \
