@@ -631,15 +631,20 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
             // this warp's halves of its Q rows -> swizzled shared memory (zeros for rows beyond the sequence); the
             // MMAs that read the tile before have finished (its last o_done was waited for below)
             {
+                uint32_t val[4][8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {  // all four loads on their way before the first is used
+                    const __nv_bfloat16* src = row_at(const_cast<__nv_bfloat16*>(p.q), quad_row + i);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) val[i][j] = 0u;
+                    if (src) load32(src, val[i]);
+                }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int rr = quad_row + i;
-                    const __nv_bfloat16* src = row_at(const_cast<__nv_bfloat16*>(p.q), rr);
-                    uint32_t val[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    if (src) load32(src, val);
                     uint4* dst = reinterpret_cast<uint4*>(sm.q[half]) + rr * 8;
-                    dst[(2 * piece) ^ (rr & 7)] = make_uint4(val[0], val[1], val[2], val[3]);
-                    dst[(2 * piece + 1) ^ (rr & 7)] = make_uint4(val[4], val[5], val[6], val[7]);
+                    dst[(2 * piece) ^ (rr & 7)] = make_uint4(val[i][0], val[i][1], val[i][2], val[i][3]);
+                    dst[(2 * piece + 1) ^ (rr & 7)] = make_uint4(val[i][4], val[i][5], val[i][6], val[i][7]);
                 }
                 fence_async_smem();
                 mbar_arrive(&sm.q_ready);

@@ -151,9 +151,9 @@ __device__ __forceinline__ void swap_pieces(T* r, int lane) {
     }
 }
 
-// 32 bytes of a table that no kernel in flight writes
+// 32 bytes of a table that no kernel in flight writes (not volatile: the compiler may issue it early)
 __device__ __forceinline__ void load32(const float* src, float (&v)[8]) {
-    asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+    asm("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                  : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(src));
 }
 // 32 bytes that an earlier kernel may have written
