@@ -613,7 +613,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
     _check(out, "out", torch.int32, 1)
     # few rows of a wide vocabulary: several blocks share a row so that the scan uses the whole GPU
-    parts = max(1, min(296 // max(n, 1), vocab // 4096, 64))
+    parts = max(1, min(1184 // max(n, 1), vocab // 4096, 64))
     scratch = torch.empty((n * parts * 2,), dtype=torch.int32, device=logits.device) if parts > 1 else None
     call("gk_argmax", ptr(logits), vocab, n, vocab, ptr(out), parts, ptr(scratch), stream_ptr())
     return out
@@ -643,9 +643,13 @@ def sample(
     if out is None:
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
     _check(out, "out", torch.int32, 1)
+    # as for argmax: several blocks share a row; eight bytes of scratch per row for the top-k thresholds (four
+    # used) and eight per row and part for the parts' results
+    parts = max(1, min(1184 // max(n, 1), vocab // 4096, 64))
+    scratch = torch.empty((2 * ((n + 1) // 2) + 2 * n * parts,), dtype=torch.int32, device=logits.device)
     call(
         "gk_sample", ptr(logits), vocab, n, vocab, float(temperature), int(top_k or 0), int(seed) & (2**64 - 1),
-        ptr(request_ids), ptr(steps), int(advance_steps), ptr(out), stream_ptr(),
+        ptr(request_ids), ptr(steps), int(advance_steps), ptr(out), parts, ptr(scratch), stream_ptr(),
     )
     return out
 

@@ -301,6 +301,20 @@ def test_sample_matches_the_plain_sampler(vocab, top_k):
     assert torch.equal(steps_dev.cpu(), steps + 1)
 
 
+@pytest.mark.parametrize("n", [40, 100, 400])
+def test_sample_and_argmax_with_many_rows(n):
+    """The number of blocks that share a row falls as the rows grow (eight, four, two, one for the top-k
+    threshold); the choice must not depend on it."""
+    vocab, top_k, seed, temperature = 5003, 7, 99, 1.3
+    logits = rand(n, vocab, seed=3, scale=2.0).float()
+    requests = torch.arange(n, dtype=torch.int32)
+    steps = (torch.arange(n, dtype=torch.int32) * 7) % 13
+    got = F().sample(logits.to(DEV), temperature, top_k, seed, requests.to(DEV), steps.to(DEV)).cpu().tolist()
+    want = [plain_sampling.sample(logits[i].numpy(), temperature, top_k, seed, int(requests[i]), int(steps[i])) for i in range(n)]
+    assert got == want
+    assert F().argmax(logits.to(DEV)).cpu().tolist() == logits.argmax(-1).tolist()
+
+
 def test_sample_follows_the_softmax():
     logits = torch.tensor([[1.0, 0.0, -1.0, 2.0, 0.5]]).repeat(4096, 1)
     z = logits[0].double() / 0.7
