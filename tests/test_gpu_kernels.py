@@ -385,7 +385,8 @@ def test_attention_decode_bf16_far_key_and_window():
 
 # ------------------------------------------------------------------ tcgen05 matrix product
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 256, 128), (8, 4096, 1024), (13, 1000, 200), (64, 384, 1024),
-                                   (65, 128, 64), (128, 128, 128), (200, 1000, 520), (2048, 1024, 3072), (300, 151936, 1024)])
+                                   (65, 128, 64), (128, 128, 128), (200, 1000, 520), (2048, 1024, 3072), (300, 151936, 1024),
+                                   (203, 1008, 520)])  # the last: rows end inside a quad of lanes, columns inside a tile
 def test_gemm_tc_plain(m, n, k):
     x = rand(m, k, seed=1).to(torch.bfloat16)
     w = rand(n, k, seed=2, scale=0.05).to(torch.bfloat16)
@@ -421,7 +422,7 @@ def test_gemm_tc_split_k(m, n, k, splits):
 
 
 @pytest.mark.parametrize("m,inter,k,splits", [(8, 3072, 1024, 1), (8, 3072, 1024, 2), (5, 100, 72, 1), (64, 224, 80, 2),
-                                               (300, 224, 136, 1), (2048, 3072, 1024, 1)])
+                                               (300, 224, 136, 1), (2048, 3072, 1024, 1), (203, 528, 136, 1)])
 def test_gemm_tc_swiglu(m, inter, k, splits):
     x = rand(m, k, seed=5).to(torch.bfloat16)
     gate = rand(inter, k, seed=6, scale=0.1).to(torch.bfloat16)
