@@ -1,4 +1,4 @@
-// Product of a few tokens with a weight matrix,  OUT[t, n] = sum_k X[t, k] * W[n, k]  for up to 16 tokens
+// Product of a few tokens with a weight matrix,  OUT[t, n] = sum_k X[t, k] * W[n, k]  for up to 16 tokens (32 for short K)
 // (every projection of a decode step: src/layers/attention.py:62-65, src/layers/swiglu.py:9-14), built for
 // latency rather than arithmetic: with so few tokens the time goes to getting the weights in, not to the
 // multiplications.
@@ -58,15 +58,20 @@ __device__ __forceinline__ void copy16_async(void* smem_dst, const void* src, in
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
 
-// TWO_ROWS: more than eight tokens (the MMA's rows 8..15 are tokens 8..15, else zero).
+// ROW_SETS: sets of eight tokens, 1, 2 or 4.  An MMA takes two sets on its rows 0..7 and 8..15 (with one set the
+// upper rows are zero); with four sets (17 to 32 tokens) every weight piece goes through two MMAs' worth of
+// tokens, with the activations of all of them in registers: short K only (a warp has at most four chunks), all
+// weights in one round, and two partial sums a thread where the group's first two weight pieces were.
 // Shared memory: [item of the round][thread] 16-byte weight pieces; the tokens' activations, a row every
 // `x_stride` bytes (the rows of two tokens a quarter-warp reads together lie in different banks); and, when the
 // weights come in more than one round, [group of the block][thread] partial sums (with one round a thread
 // leaves its partial sum where the group's first weight piece was).
-template <bool TWO_ROWS>
-__global__ void __launch_bounds__(THREADS, TWO_ROWS ? 3 : 4) gemv_mma_kernel(const GemvParams p, int round_items, int x_stride) {
+template <int ROW_SETS>
+__global__ void __launch_bounds__(THREADS, ROW_SETS == 4 ? 2 : ROW_SETS == 2 ? 3 : 4) gemv_mma_kernel(const GemvParams p, int round_items, int x_stride) {
     extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int X_ROWS = TWO_ROWS ? 16 : 8;
+    constexpr bool TWO_ROWS = ROW_SETS >= 2;
+    constexpr int TILES = (ROW_SETS + 1) / 2;  // MMAs' worth of tokens
+    constexpr int X_ROWS = 8 * ROW_SETS;
     uint4* pieces = reinterpret_cast<uint4*>(smem);
     unsigned char* xs = smem + (size_t)round_items * THREADS * 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -104,19 +109,21 @@ __global__ void __launch_bounds__(THREADS, TWO_ROWS ? 3 : 4) gemv_mma_kernel(con
     // after the block's barrier: warp g of the block finishes the block's g-th group
     auto finish = [&]() {
         if (warp >= my_groups) return;
-        // the warps' sums in their order
-        const float4* slots = partial + (size_t)warp * partial_step + lane;
+        const int col = ((int)blockIdx.x + warp * (int)gridDim.x) * ROWS + 2 * piece;
+#pragma unroll
+        for (int tile = 0; tile < TILES; ++tile) {
+        // the warps' sums in their order (a tile's partial sums lie THREADS pieces after the tile before)
+        const float4* slots = partial + (size_t)warp * partial_step + tile * THREADS + lane;
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
             const float4 v = slots[w * 32];
             sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
         }
-        // sum[0], sum[1]: token `group`, weight rows col and col + 1;  sum[2], sum[3]: token group + 8
-        const int col = ((int)blockIdx.x + warp * (int)gridDim.x) * ROWS + 2 * piece;
+        // sum[0], sum[1]: token `group` of the tile, weight rows col and col + 1;  sum[2], sum[3]: token group + 8
 #pragma unroll
         for (int half = 0; half < (TWO_ROWS ? 2 : 1); ++half) {
-            const int token = group + 8 * half;
+            const int token = 16 * tile + group + 8 * half;
             if (token >= p.tokens) continue;
             const float a = sum[2 * half], b = sum[2 * half + 1];
             if (p.swiglu) {
@@ -136,6 +143,7 @@ __global__ void __launch_bounds__(THREADS, TWO_ROWS ? 3 : 4) gemv_mma_kernel(con
                 }
             }
         }
+        }
     };
 
     request(0);  // before the kernel in front has finished
@@ -144,33 +152,49 @@ __global__ void __launch_bounds__(THREADS, TWO_ROWS ? 3 : 4) gemv_mma_kernel(con
     const uint4* wp = pieces + threadIdx.x;
     if (cpw <= X_REGS && one_round) {
         // short K: the thread's pieces of the activations straight from memory into registers, no staging
-        uint4 xr[X_REGS], xr2[X_REGS];
+        uint4 xr[TILES][X_REGS], xr2[TILES][X_REGS];
 #pragma unroll
-        for (int j = 0; j < X_REGS; ++j) {
-            const int k = (warp + j * WARPS) * CHUNK + piece * 8;
-            const bool in = j < cpw && k < p.k;
-            xr[j] = in && group < p.tokens ? *reinterpret_cast<const uint4*>(p.x + (size_t)group * p.ldx + k) : zero;
-            xr2[j] = TWO_ROWS && in && group + 8 < p.tokens ? *reinterpret_cast<const uint4*>(p.x + (size_t)(group + 8) * p.ldx + k) : zero;
+        for (int tile = 0; tile < TILES; ++tile) {
+#pragma unroll
+            for (int j = 0; j < X_REGS; ++j) {
+                const int k = (warp + j * WARPS) * CHUNK + piece * 8;
+                const bool in = j < cpw && k < p.k;
+                const int token = 16 * tile + group;
+                xr[tile][j] = in && token < p.tokens ? *reinterpret_cast<const uint4*>(p.x + (size_t)token * p.ldx + k) : zero;
+                xr2[tile][j] = TWO_ROWS && in && token + 8 < p.tokens ? *reinterpret_cast<const uint4*>(p.x + (size_t)(token + 8) * p.ldx + k) : zero;
+            }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         for (int g = 0; g < my_groups; ++g) {
-            float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+            float acc0[TILES][4], acc1[TILES][4];
+#pragma unroll
+            for (int tile = 0; tile < TILES; ++tile) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc0[tile][i] = acc1[tile][i] = 0.f;
+            }
 #pragma unroll
             for (int j = 0; j < X_REGS; ++j) {
                 if (j < cpw) {
                     const uint4 wv = *wp;
                     wp += THREADS;
-                    mma_bf16(acc0, xr[j].x, xr2[j].x, xr[j].y, xr2[j].y, wv.x, wv.y);
-                    mma_bf16(acc1, xr[j].z, xr2[j].z, xr[j].w, xr2[j].w, wv.z, wv.w);
+#pragma unroll
+                    for (int tile = 0; tile < TILES; ++tile) {
+                        mma_bf16(acc0[tile], xr[tile][j].x, xr2[tile][j].x, xr[tile][j].y, xr2[tile][j].y, wv.x, wv.y);
+                        mma_bf16(acc1[tile], xr[tile][j].z, xr2[tile][j].z, xr[tile][j].w, xr2[tile][j].w, wv.z, wv.w);
+                    }
                 }
             }
-            partial[(size_t)g * partial_step + threadIdx.x] =
-                make_float4(acc0[0] + acc1[0], acc0[1] + acc1[1], acc0[2] + acc1[2], acc0[3] + acc1[3]);
+#pragma unroll
+            for (int tile = 0; tile < TILES; ++tile)
+                partial[(size_t)g * partial_step + tile * THREADS + threadIdx.x] =
+                    make_float4(acc0[tile][0] + acc1[tile][0], acc0[tile][1] + acc1[tile][1], acc0[tile][2] + acc1[tile][2],
+                                acc0[tile][3] + acc1[tile][3]);
         }
         __syncthreads();
         finish();
         return;
     }
+    if (ROW_SETS == 4) return;  // (the host sends 17 to 32 tokens here only where the path above applies)
     // the activations of all tokens into shared memory; zeros for the rows that are no token and from K up to
     // the end of the last chunk any warp looks at
     const int x_pieces = cpw * WARPS * 4;  // 16-byte pieces of a row
@@ -242,8 +266,9 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
         int device = 0;
         cudaError_t err = cudaGetDevice(&device);
         if (err == cudaSuccess) err = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
-        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
-        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (err != cudaSuccess) { n_sms = 0; return gk_fail(GK_CUDA_ERROR, "gemv: %s", cudaGetErrorString(err)); }
     }
     const int n_groups = (p.n + ROWS - 1) / ROWS;
@@ -279,20 +304,27 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
         round_items = (int)((SMEM_MAX - fixed) / (THREADS * 16));
     }
     const size_t smem = (size_t)round_items * THREADS * 16 + x_bytes + (items > round_items ? partial_bytes : 0);
-    if (p.tokens > 8) gk_launch(gemv_mma_kernel<true>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
-    else gk_launch(gemv_mma_kernel<false>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
+    if (p.tokens > 16) {
+        GK_REQUIRE(x_in_registers && cpw >= 2, "gemv: 17 to 32 tokens need 257 <= k <= 1024 and a block's weights in one round; got k = %d, %d pieces a thread",
+                   p.k, items);
+        gk_launch(gemv_mma_kernel<4>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
+    } else if (p.tokens > 8) {
+        gk_launch(gemv_mma_kernel<2>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
+    } else {
+        gk_launch(gemv_mma_kernel<1>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
+    }
     GK_CHECK_LAUNCH("gemv");
     return GK_OK;
 }
 
 }  // namespace
 
-// OUT[t, :] = x[t, :] @ w^T for 1 to 16 tokens and up to 64 weight rows per SM; `w` [n, k] and `x` [tokens, k]
+// OUT[t, :] = x[t, :] @ w^T for 1 to 16 tokens (17 to 32 where 257 <= k <= 1024) and up to 64 weight rows per SM; `w` [n, k] and `x` [tokens, k]
 // bfloat16 with rows in steps of 8 elements (16 bytes); OUT bfloat16 or float32, [tokens, n], or with `swiglu`
 // [tokens, n / 2] bfloat16 = silu(even rows) * odd rows.
 GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const void* x, int tokens, long long ldx, void* out,
                            int out_dtype, int swiglu, void* stream) {
-    GK_REQUIRE(n > 0 && k > 0 && tokens > 0 && tokens <= 16, "gemv: takes 1 to 16 tokens and positive sizes; got %d tokens, n=%d k=%d",
+    GK_REQUIRE(n > 0 && k > 0 && tokens > 0 && tokens <= 32, "gemv: takes 1 to 32 tokens and positive sizes; got %d tokens, n=%d k=%d",
                tokens, n, k);
     GK_REQUIRE(k % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0, "gemv: k and the row strides must be multiples of 8 elements; got k=%d ldw=%lld ldx=%lld",
                k, ldw, ldx);

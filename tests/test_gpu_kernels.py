@@ -592,7 +592,10 @@ def test_gemm_tc_qkv_equals_projection_then_qk_kernel(n_q, n_kv, d, hidden, weig
     (5, 77, 8, False, torch.float32), (12, 9472, 64, False, torch.float32), (2, 7, 4104, False, torch.bfloat16),
     (16, 6144, 1024, True, torch.bfloat16), (11, 1176, 520, False, torch.bfloat16),
     # a block's share of the weights exceeds shared memory: several rounds
-    (16, 4096, 4104, False, torch.bfloat16), (5, 9472, 520, True, torch.bfloat16), (8, 2048, 8192, False, torch.float32)])
+    (16, 4096, 4104, False, torch.bfloat16), (5, 9472, 520, True, torch.bfloat16), (8, 2048, 8192, False, torch.float32),
+    # 17 to 32 tokens: two MMAs' worth of tokens per weight piece, all activations in registers
+    (17, 4096, 1024, False, torch.bfloat16), (32, 6144, 1024, True, torch.bfloat16), (25, 1000, 264, False, torch.float32),
+    (31, 446, 520, True, torch.bfloat16)])
 def test_gemv_against_plain_product(m, n, k, swiglu, out_dtype):
     x = rand(m, k, seed=1).to(torch.bfloat16)
     w = rand(n, k, seed=2, scale=k**-0.5).to(torch.bfloat16)
@@ -607,12 +610,15 @@ def test_gemv_against_plain_product(m, n, k, swiglu, out_dtype):
 
 
 def test_gemv_refuses_what_it_cannot_take():
-    x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)
-    w = torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV)
-    with pytest.raises(Exception, match="16 tokens"):
+    x = torch.zeros(33, 512, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 512, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(Exception, match="32 tokens"):
         F().gemv(x, w)
+    with pytest.raises(Exception, match="17 to 32 tokens"):  # K too long for the activations to stay in registers
+        F().gemv(torch.zeros(17, 2048, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 2048, dtype=torch.bfloat16, device=DEV))
+    assert not F().gemv_suits(17, 1024, 2048, torch.device(DEV)) and F().gemv_suits(17, 4096, 1024, torch.device(DEV))
     with pytest.raises(Exception, match="weight rows"):
-        F().gemv(x[:2], torch.zeros(F().gemv_max_rows(torch.device(DEV)) + 8, 64, dtype=torch.bfloat16, device=DEV))
+        F().gemv(x[:2], torch.zeros(F().gemv_max_rows(torch.device(DEV)) + 8, 512, dtype=torch.bfloat16, device=DEV))
     with pytest.raises(Exception, match="multiples of 8"):
         F().gemv(torch.zeros(2, 12, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV))
 
