@@ -2,8 +2,9 @@
 
 The kernel is chosen by the weight's dtype: a float32 weight always goes through the FP32-pipe
 kernel (true 32-bit: no tensor cores, no TF32), whatever the activations are; a bfloat16 weight
-goes through the tcgen05 tensor-core kernel with 32-bit accumulation (or, for shapes it does not
-take, the library product the reference itself uses).
+goes through the kernels of this library with 32-bit accumulation where tokens are few (decode) or an output
+stage is fused behind the product (SwiGLU; the q|k|v stage has an entry of its own), and through the library
+product, which the reference itself uses for every projection, where many tokens meet a plain product.
 """
 
 from __future__ import annotations
@@ -12,6 +13,13 @@ import torch
 
 from . import functional as F
 from .library import KernelError, require_device
+
+
+library_for_plain_products = True  # many-token products without a fused output stage go to the library product
+
+# The library's bfloat16 product must add up in 32-bit throughout, also where it splits K (torch's default lets
+# it reduce partial sums in bfloat16); measured, the products here are as fast with the setting off.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
 
 def _tc_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -40,5 +48,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return F.swiglu(y, interleaved=True) if swiglu else y
     if F.gemv_suits(x.shape[0], weight.shape[0], x.shape[1], x.device):
         return F.gemv(x, weight, torch.bfloat16 if swiglu else out_dtype, swiglu=swiglu)
+    if library_for_plain_products and not swiglu and x.shape[0] > F.SKINNY_M:
+        # many tokens and nothing fused behind the product: the library's product, as in the reference's own
+        # engine (nn.Linear, src/engine.py:35).  Measured on a B200 it is 1.1 to 2.7 times as fast as the
+        # tensor-memory kernel here on such shapes (it splits K where a product has few tiles and pairs SMs).
+        return F.linear_bf16(x, weight, out_dtype)
     splits = F.split_k_for(x.shape[0], weight.shape[0], x.shape[1])
     return F.gemm_tc(x, weight, torch.bfloat16 if swiglu else out_dtype, swiglu=swiglu, splits=splits)
