@@ -16,6 +16,7 @@ from .library import KernelError, require_device
 
 
 library_for_plain_products = True  # many-token products without a fused output stage go to the library product
+library_from_tokens = F.SKINNY_M    # "many": more tokens than the swap-AB orientation of the own kernel takes
 
 # The library's bfloat16 product must add up in 32-bit throughout, also where it splits K (torch's default lets
 # it reduce partial sums in bfloat16); measured, the products here are as fast with the setting off.
@@ -48,7 +49,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return F.swiglu(y, interleaved=True) if swiglu else y
     if F.gemv_suits(x.shape[0], weight.shape[0], x.shape[1], x.device):
         return F.gemv(x, weight, torch.bfloat16 if swiglu else out_dtype, swiglu=swiglu)
-    if library_for_plain_products and not swiglu and x.shape[0] > F.SKINNY_M:
+    if library_for_plain_products and not swiglu and x.shape[0] > library_from_tokens:
         # many tokens and nothing fused behind the product: the library's product, as in the reference's own
         # engine (nn.Linear, src/engine.py:35).  Measured on a B200 it is 1.1 to 2.7 times as fast as the
         # tensor-memory kernel here on such shapes (it splits K where a product has few tiles and pairs SMs).
