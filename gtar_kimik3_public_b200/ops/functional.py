@@ -181,6 +181,12 @@ def qk_norm_rope_write(
     return q_out
 
 
+# Tiles of 128 x 256 from which the q|k|v product does its output stage itself.  Below, the library product and the
+# stage as a kernel of its own are faster (1,024 tokens x 4,096 columns = 128 tiles: 16.2 against 17.7 us; 2,048
+# tokens = 256 tiles: 26.7 against 25.9): the persistent kernel leaves SMs idle and its last tile's stage exposed.
+QKV_FUSED_FROM_TILES = 200
+
+
 def qkv_fused_ok(x: torch.Tensor, weight: torch.Tensor, head_dim: int, kv: PagedKV) -> bool:
     """Whether the q|k|v projection of this step can do the attention input stage in its epilogue:
     bfloat16, enough tokens for the many-token orientation and its wide tiles, head size 64 or 128."""
@@ -188,7 +194,7 @@ def qkv_fused_ok(x: torch.Tensor, weight: torch.Tensor, head_dim: int, kv: Paged
     n = weight.shape[0]
     return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16
             and m > SKINNY_M and k % 8 == 0 and head_dim in (64, 128)
-            and n >= PREFILL_BN and -(-m // 128) * -(-n // PREFILL_BN) >= 120)
+            and n >= PREFILL_BN and -(-m // 128) * -(-n // PREFILL_BN) >= QKV_FUSED_FROM_TILES)
 
 
 def gemm_tc_qkv(
