@@ -117,6 +117,34 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def step_bytes(batch: int, kv_tokens_each: int, layers: int) -> float:
+    """Bytes a decode step has to read, from the sizes alone (both arms print it the same way): every
+    bfloat16 matrix once, the 32-bit norm weights, and the live requests' keys and values."""
+    c = BENCH_CONFIG
+    q_width = c["num_attention_heads"] * c["head_dim"]
+    kv_width = c["num_key_value_heads"] * c["head_dim"]
+    per_layer = 2 * c["hidden_size"] * (2 * q_width + 2 * kv_width + 3 * c["intermediate_size"])
+    per_layer += 4 * (2 * c["hidden_size"] + 2 * c["head_dim"])
+    head = 2 * c["vocab_size"] * c["hidden_size"] * (1 if c["tie_word_embeddings"] else 2)
+    kv = 2 * 2 * kv_width * layers * kv_tokens_each * batch
+    return layers * per_layer + head + 4 * c["hidden_size"] + kv
+
+
+def config_record(batch: int, layers: int, peak_source: str) -> dict:
+    """The ``config`` of the JSON line: every size by name, flat.  Both arms build it here."""
+    c = BENCH_CONFIG
+    return {
+        "model": "transformer (Qwen3-0.6B layer sizes)", "global_batch": batch, "seq_len": PROMPT_LEN,
+        "context_length": c["max_position_embeddings"], "parallelism": "single GPU",
+        "layers": layers, "layers_full_config": c["num_hidden_layers"], "hidden_size": c["hidden_size"],
+        "q_heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"], "head_dim": c["head_dim"],
+        "intermediate_size": c["intermediate_size"], "vocab_size": c["vocab_size"],
+        "tied_embeddings": c["tie_word_embeddings"], "prefill_tokens": PREFILL_TOKENS,
+        "l2": "no flush: a step reads %.2f GB, far above the 126 MB L2" % (step_bytes(batch, PROMPT_LEN, layers) / 1e9),
+        "peaks": peak_source,
+    }
+
+
 def make_model(dtype: str, layers: int | None = None):
     from gtar_kimik3_public_b200.generate import load
     from gtar_kimik3_public_b200.registry import config_from_dict
@@ -262,7 +290,6 @@ def run_ours(args) -> dict:
         points[f"decode_b{b}"] = round(time_decode(model, b, min(args.steps, 64), args.warmup)["tokens_per_s"], 1)
     achieved = main["bytes_per_step"] / (main["ms_per_step"] / 1e3) / 1e9
     prefill_peak = peak["bf16_tflops"] * 1e12
-    full_layers = BENCH_CONFIG["num_hidden_layers"]
     return {
         "metric": "decode tokens/s (Qwen3-0.6B layer sizes, batch 8, after 2,048-token prompts)",
         "value": round(main["tokens_per_s"], 1),
@@ -277,21 +304,144 @@ def run_ours(args) -> dict:
         "dtype": "bf16",
         "data": "synthetic: seeded uniform-random token ids, random weights (N(0, 0.02)) of the named architecture",
         "impl": "ours",
-        "config": {
-            "model": "transformer (Qwen3-0.6B layer sizes)", "global_batch": batch, "seq_len": PROMPT_LEN,
-            "context_length": config.max_position_embeddings, "parallelism": "single GPU",
-            "layers": len(model.plan.run_list), "layers_full_config": full_layers, "hidden_size": config.hidden_size,
-            "q_heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
-            "intermediate_size": config.intermediate_size, "vocab_size": config.vocab_size,
-            "tied_embeddings": config.tie_word_embeddings, "prefill_tokens": PREFILL_TOKENS,
-            "l2": "no flush: a step reads %.2f GB, far above the 126 MB L2" % (main["bytes_per_step"] / 1e9),
-            "peaks": peak_source,
-        },
+        "config": config_record(batch, len(model.plan.run_list), peak_source),
         "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": main["launches"],
         "clocks": main["clocks"],
         "prefill": {"value": round(prefill["value"], 1), "tokens": prefill["tokens"], "ms": round(prefill["ms"], 3),
                     "frac": round(prefill["flops"] / (prefill["ms"] / 1e3) / prefill_peak, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4)},
+        "points": points,
+    }
+
+
+def reference_folder() -> Path | None:
+    """Where the unmodified reference lies: ``baseline/_ref`` beside this file (a plain copy of the
+    reference's folder; it is a folder of scripts that runs from ``sys.path``), or the folder that the
+    environment variable GTAR_REFERENCE_DIR names."""
+    for folder in (os.environ.get("GTAR_REFERENCE_DIR"), ROOT / "baseline" / "_ref"):
+        if folder and (Path(folder) / "src" / "engine.py").exists():
+            return Path(folder)
+    return None
+
+
+class ReferenceArm:
+    """The reference's own generation, untouched: ``Engine(TransformerForCausalLM).generate`` (src/engine.py:22-46)
+    on the model that configs/transformer_0.6B.json describes, with the reference's own random initialisation.
+    Nothing of this repository's package is imported here."""
+
+    def __init__(self, folder: Path, device: str, layers: int | None, sizes: dict | None = None):
+        import torch
+
+        sys.path.insert(0, str(folder))
+        from src.engine import Engine
+        from src.models import ARCHITECTURES
+
+        file = json.loads((folder / "configs" / "transformer_0.6B.json").read_text())
+        config_class, model_class = ARCHITECTURES[file["arch"]]
+        fields = dict(file["model"], vocab_size=BENCH_CONFIG["vocab_size"])
+        for key, value in fields.items():  # the reference's file and the benchmark's sizes are the same model
+            assert BENCH_CONFIG[key] == value, f"{key}: the reference's config has {value}, the benchmark {BENCH_CONFIG[key]}"
+        if layers:
+            fields["num_hidden_layers"] = layers
+        if sizes:  # only the tests shrink the model (they run this arm on the CPU)
+            fields.update(sizes)
+        self.torch, self.device, self.fields = torch, device, fields
+        torch.manual_seed(0)
+        with torch.device(device):
+            model = model_class(config_class(**fields))
+        self.engine = Engine(model)
+        self.eos = fields["vocab_size"] - 1  # the command line always passes a stop token (scripts/generate.py:40,44)
+
+    def generate_seconds(self, prompts, new_tokens: int) -> float:
+        """Wall clock of one call of the public API between synchronisations, as the reference times generation
+        (scripts/benchmark_speculative.py:107-117): host token ids in, host token ids out."""
+        torch = self.torch
+        cuda = self.device.startswith("cuda")
+        if cuda:
+            torch.cuda.synchronize()
+        begin = time.perf_counter()
+        out = self.engine.generate(prompts, max_new_tokens=new_tokens, temperature=0.0, eos_token_id=self.eos).cpu()
+        if cuda:
+            torch.cuda.synchronize()
+        seconds = time.perf_counter() - begin
+        if out.shape[1] != new_tokens:  # every sequence chose the stop token: the run was cut short
+            raise RuntimeError(f"the reference stopped after {out.shape[1]} of {new_tokens} tokens")
+        return seconds
+
+    def decode(self, batch: int, prompt_len: int, steps: int, warmup: int, repeats: int = 3) -> dict:
+        """Seconds per decode step: a call that decodes warm-up + K steps minus a call that decodes warm-up steps,
+        so that the prompts' step and the set-up cancel.  (A call for n new tokens runs n - 1 decode steps.)"""
+        torch = self.torch
+        gen = torch.Generator().manual_seed(0)
+        prompts = torch.randint(0, self.fields["vocab_size"] - 1, (batch, prompt_len), generator=gen)
+        self.generate_seconds(prompts, warmup + 1)  # untimed: compiles the attention kernel, loads the libraries
+        short = [self.generate_seconds(prompts, warmup + 1) for _ in range(repeats)]
+        long = [self.generate_seconds(prompts, warmup + steps + 1) for _ in range(repeats)]
+        seconds = statistics.median(long) - statistics.median(short)
+        return {"tokens_per_s": batch * steps / seconds, "ms_per_step": seconds / steps * 1e3,
+                "h2d_bytes_per_step": batch * prompt_len * 8 // steps, "d2h_bytes_per_step": batch * 8}
+
+    def prefill(self, tokens: int, repeats: int = 3) -> float:
+        """Milliseconds of one prompt through the public API (one new token: the prompt's step and nothing else)."""
+        torch = self.torch
+        gen = torch.Generator().manual_seed(1)
+        prompt = torch.randint(0, self.fields["vocab_size"] - 1, (1, tokens), generator=gen)
+        self.generate_seconds(prompt, 1)
+        return statistics.median(self.generate_seconds(prompt, 1) for _ in range(repeats)) * 1e3
+
+
+def run_reference(args, device: str = "cuda:0", sizes: dict | None = None, prompt_len: int = PROMPT_LEN,
+                  prefill_tokens: int = PREFILL_TOKENS, batches: tuple = (1, 64)) -> dict:
+    """The reference arm: the same metric on the same configuration from the unmodified reference."""
+    folder = reference_folder()
+    if folder is None:
+        return {"impl": "reference", "unavailable": "no copy of the reference under baseline/_ref (it is not part of "
+                                                    "the repository's history) and GTAR_REFERENCE_DIR names none"}
+    import torch
+
+    if device.startswith("cuda") and not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device here: the arm is timed on a GPU only"}
+    peak, peak_source = peaks()
+    try:
+        arm = ReferenceArm(folder, device, args.layers, sizes)
+        sampler = ClockSampler()
+        sampler.start()
+        main = arm.decode(args.batch, prompt_len, args.steps, args.warmup)
+        clocks = sampler.stop()
+        prefill_ms = arm.prefill(prefill_tokens)
+        points = {f"decode_b{b}": round(arm.decode(b, prompt_len, min(args.steps, 64), args.warmup, repeats=1)["tokens_per_s"], 1)
+                  for b in batches}
+    except Exception as error:  # the line says why; the trace goes to standard error
+        import traceback
+
+        traceback.print_exc()
+        return {"impl": "reference", "unavailable": ("the reference failed here: %s: %s" % (type(error).__name__, error)).replace("\n", " ")[:300]}
+    layers = arm.fields["num_hidden_layers"]
+    achieved = step_bytes(args.batch, prompt_len + args.warmup + args.steps // 2, layers) / (main["ms_per_step"] / 1e3) / 1e9
+    c = BENCH_CONFIG
+    t = prefill_tokens
+    per_layer = 2 * t * c["hidden_size"] * ((2 * c["num_attention_heads"] + 2 * c["num_key_value_heads"]) * c["head_dim"] + 3 * c["intermediate_size"])
+    attention = 4 * c["num_attention_heads"] * c["head_dim"] * t * t / 2
+    flops = layers * (per_layer + attention) + 2 * c["hidden_size"] * c["vocab_size"]  # counted as for the own arm: the wanted row only
+    rate = round(main["tokens_per_s"], 1)
+    return {
+        "metric": "decode tokens/s (Qwen3-0.6B layer sizes, batch 8, after 2,048-token prompts)",
+        "value": rate, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: seeded uniform-random token ids, random weights of the named architecture (the reference's own init_weights)",
+        "impl": "reference",
+        "timing": "wall clock around Engine.generate between synchronisations, long call minus short call (the "
+                  "reference has no device-timed loop; value and e2e are the same measurement)",
+        "config": config_record(args.batch, layers, peak_source),
+        "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": main["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": main["d2h_bytes_per_step"]},
+        "gpu_launches": None,
+        "clocks": clocks,
+        "prefill": {"value": round(t / (prefill_ms / 1e3), 1), "tokens": t, "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4)},
         "points": points,
@@ -308,11 +458,9 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     args = parser.parse_args()
     if args.impl == "reference":
-        print(json.dumps({
-            "impl": "reference",
-            "unavailable": "the reference cannot be installed offline: pip reports \"Neither 'setup.py' nor "
-                           "'pyproject.toml' found\" (it is a folder of scripts, not a package)",
-        }))
+        if args.warmup < 3:
+            args.warmup = 3
+        print(json.dumps(run_reference(args)))
         return 0
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
