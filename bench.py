@@ -175,11 +175,12 @@ def time_decode(model, batch: int, steps: int, warmup: int, sample_clocks: bool 
     """Device-timed decoding: prompts of PROMPT_LEN in one step, then warm-up and K timed steps."""
     import torch
 
+    from gtar_kimik3_public_b200.cache import rounded_tokens
     from gtar_kimik3_public_b200.engine import Engine, StepEntry
     from gtar_kimik3_public_b200.ops import functional as F
     from gtar_kimik3_public_b200.ops import library
 
-    room = -(-(PROMPT_LEN + warmup + steps + 1) // 64) * 64
+    room = rounded_tokens(PROMPT_LEN + warmup + steps + 1)
     engine = Engine(model, batch * room, max_seqs=batch)
     prompts = random_prompts(batch, PROMPT_LEN, model.vocab_size)
     ids = list(range(batch))
@@ -221,9 +222,10 @@ def time_e2e(model, batch: int, steps: int, warmup: int) -> dict:
     every step a pinned host-to-device copy of its numbers and a device-to-host read of its tokens."""
     import torch
 
+    from gtar_kimik3_public_b200.cache import rounded_tokens
     from gtar_kimik3_public_b200.generate import Generator
 
-    room = -(-(PROMPT_LEN + warmup + steps + 2) // 64) * 64
+    room = rounded_tokens(PROMPT_LEN + warmup + steps + 2)
     generator = Generator(model, max_tokens=batch * room, max_batch=batch)
     prompts = random_prompts(batch, PROMPT_LEN, model.vocab_size)
     stamps = []
@@ -245,9 +247,10 @@ def time_e2e(model, batch: int, steps: int, warmup: int) -> dict:
 def time_prefill(model, warmup: int, repeats: int = 3) -> dict:
     import torch
 
+    from gtar_kimik3_public_b200.cache import rounded_tokens
     from gtar_kimik3_public_b200.engine import Engine, StepEntry
 
-    engine = Engine(model, -(-PREFILL_TOKENS // 64) * 64 + 64, max_seqs=1)
+    engine = Engine(model, rounded_tokens(PREFILL_TOKENS + 1), max_seqs=1)
     prompt = random_prompts(1, PREFILL_TOKENS, model.vocab_size, seed=1)[0]
     times = []
     with torch.no_grad():

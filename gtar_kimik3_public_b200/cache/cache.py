@@ -33,21 +33,37 @@ from .allocators import CacheFull, PageAllocator, SlotAllocator
 PAGE_SIZE = 64
 
 
+def rounded_tokens(n_tokens: int, page_size: int = PAGE_SIZE) -> int:
+    """What a sequence of ``n_tokens`` counts against a cache's ``max_tokens``: its length rounded up to whole pages."""
+    return -(-int(n_tokens) // page_size) * page_size
+
+
 @dataclass
 class CacheLayout:
-    """``requests[e]`` is what entry ``e`` of the model's run list needs kept (or None); an entry
-    may instead read the storage of an earlier entry: ``shared_with[e] = e'``."""
+    """``requests[e]`` is what entry ``e`` of the model's run list needs kept: one request, None, or a
+    list of requests (keys and values and a state, several states of their own shapes and types: the
+    reference's fixed-size example holds a 32-bit matrix and three rolling buffers, src/cache.py:48-57).
+    An entry may instead read the storage of an earlier entry: ``shared_with[e] = e'``."""
 
-    requests: list[KVRequest | StateRequest | None]
+    requests: list[KVRequest | StateRequest | None | list | tuple]
     shared_with: dict[int, int] = field(default_factory=dict)
+
+    def items_of(self, entry: int) -> tuple:
+        """The entry's requests as a tuple (empty for None)."""
+        request = self.requests[entry]
+        if request is None:
+            return ()
+        return tuple(request) if isinstance(request, (list, tuple)) else (request,)
 
 
 class _KVGroup:
-    def __init__(self, request: KVRequest, entries: list[int], n_slots: int, n_pages: int, max_pages_per_seq: int,
+    def __init__(self, request: KVRequest, items: list[tuple[int, int]], n_slots: int, n_pages: int, max_pages_per_seq: int,
                  page_size: int, dtype: torch.dtype, device: torch.device):
-        self.request, self.entries, self.page_size = request, entries, page_size
-        self.index_of = {e: i for i, e in enumerate(entries)}
-        shape = (len(entries), n_pages, request.n_kv_heads, page_size, request.head_dim)
+        # items: (run-list entry, place among that entry's requests) of everything stored here
+        self.request, self.items, self.page_size = request, items, page_size
+        self.entries = [entry for entry, _ in items]
+        self.index_of = {item: i for i, item in enumerate(items)}
+        shape = (len(items), n_pages, request.n_kv_heads, page_size, request.head_dim)
         self.k = torch.empty(shape, dtype=dtype, device=device)
         self.v = torch.empty(shape, dtype=dtype, device=device)
         self.pages = PageAllocator(n_pages)
@@ -114,22 +130,23 @@ class _KVGroup:
             self.table[slot].copy_(staged[i], non_blocking=True)
         self.dirty.clear()
 
-    def view(self, entry: int) -> PagedKV:
-        i = self.index_of[entry]
+    def view(self, item: tuple[int, int]) -> PagedKV:
+        i = self.index_of[item]
         return PagedKV(self.k[i], self.v[i], self.table)
 
 
 class _StateGroup:
-    def __init__(self, request: StateRequest, entries: list[int], n_slots: int, device: torch.device):
-        self.request, self.entries = request, entries
-        self.index_of = {e: i for i, e in enumerate(entries)}
-        self.state = torch.zeros((len(entries), n_slots, *request.shape), dtype=request.dtype, device=device)
+    def __init__(self, request: StateRequest, items: list[tuple[int, int]], n_slots: int, device: torch.device):
+        self.request, self.items = request, items
+        self.entries = [entry for entry, _ in items]
+        self.index_of = {item: i for i, item in enumerate(items)}
+        self.state = torch.zeros((len(items), n_slots, *request.shape), dtype=request.dtype, device=device)
 
     def open_slot(self, slot: int) -> None:
         self.state[:, slot].zero_()
 
-    def view(self, entry: int) -> torch.Tensor:
-        return self.state[self.index_of[entry]]
+    def view(self, item: tuple[int, int]) -> torch.Tensor:
+        return self.state[self.index_of[item]]
 
 
 class Cache:
@@ -152,13 +169,13 @@ class Cache:
         self.length: dict[int, int] = {}
         self.kv_groups: list[_KVGroup] = []
         self.state_groups: list[_StateGroup] = []
-        self._where: dict[int, object] = {}
-        by_request: dict[object, list[int]] = {}
-        for entry, request in enumerate(layout.requests):
+        self._where: dict[tuple[int, int], object] = {}
+        by_request: dict[object, list[tuple[int, int]]] = {}
+        for entry in range(len(layout.requests)):
             if entry in layout.shared_with:
                 continue
-            if request is not None:
-                by_request.setdefault(request, []).append(entry)
+            for place, request in enumerate(layout.items_of(entry)):
+                by_request.setdefault(request, []).append((entry, place))
         for request, entries in by_request.items():
             if isinstance(request, KVRequest):
                 # A windowed group draws on a pool as large as the others': a long prompt needs all its
@@ -172,12 +189,11 @@ class Cache:
                 self.state_groups.append(group)
             else:
                 raise TypeError(f"unknown cache request {request!r}")
-            for entry in entries:
-                self._where[entry] = group
+            for item in entries:
+                self._where[item] = group
         for entry, source in layout.shared_with.items():
-            if source not in self._where:
-                raise ValueError(f"run-list entry {entry} shares the cache of entry {source}, which keeps nothing")
-            self._where[entry] = self._where[source]
+            if not layout.items_of(source) or source in layout.shared_with:
+                raise ValueError(f"run-list entry {entry} shares the cache of entry {source}, which keeps nothing of its own")
 
     # ------------------------------------------------------------------ slots
     def open(self) -> int:
@@ -226,12 +242,14 @@ class Cache:
 
     # ------------------------------------------------------------------ views
     def view(self, entry: int):
-        """Storage of run-list entry ``entry``: a ``PagedKV``, a state tensor ``[n_slots, ...]`` or None."""
-        group = self._where.get(entry)
-        if group is None:
-            return None
+        """Storage of run-list entry ``entry``: a ``PagedKV`` or a state tensor ``[n_slots, ...]`` for a single
+        request, None for none, and for a list of requests a tuple of those in the list's order."""
         source = self.layout.shared_with.get(entry, entry)
-        return group.view(source)
+        request = self.layout.requests[source]
+        if request is None:
+            return None
+        views = tuple(self._where[(source, place)].view((source, place)) for place in range(len(self.layout.items_of(source))))
+        return views if isinstance(request, (list, tuple)) else views[0]
 
     def is_shared(self, entry: int) -> bool:
         return entry in self.layout.shared_with
@@ -244,7 +262,7 @@ class Cache:
         total = 0
         for group in self.kv_groups:
             r = group.request
-            total += 2 * len(group.entries) * r.n_kv_heads * r.head_dim * self.k_element_size()
+            total += 2 * len(group.items) * r.n_kv_heads * r.head_dim * self.k_element_size()
         return total
 
     def k_element_size(self) -> int:

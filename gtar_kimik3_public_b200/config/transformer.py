@@ -65,8 +65,9 @@ class TransformerConfig(ModelConfig):
                 f"TransformerConfig: num_attention_heads ({self.num_attention_heads}) must be a multiple of "
                 f"num_key_value_heads ({self.num_key_value_heads})"
             )
-        if self.head_dim % 2 != 0:
-            raise ConfigError(f"TransformerConfig: head_dim ({self.head_dim}) must be even for rotary pairs")
+        if self.head_dim % 8 != 0:
+            raise ConfigError(f"TransformerConfig: head_dim ({self.head_dim}) must be a multiple of 8 (the attention "
+                              "kernels read a head's row in 16- or 32-byte pieces; rotary pairs need it even)")
         if not self.rms_norm_eps > 0:
             raise ConfigError(f"TransformerConfig: rms_norm_eps must be > 0, got {self.rms_norm_eps}")
         if not self.rope_theta > 0:

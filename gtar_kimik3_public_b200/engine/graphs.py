@@ -9,6 +9,16 @@ host's work per step is one small pinned copy of those numbers.  Decode steps (o
 sequence) are captured at their first use, other shapes when they are seen a second time; the
 least recently used graphs are dropped beyond a limit.
 
+A decode shape also carries a bound on the longest sequence of the step (a power of two, at least
+``MIN_LENGTH_BOUND``, at most what the cache holds): kernels size their launches from that bound, not
+from the lengths of the day, so a short context in a cache made for long ones is not cut into as many
+pieces as the longest context would need.
+
+A step is executed exactly once, also the step at which its shape is captured: that step runs launch
+by launch (which does whatever one-time set-up the kernels need) and gives the result, the capture
+after it executes nothing, and replays serve the later steps.  A part that advances a state in place
+may therefore be graph-safe.
+
 Inside a graph every kernel is launched with programmatic stream serialization: it may start
 (and fetch weights) while the kernel before it drains, and waits for that kernel's results only
 where it first needs them.
@@ -21,13 +31,14 @@ from collections import OrderedDict
 import numpy as np
 import torch
 
-from ..ops.functional import decode_splits, set_pdl
+from ..ops.functional import set_pdl
 from .step import PackedStep, context_from_views
 
 
 class StepGraphs:
     RING = 8
     MAX_PREFILL_GRAPHS = 12
+    MIN_LENGTH_BOUND = 1024
 
     def __init__(self, model, cache, use_pdl: bool = True):
         self.model, self.cache, self.use_pdl = model, cache, use_pdl
@@ -46,8 +57,6 @@ class StepGraphs:
         self.seen: set[tuple] = set()
         self.pool = None
         self.launches: dict[tuple, int] = {}
-        layout = cache.layout.requests
-        self.n_kv = max((r.n_kv_heads for r in layout if hasattr(r, "n_kv_heads")), default=1)
 
     # ------------------------------------------------------------------ step inputs
     @staticmethod
@@ -81,9 +90,20 @@ class StepGraphs:
         self.events[turn] = event
 
     # ------------------------------------------------------------------ graphs
-    @staticmethod
-    def key_of(packed: PackedStep) -> tuple:
-        return (packed.n_tokens, packed.n_seqs, packed.n_want, packed.max_q_len if not packed.all_single else 1)
+    def length_bound(self, packed: PackedStep) -> int:
+        """The bound on sequence lengths that the step's launches are sized for."""
+        longest = self.cache.max_seq_len
+        if not packed.all_single:
+            return longest
+        bound = self.MIN_LENGTH_BOUND
+        while bound < packed.max_kv_len:
+            bound *= 2
+        return min(bound, longest)
+
+    def key_of(self, packed: PackedStep) -> tuple:
+        if packed.all_single:
+            return (packed.n_tokens, packed.n_seqs, packed.n_want, 1, self.length_bound(packed))
+        return (packed.n_tokens, packed.n_seqs, packed.n_want, packed.max_q_len, 0)
 
     def wants_graph(self, packed: PackedStep) -> bool:
         """Decode shapes always; other shapes from their second appearance on."""
@@ -105,7 +125,7 @@ class StepGraphs:
         if device_tokens is not None:
             self.meta[0:packed.n_tokens].copy_(device_tokens)
         if key not in self.graphs:
-            self._capture(key, packed)
+            return self._capture(key, packed)
         self.graphs.move_to_end(key)
         graph, logits = self.graphs[key]
         graph.replay()
@@ -114,17 +134,17 @@ class StepGraphs:
         library.launch_count += self.launches[key]
         return logits
 
-    def _capture(self, key: tuple, packed: PackedStep) -> None:
+    def _capture(self, key: tuple, packed: PackedStep) -> torch.Tensor:
+        """Runs the step launch by launch, captures its launches for the steps to come, and returns the
+        logits of the run (the capture itself executes nothing, so the step has run once)."""
         from ..ops import library
 
-        longest = self.cache.max_seq_len
-        self.model.prepare(longest - 1)
-        # launch shapes inside a graph must not depend on the lengths of the day: bounds of the cache
-        ctx = context_from_views(packed, self.views(packed), self.model.dtype, max_kv_len=longest)
-        ctx.extras["decode_splits"] = decode_splits(packed.n_seqs, self.n_kv, longest, self.cache.page_size)
-        self.model.step(ctx, self.cache)  # a plain run first: one-time set-up must not be captured
+        self.model.prepare(self.cache.max_seq_len - 1)
+        # launch shapes inside a graph must not depend on the lengths of the day: a bound stands in
+        ctx = context_from_views(packed, self.views(packed), self.model.dtype, max_kv_len=self.length_bound(packed))
+        result = self.model.step(ctx, self.cache)  # one-time set-up happens here, outside the capture
         torch.cuda.synchronize()
-        while len(self.graphs) >= self.MAX_PREFILL_GRAPHS + self.s_max:
+        while len(self.graphs) >= self.MAX_PREFILL_GRAPHS + 3 * self.s_max:
             self.graphs.popitem(last=False)
         graph = torch.cuda.CUDAGraph()
         before = set_pdl(self.use_pdl)
@@ -139,3 +159,4 @@ class StepGraphs:
         if self.pool is None:
             self.pool = graph.pool()
         self.graphs[key] = (graph, logits)
+        return result

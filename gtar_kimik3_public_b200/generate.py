@@ -14,6 +14,7 @@ from typing import Sequence
 
 import torch
 
+from .cache import rounded_tokens
 from .engine.engine import Engine
 from .engine.generation import DeviceChooser, GenerationParams, run_generation
 from .models.model import Model
@@ -34,12 +35,15 @@ def parse_dtype(name) -> torch.dtype:
         raise ValueError(f"dtype must be bfloat16 or float32, got {name!r}") from None
 
 
-def load(model_dir: str | Path, dtype="bfloat16", device: str | torch.device = "cuda:0") -> Model:
-    """Builds the model class that ``model_dir/config.json`` names and loads its safetensors."""
+def load(model_dir: str | Path, dtype="bfloat16", device: str | torch.device = "cuda:0",
+         cast_matrices: bool = False) -> Model:
+    """Builds the model class that ``model_dir/config.json`` names and loads its safetensors.
+    ``cast_matrices``: in a bfloat16 run, round matrices that the file stores in 32-bit to bfloat16
+    (by default they stay 32-bit and their projections run on the slow, exact 32-bit kernel)."""
     config = config_from_file(model_dir)
     arch = architecture(config.ARCH_NAMES[0])
     model = Model(arch.build_plan(config), config, parse_dtype(dtype), device)
-    load_weights(model, model_dir)
+    load_weights(model, model_dir, cast_matrices=cast_matrices)
     return model
 
 
@@ -50,9 +54,24 @@ class Generator:
         self.model = model
         self.max_batch = max_batch
         if max_tokens is None:
-            longest = getattr(model.config, "max_position_embeddings", None) or 4096
-            max_tokens = max_batch * longest
+            max_tokens = self.default_max_tokens(model, max_batch)
         self.engine = Engine(model, max_tokens, max_seqs=max_batch)
+
+    @staticmethod
+    def default_max_tokens(model: Model, max_batch: int, share_of_free_memory: float = 0.8) -> int:
+        """Tokens of cache when the caller names none: ``max_batch`` sequences of the longest context the
+        configuration allows, but no more than fits in most of the device memory that is free now (a
+        configuration may allow tens of thousands of positions, far more than a batch of them fits)."""
+        longest = getattr(model.config, "max_position_embeddings", None) or 4096
+        wanted = max_batch * rounded_tokens(longest)
+        per_token = model.make_cache(rounded_tokens(1), 1).kv_bytes_per_token()
+        if model.device.type != "cuda" or per_token == 0:
+            return wanted
+        free, _ = torch.cuda.mem_get_info(model.device)
+        fits = int(free * share_of_free_memory) // per_token
+        if fits < rounded_tokens(1):
+            raise RuntimeError(f"no device memory left for a cache: {free} bytes free, {per_token} bytes a token")
+        return min(wanted, fits - fits % rounded_tokens(1))
 
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64, temperature: float = 1.0,
@@ -110,8 +129,7 @@ def generate(model: Model, prompts: Sequence[Sequence[int]], max_new_tokens: int
     prompts = [list(p) for p in prompts]
     max_batch = max_batch or max(1, min(64, len(prompts)))
     if max_tokens is None:
-        page = 64
-        longest = sorted((-(-(len(p) + max_new_tokens) // page) * page for p in prompts), reverse=True)
-        max_tokens = max(page, sum(longest[:max_batch]))
+        longest = sorted((rounded_tokens(len(p) + max_new_tokens) for p in prompts), reverse=True)
+        max_tokens = max(rounded_tokens(1), sum(longest[:max_batch]))
     return Generator(model, max_tokens, max_batch).generate(
         prompts, max_new_tokens, temperature, top_k, eos_token_id, stop_ids, seed)

@@ -7,6 +7,7 @@ output.  Shapes follow the packed ("varlen") convention of the step function: ac
 
 from __future__ import annotations
 
+import functools
 from dataclasses import dataclass
 
 import torch
@@ -330,7 +331,18 @@ SKINNY_BN_MAX = 64
 SPLIT_MIN_K_BLOCKS = 4
 
 
-def split_k_for(m: int, n: int, k: int, sm_count: int = 148) -> int:
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count(device: torch.device | None = None) -> int:
+    """Multiprocessors of the device (asked once per device)."""
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
+
+
+def split_k_for(m: int, n: int, k: int) -> int:
     """How many blocks share the K range of one output tile of a skinny product (m <= SKINNY_M).
     More blocks stream weights from more SMs: about 64 blocks in all, at least four k-blocks of 64
     each, and 1, 2, 4 or 8 ways (the blocks of a tile form one cluster)."""
@@ -350,15 +362,11 @@ def set_pdl(on: bool) -> bool:
 
 GEMV_MAX_TOKENS = 16
 GEMV_MAX_TOKENS_SHORT_K = 32  # with the activations of all tokens in registers (see gemv_suits)
-_sm_counts: dict[int, int] = {}
 
 
 def gemv_max_rows(device: torch.device) -> int:
     """Most weight rows ``gemv`` takes: one block per SM, each with up to eight groups of eight rows."""
-    index = device.index if device.index is not None else torch.cuda.current_device()
-    if index not in _sm_counts:
-        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
-    return _sm_counts[index] * 64
+    return sm_count(device) * 64
 
 
 
@@ -453,7 +461,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
     return out
 
 
-def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_count: int = 148) -> int:
+@functools.lru_cache(maxsize=4096)
+def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_count: int) -> int:
     """How many blocks share a sequence's pages in decode attention.
 
     Two blocks fit an SM.  With few (sequence, kv head) pairs and a long context, as many splits as fill those
@@ -634,6 +643,12 @@ def set_attention_prefill_keys(keys: int) -> int:
     return int(library().gk_set_attention_prefill_keys(int(keys)))
 
 
+def row_parts(n_rows: int, vocab: int, device: torch.device) -> int:
+    """Blocks that share a row of logits in the token choice: about eight blocks per multiprocessor in all, slices
+    of at least 4,096 entries, at most 64 a row."""
+    return max(1, min(8 * sm_count(device) // max(n_rows, 1), vocab // 4096, 64))
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """Index of the largest logit of each row (lowest index on ties), int32."""
     require_device(logits.device)
@@ -643,7 +658,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
     _check(out, "out", torch.int32, 1)
     # few rows of a wide vocabulary: several blocks share a row so that the scan uses the whole GPU
-    parts = max(1, min(1184 // max(n, 1), vocab // 4096, 64))
+    parts = row_parts(n, vocab, logits.device)
     scratch = torch.empty((n * parts * 2,), dtype=torch.int32, device=logits.device) if parts > 1 else None
     call("gk_argmax", ptr(logits), vocab, n, vocab, ptr(out), parts, ptr(scratch), stream_ptr())
     return out
@@ -675,7 +690,7 @@ def sample(
     _check(out, "out", torch.int32, 1)
     # as for argmax: several blocks share a row; eight bytes of scratch per row for the top-k thresholds (four
     # used) and eight per row and part for the parts' results
-    parts = max(1, min(1184 // max(n, 1), vocab // 4096, 64))
+    parts = row_parts(n, vocab, logits.device)
     scratch = torch.empty((2 * ((n + 1) // 2) + 2 * n * parts,), dtype=torch.int32, device=logits.device)
     call(
         "gk_sample", ptr(logits), vocab, n, vocab, float(temperature), int(top_k or 0), int(seed) & (2**64 - 1),

@@ -49,10 +49,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return F.swiglu(y, interleaved=True) if swiglu else y
     if F.gemv_suits(x.shape[0], weight.shape[0], x.shape[1], x.device):
         return F.gemv(x, weight, torch.bfloat16 if swiglu else out_dtype, swiglu=swiglu)
-    if library_for_plain_products and not swiglu and x.shape[0] > library_from_tokens:
+    if library_for_plain_products and not swiglu and x.shape[0] > library_from_tokens and out_dtype == torch.bfloat16:
         # many tokens and nothing fused behind the product: the library's product, as in the reference's own
         # engine (nn.Linear, src/engine.py:35).  Measured on a B200 it is 1.1 to 2.7 times as fast as the
         # tensor-memory kernel here on such shapes (it splits K where a product has few tiles and pairs SMs).
+        # It writes bfloat16; a product whose result is wanted in 32-bit (the output head) stays on the own kernel,
+        # which stores its 32-bit sums, so that logits are the same numbers however many rows a step asks for.
         return F.linear_bf16(x, weight, out_dtype)
     splits = F.split_k_for(x.shape[0], weight.shape[0], x.shape[1])
     return F.gemm_tc(x, weight, torch.bfloat16 if swiglu else out_dtype, swiglu=swiglu, splits=splits)

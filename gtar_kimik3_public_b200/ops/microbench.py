@@ -94,7 +94,7 @@ def bench_attention_decode(args) -> dict:
     q = torch.randn(b, n_q, d, device=DEV, dtype=torch.bfloat16)
     kv_len = torch.full((b,), s, dtype=torch.int32, device=DEV)
     slots = torch.arange(b, dtype=torch.int32, device=DEV)
-    splits = args.splits or F.decode_splits(b, n_kv, s, 64)
+    splits = args.splits or F.decode_splits(b, n_kv, s, 64, F.sm_count())
 
     def run():
         for kv in caches:

@@ -16,7 +16,7 @@ What a part must offer:
 * ``forward(...)``: runs on the packed activations of one step.
 
 Mixers also say what they need kept between steps (``cache_request()``): keys and values for
-every position, for a window of positions, a state of fixed size, or nothing.
+every position, for a window of positions, a state of fixed size, several of these, or nothing.
 """
 
 from __future__ import annotations
@@ -117,7 +117,10 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
 
-    def cache_request(self) -> KVRequest | StateRequest | None:
+    def cache_request(self) -> KVRequest | StateRequest | None | list:
+        """What the mixer needs kept between steps: a ``KVRequest``, a ``StateRequest``, None, or a list of
+        requests (keys and values and a state; several state tensors of their own shapes and types).  ``forward``
+        gets the storage in the same form: one view, None, or a tuple of views in the list's order."""
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Any) -> torch.Tensor:

@@ -23,6 +23,7 @@ class RotaryEncoding(PositionEncoding):
         self.base = float(base)
         self.cos: torch.Tensor | None = None
         self.sin: torch.Tensor | None = None
+        self._replaced: list[torch.Tensor] = []  # shorter tables of before: captured launches may still read them
 
     def inv_freq(self) -> torch.Tensor:
         return 1.0 / (self.base ** (torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim))
@@ -31,6 +32,10 @@ class RotaryEncoding(PositionEncoding):
         have = 0 if self.cos is None else self.cos.shape[0]
         if self.cos is not None and self.cos.device == device and have > max_position:
             return
+        if self.cos is not None:
+            # A CUDA graph captured earlier holds the old tables' addresses.  Their rows stay right (a row depends
+            # on its position only), so they are kept instead of freed.
+            self._replaced += [self.cos, self.sin]
         n = max(max_position + 1, 2 * have, 64)
         positions = torch.arange(n, dtype=torch.float32, device=device)
         freqs = positions[:, None] * self.inv_freq().to(device)[None, :]

@@ -29,7 +29,11 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--random-weights", action="store_true", help="write a random model of --config and use it")
     parser.add_argument("--seed-weights", type=int, default=0, help="seed of the random weights")
     parser.add_argument("--vocab-size", type=int, default=None, help="vocabulary size if the config file has none")
+    parser.add_argument("--checkpoint", help="a checkpoint file of the reference's training loop (its --checkpoint): "
+                                             "converted to a model folder first")
     parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    parser.add_argument("--cast-matrices", action="store_true",
+                        help="bfloat16 run of a folder stored in 32-bit: round its matrices to bfloat16 at load")
     parser.add_argument("--prompt", default=None)
     parser.add_argument("--prompt-ids", default=None, help="comma-separated token ids; several prompts separated by ';'")
     parser.add_argument("--prompt-ids-file", default=None, help="JSON file: a list of token-id lists")
@@ -59,10 +63,15 @@ def main(argv=None) -> int:
         config = config_from_file(args.config, overrides)
         scratch = tempfile.TemporaryDirectory(prefix="gtar_b200_random_")
         model_dir = write_random_model(scratch.name, config, args.seed_weights)
+    elif args.checkpoint:
+        from ..weights.convert import convert_checkpoint
+
+        scratch = tempfile.TemporaryDirectory(prefix="gtar_b200_checkpoint_")
+        model_dir = convert_checkpoint(args.checkpoint, scratch.name, matrix_dtype=None)
     elif args.model:
         model_dir = Path(args.model)
     else:
-        raise SystemExit("give --model DIR, or --config FILE --random-weights")
+        raise SystemExit("give --model DIR, --checkpoint FILE, or --config FILE --random-weights")
 
     tokenizer = None
     tokenizer_path = Path(args.tokenizer) if args.tokenizer else Path(model_dir) / "tokenizer.json"
@@ -89,7 +98,8 @@ def main(argv=None) -> int:
         if eos is not None:
             stop_ids.append(eos)
 
-    model = load(model_dir, args.dtype, args.device)
+    # a checkpoint is 32-bit: as in the reference's engine its matrices are rounded for a bfloat16 run
+    model = load(model_dir, args.dtype, args.device, cast_matrices=args.cast_matrices or bool(args.checkpoint))
     config_eos = getattr(model.config, "eos_token_id", None)
     if config_eos is not None:
         stop_ids.append(config_eos)

@@ -7,12 +7,17 @@ scripts/generate.py:37, and its tolerant loader lists missing and unexpected key
 src/common.py:111-125.)
 
 Dtype rule.  In a bfloat16 run, floating-point tensors are kept in bfloat16, except that a
-tensor stored in 32-bit stays 32-bit (its projection then runs on the 32-bit kernel); integer
-tables become int32.  In a float32 run every floating-point tensor is widened to float32.
+tensor stored in 32-bit stays 32-bit; integer tables become int32.  In a float32 run every
+floating-point tensor is widened to float32.  A *matrix* that stays 32-bit in a bfloat16 run sends
+its projection through the 32-bit kernel, which is exact and some hundred times slower than the
+tensor cores: the loader says so once (a warning), and ``cast_matrices=True`` rounds such matrices
+to bfloat16 at load instead, which is what the reference's engine does with its 32-bit parameters
+at every projection (torch.autocast, src/engine.py:35).  Vectors (norm weights) stay 32-bit either way.
 """
 
 from __future__ import annotations
 
+import warnings
 from pathlib import Path
 
 import torch
@@ -62,28 +67,37 @@ def check_tensors(folder, specs: dict[str, TensorSpec], have_shapes: dict[str, t
         raise WeightsError(folder, missing, unexpected, wrong_shape, wrong_kind)
 
 
-def stored_dtype_rule(stored: torch.dtype, kind: str, run_dtype: torch.dtype) -> torch.dtype:
+def stored_dtype_rule(stored: torch.dtype, kind: str, run_dtype: torch.dtype, cast_matrices: bool = False) -> torch.dtype:
     """The dtype a tensor is kept in on the device."""
     if kind == "table":
         return torch.int32
     if run_dtype == torch.float32:
         return torch.float32
-    if stored in (torch.float32, torch.float64):
+    if stored in (torch.float32, torch.float64) and not (cast_matrices and kind == "matrix"):
         return torch.float32
     return torch.bfloat16
 
 
-def load_weights(model, folder: str | Path) -> None:
+def load_weights(model, folder: str | Path, cast_matrices: bool = False) -> None:
     """Checks the folder against ``model.tensor_specs()`` and hands the tensors to the parts."""
     files = ModelFolderTensors(folder)
     specs = model.tensor_specs()
     names = files.names()
     check_tensors(folder, specs, {n: files.shape(n) for n in names}, {n: files.dtype(n) for n in names})
     tensors = {}
+    slow = []
     for name, spec in specs.items():
         if name not in files.where:
             continue  # optional and absent
         host = files.tensor(name)
-        keep = stored_dtype_rule(host.dtype, spec.kind, model.dtype)
+        keep = stored_dtype_rule(host.dtype, spec.kind, model.dtype, cast_matrices)
+        if spec.kind == "matrix" and keep == torch.float32 and model.dtype == torch.bfloat16:
+            slow.append(name)
         tensors[name] = host.to(device=model.device, dtype=keep)
+    if slow:
+        warnings.warn(
+            f"{len(slow)} matrices of {folder} are stored in 32-bit and stay so in this bfloat16 run ({slow[0]}, ...): "
+            "their projections run on the 32-bit kernel, far slower than the tensor cores.  Load with "
+            "cast_matrices=True (command line: --cast-matrices) to round them to bfloat16 once, as the reference's "
+            "autocast does at every projection.", stacklevel=2)
     model.load(tensors)

@@ -11,17 +11,23 @@ import torch
 
 from tests.plain import model as plain
 from tests.plain.weights import read_safetensors
-from tests.tiny_configs import TINY_A, TINY_B, TINY_C
+from tests.tiny_configs import REAL_06B, REAL_4B, REAL_8B, TINY_A, TINY_B, TINY_C, TINY_LONG
 
-CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
+CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_long": TINY_LONG,
+           "real_06b": REAL_06B, "real_4b": REAL_4B, "real_8b": REAL_8B}
 WEIGHT_STD = 0.08  # wide enough that logits are O(1) and an error of 1e-3 is an error
+# at real widths the reference's own 0.02 gives logits of size O(1) (sqrt(1024) * 0.02 = 0.64)
+STD_OF = {"real_06b": 0.03, "real_4b": 0.02, "real_8b": 0.016}
+# where the plain implementation runs: the real sizes and the long sequences would take minutes on the CPU
+PLAIN_DEVICE = {"real_06b": "cuda", "real_4b": "cuda", "real_8b": "cuda", "tiny_long": "cuda"}
 
 _folders: dict[tuple, tempfile.TemporaryDirectory] = {}
 
 
-def model_folder(tag: str, seed: int = 0, std: float = WEIGHT_STD) -> Path:
+def model_folder(tag: str, seed: int = 0, std: float | None = None) -> Path:
     """A folder with config.json and model.safetensors for one of the tiny configurations, written
     by the library's random-weights mode into a temporary directory (kept for the session)."""
+    std = STD_OF.get(tag, WEIGHT_STD) if std is None else std
     key = (tag, seed, std)
     if key not in _folders:
         from gtar_kimik3_public_b200.registry import config_from_dict
@@ -34,8 +40,10 @@ def model_folder(tag: str, seed: int = 0, std: float = WEIGHT_STD) -> Path:
 
 
 @functools.lru_cache(maxsize=None)
-def plain_weights(tag: str, seed: int = 0, std: float = WEIGHT_STD):
-    return read_safetensors(model_folder(tag, seed, std) / "model.safetensors")
+def plain_weights(tag: str, seed: int = 0, std: float | None = None):
+    weights = read_safetensors(model_folder(tag, seed, std) / "model.safetensors")
+    device = PLAIN_DEVICE.get(tag, "cpu")
+    return weights if device == "cpu" else {name: tensor.to(device) for name, tensor in weights.items()}
 
 
 def requests_for(tag: str, lengths, seed: int = 7) -> list[list[int]]:
@@ -64,7 +72,7 @@ def plain_logits(tag: str, tokens: list[int], mode: str = "f64", seed: int = 0) 
                 out = plain.forward(ids, weights, CONFIGS[tag], torch.float32)
             finally:
                 plain.LOWP = None
-        _plain_cache[key] = out
+        _plain_cache[key] = out.cpu()
     return _plain_cache[key]
 
 

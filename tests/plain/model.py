@@ -1,5 +1,6 @@
 """A plain, slow implementation of the Qwen3-style dense decoder, written from the reference's
-formulas.  Whole sequences, no cache, one function for each part, PyTorch on the CPU.
+formulas.  Whole sequences, no cache, one function for each part, PyTorch on the CPU (or, for the
+tests at real layer sizes, the same lines on the device that holds the tensors it is given).
 
 It shares no code with the library under test: it reads a dict of tensors keyed by the
 reference's state-dict names and a dict of config values, nothing else.  Every function
@@ -50,7 +51,7 @@ def rotary_tables(positions: torch.Tensor, head_dim: int, theta: float) -> tuple
     Returned tables are [T, d] with the d/2 angles repeated twice (cat(freqs, freqs)).
     """
     inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
-    freqs = positions.to(torch.float32)[:, None] * inv_freq
+    freqs = positions.to(torch.float32)[:, None] * inv_freq.to(positions.device)
     emb = torch.cat((freqs, freqs), dim=-1)
     return emb.cos(), emb.sin()
 
@@ -81,7 +82,7 @@ def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, wind
     n_kv = k.shape[1]
     group = n_q // n_kv
     out = torch.empty_like(q)
-    idx = torch.arange(n_tokens)
+    idx = torch.arange(n_tokens, device=q.device)
     visible = idx[None, :] <= idx[:, None]
     if window:
         visible &= idx[None, :] > idx[:, None] - window
@@ -108,7 +109,7 @@ def attention_mixer(x: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, cf
     v = mm(x, w[prefix + "v_proj.weight"].T).view(n_tokens, n_kv, d)
     q = rms_norm(q, w[prefix + "q_norm.weight"], eps)
     k = rms_norm(k, w[prefix + "k_norm.weight"], eps)
-    cos, sin = rotary_tables(torch.arange(n_tokens), d, cfg["rope_theta"])
+    cos, sin = rotary_tables(torch.arange(n_tokens, device=x.device), d, cfg["rope_theta"])
     q = apply_rotary(q, cos, sin)
     k = apply_rotary(k, cos, sin)
     o = causal_gqa_attention(q, k, v)
@@ -136,6 +137,7 @@ def forward(ids: torch.Tensor, w: dict[str, torch.Tensor], cfg: dict, dtype: tor
     head  — src/models/transformer.py:60-67,99-101.  A tied head multiplies by the embedding
     table (transformer.py:76-77)."""
     w = {name: tensor.to(dtype) for name, tensor in w.items()}
+    ids = ids.to(w["model.embed_tokens.weight"].device)
     h = embed(ids, w["model.embed_tokens.weight"])
     for layer in range(cfg["num_hidden_layers"]):
         h = block(h, w, layer, cfg)

@@ -34,7 +34,7 @@ def test_no_size_is_defaulted():
 
 
 @pytest.mark.parametrize("key,value", [
-    ("num_key_value_heads", 3), ("head_dim", 15), ("hidden_size", 0), ("rms_norm_eps", 0.0), ("eos_token_id", 9999),
+    ("num_key_value_heads", 3), ("head_dim", 15), ("head_dim", 12), ("hidden_size", 0), ("rms_norm_eps", 0.0), ("eos_token_id", 9999),
     ("vocab_size", 2.5), ("tie_word_embeddings", 1),
 ])
 def test_bad_values_are_refused(key, value):

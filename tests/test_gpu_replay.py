@@ -173,3 +173,48 @@ def test_decode_in_batches_of_more_than_eight(tag, dtype, n_requests):
         tokens = requests[r]
         check_against_plain(tag, dtype, tokens, list(range(len(tokens))), torch.cat(got[r]), f"{tag} {dtype} request {r} of {n_requests}")
     assert engine.cache.slots.n_used == 0
+
+
+@pytest.mark.parametrize("cast", [False, True])
+def test_folder_stored_in_32_bit_run_in_bfloat16(tmp_path, cast):
+    """A folder whose matrices are stored in 32-bit, run in bfloat16.  By default a tensor stored in 32-bit stays
+    so: its projections run on the exact 32-bit kernel (the loader warns that this is slow) and the logits are
+    closer to the oracle than bfloat16 weights could make them.  With ``cast_matrices`` the matrices are rounded
+    to bfloat16 at load, as the reference's autocast rounds them at every projection (src/engine.py:35), and the
+    model is the same as one loaded from the rounded folder."""
+    import warnings
+
+    from gtar_kimik3_public_b200.engine import Engine
+    from gtar_kimik3_public_b200.generate import load
+    from gtar_kimik3_public_b200.registry import config_from_dict
+    from gtar_kimik3_public_b200.weights import write_random_model
+    from tests.plain import model as plain
+    from tests.plain.weights import read_safetensors
+
+    cfg = CONFIGS["tiny_b"]
+    folder = write_random_model(tmp_path / "f32", config_from_dict(cfg), seed=5, std=0.08, matrix_dtype=torch.float32)
+    weights = read_safetensors(folder / "model.safetensors")
+    assert weights["model.layers.0.mlp.down_proj.weight"].dtype == torch.float32
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        model = load(folder, "bfloat16", "cuda:0", cast_matrices=cast)
+    assert any("32-bit" in str(w.message) for w in caught) == (not cast)
+    kept = model.plan.layers[0].feed_forward.w_down.dtype
+    assert kept == (torch.bfloat16 if cast else torch.float32)
+    engine = Engine(model, 256, max_seqs=2)
+    (tokens,) = requests_for("tiny_b", [90], seed=5)
+    head = len(tokens) - 10
+    parts = [engine.step([_entry("r", tokens[:head], list(range(head)))])]
+    for t in range(head, len(tokens)):
+        parts.append(engine.step([_entry("r", [tokens[t]], [0])]))
+    got = torch.cat(parts).double().cpu()
+    if cast:
+        weights = {k: (v.to(torch.bfloat16).float() if v.dim() == 2 else v) for k, v in weights.items()}
+    oracle = plain.forward(torch.tensor(tokens), weights, cfg, torch.float64)
+    plain.LOWP = torch.bfloat16
+    try:
+        lowp = plain.forward(torch.tensor(tokens), weights, cfg, torch.float32).double()
+    finally:
+        plain.LOWP = None
+    err, yard = (got - oracle).abs().max().item(), (lowp - oracle).abs().max().item()
+    assert err <= 2 * yard + 1e-4, f"error {err:.3e} against a yardstick of {yard:.3e}"

@@ -8,7 +8,7 @@ def test_decode_splits_stay_within_what_the_kernels_take():
         for n_kv in (1, 2, 8):
             for length in (1, 63, 64, 65, 600, 2304, 8192, 40000):
                 pages = -(-length // 64)
-                s = decode_splits(n_seqs, n_kv, length, 64)
+                s = decode_splits(n_seqs, n_kv, length, 64, 148)
                 assert 1 <= s <= max(1, min(pages, 64)), (n_seqs, n_kv, length, s)
                 # more than eight splits (scratch and a second kernel) only for long contexts and few sequences
                 assert s in (1, 2, 4, 8) or (s >= SCRATCH_SPLITS_FROM and length >= 8192), (n_seqs, n_kv, length, s)
@@ -17,12 +17,12 @@ def test_decode_splits_stay_within_what_the_kernels_take():
 def test_decode_splits_at_measured_points():
     """The choices that measured step times (batch 1 to 64, 2,048-token contexts, 8 kv heads, 148 SMs) favour."""
     want = {1: 8, 2: 8, 8: 4, 12: 2, 16: 2, 24: 1, 32: 1, 40: 2, 48: 2, 64: 1}
-    assert {b: decode_splits(b, 8, 2304, 64) for b in want} == want
+    assert {b: decode_splits(b, 8, 2304, 64, 148) for b in want} == want
 
 
 def test_decode_splits_one_page_one_block():
-    assert decode_splits(1, 8, 40, 64) == 1
-    assert decode_splits(64, 8, 64, 64) == 1
+    assert decode_splits(1, 8, 40, 64, 148) == 1
+    assert decode_splits(64, 8, 64, 64, 148) == 1
 
 
 def test_split_k_is_a_cluster_size():
