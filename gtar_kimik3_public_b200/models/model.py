@@ -14,6 +14,7 @@ from dataclasses import dataclass, field
 import torch
 
 from ..cache import Cache, CacheLayout
+from ..ops import functional as F
 from ..parts.base import Block, Norm, Part, PositionEncoding, StepContext, TensorSpec
 from ..parts.embedding import OutputHead, TokenEmbedding
 
@@ -92,6 +93,19 @@ class Model:
         parts = [plan.embedding, plan.final_norm, plan.head, *plan.positions, *(plan.layers[e.layer] for e in plan.run_list)]
         return all(getattr(part, "graph_safe", False) for part in parts)
 
+    def persistent_decode(self, cache: Cache):
+        """The plan that runs all layers of a small decode step as one kernel on this cache (made once per cache),
+        or None if the model's layers, its sizes or the cache are not what that kernel takes."""
+        plans = self.__dict__.setdefault("_persistent_plans", {})
+        key = id(cache)
+        if key not in plans or plans[key][0]() is not cache:
+            import weakref
+
+            from .persistent_decode import build
+
+            plans[key] = (weakref.ref(cache), build(self, cache))
+        return plans[key][1]
+
     # ------------------------------------------------------------------ the forward pass of one step
     def prepare(self, max_position: int) -> None:
         for position in self.plan.positions:
@@ -104,9 +118,13 @@ class Model:
         self.prepare(ctx.max_position)
         h = plan.embedding.forward(ctx.tokens)
         pending = None
-        for index, entry in enumerate(plan.run_list):
-            ctx.extras["cache_read_only"] = cache.is_shared(index)
-            h, pending = plan.layers[entry.layer].forward(h, pending, ctx, cache.view(index))
+        persistent = self.persistent_decode(cache) if ctx.all_single and ctx.n_seqs <= F.DECODE_LAYERS_MAX_SEQS else None
+        if persistent is not None:
+            persistent.run(h, ctx)  # every layer of the run list in one kernel; the stream is complete afterwards
+        else:
+            for index, entry in enumerate(plan.run_list):
+                ctx.extras["cache_read_only"] = cache.is_shared(index)
+                h, pending = plan.layers[entry.layer].forward(h, pending, ctx, cache.view(index))
         if ctx.want_rows.numel() == 0:
             # nothing asked for: still fold the last branch into the stream so the step is whole
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)

@@ -709,3 +709,59 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
         raise KernelError(f"x is {tuple(x.shape)} but weight is {tuple(weight.shape)}")
     y = torch.mm(x, weight.t())
     return y if out_dtype == torch.bfloat16 else y.to(out_dtype)
+
+
+# ------------------------------------------------------------------ a run of layers of a decode step as one kernel
+DECODE_LAYERS_MAX_SEQS = 8
+
+
+def decode_layers_work_sizes(n_seqs: int, hidden: int, n_q: int, n_kv: int, head_dim: int, inter: int, max_kv_len: int,
+                             page_size: int) -> tuple[int, int] | None:
+    """(floats of partial results, 32-bit words of counters) that ``decode_layers`` needs for these sizes, or None if
+    the kernel does not take them (the library's message says why: ``library().gk_last_error()``)."""
+    import ctypes
+
+    from .library import library
+
+    out = (ctypes.c_longlong * 2)()
+    status = library().gk_decode_layers_plan(n_seqs, hidden, n_q, n_kv, head_dim, inter, max_kv_len, page_size, out)
+    return (int(out[0]), int(out[1])) if status == 0 else None
+
+
+def decode_layers(layer_table: torch.Tensor, n_layers: int, h: torch.Tensor, n_q: int, n_kv: int, head_dim: int, inter: int,
+                  qkv: torch.Tensor, att: torch.Tensor, act: torch.Tensor, part: torch.Tensor, words: torch.Tensor,
+                  kv_len: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, max_kv_len: int,
+                  cos: torch.Tensor | None, sin: torch.Tensor | None, norm_bf16: bool, qk_bf16: bool, scale: float,
+                  stamps: torch.Tensor | None = None) -> None:
+    """Runs ``n_layers`` pre-norm layers (RMSNorm, grouped-query attention with per-head q/k norm and rotation over
+    the paged cache, RMSNorm, SwiGLU) of a decode step on the stream ``h [n_seqs, hidden]`` (float32, updated in
+    place) as one persistent kernel.  ``layer_table``: the layers' pointers and constants as the kernel's records (96
+    bytes each, see ``models/persistent_decode.py``); ``qkv``, ``att``, ``act``, ``part``, ``words``: work areas
+    (``words`` zero before the first call; the kernel leaves it zero).  ``stamps`` (int64 ``[blocks, 5 n_layers, 2]``,
+    for measurements): every block's clock readings, in nanoseconds, at its arrival at and release from each barrier."""
+    require_device(h.device)
+    _check(h, "h", torch.float32, 2)
+    _check(layer_table, "layer_table", torch.uint8, 1)
+    n_seqs, hidden = h.shape
+    if layer_table.shape[0] < 96 * n_layers:
+        raise KernelError("the layer table is shorter than its layers")
+    for name, t, dtype in (("qkv", qkv, torch.bfloat16), ("att", att, torch.bfloat16), ("act", act, torch.bfloat16),
+                           ("part", part, torch.float32), ("words", words, torch.int32), ("kv_len", kv_len, torch.int32),
+                           ("slots", slots, torch.int32)):
+        _check(t, name, dtype)
+    _check(block_table, "block_table", torch.int32, 2)
+    if qkv.numel() < n_seqs * (n_q + 2 * n_kv) * head_dim or att.numel() < n_seqs * n_q * head_dim or act.numel() < n_seqs * inter:
+        raise KernelError("a work area is smaller than the step needs")
+    if words.numel() < 8 + n_seqs * n_kv or kv_len.shape[0] != n_seqs or slots.shape[0] != n_seqs:
+        raise KernelError("counters, lengths and slots need one entry per sequence (and kv head)")
+    table_positions = 0
+    if cos is not None:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+            raise KernelError("rotary tables must be [positions, head_dim / 2]")
+        table_positions = cos.shape[0]
+    call("gk_decode_layers", ptr(layer_table), n_layers, n_seqs, hidden, n_q, n_kv, head_dim, inter, ptr(h), ptr(qkv), ptr(att),
+         ptr(act), ptr(part), part.numel(), ptr(words), ptr(kv_len), ptr(slots), ptr(block_table), block_table.shape[1],
+         int(max_kv_len), ptr(cos), ptr(sin), table_positions, int(norm_bf16), int(qk_bf16), float(scale),
+         ptr(error_flag(h.device)), ptr(stamps), stream_ptr())

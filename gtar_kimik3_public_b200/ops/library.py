@@ -32,6 +32,8 @@ _SIGNATURES: dict[str, list] = {
     "gk_embed_rows": [P, I, P, P, I, I, P],
     "gk_add_rmsnorm": [P, P, I, P, I, P, I, P, I, I, F, P],
     "gk_swiglu": [P, P, I, I, I, I, P],
+    "gk_decode_layers_plan": [I, I, I, I, I, I, I, I, P],
+    "gk_decode_layers": [P, I, I, I, I, I, I, I, P, P, P, P, P, L, P, P, P, P, I, I, P, P, I, I, I, F, P, P, P],
     "gk_qk_norm_rope_write": [P, I, P, P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_gemm_f32": [P, I, P, P, I, I, I, I, L, L, L, P],
     "gk_attention_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],

@@ -62,6 +62,17 @@ class GQAAttention(Mixer):
     def cache_request(self):
         return KVRequest(self.n_kv, self.head_dim, self.window)
 
+    def decode_record(self):
+        if self.window or self.w_qkv.dtype != torch.bfloat16 or self.w_o.dtype != torch.bfloat16:
+            return None
+        rope = self.position
+        if rope is not None and not (hasattr(rope, "cos") and hasattr(rope, "sin") and getattr(rope, "dim", None) == self.head_dim):
+            return None  # another position encoding than tables of cos and sin over the whole head
+        return {"kind": "gqa", "hidden": self.hidden_size, "n_q": self.n_q, "n_kv": self.n_kv, "head_dim": self.head_dim,
+                "w_qkv": self.w_qkv, "w_o": self.w_o, "q_norm": self.q_norm, "k_norm": self.k_norm,
+                "has_qk_norm": self.q_norm is not None, "eps_qk": self.qk_norm_eps or 1.0,
+                "qk_dtype": None if self.q_norm is None else self.q_norm.dtype, "rope": rope, "scale": self.scale}
+
     def forward(self, x, ctx: StepContext, cache: F.PagedKV) -> torch.Tensor:
         cos = sin = None
         if self.position is not None:

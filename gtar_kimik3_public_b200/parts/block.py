@@ -32,6 +32,27 @@ class PreNormBlock(Block):
     def weight_bytes(self):
         return sum(part.weight_bytes() for _, part in self.children())
 
+    def decode_record(self) -> dict | None:
+        """What the persistent decode kernel needs of this layer (weights, constants, sizes), or None when one of
+        the four parts is not of the kind that kernel computes; each part answers for itself."""
+        pieces = {}
+        for key, part in (("in", self.input_norm), ("mixer", self.mixer), ("post", self.post_norm), ("ffn", self.feed_forward)):
+            describe = getattr(part, "decode_record", None)
+            piece = describe() if describe is not None else None
+            if piece is None:
+                return None
+            pieces[key] = piece
+        norm_in, norm_post, mixer, ffn = pieces["in"], pieces["post"], pieces["mixer"], pieces["ffn"]
+        if mixer.get("kind") != "gqa" or ffn.get("kind") != "swiglu" or norm_in.get("kind") != "rmsnorm" or norm_post.get("kind") != "rmsnorm":
+            return None
+        if not (norm_in["size"] == norm_post["size"] == mixer["hidden"] == ffn["hidden"]):
+            return None
+        if norm_in["weight"].dtype != norm_post["weight"].dtype:
+            return None
+        return {**mixer, "inter": ffn["inter"], "w_gu": ffn["w_gu"], "w_down": ffn["w_down"], "norm_in": norm_in["weight"],
+                "norm_post": norm_post["weight"], "eps_in": norm_in["eps"], "eps_post": norm_post["eps"],
+                "norm_dtype": norm_in["weight"].dtype}
+
     def forward(self, h, pending, ctx: StepContext, cache):
         x = self.input_norm.forward(h, pending, ctx.dtype)
         branch = self.mixer.forward(x, ctx, cache)

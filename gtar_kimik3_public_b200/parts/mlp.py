@@ -37,6 +37,12 @@ class SwiGLUFeedForward(FeedForward):
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
+    def decode_record(self):
+        if self.w_gate_up.dtype != torch.bfloat16 or self.w_down.dtype != torch.bfloat16:
+            return None
+        return {"kind": "swiglu", "hidden": self.hidden_size, "inter": self.intermediate_size, "w_gu": self.w_gate_up,
+                "w_down": self.w_down}
+
     def forward(self, x, ctx: StepContext) -> torch.Tensor:
         return linear(linear(x, self.w_gate_up, swiglu=True), self.w_down)
 

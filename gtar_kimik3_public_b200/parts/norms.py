@@ -26,6 +26,9 @@ class RMSNorm(Norm):
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
+    def decode_record(self):
+        return {"kind": "rmsnorm", "size": self.size, "eps": self.eps, "weight": self.weight}
+
     def forward(self, h, delta, out_dtype, rows=None):
         return F.add_rmsnorm(h, delta, self.weight, self.eps, out_dtype, rows)
 

@@ -147,7 +147,7 @@ def test_many_token_graph_serves_another_split_of_the_same_shape(tag, dtype):
     engine.check()
 
 
-@pytest.mark.parametrize("tag,dtype,n_requests", [("real_06b", "bfloat16", 40), ("real_06b", "bfloat16", 64), ("real_4b", "bfloat16", 33),
+@pytest.mark.parametrize("tag,dtype,n_requests", [("real_06b", "bfloat16", 12), ("real_06b", "bfloat16", 40), ("real_06b", "bfloat16", 64), ("real_4b", "bfloat16", 33),
                                                   ("tiny_c", "bfloat16", 40), ("tiny_a", "bfloat16", 64), ("real_06b", "float32", 40)])
 def test_decode_steps_of_many_sequences(tag, dtype, n_requests, kernel_log):
     """33 to 64 sequences: every product of a decode step runs in the swap-AB orientation on tcgen05, with K split
@@ -171,7 +171,10 @@ def test_decode_steps_of_many_sequences(tag, dtype, n_requests, kernel_log):
     while live:
         logits = engine.step([_entry(r, [requests[r][fed[r]]], [0]) for r in live])
         if steps == 0 and dtype == "bfloat16":
-            assert "gk_gemm_bf16_tc" in kernel_log, "the first decode step did not take the tensor-memory product"
+            if n_requests > 32:
+                assert "gk_gemm_bf16_tc" in kernel_log, "the first decode step did not take the tensor-memory product"
+            else:  # 9 to 32 sequences: the few-token product and decode attention fused with the q/k preparation
+                assert "gk_gemv_bf16" in kernel_log and "gk_attention_decode_fused_bf16" in kernel_log
         steps += 1
         for i, r in enumerate(live):
             got[r].append(logits[i:i + 1])
@@ -227,3 +230,43 @@ def test_a_rows_logits_do_not_depend_on_how_many_rows_are_wanted():
     assert (one[0] - many[50]).abs().max().item() < 2e-5
     rounded = many.to(torch.bfloat16).to(torch.float32)
     assert (rounded - many).abs().max().item() > 1e-4, "logits look rounded to bfloat16"
+
+
+@pytest.mark.parametrize("n_seqs", [1, 3, 8])
+def test_persistent_kernel_for_all_layers_of_a_decode_step(n_seqs, kernel_log, monkeypatch):
+    """The optional path that runs every layer of a small decode step as one persistent kernel (grid-wide barriers
+    between a layer's stages, weights and cached keys streamed through per-warp rings across them): unequal
+    sequences, the shorter ending earlier, launched one by one and replayed from graphs, over poisoned pages."""
+    from gtar_kimik3_public_b200.models import persistent_decode
+
+    monkeypatch.setattr(persistent_decode, "ENABLED", True)
+    tag, dtype = "real_06b", "bfloat16"
+    requests = requests_for(tag, [70, 3, 200, 64, 65, 129, 17, 300][:n_seqs], seed=59)
+    results = []
+    for use_graphs in (False, True):
+        engine = load_engine(tag, dtype, max_tokens=n_seqs * 512, max_seqs=n_seqs, use_graphs=use_graphs)
+        assert engine.model.persistent_decode(engine.cache) is not None
+        poison(engine)
+        fed = {r: max(1, len(requests[r]) - 6) for r in range(n_seqs)}
+        engine.step([_entry(r, requests[r][:fed[r]], []) for r in range(n_seqs)])
+        rows = {r: [] for r in range(n_seqs)}
+        live = [r for r in range(n_seqs) if fed[r] < len(requests[r])]
+        engine.end([r for r in range(n_seqs) if r not in live])
+        del kernel_log[:]
+        while live:
+            logits = engine.step([_entry(r, [requests[r][fed[r]]], [0]) for r in live])
+            for i, r in enumerate(live):
+                rows[r].append(logits[i:i + 1].clone())
+                fed[r] += 1
+            done = [r for r in live if fed[r] == len(requests[r])]
+            engine.end(done)
+            live = [r for r in live if r not in done]
+        assert "gk_decode_layers" in kernel_log and "gk_attention_decode_fused_bf16" not in kernel_log
+        engine.check()
+        for r, got in rows.items():
+            if got:
+                n = len(requests[r])
+                check_against_plain(tag, dtype, requests[r], list(range(n - len(got), n)), torch.cat(got), f"persistent decode, request {r}")
+        results.append({r: torch.cat(got) for r, got in rows.items() if got})
+    for r in results[0]:
+        assert torch.equal(results[0][r], results[1][r]), "replayed from a graph, the persistent kernel gave other numbers"
