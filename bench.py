@@ -50,6 +50,17 @@ BENCH_CONFIG = {
 }
 PROMPT_LEN = 2048
 PREFILL_TOKENS = 2048
+# BASELINE.json configs[3] and configs[4]: the Qwen3-4B and Qwen3-8B layer sizes, measured as extra points
+LARGE_CONFIGS = {
+    "qwen3_4b": {"arch": "transformer", "vocab_size": 151936, "hidden_size": 2560, "intermediate_size": 9728,
+                 "num_hidden_layers": 36, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+                 "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "tie_word_embeddings": True, "initializer_range": 0.02,
+                 "max_position_embeddings": 8192},
+    "qwen3_8b": {"arch": "transformer", "vocab_size": 151936, "hidden_size": 4096, "intermediate_size": 12288,
+                 "num_hidden_layers": 36, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+                 "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "tie_word_embeddings": False, "initializer_range": 0.02,
+                 "max_position_embeddings": 4096},
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -276,6 +287,99 @@ def time_prefill(model, warmup: int, repeats: int = 3) -> dict:
     return {"value": t / (ms / 1e3), "tokens": t, "ms": ms, "flops": flops}
 
 
+def prefill_flops(config, layers: int, lengths) -> float:
+    """Matrix products of every token, attention over the causal half of each prompt, the head for one row each."""
+    c = config
+    per_token = 2 * c.hidden_size * ((2 * c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim + 3 * c.intermediate_size)
+    attention = sum(4 * c.num_attention_heads * c.head_dim * t * t / 2 for t in lengths)
+    return layers * (per_token * sum(lengths) + attention) + 2 * c.hidden_size * c.vocab_size * len(lengths)
+
+
+def time_large(name: str, peak: dict, steps: int, warmup: int) -> dict:
+    """The 4B and 8B workloads: weights drawn on the device (a folder of these sizes would take minutes to write
+    and read), the whole number of layers.  4B: eight prompts of unequal lengths (uniform in [256, 4096], seeded) in
+    one step, then decode steps.  8B: 64 prompts of 1,024 tokens, then decode steps; and one 2,048-token prompt."""
+    import random
+
+    import torch
+
+    from gtar_kimik3_public_b200.cache import rounded_tokens
+    from gtar_kimik3_public_b200.engine import Engine, StepEntry
+    from gtar_kimik3_public_b200.models.model import Model
+    from gtar_kimik3_public_b200.ops import functional as F
+    from gtar_kimik3_public_b200.registry import architecture, config_from_dict
+    from gtar_kimik3_public_b200.weights import load_random_weights
+
+    config = config_from_dict(LARGE_CONFIGS[name])
+    model = Model(architecture(config.ARCH_NAMES[0]).build_plan(config), config, torch.bfloat16, "cuda:0")
+    load_random_weights(model, seed=0)
+    layers = len(model.plan.run_list)
+    rng = random.Random(0)
+    if name == "qwen3_4b":
+        lengths, steps, group = [rng.randint(256, 4096) for _ in range(8)], min(steps, 256), 8
+    else:
+        lengths, steps, group = [1024] * 64, min(steps, 64), 8
+    batch = len(lengths)
+    engine = Engine(model, sum(rounded_tokens(n + warmup + steps + 1) for n in lengths), max_seqs=batch)
+    gen = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, config.vocab_size, (n,), generator=gen).tolist() for n in lengths]
+    ids = list(range(batch))
+    out = {}
+    with torch.no_grad():
+        logits = None
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        for start in range(0, batch, group):
+            part = engine.step([StepEntry(i, prompts[i], [lengths[i] - 1]) for i in ids[start:start + group]])
+            logits = part if logits is None else torch.cat([logits, part])
+        end.record()
+        torch.cuda.synchronize()
+        if name == "qwen3_4b":  # the unequal prompts in one step (launched kernel by kernel: a first appearance of its shape)
+            ms = begin.elapsed_time(end)
+            out[f"{name}_prefill_unequal_tokens_per_s"] = round(sum(lengths) / (ms / 1e3), 1)
+            out[f"{name}_prefill_unequal_frac"] = round(prefill_flops(config, layers, lengths) / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)
+        tokens = F.argmax(logits)
+        for _ in range(warmup):
+            tokens = F.argmax(engine.decode_on_device(ids, tokens))
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(steps):
+            tokens = F.argmax(engine.decode_on_device(ids, tokens))
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / steps
+        kv_tokens = sum(engine.cache.length.values()) - batch * (steps // 2)
+        step_bytes_read = decode_bytes(model, engine, kv_tokens)
+        tag = f"{name}_decode_b{batch}" + ("_unequal" if name == "qwen3_4b" else "")
+        out[tag] = round(batch / (ms / 1e3), 1)
+        out[tag + "_ms"] = round(ms, 4)
+        out[tag + "_hbm_frac"] = round(step_bytes_read / (ms / 1e3) / 1e9 / peak["hbm_gbs"], 4)
+        engine.end_all()
+        del engine
+        torch.cuda.empty_cache()
+        if name == "qwen3_8b":
+            engine = Engine(model, rounded_tokens(PREFILL_TOKENS + 1), max_seqs=1)
+            prompt = torch.randint(0, config.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
+            times = []
+            for i in range(4):
+                torch.cuda.synchronize()
+                begin.record()
+                engine.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+                end.record()
+                torch.cuda.synchronize()
+                engine.end(["p"])
+                times.append(begin.elapsed_time(end))
+            ms = statistics.median(times[1:])
+            out[f"{name}_prefill_{PREFILL_TOKENS}_tokens_per_s"] = round(PREFILL_TOKENS / (ms / 1e3), 1)
+            out[f"{name}_prefill_{PREFILL_TOKENS}_frac"] = round(prefill_flops(config, layers, [PREFILL_TOKENS]) / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)
+            del engine
+    out[f"{name}_layers"] = layers
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -284,6 +388,7 @@ def run_ours(args) -> dict:
     require_device(torch.device("cuda:0"))
     peak, peak_source = peaks()
     model, config = make_model("bfloat16", args.layers)
+    layers_run = len(model.plan.run_list)
     batch = args.batch
     main = time_decode(model, batch, args.steps, args.warmup, sample_clocks=True)
     e2e = time_e2e(model, batch, args.steps, args.warmup)
@@ -291,6 +396,14 @@ def run_ours(args) -> dict:
     points = {}
     for b in (1, 64):
         points[f"decode_b{b}"] = round(time_decode(model, b, min(args.steps, 64), args.warmup)["tokens_per_s"], 1)
+    del model
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    if not args.no_large:
+        for name in LARGE_CONFIGS:
+            points.update(time_large(name, peak, args.steps, args.warmup))
     achieved = main["bytes_per_step"] / (main["ms_per_step"] / 1e3) / 1e9
     prefill_peak = peak["bf16_tflops"] * 1e12
     return {
@@ -307,7 +420,7 @@ def run_ours(args) -> dict:
         "dtype": "bf16",
         "data": "synthetic: seeded uniform-random token ids, random weights (N(0, 0.02)) of the named architecture",
         "impl": "ours",
-        "config": config_record(batch, len(model.plan.run_list), peak_source),
+        "config": config_record(batch, layers_run, peak_source),
         "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": main["launches"],
         "clocks": main["clocks"],
@@ -459,6 +572,7 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    parser.add_argument("--no-large", action="store_true", help="leave out the points at the 4B and 8B layer sizes")
     args = parser.parse_args()
     if args.impl == "reference":
         if args.warmup < 3:

@@ -61,3 +61,36 @@ def write_random_model(folder: str | Path, config: ModelConfig, seed: int, std: 
     (folder / "config.json").write_text(json.dumps(config.to_dict(), indent=2) + "\n")
     write_safetensors(folder / "model.safetensors", tensors, {"format": "pt", "seed": str(seed)})
     return folder
+
+
+def load_random_weights(model, seed: int, std: float | None = None) -> None:
+    """Fills a model with random weights drawn on its own device (no folder in between): for sizes at which
+    writing and reading a model folder would take minutes.  The values follow the same rule as
+    ``write_random_model`` (matrices N(0, std) in bfloat16, vectors 1 + N(0, 0.1) in float32) but come from the
+    device's generator, so they are not the numbers that a folder of the same seed holds."""
+    from .loader import stored_dtype_rule
+
+    if std is None:
+        std = getattr(model.config, "initializer_range", None)
+        if std is None:
+            raise ValueError("the configuration has no initializer_range; pass std")
+    gen = torch.Generator(device=model.device).manual_seed(int(seed))
+    tensors = {}
+    for name, spec in model.tensor_specs().items():
+        if spec.optional:
+            continue
+        if spec.kind == "table":
+            tensors[name] = torch.randint(0, 2**15, spec.shape, generator=gen, dtype=torch.int32, device=model.device)
+        elif spec.kind == "vector":
+            keep = stored_dtype_rule(torch.float32, spec.kind, model.dtype)
+            tensors[name] = (1.0 + 0.1 * torch.randn(spec.shape, generator=gen, device=model.device)).to(keep)
+        else:
+            keep = stored_dtype_rule(torch.bfloat16, spec.kind, model.dtype)
+            t = torch.empty(spec.shape, dtype=keep, device=model.device)
+            rows = spec.shape[0]
+            step = max(1, (1 << 26) // max(1, t[0].numel()))
+            for start in range(0, rows, step):  # row blocks: no second full-size 32-bit buffer
+                n = min(step, rows - start)
+                t[start:start + n] = (torch.randn((n, *spec.shape[1:]), generator=gen, device=model.device) * std).to(keep)
+            tensors[name] = t
+    model.load(tensors)
