@@ -10,13 +10,24 @@
 //                 B = V page (64 keys x 128, shared memory, read with the keys as the MMA's K: "MN-major")
 //                 -> O in tensor memory, 128 lanes x 128 columns
 //
-// A block owns 128 rows = (token, query head of one kv group) pairs of one sequence and one kv head.
-// Warp 0 streams K and V pages with TMA (a 2-D map over the cache seen as [pages * heads * 64, 128]);
-// warp 1 issues the MMAs; warps 2-5 are the softmax: thread = row, so maxima and sums need no
-// shuffles.  The accumulator is rescaled only when a row's maximum has grown by more than 2^8 since
-// its last rescale (the probabilities then stay below 2^8, which bfloat16 and the 32-bit sum hold
-// with room to spare), so most pages cost no pass over O.  Two blocks share an SM (256 tensor-memory
-// columns and 97 KB of shared memory each), so one block's softmax overlaps the other's products.
+// A query tile is 128 rows = (token, query head of one kv group) pairs of one sequence and one kv head.  The
+// accumulator is rescaled only when a row's maximum has grown by more than 2^8 since its last rescale (the
+// probabilities then stay below 2^8, which bfloat16 and the 32-bit sum hold with room to spare), so most steps
+// cost no pass over O.  Two kernels:
+//
+//   * attention_prefill_tc2_kernel, the default: 128 keys (two pages) a step, one block per SM with all 512
+//     tensor-memory columns (two score buffers, so the MMA warp forms the next scores while the softmax works on
+//     these; P; O), keys and values through TMA in rings of their own (three and two stages: the keys of a step
+//     are wanted a step before its values), eight softmax warps with two threads a row, and two query tiles per
+//     block, the c-th from the end and then the c-th from the start, so that under the causal mask every block
+//     has the same work.  Its own comment further down has the details.
+//   * attention_prefill_tc_kernel: 64 keys a step, one query tile per block, four softmax warps (thread = row),
+//     two blocks per SM (256 tensor-memory columns and 97 KB of shared memory each), so that one block's softmax
+//     overlaps the other's products.  Kept selectable (gk_set_attention_prefill_keys(64)); it is the slower of the
+//     two at every length measured.
+//
+// In both, warp 0 streams K and V pages with TMA (a 2-D map over the cache seen as [pages * heads * 64, 128]) and
+// warp 1 issues the MMAs.
 //
 // Every mbarrier wait is bounded; a wait that gives up records a code in *error_flag and the block
 // winds down (drains its copies, frees its tensor memory).
