@@ -5,6 +5,7 @@
     python -m gtar_kimik3_public_b200.ops.microbench --kernel attention_decode --batch 8 --context 2048
     python -m gtar_kimik3_public_b200.ops.microbench --kernel attention_prefill --tokens 2048
     python -m gtar_kimik3_public_b200.ops.microbench --kernel step --batch 8 --context 2048
+    python -m gtar_kimik3_public_b200.ops.microbench --kernel decode_layers --batch 8 --context 2048
 
 Each run launches the kernel on fresh inputs (a ring of operand sets larger than the L2 cache, so
 that every launch reads from HBM), times it with CUDA events over a graph replay, and prints one
@@ -168,9 +169,68 @@ def bench_step(args) -> dict:
             "us": round(begin.elapsed_time(end) * 1e3, 1)}
 
 
+def bench_decode_layers(args) -> dict:
+    """One decode step through the persistent kernel for all layers, with the kernel's own clock stamps: for every
+    stage of a layer in the middle of the model, how long the blocks work on it (from their release out of the barrier
+    before it to their arrival at the barrier behind it) and how long the barrier takes once the last block is there."""
+    import tempfile
+
+    from ..engine import Engine, StepEntry
+    from ..generate import load
+    from ..models import persistent_decode
+    from ..registry import config_from_dict
+    from ..weights import write_random_model
+
+    persistent_decode.ENABLED = True
+    config = config_from_dict({
+        "arch": "transformer", "vocab_size": 151936, "hidden_size": 1024, "intermediate_size": 3072,
+        "num_hidden_layers": args.layers, "num_attention_heads": args.q_heads, "num_key_value_heads": args.kv_heads,
+        "head_dim": args.head_dim, "rms_norm_eps": 1e-6, "rope_theta": 1e6, "tie_word_embeddings": True,
+        "initializer_range": 0.02, "max_position_embeddings": 4096,
+    })
+    with tempfile.TemporaryDirectory(prefix="gtar_microbench_") as folder:
+        write_random_model(folder, config, seed=0)
+        model = load(folder, "bfloat16", DEV)
+    b, s, layers = args.batch, args.context, args.layers
+    engine = Engine(model, b * (s + 64), max_seqs=b, use_graphs=False)
+    gen = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, config.vocab_size, (b, s), generator=gen).tolist()
+    ids = list(range(b))
+    blocks = F.sm_count(torch.device(DEV))
+    with torch.no_grad():
+        tokens = F.argmax(engine.step([StepEntry(i, prompts[i], [s - 1]) for i in ids]))
+        plan = model.persistent_decode(engine.cache)
+        if plan is None:
+            raise SystemExit("the persistent kernel does not take this model")
+        for _ in range(3):
+            tokens = F.argmax(engine.decode_on_device(ids, tokens))
+        stamps = torch.zeros(blocks * 5 * layers * 2 + 5 * layers * 8, dtype=torch.int64, device=DEV)
+        plan.stamps = stamps
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        tokens = F.argmax(engine.decode_on_device(ids, tokens))
+        end.record()
+        torch.cuda.synchronize()
+        plan.stamps = None
+    at = stamps[:blocks * 5 * layers * 2].view(blocks, 5 * layers, 2).cpu()
+    layer = layers // 2
+    stages = {}
+    for index, name in enumerate(("qkv", "attention", "output", "gate_up", "down")):
+        o = layer * 5 + index
+        if o == 0 or o >= 5 * layers - 1:
+            continue
+        work = (at[:, o, 0] - at[:, o - 1, 1]).double() / 1e3
+        stages[name] = {"work_us_min_median_max": [round(work.min().item(), 2), round(work.median().item(), 2), round(work.max().item(), 2)],
+                        "barrier_after_last_arrival_us": round((at[:, o, 1].double().median().item() - at[:, o, 0].max().item()) / 1e3, 2)}
+    span = (at[:, 5 * layers - 2, 1].max() - at[:, 0, 0].min()).item() / 1e3
+    return {"kernel": "decode_layers (persistent, all layers)", "batch": b, "context": s, "layers": layers,
+            "step_us": round(begin.elapsed_time(end) * 1e3, 1), "first_to_last_barrier_us": round(span, 1),
+            "stages_of_layer": layer, "stages": stages}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    parser.add_argument("--kernel", required=True, choices=["gemm", "gemv", "attention_decode", "attention_prefill", "step"])
+    parser.add_argument("--kernel", required=True, choices=["gemm", "gemv", "attention_decode", "attention_prefill", "step", "decode_layers"])
     parser.add_argument("--m", type=int, default=8)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=1024)
@@ -189,7 +249,7 @@ def main() -> int:
     args = parser.parse_args()
     F.require_device(torch.device(DEV))
     result = {"gemm": bench_gemm, "gemv": bench_gemv, "attention_decode": bench_attention_decode,
-              "attention_prefill": bench_attention_prefill, "step": bench_step}[args.kernel](args)
+              "attention_prefill": bench_attention_prefill, "step": bench_step, "decode_layers": bench_decode_layers}[args.kernel](args)
     F.check_kernel_errors(DEV)
     print(json.dumps(result))
     return 0
