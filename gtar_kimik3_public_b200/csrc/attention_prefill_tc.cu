@@ -449,13 +449,14 @@ struct alignas(1024) Smem2 {
     __nv_bfloat16 v[KV_STAGES][2][2][PAGE * 64];        // [stage][page of the step][half of the head dim][64 keys x 128 bytes]
     uint64_t k_full[K_STAGES2], k_empty[K_STAGES2], v_full[KV_STAGES], v_empty[KV_STAGES];
     uint64_t s_full[2], s_empty[2], p_full, o_done, q_ready;
-    uint64_t max_ready[2], sum_ready;  // the two halves of the rows have left their maxima / sums
+    uint64_t max_ready[2][4], sum_ready;  // the two halves of a quarter's rows have left their maxima (a barrier per quarter of the rows: only
+                                        // the two warps that share rows wait for each other) / all rows their sums
     float row_max[2][2][ROWS];  // [step parity][half of the keys][row]
     float row_sum[2][ROWS];
     uint32_t tmem_base;
 };
 
-constexpr int THREADS2 = 320;  // TMA warp, MMA warp, eight softmax warps
+constexpr int THREADS2 = 352;  // TMA warp, the warp that issues the score products, eight softmax warps, the warp that issues the P V products
 
 __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                            const __grid_constant__ CUtensorMap map_v,
@@ -496,7 +497,7 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
         for (int b = 0; b < 2; ++b) {
             mbar_init(&sm.s_full[b], 1);
             mbar_init(&sm.s_empty[b], 256);
-            mbar_init(&sm.max_ready[b], 256);
+            for (int quarter = 0; quarter < 4; ++quarter) mbar_init(&sm.max_ready[b][quarter], 64);
         }
         mbar_init(&sm.p_full, 256);
         mbar_init(&sm.o_done, 1);
@@ -566,24 +567,13 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---- MMA issuer
-            const uint32_t id_s = idesc(ROWS, KEYS2, false), id_o = idesc(ROWS, D, true);
+            // ---- issuer of the score products S = Q K^T.  It runs ahead of the softmax by one step (two score
+            // buffers).  A tcgen05.mma costs its issuing thread about 100 cycles, as long as the product takes on
+            // the tensor cores, so a thread that also waits on barriers between its products leaves the tensor
+            // cores idle meanwhile: the two kinds of product of a step have a thread each, and one fills the
+            // other's waits.
+            const uint32_t id_s = idesc(ROWS, KEYS2, false);
             bool ok = true;
-            auto issue_qk = [&](int g) {  // the scores of step g into buffer g & 1
-                const int s = g % K_STAGES2, b = g & 1;
-                if (ok) ok = mbar_wait(&sm.k_full[s], (g / K_STAGES2) & 1);
-                if (ok && g >= 2) ok = mbar_wait(&sm.s_empty[b], ((g >> 1) - 1) & 1);  // the softmax has taken what was there
-                if (!ok) return;
-                fence_after();
-#pragma unroll
-                for (int k = 0; k < D / 16; ++k) {
-                    const uint64_t da = desc_k_major(smem_u32(sm.q[k >> 2]) + (k & 3) * 32);
-                    const uint64_t db = desc_k_major(smem_u32(sm.k[s][k >> 2][0]) + (k & 3) * 32);
-                    umma_ss(tmem + COL2_S + b * KEYS2, da, db, id_s, k > 0);
-                }
-                umma_commit(&sm.k_empty[s]);  // the keys' shared memory is free once the scores are formed
-                umma_commit(&sm.s_full[b]);
-            };
             int g = 0;
             for (int u = 0; u < n_tiles && ok; ++u) {
                 int p_begin, p_end;
@@ -591,11 +581,37 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
                 const int n_iter = (p_end - p_begin + 1) / 2;
                 ok = mbar_wait(&sm.q_ready, u & 1);
                 if (!ok) break;
-                fence_after();
-                issue_qk(g);
                 for (int i = 0; i < n_iter && ok; ++i, ++g) {
-                    if (i + 1 < n_iter) issue_qk(g + 1);  // the next scores while the softmax works on these
+                    const int s = g % K_STAGES2, b = g & 1;
+                    ok = mbar_wait(&sm.k_full[s], (g / K_STAGES2) & 1);
+                    if (ok && g >= 2) ok = mbar_wait(&sm.s_empty[b], ((g >> 1) - 1) & 1);  // the softmax has taken what was there
                     if (!ok) break;
+                    fence_after();
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint64_t da = desc_k_major(smem_u32(sm.q[k >> 2]) + (k & 3) * 32);
+                        const uint64_t db = desc_k_major(smem_u32(sm.k[s][k >> 2][0]) + (k & 3) * 32);
+                        umma_ss(tmem + COL2_S + b * KEYS2, da, db, id_s, k > 0);
+                    }
+                    umma_commit(&sm.k_empty[s]);  // the keys' shared memory is free once the scores are formed
+                    umma_commit(&sm.s_full[b]);
+                }
+                // the tile's queries may be overwritten once its last scores are formed: the softmax warps wait for
+                // the tile's last o_done before they load the next tile's, and that product follows these scores
+            }
+            if (!ok) atomicExch(p.error_flag, 42);
+        }
+    } else if (warp == 10) {
+        if (lane == 0) {
+            // ---- issuer of the products O += P V
+            const uint32_t id_o = idesc(ROWS, D, true);
+            bool ok = true;
+            int g = 0;
+            for (int u = 0; u < n_tiles && ok; ++u) {
+                int p_begin, p_end;
+                span(u, p_begin, p_end);
+                const int n_iter = (p_end - p_begin + 1) / 2;
+                for (int i = 0; i < n_iter && ok; ++i, ++g) {
                     const int s = g % KV_STAGES;
                     ok = mbar_wait(&sm.p_full, g & 1);
                     if (ok) ok = mbar_wait(&sm.v_full[s], (g / KV_STAGES) & 1);
@@ -611,7 +627,7 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
                     umma_commit(&sm.o_done);       // and the accumulator holds this step
                 }
             }
-            if (!ok) atomicExch(p.error_flag, 42);
+            if (!ok) atomicExch(p.error_flag, 44);
         }
     } else {
         // ---- softmax warps: two threads a row.  Warps 2-5 take keys 0..63 of a step, warps 6-9 keys 64..127 (a
@@ -707,8 +723,8 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
                 }
                 // the row's maximum over both halves
                 sm.row_max[g & 1][half][r] = mx;
-                mbar_arrive(&sm.max_ready[g & 1]);  // (release: the store above is visible to who sees the phase end)
-                ok = mbar_wait(&sm.max_ready[g & 1], (g >> 1) & 1);
+                mbar_arrive(&sm.max_ready[g & 1][quarter]);  // (release: the store above is visible to who sees the phase end)
+                ok = mbar_wait(&sm.max_ready[g & 1][quarter], (g >> 1) & 1);
                 if (!ok) break;
                 mx = fmaxf(mx, sm.row_max[g & 1][half ^ 1][r]);
                 const float m_new = fmaxf(m_used, mx * p.sl2);
