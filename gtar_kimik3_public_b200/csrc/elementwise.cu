@@ -92,11 +92,61 @@ __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, const fl
 
 // VEC = 4: rows are read and written four elements at a time (hidden a multiple of 4, aligned rows).
 // The sum of squares is formed element by element in the same order either way.
-template <typename TD, typename TW, typename TO, int VEC>
+// KEEP > 0 (with VEC = 4): a thread keeps its KEEP groups of four elements of the row in registers between the sum of
+// squares and the scaling (rows of up to 1024 * KEEP elements), and has fetched its share of the norm's weights
+// before it waits for the kernel in front: those do not depend on it, and in a decode step this kernel is one link
+// of a chain in which every trip to memory behind the wait counts.  The sum of squares is formed in the same order.
+template <typename TD, typename TW, typename TO, int VEC, int KEEP = 0>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const TW* __restrict__ w,
                                    TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float scratch[33];
     pdl_launch_dependents();  // the next kernel may take its place on the SMs and fetch what does not depend on this one
+    if (KEEP > 0) {
+        float wv[KEEP > 0 ? KEEP : 1][4];
+#pragma unroll
+        for (int it = 0; it < KEEP; ++it) {
+            const int i = (threadIdx.x + it * blockDim.x) * 4;
+            if (i < hidden) load4(w + i, wv[it]);
+        }
+        pdl_wait();
+        const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+        float* hrow = h + (size_t)src * hidden;
+        const bool has_delta = delta != nullptr;
+        const TD* drow = delta + (size_t)src * hidden;
+        TO* orow = out + (size_t)blockIdx.x * hidden;
+        const bool write_back = (rows == nullptr) && has_delta;
+        float v[KEEP > 0 ? KEEP : 1][4];
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < KEEP; ++it) {
+            const int i = (threadIdx.x + it * blockDim.x) * 4;
+            if (i < hidden) {
+                load4(hrow + i, v[it]);
+                if (has_delta) {
+                    float d[4];
+                    load4(drow + i, d);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[it][j] += d[j];
+                }
+                if (write_back) store4(hrow + i, v[it]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ss += v[it][j] * v[it][j];
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+        for (int it = 0; it < KEEP; ++it) {
+            const int i = (threadIdx.x + it * blockDim.x) * 4;
+            if (i < hidden) {
+                float o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o[j] = (v[it][j] * inv) * wv[it][j];
+                store4(orow + i, o);
+            }
+        }
+        return;
+    }
     pdl_wait();
     const int src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* hrow = h + (size_t)src * hidden;
@@ -167,7 +217,16 @@ GK_EXPORT int gk_add_rmsnorm(float* h, const void* delta, int delta_dtype, const
     GK_DISPATCH_DTYPE(delta_dtype, TD, {
         GK_DISPATCH_DTYPE(weight_dtype, TW, {
             GK_DISPATCH_DTYPE(out_dtype, TO, {
-                if (vec)
+                if (vec && hidden <= threads * 4)
+                    gk_launch(add_rmsnorm_kernel<TD, TW, TO, 4, 1>, dim3(n_out_rows), dim3(threads), 0, s, h, (const TD*)delta,
+                              (const TW*)weight, (TO*)out, rows, hidden, eps);
+                else if (vec && hidden <= threads * 8)
+                    gk_launch(add_rmsnorm_kernel<TD, TW, TO, 4, 2>, dim3(n_out_rows), dim3(threads), 0, s, h, (const TD*)delta,
+                              (const TW*)weight, (TO*)out, rows, hidden, eps);
+                else if (vec && hidden <= threads * 16)
+                    gk_launch(add_rmsnorm_kernel<TD, TW, TO, 4, 4>, dim3(n_out_rows), dim3(threads), 0, s, h, (const TD*)delta,
+                              (const TW*)weight, (TO*)out, rows, hidden, eps);
+                else if (vec)
                     gk_launch(add_rmsnorm_kernel<TD, TW, TO, 4>, dim3(n_out_rows), dim3(threads), 0, s, h, (const TD*)delta,
                               (const TW*)weight, (TO*)out, rows, hidden, eps);
                 else
