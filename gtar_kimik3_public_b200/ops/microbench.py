@@ -136,7 +136,7 @@ def bench_step(args) -> dict:
     from ..weights import write_random_model
 
     config = config_from_dict({
-        "arch": "transformer", "vocab_size": 151936, "hidden_size": 1024, "intermediate_size": 3072,
+        "arch": "transformer", "vocab_size": 151936, "hidden_size": args.hidden, "intermediate_size": args.intermediate,
         "num_hidden_layers": args.layers, "num_attention_heads": args.q_heads, "num_key_value_heads": args.kv_heads,
         "head_dim": args.head_dim, "rms_norm_eps": 1e-6, "rope_theta": 1e6, "tie_word_embeddings": True,
         "initializer_range": 0.02, "max_position_embeddings": 4096,
@@ -242,6 +242,8 @@ def main() -> int:
     parser.add_argument("--q-heads", type=int, default=16)
     parser.add_argument("--kv-heads", type=int, default=8)
     parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--hidden", type=int, default=1024, help="step: the model's width")
+    parser.add_argument("--intermediate", type=int, default=3072, help="step: the feed-forward's width")
     parser.add_argument("--attention-path", default="auto", choices=["auto", "tcgen05", "mma"])
     parser.add_argument("--layers", type=int, default=28)
     parser.add_argument("--iters", type=int, default=5)
