@@ -814,12 +814,9 @@ cudaError_t launch_for_slots(int n_slots, int grid, size_t smem, cudaStream_t st
         if (err != cudaSuccess) return err;
         return gk_launch(kernel, dim3(grid), dim3(MK_THREADS), smem, stream, p);
     };
-    switch (n_slots) {
-        case 3: return go(decode_layers_kernel<D, 3>);
-        case 4: return go(decode_layers_kernel<D, 4>);
-        case 5: return go(decode_layers_kernel<D, 5>);
-        default: return go(decode_layers_kernel<D, 6>);
-    }
+    // two ring depths are compiled (each is a copy of the whole kernel): five slots a warp where they fit, else three
+    if (n_slots >= 5) return go(decode_layers_kernel<D, 5>);
+    return go(decode_layers_kernel<D, 3>);
 }
 
 int pow2_at_least(int v) {
@@ -908,7 +905,7 @@ GK_EXPORT int gk_decode_layers(const void* layers, int n_layers, int n_seqs, int
     int n_slots = (int)(((size_t)smem_max - fixed) / ((size_t)MK_WARPS * MK_SLOT));
     if ((size_t)smem_max < fixed || n_slots < 3)
         return gk_fail(GK_UNSUPPORTED, "decode_layers: rows of %d elements leave no room for the rings in shared memory", k_max);
-    if (n_slots > 6) n_slots = 6;
+    n_slots = n_slots >= 5 ? 5 : 3;
     const size_t smem = fixed + (size_t)n_slots * MK_WARPS * MK_SLOT;
     cudaError_t err = head_dim == 128 ? launch_for_slots<128>(n_slots, sms, smem, (cudaStream_t)stream, p)
                                       : launch_for_slots<64>(n_slots, sms, smem, (cudaStream_t)stream, p);

@@ -1089,13 +1089,14 @@ bool use_pairs(int rows_a, int rows_b) {
     int device = 0, n_sms = 148;
     if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
     const long long tiles = (long long)((rows_a + 255) / 256) * ((rows_b + 255) / 256);
-    return tiles >= 3LL * (n_sms / 2);
+    return tiles >= 6LL * (n_sms / 2);
 }
 
 }  // namespace
 
 // Whether many-token products with wide tiles run as pairs of blocks (tcgen05 cta_group::2): 0 never, 1 always,
-// 2 (the default) where there are at least three 256 x 256 tiles per pair of SMs.  Measured on a B200: 1.35
+// 2 (the default) where there are at least six 256 x 256 tiles per pair of SMs (a whole 4,096-token prompt of the
+// 0.6B sizes takes 7.4 ms with single blocks and 7.6 with pairs; from 8,192 tokens on the two are level).  Measured on a B200: 1.35
 // against 1.33 PFLOP/s at 8192^3, 1.36 against 1.32 at 4096^3, but 840 against 937 TFLOP/s on the gate|up
 // product of a 2,048-token prompt (1.7 tiles per SM: start-up and the last tile's output stage dominate, and
 // pairs make both a little longer).  Returns the old setting.
