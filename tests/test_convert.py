@@ -108,3 +108,19 @@ def test_engine_generates_the_golden_tokens_from_a_converted_checkpoint(tmp_path
     want = [data[f"greedy_{r}"].tolist() for r in range(3)]
     got = api.generate(model, prompts, max_new_tokens=len(want[0]), temperature=0.0)
     assert got == want
+
+
+def test_converter_command_line(tmp_path, capsys):
+    from gtar_kimik3_public_b200.registry import config_from_file
+    from gtar_kimik3_public_b200.weights import convert
+
+    write_checkpoint(tmp_path / "ckpt.pt", TINY_B, 1)
+    assert convert.main([str(tmp_path / "ckpt.pt"), str(tmp_path / "model"), "--dtype", "bfloat16", "--max-position-embeddings", "256",
+                         "--eos-token-id", "7"]) == 0
+    assert "model.safetensors" in capsys.readouterr().out
+    config = config_from_file(tmp_path / "model")
+    assert config.max_position_embeddings == 256 and config.eos_token_id == 7
+    stored = read_safetensors(tmp_path / "model" / "model.safetensors")
+    assert stored["lm_head.weight"].shape == (TINY_B["vocab_size"], TINY_B["hidden_size"])
+    weights = make_weights(TINY_B, 1, std=0.08)  # values bfloat16 holds exactly, so rounding the matrices changed nothing
+    assert torch.equal(stored["model.layers.1.mlp.up_proj.weight"], weights["model.layers.1.mlp.up_proj.weight"])

@@ -134,3 +134,66 @@ def test_command_line(tmp_path):
     assert out.returncode == 0, out.stderr
     lines = [line for line in out.stdout.splitlines() if line and line != "---"]
     assert [[int(t) for t in line.split(",")] for line in lines] == [plain_greedy(tag, p, 6) for p in prompts]
+
+
+def test_generator_sizes_its_cache_itself():
+    """Without ``max_tokens`` the generator takes room for ``max_batch`` sequences of the longest context the
+    configuration allows, but no more than fits in most of the free device memory."""
+    tag = "tiny_b"
+    model = api().load(model_folder(tag), "float32")
+    generator = api().Generator(model, max_batch=5)
+    assert generator.engine.cache.n_pages * generator.engine.cache.page_size == 5 * 256
+    wanted = api().Generator.default_max_tokens(model, 5)
+    assert wanted == 5 * 256
+    free, _ = torch.cuda.mem_get_info()
+    per_token = generator.engine.cache.kv_bytes_per_token()
+    little = 200 * per_token / free  # a device with room for 200 tokens: three pages
+    assert api().Generator.default_max_tokens(model, 5, share_of_free_memory=little) == 192
+    with pytest.raises(RuntimeError, match="no device memory"):
+        api().Generator.default_max_tokens(model, 5, share_of_free_memory=little / 100)
+    prompts = requests_for(tag, [4, 30], seed=28)
+    got = generator.generate(prompts, max_new_tokens=5, temperature=0.0)
+    assert got == [plain_greedy(tag, p, 5) for p in prompts]
+
+
+def test_weights_drawn_on_the_device():
+    """The random-weights mode without a folder (the benchmark's 4B and 8B points): types as the loader's rule gives
+    them, a fixed seed gives the same model, and the model steps."""
+    from gtar_kimik3_public_b200.engine import Engine, StepEntry
+    from gtar_kimik3_public_b200.models.model import Model
+    from gtar_kimik3_public_b200.registry import architecture, config_from_dict
+    from gtar_kimik3_public_b200.weights import load_random_weights
+    from tests.helpers import CONFIGS
+
+    config = config_from_dict(CONFIGS["tiny_c"])
+    logits = []
+    for seed in (3, 3, 4):
+        model = Model(architecture(config.ARCH_NAMES[0]).build_plan(config), config, torch.bfloat16, "cuda:0")
+        load_random_weights(model, seed=seed, std=0.08)
+        layer = model.plan.layers[0]
+        assert layer.mixer.w_qkv.dtype == torch.bfloat16 and layer.input_norm.weight.dtype == torch.float32
+        engine = Engine(model, 128, max_seqs=1)
+        logits.append(engine.step([StepEntry("r", list(range(1, 40)), [38])]))
+    assert torch.isfinite(logits[0]).all() and logits[0].abs().max() > 0.1
+    assert torch.equal(logits[0], logits[1]) and not torch.equal(logits[0], logits[2])
+
+
+def test_command_line_takes_a_checkpoint_of_the_reference(tmp_path):
+    """``--checkpoint FILE`` as in the reference's command line (scripts/generate.py:19-20,33-37): converted to a model
+    folder first; the greedy tokens are those stored under tests/golden/."""
+    import numpy as np
+
+    from tests.test_convert import GOLDEN, write_checkpoint
+    from tests.tiny_configs import TINY_A
+
+    write_checkpoint(tmp_path / "ckpt.pt", TINY_A, 0)
+    data = np.load(GOLDEN / "tiny_a.npz")
+    prompts = [data[f"ids_{r}"].tolist() for r in range(3)]
+    want = [data[f"greedy_{r}"].tolist() for r in range(3)]
+    arg = ";".join(",".join(str(t) for t in p) for p in prompts)
+    cmd = [sys.executable, "-m", "gtar_kimik3_public_b200.scripts.generate", "--checkpoint", str(tmp_path / "ckpt.pt"), "--dtype",
+           "float32", "--prompt-ids", arg, "--max-new-tokens", str(len(want[0])), "--temperature", "0"]
+    out = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = [line for line in out.stdout.splitlines() if line and line != "---"]
+    assert [[int(t) for t in line.split(",")] for line in lines] == want

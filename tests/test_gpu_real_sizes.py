@@ -270,3 +270,19 @@ def test_persistent_kernel_for_all_layers_of_a_decode_step(n_seqs, kernel_log, m
         results.append({r: torch.cat(got) for r, got in rows.items() if got})
     for r in results[0]:
         assert torch.equal(results[0][r], results[1][r]), "replayed from a graph, the persistent kernel gave other numbers"
+
+
+def test_decode_across_a_bound_on_the_lengths():
+    """Decode graphs are keyed by a power-of-two bound on the longest sequence of the step (launches are sized from
+    it): a sequence that grows from below 1,024 tokens to above it changes graphs on the way, and its logits do not."""
+    tag, dtype = "real_06b", "bfloat16"
+    (tokens,) = requests_for(tag, [1040], seed=61)
+    engine = load_engine(tag, dtype, max_tokens=2048, max_seqs=1)
+    poison(engine)
+    head = 1010
+    engine.step([_entry("r", tokens[:head], [])])
+    rows = [engine.step([_entry("r", [tokens[t]], [0])]) for t in range(head, len(tokens))]
+    bounds = sorted({key[4] for key in engine.graphs.graphs if key[3] == 1})
+    assert bounds == [1024, 2048], bounds
+    check_against_plain(tag, dtype, tokens, list(range(head, len(tokens))), torch.cat(rows), "decode across the bound of 1,024 tokens")
+    engine.check()
