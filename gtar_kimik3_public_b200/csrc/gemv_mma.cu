@@ -43,6 +43,19 @@ struct GemvParams {
     int n, k, tokens;
     long long ldw, ldx, ldo;
     int out_f32, swiglu;
+    // Optional: the activations are the RMSNorm of the rows of a 32-bit stream, formed here (`norm_h` set, `x` unused):
+    //   x[t, k] = bfloat16((h[t, k] * rsqrt(mean_k h[t, k]^2 + eps)) * norm_w[k])       (src/layers/rmsnorm.py:11-16)
+    // every block holds whole rows of its tokens (its threads' pieces of a row are the row), so it forms the row's
+    // sum of squares itself; the norm's weights are fetched before the wait for the kernel in front.
+    const float* norm_h;      // [tokens][ldh]
+    const void* norm_w;       // [k]
+    int norm_w_bf16;
+    float norm_eps;
+    long long ldh;
+    // Optional: the result is added to a 32-bit stream instead of stored (`resid` set, `out` unused):
+    //   resid[t, n] += bfloat16(sum)   (the projection's output is bfloat16, the stream 32-bit: src/models/transformer.py:47-48)
+    float* resid;             // [tokens][ldr]
+    long long ldr;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -66,9 +79,10 @@ __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g));
 // `x_stride` bytes (the rows of two tokens a quarter-warp reads together lie in different banks); and, when the
 // weights come in more than one round, [group of the block][thread] partial sums (with one round a thread
 // leaves its partial sum where the group's first weight piece was).
-template <int ROW_SETS>
-__global__ void __launch_bounds__(THREADS, ROW_SETS == 4 ? 2 : ROW_SETS == 2 ? 3 : 4) gemv_mma_kernel(const GemvParams p, int round_items, int x_stride) {
+template <int ROW_SETS, bool NORM = false>
+__global__ void __launch_bounds__(THREADS, NORM ? 2 : ROW_SETS == 4 ? 2 : 3) gemv_mma_kernel(const GemvParams p, int round_items, int x_stride) {
     extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float row_ss[WARPS][16];  // NORM: the warps' parts of each token's sum of squares
     constexpr bool TWO_ROWS = ROW_SETS >= 2;
     constexpr int TILES = (ROW_SETS + 1) / 2;  // MMAs' worth of tokens
     constexpr int X_ROWS = 8 * ROW_SETS;
@@ -106,6 +120,24 @@ __global__ void __launch_bounds__(THREADS, ROW_SETS == 4 ? 2 : ROW_SETS == 2 ? 3
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
+    // With the residual output stage, the stream's old values of the outputs this thread will write (warp g of the
+    // block finishes the block's g-th group) are asked for as soon as the kernel in front has finished, long before
+    // the sums are there.
+    float2 old[TILES][TWO_ROWS ? 2 : 1];
+    auto fetch_old = [&]() {
+        if (p.resid == nullptr || warp >= my_groups) return;
+        const int col = ((int)blockIdx.x + warp * (int)gridDim.x) * ROWS + 2 * piece;
+#pragma unroll
+        for (int tile = 0; tile < TILES; ++tile)
+#pragma unroll
+            for (int half = 0; half < (TWO_ROWS ? 2 : 1); ++half) {
+                const int token = 16 * tile + group + 8 * half;
+                old[tile][half] = make_float2(0.f, 0.f);
+                if (token < p.tokens && col + 1 < p.n) old[tile][half] = *reinterpret_cast<const float2*>(p.resid + (size_t)token * p.ldr + col);
+                else if (token < p.tokens && col < p.n) old[tile][half].x = p.resid[(size_t)token * p.ldr + col];
+            }
+    };
+
     // after the block's barrier: warp g of the block finishes the block's g-th group
     auto finish = [&]() {
         if (warp >= my_groups) return;
@@ -126,7 +158,13 @@ __global__ void __launch_bounds__(THREADS, ROW_SETS == 4 ? 2 : ROW_SETS == 2 ? 3
             const int token = 16 * tile + group + 8 * half;
             if (token >= p.tokens) continue;
             const float a = sum[2 * half], b = sum[2 * half + 1];
-            if (p.swiglu) {
+            if (p.resid) {
+                float* o = p.resid + (size_t)token * p.ldr + col;
+                const float na = old[tile][half].x + __bfloat162float(__float2bfloat16(a));
+                const float nb = old[tile][half].y + __bfloat162float(__float2bfloat16(b));
+                if (col + 1 < p.n) *reinterpret_cast<float2*>(o) = make_float2(na, nb);
+                else if (col < p.n) o[0] = na;
+            } else if (p.swiglu) {
                 if (col + 1 < p.n)
                     reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)token * p.ldo + (col >> 1)] = __float2bfloat16(silu(a) * b);
             } else if (p.out_f32) {
@@ -147,12 +185,106 @@ __global__ void __launch_bounds__(THREADS, ROW_SETS == 4 ? 2 : ROW_SETS == 2 ? 3
     };
 
     request(0);  // before the kernel in front has finished
+    // NORM: this thread's pieces of the norm's weights (the same for every token), also before the wait
+    float nw[NORM ? X_REGS : 1][8];
+    if (NORM) {
+#pragma unroll
+        for (int j = 0; j < X_REGS; ++j) {
+            const int k = (warp + j * WARPS) * CHUNK + piece * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) nw[NORM ? j : 0][e] = 0.f;
+            if (j < cpw && k < p.k) {
+                if (p.norm_w_bf16) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.norm_w) + k);
+                    const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r[e]));
+                        nw[NORM ? j : 0][2 * e] = f.x;
+                        nw[NORM ? j : 0][2 * e + 1] = f.y;
+                    }
+                } else {
+                    const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm_w) + k);
+                    const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm_w) + k + 4);
+                    nw[NORM ? j : 0][0] = lo.x; nw[NORM ? j : 0][1] = lo.y; nw[NORM ? j : 0][2] = lo.z; nw[NORM ? j : 0][3] = lo.w;
+                    nw[NORM ? j : 0][4] = hi.x; nw[NORM ? j : 0][5] = hi.y; nw[NORM ? j : 0][6] = hi.z; nw[NORM ? j : 0][7] = hi.w;
+                }
+            }
+        }
+    }
     pdl_wait();
+    fetch_old();
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const uint4* wp = pieces + threadIdx.x;
     if (cpw <= X_REGS && one_round) {
         // short K: the thread's pieces of the activations straight from memory into registers, no staging
         uint4 xr[TILES][X_REGS], xr2[TILES][X_REGS];
+        if (NORM) {
+            // the rows of the stream: 32 bytes a piece, their squares summed over the block, then scaled and rounded
+            static_assert(!NORM || TILES == 1, "the norm on load is built for up to 16 tokens");
+            float hv[X_REGS][8], hv2[TWO_ROWS ? X_REGS : 1][8];
+            float ss = 0.f, ss2 = 0.f;
+#pragma unroll
+            for (int j = 0; j < X_REGS; ++j) {
+                const int k = (warp + j * WARPS) * CHUNK + piece * 8;
+                const bool in = j < cpw && k < p.k;
+                const bool in1 = in && group < p.tokens, in2 = TWO_ROWS && in && group + 8 < p.tokens;
+                const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 a = in1 ? *reinterpret_cast<const float4*>(p.norm_h + (size_t)group * p.ldh + k) : z;
+                const float4 b = in1 ? *reinterpret_cast<const float4*>(p.norm_h + (size_t)group * p.ldh + k + 4) : z;
+                hv[j][0] = a.x; hv[j][1] = a.y; hv[j][2] = a.z; hv[j][3] = a.w; hv[j][4] = b.x; hv[j][5] = b.y; hv[j][6] = b.z; hv[j][7] = b.w;
+                if (TWO_ROWS) {
+                    const float4 c = in2 ? *reinterpret_cast<const float4*>(p.norm_h + (size_t)(group + 8) * p.ldh + k) : z;
+                    const float4 d = in2 ? *reinterpret_cast<const float4*>(p.norm_h + (size_t)(group + 8) * p.ldh + k + 4) : z;
+                    hv2[TWO_ROWS ? j : 0][0] = c.x; hv2[TWO_ROWS ? j : 0][1] = c.y; hv2[TWO_ROWS ? j : 0][2] = c.z; hv2[TWO_ROWS ? j : 0][3] = c.w;
+                    hv2[TWO_ROWS ? j : 0][4] = d.x; hv2[TWO_ROWS ? j : 0][5] = d.y; hv2[TWO_ROWS ? j : 0][6] = d.z; hv2[TWO_ROWS ? j : 0][7] = d.w;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < X_REGS; ++j)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    ss += hv[j][e] * hv[j][e];
+                    if (TWO_ROWS) ss2 += hv2[TWO_ROWS ? j : 0][e] * hv2[TWO_ROWS ? j : 0][e];
+                }
+            // the four lanes that share a token, then the warps in their order
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            if (TWO_ROWS) {
+                ss2 += __shfl_xor_sync(0xffffffffu, ss2, 1);
+                ss2 += __shfl_xor_sync(0xffffffffu, ss2, 2);
+            }
+            if (piece == 0) {
+                row_ss[warp][group] = ss;
+                row_ss[warp][group + 8] = ss2;
+            }
+            __syncthreads();
+            float total = 0.f, total2 = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                total += row_ss[w][group];
+                total2 += row_ss[w][group + 8];
+            }
+            const float inv = 1.0f / sqrtf(total / (float)p.k + p.norm_eps);
+            const float inv2 = 1.0f / sqrtf(total2 / (float)p.k + p.norm_eps);
+            auto pack2 = [](float lo, float hi) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                return *reinterpret_cast<uint32_t*>(&v);
+            };
+#pragma unroll
+            for (int j = 0; j < X_REGS; ++j) {
+                const float* w8 = nw[NORM ? j : 0];
+                xr[0][j] = make_uint4(pack2((hv[j][0] * inv) * w8[0], (hv[j][1] * inv) * w8[1]), pack2((hv[j][2] * inv) * w8[2], (hv[j][3] * inv) * w8[3]),
+                                      pack2((hv[j][4] * inv) * w8[4], (hv[j][5] * inv) * w8[5]), pack2((hv[j][6] * inv) * w8[6], (hv[j][7] * inv) * w8[7]));
+                if (TWO_ROWS) {
+                    const float* h2 = hv2[TWO_ROWS ? j : 0];
+                    xr2[0][j] = make_uint4(pack2((h2[0] * inv2) * w8[0], (h2[1] * inv2) * w8[1]), pack2((h2[2] * inv2) * w8[2], (h2[3] * inv2) * w8[3]),
+                                           pack2((h2[4] * inv2) * w8[4], (h2[5] * inv2) * w8[5]), pack2((h2[6] * inv2) * w8[6], (h2[7] * inv2) * w8[7]));
+                } else {
+                    xr2[0][j] = zero;
+                }
+            }
+        } else {
 #pragma unroll
         for (int tile = 0; tile < TILES; ++tile) {
 #pragma unroll
@@ -163,6 +295,7 @@ __global__ void __launch_bounds__(THREADS, ROW_SETS == 4 ? 2 : ROW_SETS == 2 ? 3
                 xr[tile][j] = in && token < p.tokens ? *reinterpret_cast<const uint4*>(p.x + (size_t)token * p.ldx + k) : zero;
                 xr2[tile][j] = TWO_ROWS && in && token + 8 < p.tokens ? *reinterpret_cast<const uint4*>(p.x + (size_t)(token + 8) * p.ldx + k) : zero;
             }
+        }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         for (int g = 0; g < my_groups; ++g) {
@@ -194,7 +327,7 @@ __global__ void __launch_bounds__(THREADS, ROW_SETS == 4 ? 2 : ROW_SETS == 2 ? 3
         finish();
         return;
     }
-    if (ROW_SETS == 4) return;  // (the host sends 17 to 32 tokens here only where the path above applies)
+    if (ROW_SETS == 4 || NORM) return;  // (the host sends 17 to 32 tokens, and the norm on load, here only where the path above applies)
     // the activations of all tokens into shared memory; zeros for the rows that are no token and from K up to
     // the end of the last chunk any warp looks at
     const int x_pieces = cpw * WARPS * 4;  // 16-byte pieces of a row
@@ -269,6 +402,8 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
         if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (err != cudaSuccess) { n_sms = 0; return gk_fail(GK_CUDA_ERROR, "gemv: %s", cudaGetErrorString(err)); }
     }
     const int n_groups = (p.n + ROWS - 1) / ROWS;
@@ -304,6 +439,14 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
         round_items = (int)((SMEM_MAX - fixed) / (THREADS * 16));
     }
     const size_t smem = (size_t)round_items * THREADS * 16 + x_bytes + (items > round_items ? partial_bytes : 0);
+    if (p.norm_h) {
+        GK_REQUIRE(p.tokens <= 16 && x_in_registers, "gemv: the norm on load takes up to 16 tokens, k <= 1024 and a block's weights in one round; got %d tokens, k = %d, %d pieces a thread",
+                   p.tokens, p.k, items);
+        if (p.tokens > 8) gk_launch(gemv_mma_kernel<2, true>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
+        else gk_launch(gemv_mma_kernel<1, true>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
+        GK_CHECK_LAUNCH("gemv");
+        return GK_OK;
+    }
     if (p.tokens > 16) {
         GK_REQUIRE(x_in_registers && cpw >= 2, "gemv: 17 to 32 tokens need 257 <= k <= 1024 and a block's weights in one round; got k = %d, %d pieces a thread",
                    p.k, items);
@@ -343,5 +486,44 @@ GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const voi
     p.ldo = swiglu ? n / 2 : n;
     p.out_f32 = out_dtype == GK_F32;
     p.swiglu = swiglu;
+    return launch_gemv(p, (cudaStream_t)stream);
+}
+
+// The same product with the activations formed here as the RMSNorm of a 32-bit stream's rows (`norm_h` [tokens, k] with
+// rows `ldh` apart, `norm_w` [k] float32 or bfloat16; up to 16 tokens, k <= 1024 and a block's weights in one round), and /
+// or with the result added to a 32-bit stream (`resid` [tokens, n], rows `ldr` apart) instead of stored.  Either pointer
+// may be null; with `norm_h` set `x` is not read, with `resid` set `out` is not written.
+GK_EXPORT int gk_gemv_bf16_stream(const void* w, int n, int k, long long ldw, const void* x, int tokens, long long ldx, void* out,
+                                  int out_dtype, int swiglu, const float* norm_h, long long ldh, const void* norm_w, int norm_w_bf16,
+                                  float norm_eps, float* resid, long long ldr, void* stream) {
+    GK_REQUIRE(n > 0 && k > 0 && tokens > 0 && tokens <= 32, "gemv: takes 1 to 32 tokens and positive sizes; got %d tokens, n=%d k=%d",
+               tokens, n, k);
+    GK_REQUIRE(k % 8 == 0 && ldw % 8 == 0, "gemv: k and the weights' row stride must be multiples of 8 elements; got k=%d ldw=%lld", k, ldw);
+    GK_REQUIRE(((uintptr_t)w & 15) == 0, "gemv: the weights must be 16-byte aligned");
+    GK_REQUIRE(norm_h != nullptr || (x != nullptr && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0), "gemv: activations must be 16-byte aligned rows");
+    GK_REQUIRE(norm_h == nullptr || (norm_w != nullptr && ldh % 4 == 0 && ((uintptr_t)norm_h & 15) == 0 && ((uintptr_t)norm_w & 15) == 0 && norm_eps > 0.f),
+               "gemv: the norm on load needs 16-byte aligned rows and weights and a positive eps");
+    GK_REQUIRE(resid == nullptr || (!swiglu && ldr % 2 == 0 && ((uintptr_t)resid & 7) == 0), "gemv: the residual output stage needs 8-byte aligned rows and no SwiGLU");
+    GK_REQUIRE(resid != nullptr || (out != nullptr && GK_VALID_DTYPE(out_dtype) && ((uintptr_t)out & 3) == 0), "gemv: bad output");
+    GK_REQUIRE(!swiglu || (n % 2 == 0 && out_dtype == GK_BF16), "gemv: the SwiGLU output stage needs an even number of rows and writes bfloat16");
+    GemvParams p = {};
+    p.w = (const __nv_bfloat16*)w;
+    p.x = (const __nv_bfloat16*)x;
+    p.out = out;
+    p.n = n;
+    p.k = k;
+    p.tokens = tokens;
+    p.ldw = ldw;
+    p.ldx = ldx;
+    p.ldo = swiglu ? n / 2 : n;
+    p.out_f32 = out_dtype == GK_F32;
+    p.swiglu = swiglu;
+    p.norm_h = norm_h;
+    p.norm_w = norm_w;
+    p.norm_w_bf16 = norm_w_bf16;
+    p.norm_eps = norm_eps;
+    p.ldh = ldh;
+    p.resid = resid;
+    p.ldr = ldr;
     return launch_gemv(p, (cudaStream_t)stream);
 }

@@ -426,6 +426,55 @@ def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.b
     return out
 
 
+def gemv_normed_suits(m: int, n: int, k: int, device: torch.device) -> bool:
+    """Whether ``gemv_stream`` can form its activations as the RMSNorm of a 32-bit stream itself: up to 16 tokens whose
+    rows (up to 1,024 long) a block's threads hold whole, and a block's weights in shared memory at once."""
+    if m > GEMV_MAX_TOKENS or k > 1024 or k % 8 or n > gemv_max_rows(device):
+        return False
+    per_warp = -(-(-(-k // 32)) // 8)
+    groups = -(-n // 8)
+    per_block = -(-groups // min(groups, gemv_max_rows(device) // 64))
+    return per_block * per_warp <= 24
+
+
+def gemv_stream(weight: torch.Tensor, x: torch.Tensor | None = None, norm: tuple | None = None, resid: torch.Tensor | None = None,
+                swiglu: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor | None:
+    """The few-token product with the residual stream at either end.
+
+    ``norm = (h, norm_weight, eps)``: the activations are the RMSNorm of the rows of the 32-bit stream ``h [tokens, k]``,
+    formed inside the kernel (no norm kernel in front).  ``resid``: the 32-bit stream ``[tokens, n]`` that the result,
+    rounded to bfloat16 as a projection's output is, is added to in place (no add in the norm kernel behind); nothing
+    is returned then.  Otherwise as ``gemv``."""
+    require_device(weight.device)
+    _check(weight, "weight", torch.bfloat16, 2)
+    n, k = weight.shape
+    if norm is not None:
+        h, norm_weight, eps = norm
+        _check(h, "h", torch.float32, 2)
+        _check(norm_weight, "norm weight", dims=1)
+        m = h.shape[0]
+        if h.shape[1] != k or norm_weight.shape[0] != k:
+            raise KernelError(f"the stream is {tuple(h.shape)} and the norm's weight {tuple(norm_weight.shape)} for rows of {k}")
+        if not gemv_normed_suits(m, n, k, weight.device):
+            raise KernelError(f"the norm on load does not take {m} tokens of {k} with {n} weight rows")
+    else:
+        _check(x, "x", torch.bfloat16, 2)
+        m = x.shape[0]
+        if x.shape[1] != k:
+            raise KernelError(f"x is {tuple(x.shape)} but weight is {tuple(weight.shape)}")
+        h, norm_weight, eps = None, None, 1.0
+    out = None
+    if resid is not None:
+        _check(resid, "resid", torch.float32, 2)
+        if tuple(resid.shape) != (m, n) or swiglu:
+            raise KernelError(f"the residual stream must be {(m, n)} (and no SwiGLU), got {tuple(resid.shape)}")
+    else:
+        out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=weight.device)
+    call("gk_gemv_bf16_stream", ptr(weight), n, k, k, ptr(x), m, k, ptr(out), dtype_code(out_dtype), int(swiglu), ptr(h), k,
+         ptr(norm_weight), int(norm_weight is not None and norm_weight.dtype == torch.bfloat16), float(eps), ptr(resid), n, stream_ptr())
+    return out
+
+
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
             splits: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` in bfloat16 on the tcgen05 tensor cores, float32 accumulation.

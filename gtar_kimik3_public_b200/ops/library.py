@@ -41,6 +41,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_gemm_bf16_tc": [P, I, L, P, I, L, I, P, I, L, L, I, I, I, I, I, P, P],
     "gk_gemm_bf16_tc_qkv": [P, I, P, I, I, I, I, P, P, I, I, F, P, P, I, I, P, P, P, P, I, I, P, P, P, P, P],
     "gk_gemv_bf16": [P, I, I, L, P, I, L, P, I, I, P],
+    "gk_gemv_bf16_stream": [P, I, I, L, P, I, L, P, I, I, P, L, P, I, F, P, L, P],
     "gk_set_pdl": [I],
     "gk_set_gemm_pairs": [I],
     "gk_set_attention_prefill_keys": [I],

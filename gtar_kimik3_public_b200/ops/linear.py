@@ -58,3 +58,29 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return F.linear_bf16(x, weight, out_dtype)
     splits = F.split_k_for(x.shape[0], weight.shape[0], x.shape[1])
     return F.gemm_tc(x, weight, torch.bfloat16 if swiglu else out_dtype, swiglu=swiglu, splits=splits)
+
+
+fold_norms_in_decode = True  # few-token steps: norms inside the products, residual adds in their output stages
+
+
+def linear_on_stream_ok(h: torch.Tensor, norm_weight: torch.Tensor | None, weight_in: torch.Tensor, weight_out: torch.Tensor) -> bool:
+    """Whether a branch ``h += (f(norm(h) @ weight_in.T)) @ weight_out.T`` of a few-token step can run with its norm
+    inside the first product (``linear_normed``) and its add inside the last (``linear_residual``)."""
+    if not fold_norms_in_decode or norm_weight is None or not h.is_cuda or h.dtype != torch.float32:
+        return False
+    if weight_in.dtype != torch.bfloat16 or weight_out.dtype != torch.bfloat16 or norm_weight.dtype not in (torch.float32, torch.bfloat16):
+        return False
+    m = h.shape[0]
+    return (m <= F.GEMV_MAX_TOKENS and F.gemv_normed_suits(m, weight_in.shape[0], weight_in.shape[1], h.device)
+            and weight_out.shape[1] % 8 == 0 and weight_out.shape[0] % 2 == 0
+            and F.gemv_suits(m, weight_out.shape[0], weight_out.shape[1], h.device))
+
+
+def linear_normed(h: torch.Tensor, norm_weight: torch.Tensor, eps: float, weight: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+    """``rmsnorm(h; norm_weight, eps) @ weight.T`` (bfloat16) with the norm formed inside the product's kernel."""
+    return F.gemv_stream(weight, norm=(h, norm_weight, eps), swiglu=swiglu)
+
+
+def linear_residual(x: torch.Tensor, weight: torch.Tensor, h: torch.Tensor) -> None:
+    """``h += bfloat16(x @ weight.T)`` in the product's output stage."""
+    F.gemv_stream(weight, x=x, resid=h)

@@ -13,7 +13,7 @@ import torch
 
 from ..ops import attention as attention_ops
 from ..ops import functional as F
-from ..ops.linear import linear
+from ..ops.linear import linear, linear_normed, linear_on_stream_ok, linear_residual
 from .base import KVRequest, Mixer, PositionEncoding, StepContext, TensorSpec, register_part
 
 
@@ -85,23 +85,40 @@ class GQAAttention(Mixer):
                               ctx.max_position, write_kv)
             o = attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
             return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
-        return self._attend(linear(x, self.w_qkv), ctx, cache, cos, sin, write_kv)
+        o = self._attend(linear(x, self.w_qkv), ctx, cache, cos, sin, write_kv)
+        return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
+
+    def on_stream_ok(self, h: torch.Tensor, norm_weight, ctx: StepContext, cache) -> bool:
+        """Whether ``forward_on_stream`` takes this step: a few tokens, one each, bfloat16 matrices of sizes the
+        few-token product takes with the norm inside (see ``ops.linear.linear_on_stream_ok``)."""
+        return (ctx.all_single and ctx.dtype == torch.bfloat16 and isinstance(cache, F.PagedKV)
+                and linear_on_stream_ok(h, norm_weight, self.w_qkv, self.w_o))
+
+    def forward_on_stream(self, h: torch.Tensor, norm_weight: torch.Tensor, norm_eps: float, ctx: StepContext, cache: F.PagedKV) -> None:
+        """``h += attention(rmsnorm(h))`` on the 32-bit stream itself: the norm is formed inside the q|k|v product and
+        the add happens in the output product's output stage, so the step has two kernels fewer a layer."""
+        cos = sin = None
+        if self.position is not None:
+            cos, sin = self.position.cos, self.position.sin
+        write_kv = not ctx.extras.get("cache_read_only", False)
+        qkv = linear_normed(h, norm_weight, norm_eps, self.w_qkv)
+        o = self._attend(qkv, ctx, cache, cos, sin, write_kv)
+        linear_residual(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o, h)
 
     def _attend(self, qkv: torch.Tensor, ctx: StepContext, cache: F.PagedKV, cos, sin, write_kv: bool) -> torch.Tensor:
+        """Attention output ``[n_tokens, n_q, head_dim]`` from the packed projection of the step's tokens."""
         if ctx.all_single and attention_ops.fused_decode_ok(qkv, cache, self.n_q, self.n_kv, self.head_dim):
             # one token per sequence: norm, rotation, cache write and attention in one kernel
             splits = attention_ops.decode_split_count(ctx, self.n_kv, cache)
             if splits <= 8:
-                o = F.attention_decode_fused(
+                return F.attention_decode_fused(
                     qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm, self.qk_norm_eps or 1.0, cos, sin,
                     cache, ctx.kv_len, ctx.slots, ctx.max_position, self.scale, self.window or 0, splits, write_kv)
-                return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
         q = F.qk_norm_rope_write(
             qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm, self.qk_norm_eps or 1.0, cos, sin,
             ctx.tok_pos, ctx.tok_seq, ctx.slots, cache, ctx.max_position, write_kv=write_kv,
         )
-        o = attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
-        return linear(o.view(ctx.n_tokens, self.n_q * self.head_dim), self.w_o)
+        return attention_ops.paged_attention(q, cache, ctx, self.scale, self.window or 0)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -53,7 +53,29 @@ class PreNormBlock(Block):
                 "norm_post": norm_post["weight"], "eps_in": norm_in["eps"], "eps_post": norm_post["eps"],
                 "norm_dtype": norm_in["weight"].dtype}
 
+    @staticmethod
+    def _plain_rmsnorm(norm):
+        """(weight, eps) of a norm that is nothing but an RMSNorm with a weight, else None."""
+        describe = getattr(norm, "decode_record", None)
+        record = describe() if describe is not None else None
+        return (record["weight"], record["eps"]) if record and record.get("kind") == "rmsnorm" else None
+
     def forward(self, h, pending, ctx: StepContext, cache):
+        # Few-token steps: a branch may work on the stream itself (``forward_on_stream``: its norm inside its first
+        # product, its add inside its last), which saves the two norm kernels of the layer.  A part that offers no such
+        # method, a norm of another kind or sizes the kernels do not take leave the branch as it is below.
+        if pending is None and ctx.n_tokens <= 16:
+            norm = self._plain_rmsnorm(self.input_norm)
+            ok = getattr(self.mixer, "on_stream_ok", None)
+            if norm is not None and ok is not None and ok(h, norm[0], ctx, cache):
+                self.mixer.forward_on_stream(h, norm[0], norm[1], ctx, cache)
+                norm = self._plain_rmsnorm(self.post_norm)
+                ok = getattr(self.feed_forward, "on_stream_ok", None)
+                if norm is not None and ok is not None and ok(h, norm[0], ctx):
+                    self.feed_forward.forward_on_stream(h, norm[0], norm[1], ctx)
+                    return h, None
+                x = self.post_norm.forward(h, None, ctx.dtype)
+                return h, self.feed_forward.forward(x, ctx)
         x = self.input_norm.forward(h, pending, ctx.dtype)
         branch = self.mixer.forward(x, ctx, cache)
         x = self.post_norm.forward(h, branch, ctx.dtype)

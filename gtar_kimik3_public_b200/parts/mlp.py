@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import functional as F
-from ..ops.linear import linear
+from ..ops.linear import linear, linear_normed, linear_on_stream_ok, linear_residual
 from .base import FeedForward, StepContext, TensorSpec, register_part
 
 
@@ -45,6 +45,14 @@ class SwiGLUFeedForward(FeedForward):
 
     def forward(self, x, ctx: StepContext) -> torch.Tensor:
         return linear(linear(x, self.w_gate_up, swiglu=True), self.w_down)
+
+    def on_stream_ok(self, h: torch.Tensor, norm_weight, ctx: StepContext) -> bool:
+        return ctx.dtype == torch.bfloat16 and linear_on_stream_ok(h, norm_weight, self.w_gate_up, self.w_down)
+
+    def forward_on_stream(self, h: torch.Tensor, norm_weight: torch.Tensor, norm_eps: float, ctx: StepContext) -> None:
+        """``h += down(silu(gate(y)) * up(y))`` with ``y = rmsnorm(h)`` formed inside the gate|up product and the add
+        in the down product's output stage."""
+        linear_residual(linear_normed(h, norm_weight, norm_eps, self.w_gate_up, swiglu=True), self.w_down, h)
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)

@@ -609,6 +609,49 @@ def test_gemv_against_plain_product(m, n, k, swiglu, out_dtype):
     assert (got.double().cpu() - y).abs().max().item() <= tol
 
 
+@pytest.mark.parametrize("m,n,k,swiglu,weight_dtype", [(8, 4096, 1024, False, torch.float32), (1, 6144, 1024, True, torch.float32),
+                                                        (16, 1000, 520, False, torch.bfloat16), (11, 446, 72, True, torch.float32),
+                                                        (3, 2048, 1000, False, torch.bfloat16)])
+def test_gemv_with_the_norm_on_load(m, n, k, swiglu, weight_dtype):
+    """The few-token product that forms its activations itself as the RMSNorm of a 32-bit stream's rows."""
+    eps = 1e-5
+    h = rand(m, k, seed=1, scale=3.0).float()
+    h[0] *= 40.0  # rows of very different sizes: a scale taken from another row would show
+    nw = (1 + 0.1 * rand(k, seed=3)).to(weight_dtype)
+    w = rand(n, k, seed=2, scale=k**-0.5).to(torch.bfloat16)
+    assert F().gemv_normed_suits(m, n, k, torch.device(DEV))
+    got = F().gemv_stream(w.to(DEV), norm=(h.to(DEV), nw.to(DEV), eps), swiglu=swiglu)
+    x = plain.rms_norm(h.double(), nw.double(), eps).to(torch.bfloat16).double()  # the product's operand is bfloat16
+    y = x @ w.double().T
+    if swiglu:
+        g, u = y[:, 0::2], y[:, 1::2]
+        y = g * torch.sigmoid(g) * u
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == tuple(y.shape)
+    # the operand may round the other way where the 32-bit norm lands on the other side of a bfloat16 boundary
+    assert (got.double().cpu() - y).abs().max().item() <= 2.0**-7 * y.abs().max().item() + 1e-5
+    assert not F().gemv_normed_suits(17, n, k, torch.device(DEV)) and not F().gemv_normed_suits(m, n, 2048, torch.device(DEV))
+    with pytest.raises(Exception, match="norm on load"):
+        F().gemv_stream(torch.zeros(64, 2048, dtype=torch.bfloat16, device=DEV), norm=(torch.zeros(2, 2048, device=DEV), torch.ones(2048, device=DEV), eps))
+
+
+@pytest.mark.parametrize("m,n,k", [(8, 1024, 2048), (1, 1024, 3072), (16, 1000, 520), (5, 78, 8), (12, 2560, 4096)])
+def test_gemv_adds_into_the_stream(m, n, k):
+    """The few-token product whose output stage adds the result, rounded to bfloat16, into a 32-bit stream."""
+    x = rand(m, k, seed=1).to(torch.bfloat16)
+    w = rand(n, k, seed=2, scale=k**-0.5).to(torch.bfloat16)
+    h = rand(m, n, seed=4, scale=5.0).float()
+    stream = h.clone().to(DEV)
+    assert F().gemv_stream(w.to(DEV), x=x.to(DEV), resid=stream) is None
+    y = (x.double() @ w.double().T).to(torch.bfloat16).double()
+    want = h.double() + y
+    assert (stream.double().cpu() - want).abs().max().item() <= 2.0**-8 * y.abs().max().item() + 1e-5
+    # and exactly what the plain product followed by an add gives
+    plain_product = F().gemv(x.to(DEV), w.to(DEV), torch.bfloat16)
+    assert torch.equal(stream, h.to(DEV) + plain_product.float())
+    with pytest.raises(Exception, match="8-byte aligned rows"):  # a stream with rows of an odd number of elements
+        F().gemv_stream(w[:77].contiguous().to(DEV), x=x.to(DEV), resid=torch.zeros(m, 77, device=DEV))
+
+
 def test_gemv_refuses_what_it_cannot_take():
     x = torch.zeros(33, 512, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(8, 512, dtype=torch.bfloat16, device=DEV)
