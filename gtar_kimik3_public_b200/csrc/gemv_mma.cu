@@ -34,6 +34,7 @@ constexpr int ROWS = 8;          // weight rows of a group = the N of the MMA
 constexpr int CHUNK = 32;        // k of one 16-byte piece per thread and row: 4 threads x 8 elements
 constexpr int MAX_GROUPS = 8;    // groups a block can take (its partial sums stay in shared memory)
 constexpr int X_REGS = 4;        // chunks per warp and group up to which the activations stay in registers
+constexpr int X_REGS_LONG = 12;  // the same for up to eight tokens (one set of rows): rows of up to 3,072 elements
 constexpr int ROUND_ITEMS = 24;  // chunks per thread whose weights fit in shared memory at once (96 KB a block)
 
 struct GemvParams {
@@ -79,8 +80,11 @@ __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g));
 // `x_stride` bytes (the rows of two tokens a quarter-warp reads together lie in different banks); and, when the
 // weights come in more than one round, [group of the block][thread] partial sums (with one round a thread
 // leaves its partial sum where the group's first weight piece was).
-template <int ROW_SETS, bool NORM = false>
-__global__ void __launch_bounds__(THREADS, NORM ? 2 : ROW_SETS == 4 ? 2 : 3) gemv_mma_kernel(const GemvParams p, int round_items, int x_stride) {
+// XR: chunks per warp and group up to which the activations stay in registers (X_REGS; 12 for up to eight tokens of
+// up to 3,072 elements: every thread fetches its own pieces straight from memory, no staging by the block, and all
+// SMs take part where the staged path would use fewer, fatter blocks).
+template <int ROW_SETS, bool NORM = false, int XR = X_REGS>
+__global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS == 4 ? 2 : 3) gemv_mma_kernel(const GemvParams p, int round_items, int x_stride) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float row_ss[WARPS][16];  // NORM: the warps' parts of each token's sum of squares
     constexpr bool TWO_ROWS = ROW_SETS >= 2;
@@ -186,10 +190,10 @@ __global__ void __launch_bounds__(THREADS, NORM ? 2 : ROW_SETS == 4 ? 2 : 3) gem
 
     request(0);  // before the kernel in front has finished
     // NORM: this thread's pieces of the norm's weights (the same for every token), also before the wait
-    float nw[NORM ? X_REGS : 1][8];
+    float nw[NORM ? XR : 1][8];
     if (NORM) {
 #pragma unroll
-        for (int j = 0; j < X_REGS; ++j) {
+        for (int j = 0; j < XR; ++j) {
             const int k = (warp + j * WARPS) * CHUNK + piece * 8;
 #pragma unroll
             for (int e = 0; e < 8; ++e) nw[NORM ? j : 0][e] = 0.f;
@@ -216,16 +220,16 @@ __global__ void __launch_bounds__(THREADS, NORM ? 2 : ROW_SETS == 4 ? 2 : 3) gem
     fetch_old();
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const uint4* wp = pieces + threadIdx.x;
-    if (cpw <= X_REGS && one_round) {
+    if (cpw <= XR && one_round) {
         // short K: the thread's pieces of the activations straight from memory into registers, no staging
-        uint4 xr[TILES][X_REGS], xr2[TILES][X_REGS];
+        uint4 xr[TILES][XR], xr2[TILES][XR];
         if (NORM) {
             // the rows of the stream: 32 bytes a piece, their squares summed over the block, then scaled and rounded
             static_assert(!NORM || TILES == 1, "the norm on load is built for up to 16 tokens");
-            float hv[X_REGS][8], hv2[TWO_ROWS ? X_REGS : 1][8];
+            float hv[XR][8], hv2[TWO_ROWS ? XR : 1][8];
             float ss = 0.f, ss2 = 0.f;
 #pragma unroll
-            for (int j = 0; j < X_REGS; ++j) {
+            for (int j = 0; j < XR; ++j) {
                 const int k = (warp + j * WARPS) * CHUNK + piece * 8;
                 const bool in = j < cpw && k < p.k;
                 const bool in1 = in && group < p.tokens, in2 = TWO_ROWS && in && group + 8 < p.tokens;
@@ -241,7 +245,7 @@ __global__ void __launch_bounds__(THREADS, NORM ? 2 : ROW_SETS == 4 ? 2 : 3) gem
                 }
             }
 #pragma unroll
-            for (int j = 0; j < X_REGS; ++j)
+            for (int j = 0; j < XR; ++j)
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     ss += hv[j][e] * hv[j][e];
@@ -272,7 +276,7 @@ __global__ void __launch_bounds__(THREADS, NORM ? 2 : ROW_SETS == 4 ? 2 : 3) gem
                 return *reinterpret_cast<uint32_t*>(&v);
             };
 #pragma unroll
-            for (int j = 0; j < X_REGS; ++j) {
+            for (int j = 0; j < XR; ++j) {
                 const float* w8 = nw[NORM ? j : 0];
                 xr[0][j] = make_uint4(pack2((hv[j][0] * inv) * w8[0], (hv[j][1] * inv) * w8[1]), pack2((hv[j][2] * inv) * w8[2], (hv[j][3] * inv) * w8[3]),
                                       pack2((hv[j][4] * inv) * w8[4], (hv[j][5] * inv) * w8[5]), pack2((hv[j][6] * inv) * w8[6], (hv[j][7] * inv) * w8[7]));
@@ -288,7 +292,7 @@ __global__ void __launch_bounds__(THREADS, NORM ? 2 : ROW_SETS == 4 ? 2 : 3) gem
 #pragma unroll
         for (int tile = 0; tile < TILES; ++tile) {
 #pragma unroll
-            for (int j = 0; j < X_REGS; ++j) {
+            for (int j = 0; j < XR; ++j) {
                 const int k = (warp + j * WARPS) * CHUNK + piece * 8;
                 const bool in = j < cpw && k < p.k;
                 const int token = 16 * tile + group;
@@ -306,7 +310,7 @@ __global__ void __launch_bounds__(THREADS, NORM ? 2 : ROW_SETS == 4 ? 2 : 3) gem
                 for (int i = 0; i < 4; ++i) acc0[tile][i] = acc1[tile][i] = 0.f;
             }
 #pragma unroll
-            for (int j = 0; j < X_REGS; ++j) {
+            for (int j = 0; j < XR; ++j) {
                 if (j < cpw) {
                     const uint4 wv = *wp;
                     wp += THREADS;
@@ -403,6 +407,7 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
         if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<1, false, X_REGS_LONG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (err == cudaSuccess) err = cudaFuncSetAttribute(gemv_mma_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (err != cudaSuccess) { n_sms = 0; return gk_fail(GK_CUDA_ERROR, "gemv: %s", cudaGetErrorString(err)); }
     }
@@ -410,7 +415,12 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
     GK_REQUIRE(n_groups <= n_sms * MAX_GROUPS, "gemv: takes up to %d weight rows on this device, got %d", n_sms * MAX_GROUPS * ROWS, p.n);
     const int n_chunks = (p.k + CHUNK - 1) / CHUNK;
     int blocks = n_groups < n_sms ? n_groups : n_sms;
-    if ((n_chunks + WARPS - 1) / WARPS > X_REGS) {
+    // up to eight tokens, no norm on load: rows of up to 3,072 elements stay in registers too (if the block's weights
+    // come in one round)
+    const int cpw_all = (n_chunks + WARPS - 1) / WARPS;
+    const bool long_registers = p.tokens <= 8 && p.norm_h == nullptr && cpw_all > X_REGS && cpw_all <= X_REGS_LONG &&
+                                ((n_groups + blocks - 1) / blocks) * cpw_all <= ROUND_ITEMS;
+    if (cpw_all > X_REGS && !long_registers) {
         // long K: every block copies all activations from L2, so fewer blocks with more groups each (as many
         // as fit in one round of weights) cost less there than they lose in the multiplications
         const int fit = ROUND_ITEMS / ((n_chunks + WARPS - 1) / WARPS);
@@ -426,7 +436,7 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
     // of 64 bytes apart (none when they stay in registers: short K and all weights in one round)
     int x_stride = cpw * WARPS * CHUNK * 2;
     if (x_stride % 128 == 0) x_stride += 64;
-    const bool x_in_registers = cpw <= X_REGS && items <= ROUND_ITEMS;
+    const bool x_in_registers = (cpw <= X_REGS || long_registers) && items <= ROUND_ITEMS;
     const size_t x_bytes = x_in_registers ? 0 : (size_t)(p.tokens > 8 ? 16 : 8) * x_stride;
     // weight pieces of as many chunks as fit beside them (a block whose share does not fit takes it in rounds and
     // keeps its partial sums in a buffer of their own)
@@ -453,6 +463,8 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
         gk_launch(gemv_mma_kernel<4>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
     } else if (p.tokens > 8) {
         gk_launch(gemv_mma_kernel<2>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
+    } else if (long_registers) {
+        gk_launch(gemv_mma_kernel<1, false, X_REGS_LONG>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
     } else {
         gk_launch(gemv_mma_kernel<1>, grid, dim3(THREADS), smem, stream, p, round_items, x_stride);
     }
