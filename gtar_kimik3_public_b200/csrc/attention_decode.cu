@@ -556,3 +556,30 @@ GK_EXPORT int gk_attention_decode_bf16_no_alloc(const void* q, const void* k_pag
     return gk_attention_decode_bf16(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q,
                                     n_kv, head_dim, max_pages, page_size, scale, window, n_splits, stream);
 }
+
+// How many clusters of `cluster` blocks of the decode attention kernel the device holds at once (blocks for a cluster
+// of one), or a negative CUDA error.  Clusters are placed inside a GPC, so this is less than the SMs' places divided by
+// the cluster size; the host's choice of the number of splits counts waves with it.
+GK_EXPORT int gk_attention_decode_resident_clusters(int head_dim, int cluster) {
+    if ((head_dim != 64 && head_dim != 128) || cluster < 1 || cluster > 8) return -1;
+    const size_t smem = head_dim == 64 ? sizeof(DecodeSmem<64>) : sizeof(DecodeSmem<128>);
+    const void* kernel = head_dim == 64 ? (const void*)attention_decode_kernel<64> : (const void*)attention_decode_kernel<128>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return -(int)err;
+    gk_prepare_kernel(kernel);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cluster * 1024, 1, 1);
+    cfg.blockDim = dim3(WARPS * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    err = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+    if (err != cudaSuccess) return -(int)err;
+    return clusters;
+}

@@ -24,7 +24,8 @@ def fused_decode_ok(qkv: torch.Tensor, kv: F.PagedKV, n_q: int, n_kv: int, head_
 def decode_split_count(ctx, n_kv: int, kv: F.PagedKV) -> int:
     """Blocks that share a sequence's pages in this layer: from the layer's own kv heads and the step's bound on
     sequence lengths (in a captured step that is a bound of the shape, not the lengths of the day)."""
-    return F.decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len, kv.page_size, F.sm_count(kv.k.device))
+    sms = F.sm_count(kv.k.device)
+    return F.decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len, kv.page_size, sms, F.decode_cluster_places(kv.k.shape[3], sms))
 
 
 def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: int = 0) -> torch.Tensor:

@@ -513,29 +513,48 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torc
     return out
 
 
+@functools.lru_cache(maxsize=None)
+def decode_cluster_places(head_dim: int, sm_count: int) -> tuple[int, int, int, int]:
+    """How many clusters of 1, 2, 4 and 8 blocks of the decode attention kernel the device holds at once.  Asked of the
+    device where there is one (clusters are placed inside a GPC, so eight-block clusters fill fewer of the SMs' places
+    than single blocks do); two blocks an SM otherwise."""
+    if torch.cuda.is_available():
+        from .library import library
+
+        got = [library().gk_attention_decode_resident_clusters(int(head_dim), c) for c in (1, 2, 4, 8)]
+        if all(g > 0 for g in got):
+            return tuple(got)
+    return tuple(2 * sm_count // c for c in (1, 2, 4, 8))
+
+
 @functools.lru_cache(maxsize=4096)
-def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_count: int) -> int:
+def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_count: int,
+                  cluster_places: tuple[int, int, int, int] | None = None) -> int:
     """How many blocks share a sequence's pages in decode attention.
 
     Two blocks fit an SM.  With few (sequence, kv head) pairs and a long context, as many splits as fill those
     places go through scratch and a second kernel.  Otherwise 1, 2, 4 or 8 splits merge inside the kernel (a
     cluster per pair, which then does the q/k preparation too), and the number is the one with the lowest
-    estimate of  waves of blocks x (pages a block streams + 8 pages' worth of time for what a block does
-    besides).  It agrees with step times measured at batch 1 to 64 with 2,048-token contexts; against the old
-    "fill the places once" rule it gains 7 to 13% at batch 12, 40 and 48 (clusters of three place badly: two
-    splits are faster; 320 or 384 pairs are better cut in two than run as one and a bit waves)."""
+    estimate of  waves of clusters x (pages a block streams + 8 pages' worth of time for what a block does
+    besides); ``cluster_places`` says how many clusters of 1, 2, 4 and 8 blocks run at once (default: two blocks
+    an SM, whatever the cluster).  It agrees with step times measured at batch 1 to 64 with 2,048-token contexts;
+    against the old "fill the places once" rule it gains 7 to 13% at batch 12, 40 and 48 (clusters of three place
+    badly: two splits are faster; 320 or 384 pairs are better cut in two than run as one and a bit waves)."""
     pairs = max(1, n_seqs * n_kv)
     pages = max(1, -(-max_kv_len // page_size))
     places = 2 * sm_count
     fill = max(1, min(places // pairs, pages, 64))
     if fill >= SCRATCH_SPLITS_FROM and max_kv_len >= 8192:
         return fill
+    if cluster_places is None:
+        cluster_places = tuple(places // c for c in (1, 2, 4, 8))
+    at_once = dict(zip((1, 2, 4, 8), cluster_places))
 
     def estimate(splits: int) -> float:
         # clusters of eight that have to share SMs cost more besides their pages than the eight say (four sequences of
         # 2,048 tokens: 0.82 ms a step with four splits, 0.89 with eight; one and two sequences are faster with eight)
         besides = 13.0 if splits == 8 and pairs * splits > sm_count else 8.0
-        return -(-pairs * splits // places) * (pages / splits + besides)
+        return -(-pairs // max(1, at_once[splits])) * (pages / splits + besides)
 
     return min((s for s in (1, 2, 4, 8) if s <= pages), key=lambda s: (estimate(s), -s))
 

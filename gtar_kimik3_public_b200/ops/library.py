@@ -43,6 +43,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_gemv_bf16": [P, I, I, L, P, I, L, P, I, I, P],
     "gk_gemv_bf16_stream": [P, I, I, L, P, I, L, P, I, I, P, L, P, I, F, P, L, P],
     "gk_set_pdl": [I],
+    "gk_attention_decode_resident_clusters": [I, I],
     "gk_set_gemm_pairs": [I],
     "gk_set_attention_prefill_keys": [I],
     "gk_attention_decode_fused_bf16": [P, P, P, I, I, F, P, P, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
