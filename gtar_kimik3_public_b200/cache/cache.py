@@ -73,6 +73,7 @@ class _KVGroup:
         self.owned: dict[int, dict[int, int]] = {}  # slot -> {page index in sequence: page}
         self.upto: dict[int, int] = {}  # slot -> one past the highest page index the sequence ever had
         self.dirty: set[int] = set()
+        self._staging = None  # pinned copies of the table for uploads, made at the first upload
 
     def open_slot(self, slot: int) -> None:
         self.owned[slot] = {}
@@ -115,19 +116,37 @@ class _KVGroup:
             self.upto[slot] = last + 1
             self.dirty.add(slot)
 
+    STAGING_RING = 8
+
     def sync(self) -> None:
         """Sends the changed rows of the page table to the device.  The rows are copied into a
         pinned buffer of their own first: the host goes on changing ``table_host`` (a slot that is
         given back and used again) while earlier copies may still wait in the stream, and a copy
-        must carry the numbers of the step it was issued for."""
+        must carry the numbers of the step it was issued for.  The pinned buffers are a small ring,
+        each guarded by an event, so that none is written while a copy out of it may still wait."""
         if not self.dirty:
             return
         slots = sorted(self.dirty)
-        staged = torch.from_numpy(self.table_host[slots])  # fancy indexing copies
-        if self.table.is_cuda:
-            staged = staged.pin_memory()
-        for i, slot in enumerate(slots):
-            self.table[slot].copy_(staged[i], non_blocking=True)
+        if not self.table.is_cuda:
+            self.table[slots] = torch.from_numpy(self.table_host[slots])
+            self.dirty.clear()
+            return
+        if self._staging is None:
+            self._staging = [torch.empty(self.table_host.shape, dtype=torch.int32).pin_memory() for _ in range(self.STAGING_RING)]
+            self._staging_np = [t.numpy() for t in self._staging]
+            self._staging_events = [None] * self.STAGING_RING
+            self._staging_turn = 0
+        turn = self._staging_turn
+        self._staging_turn = (turn + 1) % self.STAGING_RING
+        if self._staging_events[turn] is not None:
+            self._staging_events[turn].synchronize()
+        staged, staged_np = self._staging[turn], self._staging_np[turn]
+        for slot in slots:
+            staged_np[slot] = self.table_host[slot]
+            self.table[slot].copy_(staged[slot], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._staging_events[turn] = event
         self.dirty.clear()
 
     def view(self, item: tuple[int, int]) -> PagedKV:

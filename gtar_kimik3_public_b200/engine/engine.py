@@ -9,6 +9,7 @@ places, and a sequence that ends gives its storage back while the others go on.
 
 from __future__ import annotations
 
+import array
 import os
 from dataclasses import dataclass, field
 
@@ -18,6 +19,18 @@ import torch
 from ..cache import Cache, CacheFull
 from ..models.model import Model
 from .step import SequenceStep, pack_step, plan_step
+
+
+def _token_array(tokens) -> np.ndarray:
+    """The ids as an int64 array.  A list of Python ints goes through ``array.array`` (about half the time of
+    ``np.asarray`` for a prompt of a few thousand tokens); anything else, or a list that holds other things, takes
+    numpy's own conversion and its errors."""
+    if type(tokens) is list:
+        try:
+            return np.frombuffer(array.array("q", tokens), dtype=np.int64)
+        except (TypeError, OverflowError):
+            pass
+    return np.asarray(tokens, dtype=np.int64)
 
 
 @dataclass
@@ -90,7 +103,7 @@ class Engine:
         q_lens = [len(e.tokens) for e in entries]
         if min(q_lens) == 0:
             raise ValueError(f"request {entries[q_lens.index(0)].id!r} brings no token")
-        parts = [np.asarray(e.tokens, dtype=np.int64) for e in entries]
+        parts = [_token_array(e.tokens) for e in entries]
         if any(part.ndim != 1 for part in parts):
             raise ValueError("tokens must be a flat list of ids")
         flat = parts[0] if len(parts) == 1 else np.concatenate(parts)

@@ -73,7 +73,13 @@ def pack_step(sequences: list[SequenceStep], vocab_size: int, check_tokens: bool
     past = [s.past_len for s in sequences]
     n_seqs = len(sequences)
     past_np = np.asarray(past, dtype=np.int32)
-    if max(q_lens) == 1:  # a decode step: one token each
+    if n_seqs == 1 and q_lens[0] > 1:  # one prompt (or continuation): nothing to repeat or add up
+        n = q_lens[0]
+        starts = np.array([0, n], dtype=np.int32)
+        tokens = np.asarray(sequences[0].tokens, dtype=np.int64)
+        tok_seq = np.zeros(n, dtype=np.int32)
+        tok_pos = np.arange(past[0], past[0] + n, dtype=np.int32)
+    elif max(q_lens) == 1:  # a decode step: one token each
         starts = np.arange(n_seqs + 1, dtype=np.int32)
         tokens = np.asarray([s.tokens[0] for s in sequences], dtype=np.int64)
         tok_seq, tok_pos = starts[:-1], past_np
