@@ -26,7 +26,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from ..ops.functional import PagedKV
+from ..ops.functional import DecodeWork, PagedKV
 from ..parts.base import KVRequest, StateRequest
 from .allocators import CacheFull, PageAllocator, SlotAllocator
 
@@ -74,6 +74,7 @@ class _KVGroup:
         self.upto: dict[int, int] = {}  # slot -> one past the highest page index the sequence ever had
         self.dirty: set[int] = set()
         self._staging = None  # pinned copies of the table for uploads, made at the first upload
+        self._work = None  # decode attention's scratch for this group's layers, made with the first view
 
     def open_slot(self, slot: int) -> None:
         self.owned[slot] = {}
@@ -151,7 +152,9 @@ class _KVGroup:
 
     def view(self, item: tuple[int, int]) -> PagedKV:
         i = self.index_of[item]
-        return PagedKV(self.k[i], self.v[i], self.table)
+        if self._work is None and self.table.is_cuda:
+            self._work = DecodeWork(self.table.device)
+        return PagedKV(self.k[i], self.v[i], self.table, self._work)
 
 
 class _StateGroup:

@@ -1156,17 +1156,20 @@ GK_EXPORT int gk_gemm_bf16_tc(const void* a, int rows_a, long long lda, const vo
     dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
     GK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;
+    int device = 0, n_sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+    const bool one_wave = (long long)grid.x * grid.y * grid.z <= n_sms;
     switch (bn) {
-        // skinny products are bound by memory latency: as many bytes in flight per block as fit
+        // skinny products are bound by memory latency: as many bytes in flight per block as fit where every block
+        // has an SM of its own; where blocks follow one another on an SM (the output head: 1,187 tiles), two
+        // resident blocks with half the ring each, so that one streams while the other starts up or writes out
         case 16: return launch<16, 5>(ma, mb, p, grid, s);
-        case 32: return launch<32, 9>(ma, mb, p, grid, s);
-        case 64: return launch<64, 8>(ma, mb, p, grid, s);
+        case 32: return one_wave ? launch<32, 9>(ma, mb, p, grid, s) : launch<32, 5>(ma, mb, p, grid, s);
+        case 64: return one_wave ? launch<64, 8>(ma, mb, p, grid, s) : launch<64, 4>(ma, mb, p, grid, s);
         case 128: {
             // one block per SM at most: a deeper ring instead of a second resident block (the k-blocks in flight
             // have to cover the 1.3 us a TMA load takes, and 3 stages of 32 KB cover 0.5 us of MMAs)
-            int device = 0, n_sms = 148;
-            if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
-            if ((long long)grid.x * grid.y * grid.z <= n_sms) return launch<128, 6>(ma, mb, p, grid, s);
+            if (one_wave) return launch<128, 6>(ma, mb, p, grid, s);
             return launch<128, 3>(ma, mb, p, grid, s);
         }
         case 256: return launch<256, 4>(ma, mb, p, grid, s);

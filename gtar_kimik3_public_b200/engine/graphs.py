@@ -9,10 +9,12 @@ host's work per step is one small pinned copy of those numbers.  Decode steps (o
 sequence) are captured at their first use, other shapes when they are seen a second time; the
 least recently used graphs are dropped beyond a limit.
 
-A decode shape also carries a bound on the longest sequence of the step (a power of two, at least
-``MIN_LENGTH_BOUND``, at most what the cache holds): kernels size their launches from that bound, not
-from the lengths of the day, so a short context in a cache made for long ones is not cut into as many
-pieces as the longest context would need.
+A decode shape also carries a bound on the longest sequence of the step (``MIN_LENGTH_BOUND`` times a
+power of two or one and a half times that: 1,024, 1,536, 2,048, 3,072, ..., at most what the cache holds):
+kernels size their launches from that bound, not from the lengths of the day, so a short context in a
+cache made for long ones is not cut into as many pieces as the longest context would need.  Where a
+launch shape is a matter of speed only (into how many blocks a sequence's pages are cut), it is chosen
+for the middle of the lengths that the bound covers.
 
 A step is executed exactly once, also the step at which its shape is captured: that step runs launch
 by launch (which does whatever one-time set-up the kernels need) and gives the result, the capture
@@ -90,15 +92,21 @@ class StepGraphs:
         self.events[turn] = event
 
     # ------------------------------------------------------------------ graphs
-    def length_bound(self, packed: PackedStep) -> int:
-        """The bound on sequence lengths that the step's launches are sized for."""
+    def length_bounds(self, packed: PackedStep) -> tuple[int, int]:
+        """The bound on sequence lengths that the step's launches are sized for, and the middle of the lengths
+        that share this bound (0 where the bound is not one of a decode step)."""
         longest = self.cache.max_seq_len
         if not packed.all_single:
-            return longest
-        bound = self.MIN_LENGTH_BOUND
+            return longest, 0
+        below, bound = 0, self.MIN_LENGTH_BOUND
         while bound < packed.max_kv_len:
-            bound *= 2
-        return min(bound, longest)
+            # 1, 1.5, 2, 3, 4, 6, ... times the least bound
+            below, bound = bound, (bound * 3 // 2 if bound & (bound - 1) == 0 else bound * 4 // 3)
+        bound = min(bound, longest)
+        return bound, max(1, (below + bound + 1) // 2)
+
+    def length_bound(self, packed: PackedStep) -> int:
+        return self.length_bounds(packed)[0]
 
     def key_of(self, packed: PackedStep) -> tuple:
         if packed.all_single:
@@ -141,7 +149,8 @@ class StepGraphs:
 
         self.model.prepare(self.cache.max_seq_len - 1)
         # launch shapes inside a graph must not depend on the lengths of the day: a bound stands in
-        ctx = context_from_views(packed, self.views(packed), self.model.dtype, max_kv_len=self.length_bound(packed))
+        bound, typical = self.length_bounds(packed)
+        ctx = context_from_views(packed, self.views(packed), self.model.dtype, max_kv_len=bound, typical_kv_len=typical)
         result = self.model.step(ctx, self.cache)  # one-time set-up happens here, outside the capture
         torch.cuda.synchronize()
         while len(self.graphs) >= self.MAX_PREFILL_GRAPHS + 3 * self.s_max:

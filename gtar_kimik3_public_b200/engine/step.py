@@ -107,13 +107,13 @@ def pack_step(sequences: list[SequenceStep], vocab_size: int, check_tokens: bool
 
 
 def context_from_views(packed: PackedStep, views: list[torch.Tensor], dtype: torch.dtype, max_kv_len: int | None = None,
-                       device_tokens: torch.Tensor | None = None) -> StepContext:
+                       device_tokens: torch.Tensor | None = None, typical_kv_len: int = 0) -> StepContext:
     max_kv = packed.max_kv_len if max_kv_len is None else max_kv_len
     return StepContext(
         n_tokens=packed.n_tokens, n_seqs=packed.n_seqs, dtype=dtype,
         tokens=views[0] if device_tokens is None else device_tokens, tok_pos=views[1], tok_seq=views[2], cu_q=views[3],
         slots=views[4], kv_len=views[5], want_rows=views[6], max_q_len=packed.max_q_len, max_kv_len=max_kv,
-        max_position=max_kv - 1, all_single=packed.all_single, host_q_len=packed.q_lens, host_past_len=packed.past,
+        max_position=max_kv - 1, all_single=packed.all_single, typical_kv_len=typical_kv_len, host_q_len=packed.q_lens, host_past_len=packed.past,
         host_slots=packed.slots,
     )
 

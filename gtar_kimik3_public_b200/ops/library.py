@@ -47,6 +47,8 @@ _SIGNATURES: dict[str, list] = {
     "gk_set_gemm_pairs": [I],
     "gk_set_attention_prefill_keys": [I],
     "gk_attention_decode_fused_bf16": [P, P, P, I, I, F, P, P, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    "gk_attention_decode_flat_bf16": [P, P, P, P, I, I, F, P, P, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    "gk_attention_decode_flat_resident_blocks": [I],
     "gk_attention_decode_bf16_no_alloc": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_prefill_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
     "gk_attention_prefill_tc_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, F, I, P, P],

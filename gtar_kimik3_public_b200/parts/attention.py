@@ -109,6 +109,10 @@ class GQAAttention(Mixer):
         """Attention output ``[n_tokens, n_q, head_dim]`` from the packed projection of the step's tokens."""
         if ctx.all_single and attention_ops.fused_decode_ok(qkv, cache, self.n_q, self.n_kv, self.head_dim):
             # one token per sequence: norm, rotation, cache write and attention in one kernel
+            if attention_ops.decode_flat_preferred(ctx, self.n_kv, cache):
+                return F.attention_decode_flat(
+                    None, qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm, self.k_norm, self.qk_norm_eps or 1.0, cos,
+                    sin, cache, ctx.kv_len, ctx.slots, ctx.max_position, self.scale, self.window or 0, 0, write_kv)
             splits = attention_ops.decode_split_count(ctx, self.n_kv, cache)
             if splits <= 8:
                 return F.attention_decode_fused(

@@ -76,6 +76,9 @@ class StepContext:
     max_kv_len: int
     max_position: int
     all_single: bool  # every sequence brings exactly one token (a decode step)
+    # where max_kv_len is a bound for many steps to come and not the longest length of this one: a length in the
+    # middle of what the bound covers, to choose launch shapes by (0: there is none, max_kv_len is the length)
+    typical_kv_len: int = 0
     host_q_len: list[int] = field(default_factory=list)
     host_past_len: list[int] = field(default_factory=list)
     host_slots: list[int] = field(default_factory=list)

@@ -383,6 +383,71 @@ def test_attention_decode_bf16_far_key_and_window():
         fill_pages(kv, table, int(slots[0]), k.to(dtype), v.to(dtype))
 
 
+@pytest.mark.parametrize("n_q,n_kv,d", [(4, 4, 64), (16, 8, 128), (6, 2, 128), (16, 1, 64), (12, 3, 128)])
+@pytest.mark.parametrize("n_blocks", [1, 2, 7, 64, 0, 1000])
+def test_attention_decode_dealt_evenly(n_q, n_kv, d, n_blocks):
+    """The kernel that cuts the line of all sequences' pages into equal pieces: pieces that end inside a pair, pairs
+    spread over many blocks, more blocks than pages; twice in a row, since the ticket counters must be left at zero."""
+    dtype = torch.bfloat16
+    lens = [1, 63, 64, 65, 777, 1000, 130, 2, 128]
+    kv, slots, table = scrambled_pages(len(lens), 1000, n_kv, d, dtype, seed=12)
+    kv.work = F().DecodeWork(torch.device(DEV))
+    qs, wants = [], []
+    for i, n in enumerate(lens):
+        k = rand(n, n_kv, d, seed=60 + i).to(dtype)
+        v = rand(n, n_kv, d, seed=70 + i).to(dtype)
+        q = rand(1, n_q, d, seed=80 + i).to(dtype)
+        fill_pages(kv, table, int(slots[i]), k, v)
+        qs.append(q)
+        wants.append(dense_attention(q.double(), k.double(), v.double(), n - 1))
+    kv_len = torch.tensor(lens, dtype=torch.int32).to(DEV)
+    want = torch.cat(wants)
+    for turn in range(2):
+        out = F().attention_decode_flat(torch.cat(qs).to(DEV), None, n_q, n_kv, d, None, None, 1.0, None, None, kv, kv_len,
+                                        slots.to(DEV), max(lens) - 1, d**-0.5, 0, n_blocks)
+        got = out.double().cpu()
+        assert torch.isfinite(got).all()  # the poisoned places beyond each length were not used
+        assert (got - want).abs().max().item() < 1.5 * BF16_ULP * want.abs().max().item() + 2e-3, turn
+        assert int(kv.work.tickets.abs().sum()) == 0
+
+
+def test_attention_decode_dealt_evenly_far_key_and_window():
+    dtype, n_q, n_kv, d, n = torch.bfloat16, 8, 2, 128, 900
+    kv, slots, table = scrambled_pages(1, n, n_kv, d, dtype, seed=13)
+    k = rand(n, n_kv, d, seed=1, scale=0.1)
+    v = rand(n, n_kv, d, seed=2)
+    q = rand(1, n_q, d, seed=3, scale=0.1)
+    k[5, 0] = 3.0
+    q[0, 1] = 3.0   # query head 1 (kv head 0) must find key 5
+    k[517, 1] = 3.0
+    q[0, 6] = 3.0   # query head 6 (kv head 1) must find key 517
+    fill_pages(kv, table, int(slots[0]), k.to(dtype), v.to(dtype))
+    kv_len = torch.tensor([n], dtype=torch.int32).to(DEV)
+
+    def run(window, blocks):
+        return F().attention_decode_flat(q.to(dtype).to(DEV), None, n_q, n_kv, d, None, None, 1.0, None, None, kv, kv_len,
+                                         slots.to(DEV), n - 1, d**-0.5, window, blocks).double().cpu()
+
+    for blocks in (1, 5, 0):
+        out = run(0, blocks)
+        assert (out[0, 1] - v[5, 0].to(dtype).double()).abs().max() < 1e-2
+        assert (out[0, 6] - v[517, 1].to(dtype).double()).abs().max() < 1e-2
+        # a window of 400 hides key 5 (visible keys are 500..899) but not key 517
+        win = run(400, blocks)
+        want = dense_attention(q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double(), n - 1, 400)
+        assert (win - want).abs().max() < 2e-2
+        assert (win[0, 1] - v[5, 0].to(dtype).double()).abs().max() > 0.1
+        # the key at the window's edge: 500 is the last one inside, 499 the first outside
+        k2 = k.clone()
+        k2[499, 0] = 6.0
+        k2[500, 0] = 3.0
+        k2[5, 0] = 0.0
+        fill_pages(kv, table, int(slots[0]), k2.to(dtype), v.to(dtype))
+        edge = run(400, blocks)
+        assert (edge[0, 1] - v[500, 0].to(dtype).double()).abs().max() < 1e-2
+        fill_pages(kv, table, int(slots[0]), k.to(dtype), v.to(dtype))
+
+
 # ------------------------------------------------------------------ tcgen05 matrix product
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 256, 128), (8, 4096, 1024), (13, 1000, 200), (64, 384, 1024),
                                    (65, 128, 64), (128, 128, 128), (200, 1000, 520), (2048, 1024, 3072), (300, 151936, 1024),
@@ -515,14 +580,17 @@ def test_attention_decode_fused_equals_the_separate_kernels(n_q, n_kv, d, weight
     cos, sin = cos[:, : d // 2].contiguous().to(DEV), sin[:, : d // 2].contiguous().to(DEV)
     kv_len = torch.tensor(lens, dtype=torch.int32).to(DEV)
     results = []
-    for fused in (False, True):
+    for fused in (False, True, "dealt evenly", "dealt evenly, three blocks"):
         kv, slots, table = scrambled_pages(len(lens), 1000, n_kv, d, dtype, seed=16)
         for i, n in enumerate(lens):  # the cached past of each sequence (everything but the new token)
             if n > 1:
                 fill_pages(kv, table, int(slots[i]), rand(n - 1, n_kv, d, seed=20 + i).to(dtype), rand(n - 1, n_kv, d, seed=30 + i).to(dtype))
         pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32).to(DEV)
         seq = torch.arange(len(lens), dtype=torch.int32).to(DEV)
-        if fused:
+        if isinstance(fused, str):
+            out = F().attention_decode_flat(None, qkv.to(DEV), n_q, n_kv, d, wq.to(DEV), wk.to(DEV), eps, cos, sin, kv, kv_len,
+                                            slots.to(DEV), max(lens) - 1, d**-0.5, 0, 3 if "three" in fused else 0)
+        elif fused:
             out = F().attention_decode_fused(qkv.to(DEV), n_q, n_kv, d, wq.to(DEV), wk.to(DEV), eps, cos, sin, kv, kv_len,
                                              slots.to(DEV), max(lens) - 1, d**-0.5, 0, n_splits)
         else:
@@ -532,12 +600,13 @@ def test_attention_decode_fused_equals_the_separate_kernels(n_q, n_kv, d, weight
         new_k = torch.stack([kv.k[int(table[slots[i], (n - 1) // 64]), :, (n - 1) % 64] for i, n in enumerate(lens)])
         new_v = torch.stack([kv.v[int(table[slots[i], (n - 1) // 64]), :, (n - 1) % 64] for i, n in enumerate(lens)])
         results.append((out.float().cpu(), new_k.float().cpu(), new_v.float().cpu()))
-    (out_a, k_a, v_a), (out_b, k_b, v_b) = results
-    assert torch.isfinite(out_b).all()
-    assert torch.equal(v_a, v_b)
-    # the same formulas in the same precision; the fused kernel may contract a multiply-add differently
-    assert (k_a - k_b).abs().max() <= 2.0**-7 * k_a.abs().max()
-    assert (out_a - out_b).abs().max() <= 2.0**-7 * out_a.abs().max() + 1e-3
+    out_a, k_a, v_a = results[0]
+    for out_b, k_b, v_b in results[1:]:
+        assert torch.isfinite(out_b).all()
+        assert torch.equal(v_a, v_b)
+        # the same formulas in the same precision; the fused kernels may contract a multiply-add differently
+        assert (k_a - k_b).abs().max() <= 2.0**-7 * k_a.abs().max()
+        assert (out_a - out_b).abs().max() <= 2.0**-7 * out_a.abs().max() + 1e-3
 
 
 # ------------------------------------------------------------------ q|k|v projection with the attention input stage in its epilogue

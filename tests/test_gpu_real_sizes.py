@@ -152,6 +152,25 @@ def test_many_token_graph_serves_another_split_of_the_same_shape(tag, dtype):
 def test_decode_steps_of_many_sequences(tag, dtype, n_requests, kernel_log):
     """33 to 64 sequences: every product of a decode step runs in the swap-AB orientation on tcgen05, with K split
     among the blocks of a cluster where K is long enough (the real sizes)."""
+    expect = []
+    if dtype == "bfloat16":
+        # 9 to 32 sequences: the few-token product and decode attention fused with the q/k preparation
+        expect = ["gk_gemm_bf16_tc"] if n_requests > 32 else ["gk_gemv_bf16", "gk_attention_decode_fused_bf16"]
+    _decode_many(tag, dtype, n_requests, kernel_log, expect)
+
+
+@pytest.mark.parametrize("tag,n_requests", [("real_06b", 12), ("real_06b", 40), ("real_4b", 33), ("tiny_c", 40), ("tiny_c", 3)])
+def test_decode_steps_with_the_pages_dealt_evenly(tag, n_requests, kernel_log, monkeypatch):
+    """The decode attention kernel that cuts the line of all sequences' pages into equal pieces, forced for every
+    step: sequences of unequal lengths that end one after another, inside captured steps."""
+    from gtar_kimik3_public_b200.ops import attention as attention_ops
+
+    monkeypatch.setattr(attention_ops, "DECODE_FLAT", "always")
+    _decode_many(tag, "bfloat16", n_requests, kernel_log, ["gk_attention_decode_flat_bf16"])
+    assert "gk_attention_decode_fused_bf16" not in kernel_log and "gk_attention_decode_bf16" not in kernel_log
+
+
+def _decode_many(tag, dtype, n_requests, kernel_log, expect):
     lengths = [6 + (11 * i) % 90 for i in range(n_requests)]
     requests = requests_for(tag, lengths, seed=43)
     engine = load_engine(tag, dtype, max_tokens=n_requests * 128, max_seqs=n_requests)
@@ -170,11 +189,9 @@ def test_decode_steps_of_many_sequences(tag, dtype, n_requests, kernel_log):
     steps = 0
     while live:
         logits = engine.step([_entry(r, [requests[r][fed[r]]], [0]) for r in live])
-        if steps == 0 and dtype == "bfloat16":
-            if n_requests > 32:
-                assert "gk_gemm_bf16_tc" in kernel_log, "the first decode step did not take the tensor-memory product"
-            else:  # 9 to 32 sequences: the few-token product and decode attention fused with the q/k preparation
-                assert "gk_gemv_bf16" in kernel_log and "gk_attention_decode_fused_bf16" in kernel_log
+        if steps == 0:
+            for name in expect:
+                assert name in kernel_log, f"the first decode step did not call {name}"
         steps += 1
         for i, r in enumerate(live):
             got[r].append(logits[i:i + 1])
@@ -273,8 +290,9 @@ def test_persistent_kernel_for_all_layers_of_a_decode_step(n_seqs, kernel_log, m
 
 
 def test_decode_across_a_bound_on_the_lengths():
-    """Decode graphs are keyed by a power-of-two bound on the longest sequence of the step (launches are sized from
-    it): a sequence that grows from below 1,024 tokens to above it changes graphs on the way, and its logits do not."""
+    """Decode graphs are keyed by a bound on the longest sequence of the step (1,024, 1,536, 2,048, ...: launches are
+    sized from it): a sequence that grows from below 1,024 tokens to above it changes graphs on the way, and its logits
+    do not."""
     tag, dtype = "real_06b", "bfloat16"
     (tokens,) = requests_for(tag, [1040], seed=61)
     engine = load_engine(tag, dtype, max_tokens=2048, max_seqs=1)
@@ -283,6 +301,6 @@ def test_decode_across_a_bound_on_the_lengths():
     engine.step([_entry("r", tokens[:head], [])])
     rows = [engine.step([_entry("r", [tokens[t]], [0])]) for t in range(head, len(tokens))]
     bounds = sorted({key[4] for key in engine.graphs.graphs if key[3] == 1})
-    assert bounds == [1024, 2048], bounds
+    assert bounds == [1024, 1536], bounds
     check_against_plain(tag, dtype, tokens, list(range(head, len(tokens))), torch.cat(rows), "decode across the bound of 1,024 tokens")
     engine.check()

@@ -44,3 +44,33 @@ def test_split_k_is_a_cluster_size():
     for m in (1, 8, 17, 64):
         for n, k in ((4096, 1024), (6144, 1024), (1024, 2048), (1024, 3072), (151936, 1024), (128, 64)):
             assert split_k_for(m, n, k) in (1, 2, 4, 8)
+
+
+def test_length_bounds_of_captured_decode_steps():
+    """1, 1.5, 2, 3, 4, ... times the least bound, never beyond the cache; launch shapes are chosen for the middle of
+    the lengths a bound covers."""
+    from types import SimpleNamespace
+
+    from gtar_kimik3_public_b200.engine.graphs import StepGraphs
+
+    graphs = SimpleNamespace(cache=SimpleNamespace(max_seq_len=40960), MIN_LENGTH_BOUND=StepGraphs.MIN_LENGTH_BOUND)
+    got = {}
+    for length in (1, 1024, 1025, 1536, 1537, 2049, 3072, 3073, 4097, 40000):
+        step = SimpleNamespace(all_single=True, max_kv_len=length)
+        got[length] = StepGraphs.length_bounds(graphs, step)
+        bound, typical = got[length]
+        assert length <= bound <= 40960 and typical <= bound
+    assert got[1] == got[1024] == (1024, 512)
+    assert got[1025] == got[1536] == (1536, 1280)
+    assert got[1537] == (2048, 1792) and got[2049] == got[3072] == (3072, 2560) and got[3073] == (4096, 3584)
+    assert got[4097] == (6144, 5120) and got[40000] == (40960, 36864)
+    assert StepGraphs.length_bounds(graphs, SimpleNamespace(all_single=False, max_kv_len=77)) == (40960, 0)
+
+
+def test_twenty_four_sequences_are_not_cut():
+    """192 (sequence, kv head) pairs of some 2,500 tokens each fit the device at once uncut; cut in four they are 192
+    clusters where 71 run at once (measured: 48 us an attention kernel cut in four, which a bound of 4,096 tokens
+    taken for the length had chosen; 31 us is what its pages take)."""
+    places = (296, 148, 71, 33)
+    assert decode_splits(24, 8, 2560, 64, 148, places) == 1
+    assert decode_splits(24, 8, 3584, 64, 148, places) == 1
