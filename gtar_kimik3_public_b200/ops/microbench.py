@@ -95,16 +95,24 @@ def bench_attention_decode(args) -> dict:
     q = torch.randn(b, n_q, d, device=DEV, dtype=torch.bfloat16)
     kv_len = torch.full((b,), s, dtype=torch.int32, device=DEV)
     slots = torch.arange(b, dtype=torch.int32, device=DEV)
-    splits = args.splits or F.decode_splits(b, n_kv, s, 64, F.sm_count())
+    splits = args.splits or F.decode_splits(b, n_kv, s, 64, F.sm_count(), F.decode_cluster_places(d, F.sm_count()))
+    if args.dealt_evenly:
+        work = F.DecodeWork(torch.device(DEV))
+        for kv in caches:
+            kv.work = work
 
     def run():
         for kv in caches:
-            F.attention_decode(q, kv, kv_len, slots, d**-0.5, 0, splits)
+            if args.dealt_evenly:
+                F.attention_decode_flat(q, None, n_q, n_kv, d, None, None, 1.0, None, None, kv, kv_len, slots, s - 1, d**-0.5)
+            else:
+                F.attention_decode(q, kv, kv_len, slots, d**-0.5, 0, splits)
 
     us = _time_graph(run, args.iters) / ring
     nbytes = b * s * n_kv * d * 2 * 2
     return {"kernel": "attention_decode", "batch": b, "context": s, "q_heads": n_q, "kv_heads": n_kv, "head_dim": d,
-            "splits": splits, "us": round(us, 2), "kv_gb_s": round(nbytes / us / 1e3, 1)}
+            "splits": "pages dealt evenly" if args.dealt_evenly else splits, "us": round(us, 2),
+            "kv_gb_s": round(nbytes / us / 1e3, 1)}
 
 
 def bench_attention_prefill(args) -> dict:
@@ -236,6 +244,8 @@ def main() -> int:
     parser.add_argument("--k", type=int, default=1024)
     parser.add_argument("--splits", type=int, default=0)
     parser.add_argument("--swiglu", action="store_true")
+    parser.add_argument("--dealt-evenly", action="store_true",
+                        help="attention_decode: the kernel that cuts the line of all sequences' pages into equal pieces")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=2048)
     parser.add_argument("--tokens", type=int, default=2048)
