@@ -286,6 +286,8 @@ __device__ __forceinline__ void write_columns(const GemmParams& p, uint32_t t_ro
     }
 }
 
+__host__ __device__ constexpr bool split_pushes(int bn) { return bn <= 64; }
+
 template <int BN, int STAGES>
 struct alignas(1024) GemmSmem {
     __nv_bfloat16 a[STAGES][BM * BK];
@@ -303,6 +305,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     GemmSmem<BN, STAGES>& sm =
         *reinterpret_cast<GemmSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;  // a power of two >= 32 (BN is 16, 32, 64, 128 or 256)
+    // with K split over a cluster, narrow tiles are summed from a region of their own behind the stages (present
+    // only in launches that split K), which the other blocks write into; wide tiles are fetched from the others' stages
+    constexpr bool PUSH = split_pushes(BN);
+    float* split_sums = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(&sm) + sizeof(GemmSmem<BN, STAGES>));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
     const int kb_begin = split * p.k_blocks_per_split;
@@ -404,21 +410,46 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         if (gridDim.z == 1) {
             write_columns(p, t_row, have_acc, row_a, a_ok, tile_b * BN, 0, BN, lane);
         } else {
-            // split-K: this block's partial tile goes to its own shared memory, [column][row] float32,
-            // over the pipeline stages (every copy has landed and every MMA has read them by now)
-            float* stage = reinterpret_cast<float*>(sm.a[0]);
             const int row_in_tile = quarter * 32 + lane;
+            if (PUSH) {
+                // split-K, narrow tiles: a row of this block's partial tile goes straight into the shared memory
+                // of the block that will sum that row (a region beside its pipeline stages, which its own MMAs may
+                // still be reading), as [source block][column][row of the owner's share] float32.  The stores are
+                // posted: nobody waits for a trip between SMs, as a block that fetched the others' tiles would.
+                const int n_ranks = gridDim.z, rows_per = BM / n_ranks;
+                const int owner = row_in_tile / rows_per, row_local = row_in_tile % rows_per;
+                const uint32_t mine = smem_u32(split_sums) + (uint32_t)((int)blockIdx.z * rows_per * BN + row_local) * 4u;
+                uint32_t dst;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(mine), "r"(owner));
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float v[16];
-                if (have_acc) {
-                    tmem_ld16(t_row + c0, v);
-                } else {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    if (have_acc) {
+                        tmem_ld16(t_row + c0, v);
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst + (uint32_t)((c0 + i) * rows_per) * 4u), "f"(v[i]) : "memory");
                 }
+            } else {
+                // split-K: this block's partial tile goes to its own shared memory, [column][row] float32,
+                // over the pipeline stages (every copy has landed and every MMA has read them by now)
+                float* stage = reinterpret_cast<float*>(sm.a[0]);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    if (have_acc) {
+                        tmem_ld16(t_row + c0, v);
+                    } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) stage[(c0 + i) * BM + row_in_tile] = v[i];
+                        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) stage[(c0 + i) * BM + row_in_tile] = v[i];
+                }
             }
         }
     }
@@ -436,6 +467,16 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             // block's partial tile (all issued before the first is used), added in the order of the
             // splits; two such groups are in flight per thread.
             auto load_parts = [&](int row, int col, float4 (&part)[8]) {
+                if (PUSH) {
+                    // the others have delivered: every block's share of these rows is in this block's own memory
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        part[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (r < n_ranks)
+                            part[r] = *reinterpret_cast<const float4*>(split_sums + r * rows_per * BN + col * rows_per + (row - rank * rows_per));
+                    }
+                    return;
+                }
                 const uint32_t local = stage_addr + (uint32_t)(col * BM + row) * 4u;
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
@@ -516,9 +557,11 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 }
             }
         }
-        // nobody leaves while its shared memory may still be read
-        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (!PUSH) {
+            // nobody leaves while its shared memory may still be read
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -1027,10 +1070,12 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     static_assert(STAGES * (BM + BN) * BK * 2 >= BM * BN * 4, "the partial tile must fit in the pipeline stages");
-    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+    constexpr size_t split_bytes = split_pushes(BN) ? (size_t)BM * BN * sizeof(float) : 0;
+    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024 + (grid.z > 1 ? split_bytes : 0);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)(sizeof(GemmSmem<BN, STAGES>) + 1024 + split_bytes));
         if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(err));
         configured = true;
     }
