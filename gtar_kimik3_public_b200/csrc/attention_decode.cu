@@ -48,13 +48,17 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = n_q / n_kv;
     pdl_launch_dependents();
-    // Lengths, slots and the page table are step inputs (copied in before the step's first kernel),
-    // and every page but the one holding the new token was written by earlier steps: all of that may
-    // be read while the kernel before this one (which writes the new token's key and value and the
-    // queries) is still running.
+    // Two trips to memory before the wait, not one after another for every item: the length, the slot and the norm
+    // weights first; then, from the length and the slot, the ids of the first pages and the rotation's row.
     const int len = kv_len[seq];
+    const int slot = slots[seq];
+    float w_q = 1.f, w_k = 1.f;  // thread c holds element c (a head has at most as many elements as the block threads)
+    if (fused.qkv && fused.use_norm && tid < D) {
+        w_q = weight_at(fused.wq, fused.weights_bf16, tid);
+        w_k = weight_at(fused.wk, fused.weights_bf16, tid);
+    }
     const int lo = (window > 0 && len - window > 0) ? len - window : 0;  // first visible key
-    const int* pages = block_table + (size_t)slots[seq] * max_pages;
+    const int* pages = block_table + (size_t)slot * max_pages;
     const int first_page = lo / PAGE, end_page = (len + PAGE - 1) / PAGE;
     const int per_split = (end_page - first_page + n_splits - 1) / n_splits;
     const int p_begin = first_page + split * per_split;
@@ -62,33 +66,51 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const int n_iter = max(p_end - p_begin, 0);
     const int new_page = (len - 1) / PAGE;
 
+    auto issue_page = [&](int it, int page) {
+        const int p = p_begin + it;
+        const int valid = min(PAGE, len - p * PAGE);
+        const size_t base = ((size_t)page * n_kv + hk) * PAGE * D;
+        const int stage = it % STAGES;
+        load_tile_async<D>(sm.k[stage], k_pages + base, D, PAGE, valid, tid, WARPS * 32);
+        load_tile_async<D>(sm.v[stage], v_pages + base, D, PAGE, valid, tid, WARPS * 32);
+    };
     auto issue = [&](int it) {
-        if (it < n_iter) {
-            const int p = p_begin + it;
-            const int page = pages[p];
-            const int valid = min(PAGE, len - p * PAGE);
-            const size_t base = ((size_t)page * n_kv + hk) * PAGE * D;
-            const int stage = it % STAGES;
-            load_tile_async<D>(sm.k[stage], k_pages + base, D, PAGE, valid, tid, WARPS * 32);
-            load_tile_async<D>(sm.v[stage], v_pages + base, D, PAGE, valid, tid, WARPS * 32);
-        }
+        if (it < n_iter) issue_page(it, pages[p_begin + it]);
         cp_async_commit();
     };
-    int early = 0;
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s)
-        if (early == s && s < n_iter && p_begin + s < new_page) {
-            issue(s);
-            early = s + 1;
+    // Lengths, slots and the page table are step inputs (copied in before the step's first kernel),
+    // and every page but the one holding the new token was written by earlier steps: all of that may
+    // be read while the kernel before this one (which writes the new token's key and value and the
+    // queries) is still running.
+    static_assert(STAGES == 3, "two pages are asked for ahead of the loop");
+    int early = 0, early_page0 = 0, early_page1 = 0;
+    if (0 < n_iter && p_begin < new_page) {
+        early_page0 = pages[p_begin];
+        early = 1;
+        if (1 < n_iter && p_begin + 1 < new_page) {
+            early_page1 = pages[p_begin + 1];
+            early = 2;
         }
-    if (fused.qkv) {
-        for (int c = tid; c < D; c += WARPS * 32) {
-            sm.wq[c] = fused.use_norm ? weight_at(fused.wq, fused.weights_bf16, c) : 1.f;
-            sm.wk[c] = fused.use_norm ? weight_at(fused.wk, fused.weights_bf16, c) : 1.f;
-            if (c < D / 2) {
-                sm.cos[c] = fused.cos_table ? fused.cos_table[(size_t)(len - 1) * (D / 2) + c] : 1.f;
-                sm.sin[c] = fused.cos_table ? fused.sin_table[(size_t)(len - 1) * (D / 2) + c] : 0.f;
-            }
+    }
+    float cs = 1.f, sn = 0.f;
+    if (fused.qkv && fused.cos_table && tid < D / 2) {
+        cs = fused.cos_table[(size_t)(len - 1) * (D / 2) + tid];
+        sn = fused.sin_table[(size_t)(len - 1) * (D / 2) + tid];
+    }
+    if (early > 0) {
+        issue_page(0, early_page0);
+        cp_async_commit();
+    }
+    if (early > 1) {
+        issue_page(1, early_page1);
+        cp_async_commit();
+    }
+    if (fused.qkv && tid < D) {
+        sm.wq[tid] = w_q;
+        sm.wk[tid] = w_k;
+        if (tid < D / 2) {
+            sm.cos[tid] = cs;
+            sm.sin[tid] = sn;
         }
     }
     pdl_wait();
