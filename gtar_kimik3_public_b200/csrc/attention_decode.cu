@@ -8,9 +8,9 @@
 // Grid (split, kv head, sequence).  A sequence's pages are divided among `n_splits` blocks so
 // that small batches still fill the GPU; each block streams its pages through a multi-stage
 // cp.async pipeline, its four warps taking 16 keys of a page each, and ends with an unnormalised
-// partial result (max, sum, output).  Up to eight splits form a thread-block cluster and are merged
-// by its first block through distributed shared memory; more splits leave their partial results in
-// scratch memory and a second kernel merges them.
+// partial result (max, sum, output).  Up to eight splits form a thread-block cluster: every block sends its
+// partial outputs into the shared memory of the block that merges them (each block merges a share); more
+// splits leave their partial results in scratch memory and a second kernel merges them.
 // Lengths come from device memory, so a captured launch stays valid as sequences grow.
 //
 // Softmax statistics and accumulators are 32-bit; probabilities are rounded to bfloat16 for
@@ -33,6 +33,11 @@ struct DecodeSmem {
     // what the fused input stage needs and no kernel of the step writes: the q and k norm weights and the
     // rotation of the new token's position, fetched while the kernel in front still runs
     float wq[D], wk[D], cos[D / 2], sin[D / 2];
+    // Where the other blocks of a cluster leave their partial results for the outputs that this block merges
+    // ([source block][this block's outputs]) and their maxima and sums ([source block][head of the group][2]): a
+    // region of its own, since they arrive while this block may still be streaming pages through the stages.
+    float from_o[16 * D + 8 * 32];
+    float from_ml[8 * 16 * 2];
 };
 
 template <int D>
@@ -318,8 +323,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         }
     }
     __syncthreads();
-    float* cl_o = red_ml + WARPS * 16 * 2;   // [group][D]   this block's result, for the cluster merge
-    float* cl_ml = cl_o + 16 * D;            // [group][2]
+    // With a cluster, outputs are dealt out in units of 32: unit u is merged by block u % n_splits, which holds
+    // room for cap = (units a block can have) * 32 values from every block.
+    const int units = (group * D + 31) / 32;
+    const int cap = ((units + n_splits - 1) / n_splits) * 32;
     for (int idx = tid; idx < group * D; idx += WARPS * 32) {
         const int r = idx / D, c = idx % D;
         float mm = -INFINITY;
@@ -338,10 +345,20 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         if (n_splits == 1) {
             out[((size_t)seq * n_q + hq) * D + c] = __float2bfloat16_rn(acc / ll);
         } else if (cluster_merge) {
-            cl_o[r * D + c] = acc;
+            // The splits of one (sequence, kv head) are one cluster: a block sends each of its partial outputs
+            // straight into the shared memory of the block that merges that output, and its maxima and sums to
+            // every block (posted stores: nobody fetches from another SM and waits), no scratch, no second kernel.
+            const int unit = idx >> 5, owner = unit % n_splits;
+            const uint32_t at = smem_u32(sm.from_o + split * cap + (unit / n_splits) * 32 + (idx & 31));
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(at), "r"(owner));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(acc) : "memory");
             if (c == 0) {
-                cl_ml[r * 2] = mm;
-                cl_ml[r * 2 + 1] = ll;
+                const uint32_t ml_at = smem_u32(sm.from_ml + (split * 16 + r) * 2);
+                for (int to = 0; to < n_splits; ++to) {
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(ml_at), "r"(to));
+                    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote), "f"(mm), "f"(ll) : "memory");
+                }
             }
         } else {
             const size_t at = ((size_t)seq * n_q + hq) * n_splits + split;
@@ -353,48 +370,38 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         }
     }
     if (n_splits > 1 && cluster_merge) {
-        // The splits of one (sequence, kv head) are one cluster: the partial results of all of them are
-        // merged through distributed shared memory, in split order; no scratch, no second kernel.
+        // everything sent has arrived once every block of the cluster is here
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-        {
-            // every block merges its own share of the group's outputs: elements split, split + n_splits, ...
-            // in units of 32 (a warp reads consecutive words of every block's result)
-            const uint32_t o_addr = smem_u32(cl_o), ml_addr = smem_u32(cl_ml);
-            for (int unit = split + warp * n_splits; unit * 32 < group * D; unit += WARPS * n_splits) {
-                const int idx = unit * 32 + lane;
-                if (idx >= group * D) break;
-                const int r = idx / D;
-                float ms[8], ls[8], os[8];
+        // every block merges its own share of the group's outputs, in split order, from its own shared memory
+        for (int unit = split + warp * n_splits; unit < units; unit += WARPS * n_splits) {
+            const int idx = unit * 32 + lane;
+            if (idx >= group * D) break;
+            const int r = idx / D;
+            float ms[8], ls[8], os[8];
 #pragma unroll
-                for (int sp = 0; sp < 8; ++sp) {
-                    ms[sp] = -INFINITY;
-                    ls[sp] = os[sp] = 0.f;
-                    if (sp < n_splits) {
-                        uint32_t ra, rb;
-                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(ml_addr + (uint32_t)r * 8u), "r"(sp));
-                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(o_addr + (uint32_t)idx * 4u), "r"(sp));
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ms[sp]) : "r"(ra) : "memory");
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ls[sp]) : "r"(ra + 4u) : "memory");
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(os[sp]) : "r"(rb) : "memory");
-                    }
+            for (int sp = 0; sp < 8; ++sp) {
+                ms[sp] = -INFINITY;
+                ls[sp] = os[sp] = 0.f;
+                if (sp < n_splits) {
+                    ms[sp] = sm.from_ml[(sp * 16 + r) * 2];
+                    ls[sp] = sm.from_ml[(sp * 16 + r) * 2 + 1];
+                    os[sp] = sm.from_o[sp * cap + (unit / n_splits) * 32 + lane];
                 }
-                float mm = -INFINITY;
-#pragma unroll
-                for (int sp = 0; sp < 8; ++sp) mm = fmaxf(mm, ms[sp]);
-                float ll = 0.f, acc = 0.f;
-#pragma unroll
-                for (int sp = 0; sp < 8; ++sp)
-                    if (sp < n_splits && ms[sp] != -INFINITY) {
-                        const float f = exp2f(ms[sp] - mm);
-                        ll += ls[sp] * f;
-                        acc += os[sp] * f;
-                    }
-                out[((size_t)seq * n_q + hk * group + r) * D + (idx % D)] = __float2bfloat16_rn(acc / ll);
             }
+            float mm = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) mm = fmaxf(mm, ms[sp]);
+            float ll = 0.f, acc = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp)
+                if (sp < n_splits && ms[sp] != -INFINITY) {
+                    const float f = exp2f(ms[sp] - mm);
+                    ll += ls[sp] * f;
+                    acc += os[sp] * f;
+                }
+            out[((size_t)seq * n_q + hk * group + r) * D + (idx % D)] = __float2bfloat16_rn(acc / ll);
         }
-        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
 }
 
@@ -424,7 +431,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
                   const int* kv_len, const int* slots, const int* block_table, int n_seqs, int n_q, int n_kv,
                   int max_pages, float scale, int window, int n_splits, cudaStream_t stream, const FusedQkv& fused) {
     const size_t stage_bytes = sizeof(DecodeSmem<D>);
-    const size_t merge_bytes = ((size_t)WARPS * 16 * (D + 2) + 16 * (D + 2)) * sizeof(float);
+    const size_t merge_bytes = (size_t)WARPS * 16 * (D + 2) * sizeof(float);
     const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
     static bool configured = false;  // per template instance; the attribute is per device function
     if (!configured) {
