@@ -327,6 +327,12 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     // room for cap = (units a block can have) * 32 values from every block.
     const int units = (group * D + 31) / 32;
     const int cap = ((units + n_splits - 1) / n_splits) * 32;
+    // unit / n_splits and unit % n_splits by shift and mask where the splits are a power of two (the host's choice
+    // always is): these sit in the kernel's tail, where a division's chain of instructions hides behind nothing
+    const bool pow2 = (n_splits & (n_splits - 1)) == 0;
+    const int split_shift = __ffs(n_splits) - 1;
+    auto unit_owner = [&](int unit) { return pow2 ? unit & (n_splits - 1) : unit % n_splits; };
+    auto unit_place = [&](int unit) { return pow2 ? unit >> split_shift : unit / n_splits; };
     for (int idx = tid; idx < group * D; idx += WARPS * 32) {
         const int r = idx / D, c = idx % D;
         float mm = -INFINITY;
@@ -348,8 +354,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
             // The splits of one (sequence, kv head) are one cluster: a block sends each of its partial outputs
             // straight into the shared memory of the block that merges that output, and its maxima and sums to
             // every block (posted stores: nobody fetches from another SM and waits), no scratch, no second kernel.
-            const int unit = idx >> 5, owner = unit % n_splits;
-            const uint32_t at = smem_u32(sm.from_o + split * cap + (unit / n_splits) * 32 + (idx & 31));
+            const int unit = idx >> 5, owner = unit_owner(unit);
+            const uint32_t at = smem_u32(sm.from_o + split * cap + unit_place(unit) * 32 + (idx & 31));
             uint32_t remote;
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(at), "r"(owner));
             asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(acc) : "memory");
@@ -386,7 +392,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
                 if (sp < n_splits) {
                     ms[sp] = sm.from_ml[(sp * 16 + r) * 2];
                     ls[sp] = sm.from_ml[(sp * 16 + r) * 2 + 1];
-                    os[sp] = sm.from_o[sp * cap + (unit / n_splits) * 32 + lane];
+                    os[sp] = sm.from_o[sp * cap + unit_place(unit) * 32 + lane];
                 }
             }
             float mm = -INFINITY;

@@ -417,7 +417,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 // still be reading), as [source block][column][row of the owner's share] float32.  The stores are
                 // posted: nobody waits for a trip between SMs, as a block that fetched the others' tiles would.
                 const int n_ranks = gridDim.z, rows_per = BM / n_ranks;
-                const int owner = row_in_tile / rows_per, row_local = row_in_tile % rows_per;
+                const int owner = row_in_tile >> (__ffs(rows_per) - 1), row_local = row_in_tile & (rows_per - 1);  // a power of two
                 const uint32_t mine = smem_u32(split_sums) + (uint32_t)((int)blockIdx.z * rows_per * BN + row_local) * 4u;
                 uint32_t dst;
                 asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(mine), "r"(owner));
@@ -504,25 +504,31 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 return acc;
             };
             char* out = reinterpret_cast<char*>(p.out);
-            const int quads = rows_per / 4, count = quads * BN;
+            // (a power of two: rows and columns by shift and mask, since a division is some two hundred cycles of
+            // dependent instructions for a warp that has its scheduler to itself)
+            const int quads = rows_per / 4, count = quads * BN, quads_shift = __ffs(quads) - 1;
             const bool swiglu = p.epilogue == EPI_SWIGLU_A;
             // 8-byte (plain, bfloat16) / 16-byte (plain, float32) / 4-byte (SwiGLU) stores need aligned rows
             const bool vec = p.stride_a == 1 && !swiglu && ((uintptr_t)out & 15) == 0 &&
                              (p.stride_b * (p.out_dtype == GK_F32 ? 4 : 2)) % 16 == 0;
+            // Thread e takes the group of four rows e % quads of the columns e / quads, e / quads + 128 / quads, ...:
+            // its rows, and what follows from them, are the same for all its columns.
             constexpr int U = 2;
-            for (int base = e; base < count; base += 128 * U) {
+            const int col_step = 128 >> quads_shift;  // may exceed a narrow tile's width: then some threads have no column
+            const int row = rank * rows_per + 4 * (e & (quads - 1)), row_a = tile_a * BM + row;
+            const int col0 = e >> quads_shift;
+            const bool rows_in = row_a < p.rows_a, four_in = row_a + 3 < p.rows_a;
+            (void)count;
+            for (int col = col0; col < BN; col += U * col_step) {
                 float4 part[U][8];
 #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int idx = base + u * 128;
-                    if (idx < count) load_parts(rank * rows_per + 4 * (idx % quads), idx / quads, part[u]);
-                }
+                for (int u = 0; u < U; ++u)
+                    if (col + u * col_step < BN) load_parts(row, col + u * col_step, part[u]);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int idx = base + u * 128;
-                    if (idx >= count) continue;
-                    const int row_a = tile_a * BM + rank * rows_per + 4 * (idx % quads), rb = tile_b * BN + idx / quads;
-                    if (row_a >= p.rows_a || rb >= p.rows_b) continue;
+                    if (col + u * col_step >= BN) continue;
+                    const int rb = tile_b * BN + col + u * col_step;
+                    if (!rows_in || rb >= p.rows_b) continue;
                     const float4 v = add_up(part[u]);
                     const float vs[4] = {v.x, v.y, v.z, v.w};
                     if (swiglu) {
@@ -533,7 +539,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                                 store_out<__nv_bfloat16>(out, at, silu(vs[i]) * vs[i + 1]);
                             }
                         }
-                    } else if (vec && row_a + 3 < p.rows_a) {
+                    } else if (vec && four_in) {
                         const long long at = (long long)row_a + (long long)rb * p.stride_b;
                         if (p.out_dtype == GK_F32) {
                             *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at) = v;
