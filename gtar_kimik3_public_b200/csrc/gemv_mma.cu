@@ -107,10 +107,10 @@ __global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS ==
 
     // The weights of items first .. first + round_items - 1 (item = group of the block * cpw + chunk of the warp),
     // on their way to shared memory.
-    auto request = [&](int first) {
+    auto request_into = [&](int first, int count, uint4* dst) {
         int g = first / cpw, j = first % cpw;
-        uint4* dst = pieces + threadIdx.x;
-        for (int item = first; item < first + round_items && item < n_items; ++item) {
+        dst += threadIdx.x;
+        for (int item = first; item < first + count && item < n_items; ++item) {
             const int row = ((int)blockIdx.x + g * (int)gridDim.x) * ROWS + group;
             const int k = (warp + j * WARPS) * CHUNK + piece * 8;
             const bool in = row < p.n && k < p.k;
@@ -123,6 +123,10 @@ __global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS ==
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    // A block whose share exceeds shared memory takes it in rounds of half the space: two rounds are on their way
+    // while a third is multiplied (a thread reads only the pieces it asked for itself, so it may ask for the round
+    // after next into the half it has just finished with, without a barrier).
+    const int half_items = round_items / 2;
 
     // With the residual output stage, the stream's old values of the outputs this thread will write (warp g of the
     // block finishes the block's g-th group) are asked for as soon as the kernel in front has finished, long before
@@ -188,7 +192,13 @@ __global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS ==
         }
     };
 
-    request(0);  // before the kernel in front has finished
+    // before the kernel in front has finished
+    if (one_round) {
+        request_into(0, round_items, pieces);
+    } else {
+        request_into(0, half_items, pieces);
+        request_into(half_items, half_items, pieces + (size_t)half_items * THREADS);
+    }
     // NORM: this thread's pieces of the norm's weights (the same for every token), also before the wait
     float nw[NORM ? XR : 1][8];
     if (NORM) {
@@ -367,16 +377,18 @@ __global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS ==
                 make_float4(acc0[0] + acc1[0], acc0[1] + acc1[1], acc0[2] + acc1[2], acc0[3] + acc1[3]);
         }
     } else {
-        // a block's share exceeds shared memory: the weights come in rounds
-        int in_round = 0;
+        // a block's share exceeds shared memory: the weights come in rounds of half the space
+        int in_round = half_items, round = -1;
         for (int g = 0; g < my_groups; ++g) {
             float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
             const unsigned char* xa_at = xa_first;
             for (int j = 0; j < cpw; ++j) {
-                if (in_round == round_items) {
-                    request(g * cpw + j);
-                    asm volatile("cp.async.wait_group 0;" ::: "memory");
-                    wp = pieces + threadIdx.x;
+                if (in_round == half_items) {
+                    ++round;
+                    // the half just finished with takes the round after next (rounds 0 and 1 were asked for above)
+                    if (round >= 1) request_into((round + 1) * half_items, half_items, pieces + (size_t)((round + 1) & 1) * half_items * THREADS);
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the newest: this round's pieces are here
+                    wp = pieces + (size_t)(round & 1) * half_items * THREADS + threadIdx.x;
                     in_round = 0;
                 }
                 chunk(*wp, xa_at, acc0, acc1);
@@ -447,6 +459,11 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
         GK_REQUIRE(fixed + THREADS * 16 <= SMEM_MAX, "gemv: k = %d with %d tokens needs %zu bytes of shared memory for the activations alone, more than %zu",
                    p.k, p.tokens, fixed, SMEM_MAX);
         round_items = (int)((SMEM_MAX - fixed) / (THREADS * 16));
+    }
+    if (items > round_items) {
+        // in rounds anyway: as many pieces on their way as the block's shared memory holds
+        const int most = (int)((SMEM_MAX - x_bytes - partial_bytes) / (THREADS * 16));
+        round_items = items < most ? items : most;
     }
     const size_t smem = (size_t)round_items * THREADS * 16 + x_bytes + (items > round_items ? partial_bytes : 0);
     if (p.norm_h) {
