@@ -18,9 +18,10 @@
 //   * attention_prefill_tc2_kernel, the default: 128 keys (two pages) a step, one block per SM with all 512
 //     tensor-memory columns (two score buffers, so the MMA warp forms the next scores while the softmax works on
 //     these; P; O), keys and values through TMA in rings of their own (three and two stages: the keys of a step
-//     are wanted a step before its values), eight softmax warps with two threads a row, and two query tiles per
-//     block, the c-th from the end and then the c-th from the start, so that under the causal mask every block
-//     has the same work.  Its own comment further down has the details.
+//     are wanted a step before its values), eight softmax warps with two threads a row, and a query tile a
+//     block, the tiles with the most keys first in the grid (the SMs take blocks in the order of their index, so
+//     the light tiles fill what the heavy ones leave); or, selectable, two query tiles per block, the c-th from
+//     the end and then the c-th from the start.  Its own comment further down has the details.
 //   * attention_prefill_tc_kernel: 64 keys a step, one query tile per block, four softmax warps (thread = row),
 //     two blocks per SM (256 tensor-memory columns and 97 KB of shared memory each), so that one block's softmax
 //     overlaps the other's products.  Kept selectable (gk_set_attention_prefill_keys(64)); it is the slower of the
@@ -175,6 +176,7 @@ struct Params {
     float sl2;
     int window;
     int* error_flag;
+    int one_tile;  // tc2: a query tile a block, heaviest first (grid: kv head, sequence, tile), instead of a heavy and a light one
 };
 
 __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
@@ -434,8 +436,8 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const 
 // MMA warp forms the next scores while the softmax warps work on these; P (64 columns) and O (128) beside
 // them.  Eight softmax warps, two threads a row (the exponentials are what a step waits for longest).  A step of 128 keys costs as many tcgen05.mma as a step of 64 (an instruction costs about 84 cycles
 // whether its N is 64 or 128), and the chain of dependent steps of a query tile is half as long.  A block
-// takes two query tiles one after the other, the c-th from the end and the c-th from the start: under the
-// causal mask their work adds up to the same for every block, so one wave of blocks ends together.
+// takes one query tile (the default; heaviest tiles first in the grid) or two one after the other, the c-th from
+// the end and the c-th from the start: under the causal mask their work adds up to the same for every block.
 constexpr int KEYS2 = 2 * PAGE;
 constexpr int K_STAGES2 = 3;
 constexpr uint32_t COL2_S = 0, COL2_P = 256, COL2_O = 320;  // S: 2 x 128, P: 64 (bf16 pairs), O: 128
@@ -464,15 +466,21 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
     extern __shared__ unsigned char smem_raw[];
     Smem2& sm = *reinterpret_cast<Smem2*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int seq = blockIdx.z, hk = blockIdx.y;
+    // Two ways of dealing out the query tiles.  Pairs (grid: pair, kv head, sequence): a block takes the c-th tile
+    // from the end and the c-th from the start, equal work for every block, right where all blocks run at once.
+    // One tile a block (grid: kv head, sequence, tile from the end): blocks are handed to the SMs in the order of
+    // their index, so the heaviest tiles start first and the light ones fill what is left, which wastes less than
+    // whole waves of equal pairs do where there are several blocks an SM.
+    const int seq = p.one_tile ? blockIdx.y : blockIdx.z, hk = p.one_tile ? blockIdx.x : blockIdx.y;
+    const int first = p.one_tile ? blockIdx.z : blockIdx.x;
     const int group = p.n_q / p.n_kv;
     const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
     const int n_rows = q_len * group;
     const int n_blocks = (n_rows + ROWS - 1) / ROWS;
-    if (2 * (int)blockIdx.x >= n_blocks) return;  // whole block, before any barrier or allocation
+    if ((p.one_tile ? first : 2 * first) >= n_blocks) return;  // whole block, before any barrier or allocation
     // the block's query tiles: the heavy one first
-    const int tile_of[2] = {n_blocks - 1 - (int)blockIdx.x, (int)blockIdx.x};
-    const int n_tiles = tile_of[0] > tile_of[1] ? 2 : 1;
+    const int tile_of[2] = {n_blocks - 1 - first, p.one_tile ? -1 : first};
+    const int n_tiles = tile_of[0] > tile_of[1] && !p.one_tile ? 2 : 1;
     const int len = p.kv_len[seq], past = len - q_len;
     const int* pages = p.block_table + (size_t)p.slots[seq] * p.max_pages;
     // pages [p_begin, p_end) of query tile u, in steps of two
@@ -838,6 +846,7 @@ int make_page_map(CUtensorMap* map, const void* base, long long rows) {
 }
 
 int g_attention_prefill_keys = KEYS2;  // 128 (the default) or 64
+int g_attention_prefill_one_tile = 1;  // with 128 keys a step: 1 (the default) a query tile a block, heaviest first; 0 a heavy and a light tile a block
 
 }  // namespace
 
@@ -880,6 +889,7 @@ GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     p.sl2 = scale * 1.4426950408889634f;
     p.window = window;
     p.error_flag = error_flag;
+    p.one_tile = 0;
     const int group = n_q / n_kv;
     const long long blocks = ((long long)max_q_len * group + ROWS - 1) / ROWS;
     GK_REQUIRE(blocks <= 2147483647LL, "attention_prefill_tc: too many rows");
@@ -892,7 +902,11 @@ GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
             if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: %s", cudaGetErrorString(err));
             configured2 = true;
         }
+        // measured for one prompt, a tile a block against pairs: 35.7 against 38.8 us at 2,048 tokens, 104 against 120 at
+        // 4,096, 332 against 375 at 8,192, 1,170 against 1,186 at 16,384
+        p.one_tile = g_attention_prefill_one_tile && blocks <= 65535;
         dim3 grid2((unsigned)((blocks + 1) / 2), n_kv, n_seqs);
+        if (p.one_tile) grid2 = dim3(n_kv, n_seqs, (unsigned)blocks);
         gk_launch(attention_prefill_tc2_kernel, grid2, dim3(THREADS2), smem2, (cudaStream_t)stream, mk, mv, p);
         GK_CHECK_LAUNCH("attention_prefill_tc2");
         return GK_OK;
@@ -905,6 +919,14 @@ GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
 
 // Keys per step of the tcgen05 prefill attention: 128 (the default: one block per SM, two score buffers, eight
 // softmax warps, pairs of query tiles) or 64 (two blocks per SM, one query tile each).  Returns the old setting.
+// With 128 keys a step: 1 (the default) = a query tile a block with the heaviest first, 0 = a heavy and a light query
+// tile a block.  Returns the old setting.
+GK_EXPORT int gk_set_attention_prefill_one_tile(int mode) {
+    const int before = g_attention_prefill_one_tile;
+    g_attention_prefill_one_tile = mode ? 1 : 0;
+    return before;
+}
+
 GK_EXPORT int gk_set_attention_prefill_keys(int keys) {
     const int before = g_attention_prefill_keys;
     g_attention_prefill_keys = keys == PAGE ? PAGE : KEYS2;

@@ -857,6 +857,14 @@ def set_attention_prefill_keys(keys: int) -> int:
     return int(library().gk_set_attention_prefill_keys(int(keys)))
 
 
+def set_attention_prefill_one_tile(mode: int) -> int:
+    """How the tcgen05 prefill attention (128 keys a step) deals out its query tiles: 1 (the default) = a tile a
+    block with the heaviest first, 0 = a heavy and a light tile a block.  Returns the old setting."""
+    from .library import library
+
+    return int(library().gk_set_attention_prefill_one_tile(int(mode)))
+
+
 def row_parts(n_rows: int, vocab: int, device: torch.device) -> int:
     """Blocks that share a row of logits in the token choice: about eight blocks per multiprocessor in all, slices
     of at least 4,096 entries, at most 64 a row."""

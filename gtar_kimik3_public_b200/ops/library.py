@@ -46,6 +46,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_attention_decode_resident_clusters": [I, I],
     "gk_set_gemm_pairs": [I],
     "gk_set_attention_prefill_keys": [I],
+    "gk_set_attention_prefill_one_tile": [I],
     "gk_attention_decode_fused_bf16": [P, P, P, I, I, F, P, P, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_decode_flat_bf16": [P, P, P, P, I, I, F, P, P, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_decode_flat_resident_blocks": [I],
