@@ -55,6 +55,8 @@ class DecodeWork:
     counter per (sequence, kv head), zero between launches (the kernel sets back what it counts up).  Buffers that
     are outgrown stay alive: a captured graph may still name them."""
 
+    MIN_FLOATS, MIN_PAIRS = 1 << 18, 1024  # the least that is asked of the allocator, so that growth is rare
+
     def __init__(self, device: torch.device):
         self.device = device
         self.part: torch.Tensor | None = None
@@ -65,11 +67,11 @@ class DecodeWork:
         if self.part is None or self.part.numel() < n_floats:
             if self.part is not None:
                 self.outgrown.append(self.part)
-            self.part = torch.empty((max(n_floats, 1 << 18),), dtype=torch.float32, device=self.device)
+            self.part = torch.empty((max(n_floats, self.MIN_FLOATS),), dtype=torch.float32, device=self.device)
         if self.tickets is None or self.tickets.numel() < n_pairs:
             if self.tickets is not None:
                 self.outgrown.append(self.tickets)
-            self.tickets = torch.zeros((max(n_pairs, 1024),), dtype=torch.int32, device=self.device)
+            self.tickets = torch.zeros((max(n_pairs, self.MIN_PAIRS),), dtype=torch.int32, device=self.device)
         return self.part, self.tickets
 
 

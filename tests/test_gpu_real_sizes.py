@@ -170,6 +170,48 @@ def test_decode_steps_with_the_pages_dealt_evenly(tag, n_requests, kernel_log, m
     assert "gk_attention_decode_fused_bf16" not in kernel_log and "gk_attention_decode_bf16" not in kernel_log
 
 
+def test_decode_work_outgrown_by_a_larger_batch_stays_valid_for_captured_steps(monkeypatch):
+    """The scratch and the ticket counters of the evenly dealt decode attention belong to the cache group and grow with
+    the batch; the captured steps of a smaller batch keep the buffers they were captured with.  Twelve sequences, then
+    forty (the buffers grow), then twelve again in the slots given back: all against the plain implementation."""
+    from gtar_kimik3_public_b200.ops import attention as attention_ops
+
+    from gtar_kimik3_public_b200.ops.functional import DecodeWork
+
+    monkeypatch.setattr(attention_ops, "DECODE_FLAT", "always")
+    monkeypatch.setattr(DecodeWork, "MIN_FLOATS", 1)
+    monkeypatch.setattr(DecodeWork, "MIN_PAIRS", 1)
+    tag, dtype = "tiny_c", "bfloat16"
+    engine = load_engine(tag, dtype, max_tokens=40 * 128, max_seqs=40)
+    poison(engine)
+    work = None
+    for turn, n_requests in enumerate((12, 40, 12)):
+        lengths = [5 + (7 * i + turn) % 60 for i in range(n_requests)]
+        requests = requests_for(tag, lengths, seed=70 + turn)
+        batch = [f"{turn}.{i}" for i in range(n_requests)]
+        head = {r: len(t) - 3 for r, t in zip(batch, requests)}
+        tokens = dict(zip(batch, requests))
+        engine.step([_entry(r, tokens[r][:head[r]], []) for r in batch])
+        rows = {r: [] for r in batch}
+        for k in range(3):
+            logits = engine.step([_entry(r, [tokens[r][head[r] + k]], [0]) for r in batch])
+            for i, r in enumerate(batch):
+                rows[r].append(logits[i:i + 1])
+        engine.end(batch)
+        for r in batch:
+            check_against_plain(tag, dtype, tokens[r], list(range(head[r], head[r] + 3)), torch.cat(rows[r]), f"turn {turn} request {r}")
+        group = engine.cache.kv_groups[0]
+        if turn == 0:
+            work = group._work
+            first_part, first_tickets = work.part, work.tickets
+        assert int(group._work.tickets.abs().sum()) == 0
+    assert work is engine.cache.kv_groups[0]._work
+    assert work.part is not first_part and work.tickets is not first_tickets  # forty sequences outgrew twelve's buffers
+    assert any(t is first_part for t in work.outgrown) and int(first_tickets.abs().sum()) == 0
+    engine.check()
+    assert engine.cache.slots.n_used == 0
+
+
 def _decode_many(tag, dtype, n_requests, kernel_log, expect):
     lengths = [6 + (11 * i) % 90 for i in range(n_requests)]
     requests = requests_for(tag, lengths, seed=43)
