@@ -592,11 +592,12 @@ def decode_flat_wins(n_seqs: int, n_kv: int, kv_len: int, page_size: int, sm_cou
 
     The evenly dealt kernel costs some 7 us more than the equal cut where that fits the device (partial results
     through scratch, a ticket per part, a merge by whoever comes last), so it is chosen where the equal cut fits
-    badly: where its blocks fill less than 70% of the places they could have (and a block would still have 16
+    badly: where its blocks fill less than two thirds of the places they could have (and a block would still have 16
     pages and more to stream), or where they come in waves of which the last is thin.  Measured, 28 layers of the
     0.6B sizes, contexts of 2,048, ms a step with the equal cut against dealt evenly: 20 sequences 1.96 / 1.79,
     24: 1.96 / 1.91, 40: 3.28 / 2.77, 48: 3.34 / 3.13, 56: 3.60 / 3.42; but 8: 0.90 / 1.11, 16: 1.35 / 1.53,
-    32: 2.05 / 2.24, 64: 3.64 / 3.65."""
+    32: 2.05 / 2.24, 64: 3.64 / 3.65; with contexts of 8,192: 12 sequences 2.95 / 2.60, 20: 4.47 / 3.80, 40: 7.35 / 6.78, but
+    6 (48 pairs cut in four fill 68% of the places for clusters of four): 1.67 / 1.73."""
     splits = decode_splits(n_seqs, n_kv, kv_len, page_size, sm_count, cluster_places)
     if splits > 8:
         return False
@@ -608,7 +609,7 @@ def decode_flat_wins(n_seqs: int, n_kv: int, kv_len: int, page_size: int, sm_cou
     waves = -(-pairs // at_once)
     fill = pairs / (waves * at_once)
     if waves == 1:
-        return fill < 0.70 and pairs * pages >= 16 * flat_places
+        return fill < 0.66 and pairs * pages >= 16 * flat_places
     return waves >= 3 or fill < 0.86
 
 
