@@ -74,3 +74,20 @@ def test_twenty_four_sequences_are_not_cut():
     places = (296, 148, 71, 33)
     assert decode_splits(24, 8, 2560, 64, 148, places) == 1
     assert decode_splits(24, 8, 3584, 64, 148, places) == 1
+
+
+def test_the_even_deal_where_the_equal_cut_fits_badly():
+    """Measured (28 layers of the 0.6B sizes, ms a step, equal cut / dealt evenly): contexts of 2,048: 20 sequences 1.96 /
+    1.79, 24: 1.96 / 1.91, 40: 3.28 / 2.77, 48: 3.34 / 3.13, 56: 3.60 / 3.42, but 8: 0.90 / 1.11, 16: 1.35 / 1.53, 32: 2.05 /
+    2.24, 64: 3.64 / 3.65; contexts of 8,192: 12: 2.95 / 2.60, 20: 4.47 / 3.80, but 6: 1.67 / 1.73."""
+    from gtar_kimik3_public_b200.ops.functional import decode_flat_wins
+
+    places = (296, 148, 71, 33)
+    evenly = {b: decode_flat_wins(b, 8, 2560, 64, 148, places, 296) for b in (1, 8, 16, 20, 24, 32, 40, 48, 56, 64)}
+    assert evenly == {1: False, 8: False, 16: False, 20: True, 24: True, 32: False, 40: True, 48: True, 56: True, 64: False}
+    assert decode_flat_wins(12, 8, 7168, 64, 148, places, 296) and decode_flat_wins(20, 8, 7168, 64, 148, places, 296)
+    assert not decode_flat_wins(6, 8, 7168, 64, 148, places, 296)
+    # few pages a block: the parts, tickets and merges of the even deal cost more than it saves
+    assert not decode_flat_wins(20, 8, 512, 64, 148, places, 296)
+    # more than eight splits go through scratch and a second kernel: not this kernel's case
+    assert not decode_flat_wins(1, 8, 40000, 64, 148, places, 296)
