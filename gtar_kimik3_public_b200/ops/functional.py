@@ -608,8 +608,16 @@ def decode_flat_wins(n_seqs: int, n_kv: int, kv_len: int, page_size: int, sm_cou
     at_once = max(1, dict(zip((1, 2, 4, 8), cluster_places))[splits])
     waves = -(-pairs // at_once)
     fill = pairs / (waves * at_once)
+    per_block = pairs * pages / flat_places  # pages a block streams when they are dealt evenly
     if waves == 1:
-        return fill < 0.66 and pairs * pages >= 16 * flat_places
+        if splits == 8 and pairs * 8 > sm_count:
+            # clusters of eight that share SMs stream long contexts badly (16,400 tokens: 4 sequences 2.43 / 2.09 ms,
+            # 32,800: 3 sequences 3.11 / 2.61, 4: 3.99 / 3.18; but 8,200: 3 sequences 1.13 / 1.30, 16,400: 3: 1.71 / 1.84)
+            # (the more of the SMs hold two blocks, the sooner: 8,200 tokens, 4 sequences: 1.56 / 1.45)
+            return per_block >= (16 if pairs * 8 > 1.5 * sm_count else 30)
+        if splits >= 4 and fill < 0.80 and per_block >= 30:
+            return True  # (16,384 tokens, 6 sequences cut in four: 3.03 / 2.72)
+        return fill < 0.66 and per_block >= 16
     return waves >= 3 or fill < 0.86
 
 

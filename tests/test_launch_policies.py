@@ -91,3 +91,19 @@ def test_the_even_deal_where_the_equal_cut_fits_badly():
     assert not decode_flat_wins(20, 8, 512, 64, 148, places, 296)
     # more than eight splits go through scratch and a second kernel: not this kernel's case
     assert not decode_flat_wins(1, 8, 40000, 64, 148, places, 296)
+
+
+def test_the_even_deal_for_a_few_long_sequences():
+    """Clusters of eight that share SMs stream long contexts badly (ms a step, equal cut / dealt evenly: 16,400 tokens,
+    4 sequences 2.43 / 2.09, 6: 3.03 / 2.72; 32,800 tokens, 3: 3.11 / 2.61, 4: 3.99 / 3.18), but one and two sequences
+    (all their blocks have an SM each) and shorter contexts stay with the equal cut (8,200 tokens, 3: 1.13 / 1.30; 16,400
+    tokens, 3: 1.71 / 1.84).  The lengths below are the middles of the bounds that captured steps of those contexts get."""
+    from gtar_kimik3_public_b200.ops.functional import decode_flat_wins
+
+    places = (296, 148, 71, 33)
+    assert decode_flat_wins(4, 8, 20480, 64, 148, places, 296) and decode_flat_wins(6, 8, 20480, 64, 148, places, 296)
+    assert decode_flat_wins(3, 8, 36864, 64, 148, places, 296) and decode_flat_wins(4, 8, 36864, 64, 148, places, 296)
+    assert not decode_flat_wins(3, 8, 10240, 64, 148, places, 296) and not decode_flat_wins(3, 8, 20480, 64, 148, places, 296)
+    assert decode_flat_wins(4, 8, 10240, 64, 148, places, 296) and not decode_flat_wins(4, 8, 5120, 64, 148, places, 296)
+    for length in (10240, 20480, 36864):
+        assert not decode_flat_wins(1, 8, length, 64, 148, places, 296) and not decode_flat_wins(2, 8, length, 64, 148, places, 296)
