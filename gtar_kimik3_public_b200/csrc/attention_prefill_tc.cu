@@ -474,6 +474,11 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
     const int seq = p.one_tile ? blockIdx.y : blockIdx.z, hk = p.one_tile ? blockIdx.x : blockIdx.y;
     const int first = p.one_tile ? blockIdx.z : blockIdx.x;
     const int group = p.n_q / p.n_kv;
+    // row / group and row % group by shift and mask where the group is a power of two (a division is some two hundred
+    // cycles of dependent instructions, and a tile's queries and results each cost a thread four of them)
+    const int group_shift = (group & (group - 1)) == 0 ? __ffs(group) - 1 : -1;
+    auto over_group = [&](int x) { return group_shift >= 0 ? x >> group_shift : x / group; };
+    auto in_group = [&](int x) { return group_shift >= 0 ? x & (group - 1) : x % group; };
     const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
     const int n_rows = q_len * group;
     const int n_blocks = (n_rows + ROWS - 1) / ROWS;
@@ -487,7 +492,7 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
     auto span = [&](int u, int& p_begin, int& p_end) {
         const int row0 = tile_of[u] * ROWS;
         const int last_row = min(row0 + ROWS, n_rows) - 1;
-        const int max_pos = past + last_row / group, min_pos = past + row0 / group;
+        const int max_pos = past + over_group(last_row), min_pos = past + over_group(row0);
         const int lo = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
         p_begin = lo / PAGE;
         p_end = max_pos / PAGE + 1;
@@ -652,7 +657,7 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
             const int n_iter = (p_end - p_begin + 1) / 2;
             const int row = tile_of[u] * ROWS + r;
             const bool row_ok = row < n_rows;
-            const int tok = row_ok ? row / group : 0;
+            const int tok = row_ok ? over_group(row) : 0;
             const int pos = past + tok;
             // Where this warp's half of the row `rr` of the tile lies in the queries or the output (null: no such row).
             // The four lanes of a quad work on the rows of the quad together, 32 bytes of a row's 128 each, so that
@@ -661,7 +666,7 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
             auto row_at = [&](__nv_bfloat16* base, int rr) -> __nv_bfloat16* {
                 const int row_i = tile_of[u] * ROWS + rr;
                 if (row_i >= n_rows) return nullptr;
-                return base + ((size_t)(q_begin + row_i / group) * p.n_q + hk * group + row_i % group) * D + half * 64 + piece * 16;
+                return base + ((size_t)(q_begin + over_group(row_i)) * p.n_q + hk * group + in_group(row_i)) * D + half * 64 + piece * 16;
             };
             // this warp's halves of its Q rows -> swizzled shared memory (zeros for rows beyond the sequence); the
             // MMAs that read the tile before have finished (its last o_done was waited for below)
