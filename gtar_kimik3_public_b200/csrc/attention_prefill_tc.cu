@@ -498,6 +498,39 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
         p_end = max_pos / PAGE + 1;
     };
 
+    // A softmax warp's halves of a tile's Q rows -> swizzled shared memory (zeros for rows beyond the sequence).  The four
+    // lanes of a quad work on the rows of the quad together, 32 bytes of a row's 128 each, so that a load or store of
+    // the warp touches eight whole lines instead of 32 partly.  (`half`: which 64 of the head's 128 elements.)
+    auto query_row = [&](__nv_bfloat16* base, int tile, int rr, int half_of_head) -> __nv_bfloat16* {
+        const int row_i = tile * ROWS + rr;
+        if (row_i >= n_rows) return nullptr;
+        return base + ((size_t)(q_begin + over_group(row_i)) * p.n_q + hk * group + in_group(row_i)) * D + half_of_head * 64 + (lane & 3) * 16;
+    };
+    auto load_queries = [&](int tile) {
+        const int quad_row = (warp & 3) * 32 + (lane & ~3), piece = lane & 3, half_of_head = (warp - 2) >> 2;
+        uint32_t val[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // all four loads on their way before the first is used
+            const __nv_bfloat16* src = query_row(const_cast<__nv_bfloat16*>(p.q), tile, quad_row + i, half_of_head);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) val[i][j] = 0u;
+            if (src) load32(src, val[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int rr = quad_row + i;
+            uint4* dst = reinterpret_cast<uint4*>(sm.q[half_of_head]) + rr * 8;
+            dst[(2 * piece) ^ (rr & 7)] = make_uint4(val[i][0], val[i][1], val[i][2], val[i][3]);
+            dst[(2 * piece + 1) ^ (rr & 7)] = make_uint4(val[i][4], val[i][5], val[i][6], val[i][7]);
+        }
+        fence_async_smem();
+    };
+    // The block's first tile of queries comes in while thread 0 sets up the barriers and warp 1 the tensor memory.
+    if (warp >= 2 && warp < 10) {
+        pdl_wait();  // queries come from the kernel before
+        load_queries(tile_of[0]);
+    }
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < K_STAGES2; ++s) {
             mbar_init(&sm.k_full[s], 1);
@@ -659,36 +692,12 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
             const bool row_ok = row < n_rows;
             const int tok = row_ok ? over_group(row) : 0;
             const int pos = past + tok;
-            // Where this warp's half of the row `rr` of the tile lies in the queries or the output (null: no such row).
-            // The four lanes of a quad work on the rows of the quad together, 32 bytes of a row's 128 each, so that
-            // a load or store of the warp touches eight whole lines instead of 32 partly.
-            const int quad_row = quarter * 32 + (lane & ~3), piece = lane & 3;
-            auto row_at = [&](__nv_bfloat16* base, int rr) -> __nv_bfloat16* {
-                const int row_i = tile_of[u] * ROWS + rr;
-                if (row_i >= n_rows) return nullptr;
-                return base + ((size_t)(q_begin + over_group(row_i)) * p.n_q + hk * group + in_group(row_i)) * D + half * 64 + piece * 16;
-            };
-            // this warp's halves of its Q rows -> swizzled shared memory (zeros for rows beyond the sequence); the
-            // MMAs that read the tile before have finished (its last o_done was waited for below)
-            {
-                uint32_t val[4][8];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {  // all four loads on their way before the first is used
-                    const __nv_bfloat16* src = row_at(const_cast<__nv_bfloat16*>(p.q), quad_row + i);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) val[i][j] = 0u;
-                    if (src) load32(src, val[i]);
-                }
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int rr = quad_row + i;
-                    uint4* dst = reinterpret_cast<uint4*>(sm.q[half]) + rr * 8;
-                    dst[(2 * piece) ^ (rr & 7)] = make_uint4(val[i][0], val[i][1], val[i][2], val[i][3]);
-                    dst[(2 * piece + 1) ^ (rr & 7)] = make_uint4(val[i][4], val[i][5], val[i][6], val[i][7]);
-                }
-                fence_async_smem();
-                mbar_arrive(&sm.q_ready);
-            }
+            const int quad_row = quarter * 32 + (lane & ~3);
+            auto row_at = [&](__nv_bfloat16* base, int rr) -> __nv_bfloat16* { return query_row(base, tile_of[u], rr, half); };
+            // the block's first tile is in shared memory already; a later one may come in now that the MMAs that read
+            // the tile before have finished (its last o_done was waited for below)
+            if (u > 0) load_queries(tile_of[u]);
+            mbar_arrive(&sm.q_ready);
             float m_used = -INFINITY, l = 0.f;
             for (int i = 0; i < n_iter && ok; ++i, ++g) {
                 const int s = g % KV_STAGES, b = g & 1;
