@@ -177,6 +177,7 @@ struct Params {
     int window;
     int* error_flag;
     int one_tile;  // tc2: a query tile a block, heaviest first (grid: kv head, sequence, tile), instead of a heavy and a light one
+    int n_seqs, n_items;  // tc5: the list of tiles is n_items long: (tile counted from the end, sequence, kv head)
 };
 
 __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
@@ -828,6 +829,382 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
     }
 }
 
+// ---------------------------------------------------------------- the same, with blocks that stay
+// The kernel above, but a block per SM that stays and takes query tiles from the launch's list one after another (the
+// list: tile counted from the end, then sequence, then kv head, so the heaviest tiles come first; block b of G takes
+// entries b, 2G - 1 - b, 2G + b, ...: back and forth, so that every block gets heavy and light ones).  What a tile
+// costs beside its steps (set-up of barriers and tensor memory, queries in, first scores, the next block's start:
+// 3.8 us of 5.3 at 2,048 tokens) then falls under the steps of the tile before: the queries of the next tile come by
+// TMA (a 3-D map over [token, head, 128]: a box of 128 / group tokens x group heads x 64 elements is a tile's 128 rows
+// in the order the rows have) as soon as the last scores of the tile in hand are formed, and its first scores are
+// formed while the softmax warps still write out the result.  Needs a group size that divides 128.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+
+struct alignas(1024) Smem5 {
+    __nv_bfloat16 q[2][ROWS * 64];
+    __nv_bfloat16 k[K_STAGES2][2][2][PAGE * 64];
+    __nv_bfloat16 v[KV_STAGES][2][2][PAGE * 64];
+    uint64_t k_full[K_STAGES2], k_empty[K_STAGES2], v_full[KV_STAGES], v_empty[KV_STAGES];
+    uint64_t s_full[2], s_empty[2], p_full, o_done;
+    uint64_t q_full, q_empty, o_free;     // a tile's queries have landed / its last scores are formed / its result is read
+    uint64_t max_ready[2][4], sum_ready;
+    float row_max[2][2][ROWS];
+    float row_sum[2][ROWS];
+    uint32_t tmem_base;
+};
+
+struct Tile {
+    int seq, hk, tile;         // the tile-th 128 rows of (sequence, kv head)
+    int q_begin, n_rows, len, past;
+    const int* pages;
+    int p_begin, p_end;        // its pages, taken in steps of two
+};
+
+// Entry `item` of the launch's list; false if the sequence has no such tile.
+__device__ __forceinline__ bool tile_of_item(const Params& p, int item, int group, Tile& t) {
+    const int per = p.n_kv * p.n_seqs;
+    const int from_end = item / per, rem = item - from_end * per;
+    t.seq = rem / p.n_kv;
+    t.hk = rem - t.seq * p.n_kv;
+    t.q_begin = p.cu_q[t.seq];
+    const int q_len = p.cu_q[t.seq + 1] - t.q_begin;
+    t.n_rows = q_len * group;
+    t.tile = (t.n_rows + ROWS - 1) / ROWS - 1 - from_end;
+    if (t.tile < 0) return false;
+    t.len = p.kv_len[t.seq];
+    t.past = t.len - q_len;
+    t.pages = p.block_table + (size_t)p.slots[t.seq] * p.max_pages;
+    const int row0 = t.tile * ROWS, last_row = min(row0 + ROWS, t.n_rows) - 1;
+    const int max_pos = t.past + last_row / group, min_pos = t.past + row0 / group;
+    const int lo = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
+    t.p_begin = lo / PAGE;
+    t.p_end = max_pos / PAGE + 1;
+    return true;
+}
+
+__global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                           const __grid_constant__ CUtensorMap map_v,
+                                                                           const __grid_constant__ CUtensorMap map_q,
+                                                                           const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    Smem5& sm = *reinterpret_cast<Smem5*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = p.n_q / p.n_kv;
+    const int G = gridDim.x, me = blockIdx.x;
+    // the block's next tile after round `r` of the list (r = -1: its first); false when the list is through
+    auto next_tile = [&](int& r, Tile& t) -> bool {
+        for (++r; r * G < p.n_items; ++r) {
+            const int item = r * G + ((r & 1) ? G - 1 - me : me);
+            if (item < p.n_items && tile_of_item(p, item, group, t)) return true;
+        }
+        return false;
+    };
+    auto steps_of = [](const Tile& t) { return (t.p_end - t.p_begin + 1) / 2; };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < K_STAGES2; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+        }
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&sm.s_full[b], 1);
+            mbar_init(&sm.s_empty[b], 256);
+            for (int quarter = 0; quarter < 4; ++quarter) mbar_init(&sm.max_ready[b][quarter], 64);
+        }
+        mbar_init(&sm.p_full, 256);
+        mbar_init(&sm.o_done, 1);
+        mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.q_empty, 1);
+        mbar_init(&sm.o_free, 256);
+        mbar_init(&sm.sum_ready, 256);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        pdl_launch_dependents();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512u));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    pdl_wait();  // queries and the new keys and values come from the kernel before
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: a tile's queries, then per step two pages of K and of V; the keys run ahead of the values
+            bool ok = true;
+            auto load = [&](int g, const Tile& t, int i, bool keys) {
+                const int pg = t.p_begin + 2 * i;
+                const int n_pages = min(2, t.p_end - pg);
+                if (keys) {
+                    const int s = g % K_STAGES2;
+                    if (g >= K_STAGES2) ok = mbar_wait(&sm.k_empty[s], ((g / K_STAGES2) - 1) & 1);
+                    if (!ok) return;
+                    mbar_expect_tx(&sm.k_full[s], (uint32_t)n_pages * 2 * PAGE * 64 * 2);
+                    for (int j = 0; j < n_pages; ++j) {
+                        const int y = (t.pages[pg + j] * p.n_kv + t.hk) * PAGE;
+                        tma_load_2d(sm.k[s][0][j], &map_k, 0, y, &sm.k_full[s]);
+                        tma_load_2d(sm.k[s][1][j], &map_k, 64, y, &sm.k_full[s]);
+                    }
+                } else {
+                    const int s = g % KV_STAGES;
+                    if (g >= KV_STAGES) ok = mbar_wait(&sm.v_empty[s], ((g / KV_STAGES) - 1) & 1);
+                    if (!ok) return;
+                    mbar_expect_tx(&sm.v_full[s], (uint32_t)n_pages * 2 * PAGE * 64 * 2);
+                    for (int j = 0; j < n_pages; ++j) {
+                        const int y = (t.pages[pg + j] * p.n_kv + t.hk) * PAGE;
+                        tma_load_2d(sm.v[s][j][0], &map_v, 0, y, &sm.v_full[s]);
+                        tma_load_2d(sm.v[s][j][1], &map_v, 64, y, &sm.v_full[s]);
+                    }
+                }
+            };
+            // queries of the n-th tile of the block, once the last scores of the tile before are formed
+            auto load_queries = [&](const Tile& t, int n) {
+                if (n > 0) ok = mbar_wait(&sm.q_empty, (n - 1) & 1);
+                if (!ok) return;
+                mbar_expect_tx(&sm.q_full, (uint32_t)(2 * ROWS * 64 * 2));
+                const int token = t.q_begin + t.tile * (ROWS / group);
+                tma_load_3d(sm.q[0], &map_q, 0, t.hk * group, token, &sm.q_full);
+                tma_load_3d(sm.q[1], &map_q, 64, t.hk * group, token, &sm.q_full);
+            };
+            Tile tk, tv;
+            int rk = -1, rv = -1, ik = 0, iv = 0, n_k = 0;
+            int g_k = 0, g_v = 0;  // steps whose keys / values have been asked for
+            bool more_k = next_tile(rk, tk), more_v = next_tile(rv, tv);
+            if (more_k) load_queries(tk, 0);
+            while (ok && (more_k || more_v)) {
+                if (more_k && g_k <= g_v + 1) {  // keys at most two steps ahead of the values
+                    load(g_k++, tk, ik, true);
+                    if (++ik == steps_of(tk)) {
+                        ik = 0;
+                        more_k = next_tile(rk, tk);
+                        if (more_k && ok) load_queries(tk, ++n_k);
+                    }
+                } else {
+                    load(g_v++, tv, iv, false);
+                    if (++iv == steps_of(tv)) {
+                        iv = 0;
+                        more_v = next_tile(rv, tv);
+                    }
+                }
+            }
+            if (!ok) atomicExch(p.error_flag, 61);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- issuer of the score products S = Q K^T, a step ahead of the softmax (two score buffers)
+            const uint32_t id_s = idesc(ROWS, KEYS2, false);
+            bool ok = true;
+            int g = 0, n = 0, r = -1;
+            Tile t;
+            while (ok && next_tile(r, t)) {
+                const int n_iter = steps_of(t);
+                ok = mbar_wait(&sm.q_full, n & 1);
+                if (!ok) break;
+                for (int i = 0; i < n_iter && ok; ++i, ++g) {
+                    const int s = g % K_STAGES2, b = g & 1;
+                    ok = mbar_wait(&sm.k_full[s], (g / K_STAGES2) & 1);
+                    if (ok && g >= 2) ok = mbar_wait(&sm.s_empty[b], ((g >> 1) - 1) & 1);  // the softmax has taken what was there
+                    if (!ok) break;
+                    fence_after();
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint64_t da = desc_k_major(smem_u32(sm.q[k >> 2]) + (k & 3) * 32);
+                        const uint64_t db = desc_k_major(smem_u32(sm.k[s][k >> 2][0]) + (k & 3) * 32);
+                        umma_ss(tmem + COL2_S + b * KEYS2, da, db, id_s, k > 0);
+                    }
+                    umma_commit(&sm.k_empty[s]);  // the keys' shared memory is free once the scores are formed
+                    umma_commit(&sm.s_full[b]);
+                }
+                umma_commit(&sm.q_empty);  // and so are the queries', once the tile's last scores are
+                ++n;
+            }
+            if (!ok) atomicExch(p.error_flag, 62);
+        }
+    } else if (warp == 10) {
+        if (lane == 0) {
+            // ---- issuer of the products O += P V
+            const uint32_t id_o = idesc(ROWS, D, true);
+            bool ok = true;
+            int g = 0, n = 0, r = -1;
+            Tile t;
+            while (ok && next_tile(r, t)) {
+                const int n_iter = steps_of(t);
+                for (int i = 0; i < n_iter && ok; ++i, ++g) {
+                    const int s = g % KV_STAGES;
+                    ok = mbar_wait(&sm.p_full, g & 1);
+                    if (ok) ok = mbar_wait(&sm.v_full[s], (g / KV_STAGES) & 1);
+                    // a tile's first product overwrites the accumulator: the result of the tile before has been read
+                    if (ok && i == 0 && n > 0) ok = mbar_wait(&sm.o_free, (n - 1) & 1);
+                    if (!ok) break;
+                    fence_after();
+#pragma unroll
+                    for (int j = 0; j < KEYS2 / 16; ++j) {
+                        const uint64_t db = desc_mn_major(smem_u32(sm.v[s][j >> 2][0]) + (j & 3) * 16 * 128, PAGE * 128);
+                        umma_ts(tmem + COL2_O, tmem + COL2_P + j * 8, db, id_o, i > 0 || j > 0);
+                    }
+                    umma_commit(&sm.v_empty[s]);
+                    umma_commit(&sm.o_done);
+                }
+                ++n;
+            }
+            if (!ok) atomicExch(p.error_flag, 64);
+        }
+    } else {
+        // ---- softmax warps: two threads a row, as in the kernel above
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int quad_row = quarter * 32 + (lane & ~3), piece = lane & 3;
+        bool ok = true;
+        int g = 0, n = 0, round = -1;
+        Tile t;
+        while (ok && next_tile(round, t)) {
+            const int p_begin = t.p_begin, p_end = t.p_end, len = t.len;
+            const int n_iter = steps_of(t);
+            const int row = t.tile * ROWS + r;
+            const bool row_ok = row < t.n_rows;
+            const int tok = row_ok ? row / group : 0;
+            const int pos = t.past + tok;
+            float m_used = -INFINITY, l = 0.f;
+            for (int i = 0; i < n_iter && ok; ++i, ++g) {
+                const int s = g % KV_STAGES, b = g & 1;
+                const int key_base = (p_begin + 2 * i) * PAGE + half * 64;  // the first key this thread looks at
+                const uint32_t s_cols = tmem + lane_base + COL2_S + b * KEYS2 + half * 64;
+                ok = mbar_wait(&sm.s_full[b], (g >> 1) & 1);
+                if (!ok) break;
+                fence_after();
+                uint32_t raw[2][32];
+                tmem_ld32(s_cols, raw[0]);
+                tmem_ld32(s_cols + 32, raw[1]);
+                tmem_wait_ld();
+                fence_before();
+                mbar_arrive(&sm.s_empty[b]);  // the scores are in registers: the buffer may be overwritten
+                const int step_base = (p_begin + 2 * i) * PAGE;
+                const int valid = min(len - step_base, min(2, p_end - (p_begin + 2 * i)) * PAGE);
+                if (valid < KEYS2) {
+                    ok = mbar_wait(&sm.v_full[s], (g / KV_STAGES) & 1);
+                    if (!ok) break;
+                    for (int idx = half * 128 + r; idx < (KEYS2 - valid) * 16; idx += 256) {
+                        const int vr = valid + idx / 16, chunk = idx % 16;
+                        reinterpret_cast<uint4*>(sm.v[s][vr >> 6][chunk >> 3])[(vr & 63) * 8 + (chunk & 7)] = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_async_smem();
+                }
+                if (key_base + 63 > pos || p.window > 0) {
+                    const int hidden_upto = p.window > 0 ? pos - p.window : -1;
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        const int key = key_base + c;
+                        const bool hidden = (key > pos) | (key <= hidden_upto);
+                        raw[c >> 5][c & 31] = hidden ? 0xff800000u : raw[c >> 5][c & 31];
+                    }
+                }
+                float mx;
+                {
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(raw[c >> 5][c & 31]));
+                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                }
+                sm.row_max[g & 1][half][r] = mx;
+                mbar_arrive(&sm.max_ready[g & 1][quarter]);
+                ok = mbar_wait(&sm.max_ready[g & 1][quarter], (g >> 1) & 1);
+                if (!ok) break;
+                mx = fmaxf(mx, sm.row_max[g & 1][half ^ 1][r]);
+                const float m_new = fmaxf(m_used, mx * p.sl2);
+                float corr = 1.0f;
+                if (m_new > m_used + RESCALE_THRESHOLD || m_used == -INFINITY) {
+                    corr = m_used == -INFINITY ? 0.f : exp2f(m_used - m_new);
+                    m_used = m_new;
+                }
+                const float ref = m_used == -INFINITY ? 0.f : m_used;
+                uint32_t packed[32];
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < 64; c += 2) {
+                    const float e0 = ex2(fmaf(__uint_as_float(raw[c >> 5][c & 31]), p.sl2, -ref));
+                    const float e1 = ex2(fmaf(__uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]), p.sl2, -ref));
+                    sum4[(c >> 1) & 3] += e0 + e1;
+                    __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
+                    packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+                }
+                l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+                if (g > 0) {
+                    ok = mbar_wait(&sm.o_done, (g - 1) & 1);
+                    if (!ok) break;
+                    fence_after();
+                }
+                if (i > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+                    for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem + lane_base + COL2_O + c0, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+                        tmem_st32(tmem + lane_base + COL2_O + c0, o);
+                    }
+                }
+                tmem_st32(tmem + lane_base + COL2_P + half * 32, packed);
+                tmem_wait_st();
+                fence_before();
+                mbar_arrive(&sm.p_full);
+            }
+            if (!ok) break;
+            // ---- the tile's result: O / l, this thread's half of the columns; l is the sum of both halves' sums
+            sm.row_sum[half][r] = l;
+            mbar_arrive(&sm.sum_ready);
+            ok = mbar_wait(&sm.o_done, (g - 1) & 1);
+            if (ok) ok = mbar_wait(&sm.sum_ready, n & 1);
+            if (!ok) break;
+            fence_after();
+            const float inv = 1.0f / (sm.row_sum[0][r] + sm.row_sum[1][r]);
+            uint32_t packed[32];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem + lane_base + COL2_O + half * 64 + c0, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+                    packed[(c0 + c) >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                }
+            }
+            fence_before();
+            mbar_arrive(&sm.o_free);  // the accumulator is in registers: the next tile's first product may overwrite it
+            swap_pieces<uint32_t, 8>(packed, lane);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row_i = t.tile * ROWS + quad_row + i;
+                if (row_i < t.n_rows) {
+                    __nv_bfloat16* dst = p.out + ((size_t)(t.q_begin + row_i / group) * p.n_q + t.hk * group + row_i % group) * D + half * 64 + piece * 16;
+                    store32(dst, packed + 8 * i);
+                }
+            }
+            ++n;
+        }
+        if (!ok && lane == 0) atomicExch(p.error_flag, 63);
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -859,18 +1236,34 @@ int make_page_map(CUtensorMap* map, const void* base, long long rows) {
     return GK_OK;
 }
 
+// The queries [n_tokens, n_q, 128] as a 3-D tensor; a box is 128 / group tokens x group heads x 64 elements.
+int make_query_map(CUtensorMap* map, const void* base, long long n_tokens, int n_q, int group) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)n_q, (cuuint64_t)n_tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)D * sizeof(__nv_bfloat16), (cuuint64_t)n_q * D * sizeof(__nv_bfloat16)};
+    cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)(ROWS / group)};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: cuTensorMapEncodeTiled (queries) failed with code %d", (int)r);
+    return GK_OK;
+}
+
 int g_attention_prefill_keys = KEYS2;  // 128 (the default) or 64
+int g_attention_prefill_stay = 0;      // with 128 keys a step: blocks that stay and take tiles from a list (needs the token count and a group that divides 128)
 int g_attention_prefill_one_tile = 1;  // with 128 keys a step: 1 (the default) a query tile a block, heaviest first; 0 a heavy and a light tile a block
 
 }  // namespace
 
 // Same arguments as gk_attention_prefill_bf16 plus the number of pages of the layer's storage and the
 // device error flag of the bounded waits.  head_dim must be 128.
-GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
-                                           const int* cu_q, const int* kv_len, const int* slots, const int* block_table,
-                                           int n_seqs, int max_q_len, int n_q, int n_kv, int head_dim, int max_pages,
-                                           int page_size, long long n_pages, float scale, int window, int* error_flag,
-                                           void* stream) {
+static int prefill_tc_entry(const void* q, const void* k_pages, const void* v_pages, void* out,
+                            const int* cu_q, const int* kv_len, const int* slots, const int* block_table,
+                            int n_seqs, int max_q_len, int n_q, int n_kv, int head_dim, int max_pages,
+                            int page_size, long long n_pages, float scale, int window, int* error_flag,
+                            void* stream, long long n_tokens) {
     GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill_tc: bad head counts %d/%d", n_q, n_kv);
     GK_REQUIRE(page_size == PAGE && head_dim == D, "attention_prefill_tc: needs page_size %d and head_dim %d", PAGE, D);
     GK_REQUIRE(n_kv <= 65535 && n_seqs <= 65535 && window >= 0 && max_q_len >= 0 && n_pages > 0, "attention_prefill_tc: bad sizes");
@@ -904,10 +1297,35 @@ GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     p.window = window;
     p.error_flag = error_flag;
     p.one_tile = 0;
+    p.n_seqs = n_seqs;
+    p.n_items = 0;
     const int group = n_q / n_kv;
     const long long blocks = ((long long)max_q_len * group + ROWS - 1) / ROWS;
     GK_REQUIRE(blocks <= 2147483647LL, "attention_prefill_tc: too many rows");
     // measured for one prompt: 42 against 58 us at 2,048 tokens, 396 against 442 us at 8,192
+    if (g_attention_prefill_keys == KEYS2 && g_attention_prefill_stay && n_tokens > 0 && ROWS % group == 0 &&
+        blocks * n_kv * n_seqs < 2147483647LL) {
+        CUtensorMap mq;
+        status = make_query_map(&mq, q, n_tokens, n_q, group);
+        if (status) return status;
+        const size_t smem5 = sizeof(Smem5) + 1024;
+        static bool configured5 = false;
+        static int n_sms = 0;
+        if (!configured5) {
+            cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem5);
+            int device = 0;
+            if (err == cudaSuccess) err = cudaGetDevice(&device);
+            if (err == cudaSuccess) err = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+            if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: %s", cudaGetErrorString(err));
+            configured5 = true;
+        }
+        p.n_seqs = n_seqs;
+        p.n_items = (int)(blocks * n_kv * n_seqs);
+        dim3 grid5((unsigned)(p.n_items < n_sms ? p.n_items : n_sms));
+        gk_launch(attention_prefill_tc5_kernel, grid5, dim3(THREADS2), smem5, (cudaStream_t)stream, mk, mv, mq, p);
+        GK_CHECK_LAUNCH("attention_prefill_tc5");
+        return GK_OK;
+    }
     if (g_attention_prefill_keys == KEYS2) {
         const size_t smem2 = sizeof(Smem2) + 1024;
         static bool configured2 = false;
@@ -929,6 +1347,34 @@ GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     gk_launch(attention_prefill_tc_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, mk, mv, p);
     GK_CHECK_LAUNCH("attention_prefill_tc");
     return GK_OK;
+}
+
+GK_EXPORT int gk_attention_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                           const int* cu_q, const int* kv_len, const int* slots, const int* block_table,
+                                           int n_seqs, int max_q_len, int n_q, int n_kv, int head_dim, int max_pages,
+                                           int page_size, long long n_pages, float scale, int window, int* error_flag,
+                                           void* stream) {
+    return prefill_tc_entry(q, k_pages, v_pages, out, cu_q, kv_len, slots, block_table, n_seqs, max_q_len, n_q, n_kv, head_dim,
+                            max_pages, page_size, n_pages, scale, window, error_flag, stream, 0);
+}
+
+// The same with the number of tokens in `q` (its first dimension), which the kernel with blocks that stay needs for
+// the tensor map of the queries.
+GK_EXPORT int gk_attention_prefill_tc_tokens_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                                  const int* cu_q, const int* kv_len, const int* slots, const int* block_table,
+                                                  int n_seqs, int max_q_len, int n_q, int n_kv, int head_dim, int max_pages,
+                                                  int page_size, long long n_pages, float scale, int window, int* error_flag,
+                                                  void* stream, long long n_tokens) {
+    return prefill_tc_entry(q, k_pages, v_pages, out, cu_q, kv_len, slots, block_table, n_seqs, max_q_len, n_q, n_kv, head_dim,
+                            max_pages, page_size, n_pages, scale, window, error_flag, stream, n_tokens);
+}
+
+// With 128 keys a step: 1 = blocks that stay and take query tiles from the launch's list (where the token count is
+// given and the group divides 128), 0 = a block a tile (or a pair of tiles).  Returns the old setting.
+GK_EXPORT int gk_set_attention_prefill_stay(int mode) {
+    const int before = g_attention_prefill_stay;
+    g_attention_prefill_stay = mode ? 1 : 0;
+    return before;
 }
 
 // Keys per step of the tcgen05 prefill attention: 128 (the default: one block per SM, two score buffers, eight

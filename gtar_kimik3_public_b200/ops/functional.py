@@ -846,9 +846,9 @@ def attention_prefill(
         raise KernelError("the tcgen05 prefill attention takes head size 128 only")
     if tensor_cores == "tcgen05" or (tensor_cores == "auto" and d == 128):
         call(
-            "gk_attention_prefill_tc_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(cu_q), ptr(kv_len), ptr(slots),
+            "gk_attention_prefill_tc_tokens_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(cu_q), ptr(kv_len), ptr(slots),
             ptr(kv.block_table), n_seqs, int(max_q_len), n_q, n_kv, d, kv.max_pages, kv.page_size, kv.k.shape[0],
-            float(scale), int(window), ptr(error_flag(q.device)), stream_ptr(),
+            float(scale), int(window), ptr(error_flag(q.device)), stream_ptr(), int(q.shape[0]),
         )
         return out
     call(
@@ -866,6 +866,15 @@ def set_attention_prefill_keys(keys: int) -> int:
     from .library import library
 
     return int(library().gk_set_attention_prefill_keys(int(keys)))
+
+
+def set_attention_prefill_stay(mode: int) -> int:
+    """Whether the tcgen05 prefill attention (128 keys a step) runs as blocks that stay, one an SM, and take query tiles
+    from the launch's list with the next tile's queries and first scores under the tile in hand (1), or as a block a
+    tile (0).  Returns the old setting."""
+    from .library import library
+
+    return int(library().gk_set_attention_prefill_stay(int(mode)))
 
 
 def set_attention_prefill_one_tile(mode: int) -> int:

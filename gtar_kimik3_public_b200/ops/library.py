@@ -53,6 +53,8 @@ _SIGNATURES: dict[str, list] = {
     "gk_attention_decode_bf16_no_alloc": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_prefill_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
     "gk_attention_prefill_tc_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, F, I, P, P],
+    "gk_attention_prefill_tc_tokens_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, F, I, P, P, L],
+    "gk_set_attention_prefill_stay": [I],
     "gk_argmax": [P, L, I, I, P, I, P, P],
     "gk_sample": [P, L, I, I, F, I, U, P, P, I, P, I, P, P],
 }

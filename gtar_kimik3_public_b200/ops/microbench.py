@@ -127,10 +127,12 @@ def bench_attention_prefill(args) -> dict:
         F.attention_prefill(q, kv, cu_q, kv_len, slots, t, d**-0.5, tensor_cores=args.attention_path)
 
     before = F.set_attention_prefill_one_tile(args.one_tile)
+    stay = F.set_attention_prefill_stay(args.stay)
     try:
         us = _time_graph(run, args.iters)
     finally:
         F.set_attention_prefill_one_tile(before)
+        F.set_attention_prefill_stay(stay)
     flops = 4 * n_q * d * t * t / 2
     return {"kernel": "attention_prefill", "path": args.attention_path, "tokens": t, "q_heads": n_q, "kv_heads": n_kv, "head_dim": d,
             "us": round(us, 2), "tflop_s": round(flops / us / 1e6, 1)}
@@ -259,6 +261,8 @@ def main() -> int:
     parser.add_argument("--hidden", type=int, default=1024, help="step: the model's width")
     parser.add_argument("--intermediate", type=int, default=3072, help="step: the feed-forward's width")
     parser.add_argument("--attention-path", default="auto", choices=["auto", "tcgen05", "mma"])
+    parser.add_argument("--stay", type=int, default=0, choices=[0, 1],
+                        help="attention_prefill on tcgen05: 1 = blocks that stay and take query tiles from a list")
     parser.add_argument("--one-tile", type=int, default=1, choices=[0, 1],
                         help="attention_prefill on tcgen05: 1 = a query tile a block, heaviest first (the default), 0 = a heavy and a light tile a block")
     parser.add_argument("--layers", type=int, default=28)

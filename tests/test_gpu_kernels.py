@@ -510,22 +510,26 @@ def test_swiglu_interleaved():
 # ------------------------------------------------------------------ bfloat16 flash prefill attention
 def prefill_attention(path, *args, **kwargs):
     """``path``: "mma", "tcgen05_128", "tcgen05_64" (the tcgen05 kernels with 128 or 64 keys per step) or
-    "tcgen05_128_pairs" (128 keys per step, a heavy and a light query tile a block instead of a tile a block)."""
+    "tcgen05_128_pairs" (128 keys per step, a heavy and a light query tile a block instead of a tile a block), or
+    "tcgen05_128_stay" (128 keys per step, blocks that stay and take tiles from a list)."""
     if not path.startswith("tcgen05_"):
         return F().attention_prefill(*args, tensor_cores=path, **kwargs)
     before = F().set_attention_prefill_keys(int(path[8:].split("_")[0]))
     one = F().set_attention_prefill_one_tile(0 if path.endswith("_pairs") else 1)
+    stay = F().set_attention_prefill_stay(1 if path.endswith("_stay") else 0)
     try:
         return F().attention_prefill(*args, tensor_cores="tcgen05", **kwargs)
     finally:
         F().set_attention_prefill_keys(before)
         F().set_attention_prefill_one_tile(one)
+        F().set_attention_prefill_stay(stay)
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,path", [(4, 4, 64, "mma"), (16, 8, 128, "mma"), (6, 2, 128, "mma"), (3, 1, 64, "mma"),
                                               (16, 8, 128, "tcgen05_128"), (6, 2, 128, "tcgen05_128"), (4, 4, 128, "tcgen05_128"),
                                               (16, 8, 128, "tcgen05_64"), (6, 2, 128, "tcgen05_64"), (4, 4, 128, "tcgen05_64"),
-                                              (16, 8, 128, "tcgen05_128_pairs"), (6, 2, 128, "tcgen05_128_pairs"), (4, 4, 128, "tcgen05_128_pairs")])
+                                              (16, 8, 128, "tcgen05_128_pairs"), (6, 2, 128, "tcgen05_128_pairs"), (4, 4, 128, "tcgen05_128_pairs"),
+                                              (16, 8, 128, "tcgen05_128_stay"), (8, 2, 128, "tcgen05_128_stay"), (4, 4, 128, "tcgen05_128_stay")])
 def test_attention_prefill_bf16_varlen(n_q, n_kv, d, path):
     dtype = torch.bfloat16
     lens, past = [1, 777, 1000, 64, 130], [0, 700, 0, 0, 129]  # whole prompts, a continuation, a single token
@@ -548,7 +552,7 @@ def test_attention_prefill_bf16_varlen(n_q, n_kv, d, path):
     assert (got - want).abs().max().item() < 1.5 * BF16_ULP * want.abs().max().item() + 2e-3
 
 
-@pytest.mark.parametrize("path", ["mma", "tcgen05_128", "tcgen05_64", "tcgen05_128_pairs"])
+@pytest.mark.parametrize("path", ["mma", "tcgen05_128", "tcgen05_64", "tcgen05_128_pairs", "tcgen05_128_stay"])
 def test_attention_prefill_bf16_far_key_and_window(path):
     dtype, n_q, n_kv, d, n = torch.bfloat16, 4, 2, 128, 900
     kv, slots, table = scrambled_pages(1, n, n_kv, d, dtype, seed=15)
