@@ -1252,7 +1252,7 @@ int make_query_map(CUtensorMap* map, const void* base, long long n_tokens, int n
 }
 
 int g_attention_prefill_keys = KEYS2;  // 128 (the default) or 64
-int g_attention_prefill_stay = 0;      // with 128 keys a step: blocks that stay and take tiles from a list (needs the token count and a group that divides 128)
+int g_attention_prefill_stay = 2;      // with 128 keys a step: blocks that stay and take tiles from a list: 0 never, 1 always, 2 (default) where the tiles are more than the SMs (needs the token count and a group that divides 128)
 int g_attention_prefill_one_tile = 1;  // with 128 keys a step: 1 (the default) a query tile a block, heaviest first; 0 a heavy and a light tile a block
 
 }  // namespace
@@ -1303,19 +1303,23 @@ static int prefill_tc_entry(const void* q, const void* k_pages, const void* v_pa
     const long long blocks = ((long long)max_q_len * group + ROWS - 1) / ROWS;
     GK_REQUIRE(blocks <= 2147483647LL, "attention_prefill_tc: too many rows");
     // measured for one prompt: 42 against 58 us at 2,048 tokens, 396 against 442 us at 8,192
-    if (g_attention_prefill_keys == KEYS2 && g_attention_prefill_stay && n_tokens > 0 && ROWS % group == 0 &&
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) n_sms = 148;
+    }
+    // measured for one prompt, blocks that stay against a block a tile: 22.4 against 21.5 us at 1,024 tokens (a tile an
+    // SM: nothing to put under anything), 35.0 against 37.3 at 2,048, 99 against 104 at 4,096, 322 against 328 at 8,192
+    const bool stay = g_attention_prefill_stay == 1 || (g_attention_prefill_stay == 2 && blocks * n_kv * n_seqs > n_sms);
+    if (g_attention_prefill_keys == KEYS2 && stay && n_tokens > 0 && ROWS % group == 0 &&
         blocks * n_kv * n_seqs < 2147483647LL) {
         CUtensorMap mq;
         status = make_query_map(&mq, q, n_tokens, n_q, group);
         if (status) return status;
         const size_t smem5 = sizeof(Smem5) + 1024;
         static bool configured5 = false;
-        static int n_sms = 0;
         if (!configured5) {
             cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem5);
-            int device = 0;
-            if (err == cudaSuccess) err = cudaGetDevice(&device);
-            if (err == cudaSuccess) err = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
             if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "attention_prefill_tc: %s", cudaGetErrorString(err));
             configured5 = true;
         }
@@ -1369,11 +1373,12 @@ GK_EXPORT int gk_attention_prefill_tc_tokens_bf16(const void* q, const void* k_p
                             max_pages, page_size, n_pages, scale, window, error_flag, stream, n_tokens);
 }
 
-// With 128 keys a step: 1 = blocks that stay and take query tiles from the launch's list (where the token count is
-// given and the group divides 128), 0 = a block a tile (or a pair of tiles).  Returns the old setting.
+// With 128 keys a step: blocks that stay and take query tiles from the launch's list (where the token count is given
+// and the group divides 128): 1 = always, 2 (the default) = where the tiles are more than the SMs, 0 = never (a block a
+// tile, or a pair of tiles).  Returns the old setting.
 GK_EXPORT int gk_set_attention_prefill_stay(int mode) {
     const int before = g_attention_prefill_stay;
-    g_attention_prefill_stay = mode ? 1 : 0;
+    g_attention_prefill_stay = mode < 0 ? 0 : mode > 2 ? 2 : mode;
     return before;
 }
 

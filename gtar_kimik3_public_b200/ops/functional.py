@@ -870,8 +870,8 @@ def set_attention_prefill_keys(keys: int) -> int:
 
 def set_attention_prefill_stay(mode: int) -> int:
     """Whether the tcgen05 prefill attention (128 keys a step) runs as blocks that stay, one an SM, and take query tiles
-    from the launch's list with the next tile's queries and first scores under the tile in hand (1), or as a block a
-    tile (0).  Returns the old setting."""
+    from the launch's list with the next tile's queries and first scores under the tile in hand: 1 = always, 2 (the
+    default) = where the launch has more tiles than the device SMs, 0 = never (a block a tile).  Returns the old setting."""
     from .library import library
 
     return int(library().gk_set_attention_prefill_stay(int(mode)))

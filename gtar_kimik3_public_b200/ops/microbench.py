@@ -261,8 +261,8 @@ def main() -> int:
     parser.add_argument("--hidden", type=int, default=1024, help="step: the model's width")
     parser.add_argument("--intermediate", type=int, default=3072, help="step: the feed-forward's width")
     parser.add_argument("--attention-path", default="auto", choices=["auto", "tcgen05", "mma"])
-    parser.add_argument("--stay", type=int, default=0, choices=[0, 1],
-                        help="attention_prefill on tcgen05: 1 = blocks that stay and take query tiles from a list")
+    parser.add_argument("--stay", type=int, default=2, choices=[0, 1, 2],
+                        help="attention_prefill on tcgen05: blocks that stay and take query tiles from a list: 1 = always, 0 = never, 2 = the library's choice")
     parser.add_argument("--one-tile", type=int, default=1, choices=[0, 1],
                         help="attention_prefill on tcgen05: 1 = a query tile a block, heaviest first (the default), 0 = a heavy and a light tile a block")
     parser.add_argument("--layers", type=int, default=28)

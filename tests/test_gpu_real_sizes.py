@@ -60,7 +60,7 @@ def test_long_prompt_whole_and_last_32_one_by_one(tag, dtype, kernel_log):
     check_against_plain(tag, dtype, tokens, places, whole, f"{tag} {dtype} whole")
     if dtype == "bfloat16":  # the paths that the benchmark times did run
         assert "gk_gemm_bf16_tc_qkv" in kernel_log, "the q|k|v product did not take its fused output stage"
-        assert "gk_attention_prefill_tc_bf16" in kernel_log, "prefill attention did not take the tcgen05 kernel"
+        assert "gk_attention_prefill_tc_tokens_bf16" in kernel_log, "prefill attention did not take the tcgen05 kernel"
     del kernel_log[:]
     head = n - 32
     parts = [engine.step([_entry("cut", tokens[:head], list(range(head)))])]
