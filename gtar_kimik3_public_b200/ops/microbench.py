@@ -183,6 +183,47 @@ def bench_step(args) -> dict:
             "us": round(begin.elapsed_time(end) * 1e3, 1)}
 
 
+def bench_prefill_step(args) -> dict:
+    """One step over ``--batch`` whole prompts of ``--tokens`` tokens of a random model of the given layer sizes,
+    launched kernel by kernel between cudaProfilerStart/Stop (after two steps of the same shape that are not listed)."""
+    import tempfile
+
+    from ..engine import Engine, StepEntry
+    from ..generate import load
+    from ..registry import config_from_dict
+    from ..weights import write_random_model
+
+    config = config_from_dict({
+        "arch": "transformer", "vocab_size": 151936, "hidden_size": args.hidden, "intermediate_size": args.intermediate,
+        "num_hidden_layers": args.layers, "num_attention_heads": args.q_heads, "num_key_value_heads": args.kv_heads,
+        "head_dim": args.head_dim, "rms_norm_eps": 1e-6, "rope_theta": 1e6, "tie_word_embeddings": True,
+        "initializer_range": 0.02, "max_position_embeddings": max(4096, args.tokens),
+    })
+    with tempfile.TemporaryDirectory(prefix="gtar_microbench_") as folder:
+        write_random_model(folder, config, seed=0)
+        model = load(folder, "bfloat16", DEV)
+    b, s = args.batch, args.tokens
+    engine = Engine(model, b * (s + 64), max_seqs=b, use_graphs=False)
+    gen = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, config.vocab_size, (b, s), generator=gen).tolist()
+    ids = list(range(b))
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.no_grad():
+        for turn in range(3):
+            if turn == 2:
+                torch.cuda.synchronize()
+                torch.cuda.profiler.start()
+                begin.record()
+            engine.step([StepEntry(i, prompts[i], [s - 1]) for i in ids])
+            if turn == 2:
+                end.record()
+                torch.cuda.synchronize()
+                torch.cuda.profiler.stop()
+            engine.end(ids)
+    return {"kernel": "prefill step, kernel by kernel", "batch": b, "tokens": s, "layers": args.layers,
+            "us": round(begin.elapsed_time(end) * 1e3, 1)}
+
+
 def bench_decode_layers(args) -> dict:
     """One decode step through the persistent kernel for all layers, with the kernel's own clock stamps: for every
     stage of a layer in the middle of the model, how long the blocks work on it (from their release out of the barrier
@@ -244,7 +285,7 @@ def bench_decode_layers(args) -> dict:
 
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    parser.add_argument("--kernel", required=True, choices=["gemm", "gemv", "attention_decode", "attention_prefill", "step", "decode_layers"])
+    parser.add_argument("--kernel", required=True, choices=["gemm", "gemv", "attention_decode", "attention_prefill", "step", "prefill_step", "decode_layers"])
     parser.add_argument("--m", type=int, default=8)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=1024)
@@ -271,7 +312,7 @@ def main() -> int:
     args = parser.parse_args()
     F.require_device(torch.device(DEV))
     result = {"gemm": bench_gemm, "gemv": bench_gemv, "attention_decode": bench_attention_decode,
-              "attention_prefill": bench_attention_prefill, "step": bench_step, "decode_layers": bench_decode_layers}[args.kernel](args)
+              "attention_prefill": bench_attention_prefill, "step": bench_step, "prefill_step": bench_prefill_step, "decode_layers": bench_decode_layers}[args.kernel](args)
     F.check_kernel_errors(DEV)
     print(json.dumps(result))
     return 0

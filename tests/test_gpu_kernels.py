@@ -76,6 +76,32 @@ def test_add_rmsnorm(hidden, out_dtype, weight_dtype):
     assert torch.equal(got3.cpu(), got.cpu()[rows.long()]) and torch.equal(hd3.cpu(), h)
 
 
+@pytest.mark.parametrize("hidden", [1024, 72, 900])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm_of_many_rows_equals_the_same_rows_a_few_at_a_time(hidden, out_dtype):
+    """Many short rows take a kernel with a warp a row; its numbers are bit for bit those of the block-a-row kernel,
+    so a row's norm does not depend on how many rows its step has."""
+    n, eps = 515, 2e-6  # a last block with three rows
+    h = rand(n, hidden, seed=11, scale=3.0).float()
+    delta = rand(n, hidden, seed=12).to(out_dtype)
+    w = (1 + 0.1 * rand(hidden, seed=13)).to(out_dtype)
+    whole_h = h.to(DEV)
+    whole = F().add_rmsnorm(whole_h, delta.to(DEV), w.to(DEV), eps, out_dtype)
+    close(whole, plain.rms_norm(h.double() + delta.double(), w.double(), eps), out_dtype, "many rows")
+    assert torch.equal(whole_h.cpu(), h + delta.float())
+    for first in (0, 100, 505):
+        part_h = h[first:first + 10].to(DEV)
+        part = F().add_rmsnorm(part_h, delta[first:first + 10].to(DEV), w.to(DEV), eps, out_dtype)
+        assert torch.equal(part.cpu(), whole.cpu()[first:first + 10])
+        assert torch.equal(part_h.cpu(), whole_h.cpu()[first:first + 10])
+    rows = torch.arange(n - 1, -1, -1, dtype=torch.int32)
+    untouched = h.to(DEV)
+    picked = F().add_rmsnorm(untouched, delta.to(DEV), w.to(DEV), eps, out_dtype, rows=rows.to(DEV))
+    assert torch.equal(picked.cpu(), whole.cpu().flip(0)) and torch.equal(untouched.cpu(), h)
+    alone = F().add_rmsnorm(h.to(DEV), None, w.to(DEV), eps, out_dtype)
+    close(alone, plain.rms_norm(h.double(), w.double(), eps), out_dtype, "many rows without delta")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_swiglu(dtype):
     n, inter = 5, 224 + 3
