@@ -111,6 +111,7 @@ __device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (
 template <int D>
 __device__ __forceinline__ void softmax_update(float (&s)[2][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4],
                                                uint32_t (&p)[4], float sl2) {
+    float corrs[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         float mx = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
@@ -133,10 +134,18 @@ __device__ __forceinline__ void softmax_update(float (&s)[2][4], float (&m)[2], 
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         l[h] = l[h] * corr + sum;
         m[h] = m_new;
+        corrs[h] = corr;
+    }
+    // The accumulator is rescaled only where some row of the warp has a new maximum: a factor of exactly one changes
+    // nothing, and after a sequence's first keys that is the usual case (64 multiplications of every 16 keys' 250
+    // instructions).
+    if (__any_sync(0xffffffffu, corrs[0] != 1.f || corrs[1] != 1.f)) {
 #pragma unroll
         for (int j = 0; j < D / 8; ++j) {
-            o[j][2 * h] *= corr;
-            o[j][2 * h + 1] *= corr;
+            o[j][0] *= corrs[0];
+            o[j][1] *= corrs[0];
+            o[j][2] *= corrs[1];
+            o[j][3] *= corrs[1];
         }
     }
     p[0] = pack_bf16(s[0][0], s[0][1]);
