@@ -71,16 +71,15 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const int n_iter = max(p_end - p_begin, 0);
     const int new_page = (len - 1) / PAGE;
 
-    auto issue_page = [&](int it, int page) {
+    auto issue_page = [&](int it, int page, int stage) {  // stage = it % STAGES, which the caller has at hand
         const int p = p_begin + it;
         const int valid = min(PAGE, len - p * PAGE);
         const size_t base = ((size_t)page * n_kv + hk) * PAGE * D;
-        const int stage = it % STAGES;
-        load_tile_async<D>(sm.k[stage], k_pages + base, D, PAGE, valid, tid, WARPS * 32);
-        load_tile_async<D>(sm.v[stage], v_pages + base, D, PAGE, valid, tid, WARPS * 32);
+        load_page_async<D, WARPS * 32>(sm.k[stage], k_pages + base, valid, tid);
+        load_page_async<D, WARPS * 32>(sm.v[stage], v_pages + base, valid, tid);
     };
-    auto issue = [&](int it) {
-        if (it < n_iter) issue_page(it, pages[p_begin + it]);
+    auto issue = [&](int it, int stage) {
+        if (it < n_iter) issue_page(it, pages[p_begin + it], stage);
         cp_async_commit();
     };
     // Lengths, slots and the page table are step inputs (copied in before the step's first kernel),
@@ -103,11 +102,11 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         sn = fused.sin_table[(size_t)(len - 1) * (D / 2) + tid];
     }
     if (early > 0) {
-        issue_page(0, early_page0);
+        issue_page(0, early_page0, 0);
         cp_async_commit();
     }
     if (early > 1) {
-        issue_page(1, early_page1);
+        issue_page(1, early_page1, 1);
         cp_async_commit();
     }
     if (fused.qkv && tid < D) {
@@ -122,7 +121,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     if (fused.qkv) __syncthreads();  // the constants above, for every warp
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s)
-        if (s >= early) issue(s);
+        if (s >= early) issue(s, s);
 
     // The new token's raw key and value are asked for first (by the warp of the block that will write them), so
     // that they are on their way while the queries are prepared.
@@ -264,11 +263,14 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
 
-    for (int it = 0; it < n_iter; ++it) {
+    const int key0 = warp * 16;
+    const uint32_t k_offset = k_lane_offset<D>(key0, lane), v_offset = v_lane_offset<D>(key0, lane);
+    const uint32_t k_tiles = smem_u32(sm.k[0]), v_tiles = smem_u32(sm.v[0]);
+    constexpr uint32_t TILE_BYTES = PAGE * D * 2;
+    for (int it = 0, stage = 0; it < n_iter; ++it, stage = stage + 1 == STAGES ? 0 : stage + 1) {
         cp_async_wait<STAGES - 2>();
         __syncthreads();  // page `it` has landed for everyone; the stage issued next was consumed an iteration ago
-        issue(it + STAGES - 1);
-        const int stage = it % STAGES;
+        issue(it + STAGES - 1, stage == 0 ? STAGES - 1 : stage - 1);
         if (owns_new && p_begin + it == new_page) {  // block-uniform
             if (warp == 0) {
                 const int row = pos_new % PAGE;
@@ -282,21 +284,22 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
             }
             __syncthreads();
         }
-        const int key0 = warp * 16;
         const int abs0 = (p_begin + it) * PAGE + key0;
         if (abs0 < len && abs0 + 16 > lo) {  // warp-uniform: skip sixteen keys that are all hidden
             float s[2][4];
-            qk_16keys<D>(s, qf, sm.k[stage], key0, lane);
+            qk_16keys_at<D>(s, qf, k_tiles + stage * TILE_BYTES, k_offset);
+            if (abs0 + 16 > len || abs0 < lo) {  // warp-uniform: only the sixteen keys at an edge have hidden ones
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+                for (int n = 0; n < 2; ++n)
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const int key = abs0 + n * 8 + (lane & 3) * 2 + c;
-                    if (key >= len || key < lo) s[n][c] = s[n][2 + c] = -INFINITY;
-                }
+                    for (int c = 0; c < 2; ++c) {
+                        const int key = abs0 + n * 8 + (lane & 3) * 2 + c;
+                        if (key >= len || key < lo) s[n][c] = s[n][2 + c] = -INFINITY;
+                    }
+            }
             uint32_t p[4];
             softmax_update<D>(s, m, l, o, p, sl2);
-            pv_16keys<D>(o, p, sm.v[stage], key0, lane);
+            pv_16keys_at<D>(o, p, v_tiles + stage * TILE_BYTES, v_offset);
         }
     }
     cp_async_wait<0>();

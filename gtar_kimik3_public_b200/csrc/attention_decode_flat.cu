@@ -199,16 +199,16 @@ __global__ void __launch_bounds__(THREADS) attention_decode_flat_kernel(const Fl
     }
     Cursor ic = cc;  // the unit asked for next
 
-    int issued = 0;
+    int issued = 0, issue_stage = 0;  // issue_stage = issued % NST
     auto issue = [&]() {
         if (issued < count) {
             const int page = ic.pages[ic.page];
             const int valid = min(PAGE, ic.len - ic.page * PAGE);
             const size_t base = ((size_t)page * p.n_kv + ic.head) * PAGE * D;
-            const int stage = issued % NST;
-            load_tile_async<D>(sm.k[stage], p.k_pages + base, D, PAGE, valid, tid, THREADS);
-            load_tile_async<D>(sm.v[stage], p.v_pages + base, D, PAGE, valid, tid, THREADS);
+            load_page_async<D, THREADS>(sm.k[issue_stage], p.k_pages + base, valid, tid);
+            load_page_async<D, THREADS>(sm.v[issue_stage], p.v_pages + base, valid, tid);
             ++issued;
+            issue_stage = issue_stage + 1 == NST ? 0 : issue_stage + 1;
             if (issued < count) advance(ic, p);
         }
         cp_async_commit();
@@ -272,7 +272,11 @@ __global__ void __launch_bounds__(THREADS) attention_decode_flat_kernel(const Fl
 
     if (ahead && tid * 16 < record_bytes) records[tid] = fetch(cc, tid);
 
-    for (int it = 0; it < count; ++it) {
+    const int key0 = warp * 16;
+    const uint32_t k_offset = k_lane_offset<D>(key0, lane), v_offset = v_lane_offset<D>(key0, lane);
+    const uint32_t k_tiles = smem_u32(sm.k[0]), v_tiles = smem_u32(sm.v[0]);
+    constexpr uint32_t TILE_BYTES = PAGE * D * 2;
+    for (int it = 0, stage = 0; it < count; ++it, stage = stage + 1 == NST ? 0 : stage + 1) {
         cp_async_wait<NST - 2>();
         __syncthreads();  // unit `it` has landed for everyone; the stage asked for next was used an iteration ago
         issue();
@@ -406,7 +410,6 @@ __global__ void __launch_bounds__(THREADS) attention_decode_flat_kernel(const Fl
             }
         }
 
-        const int stage = it % NST;
         const bool last_page = cc.page == cc.end_page - 1;
         if (owns_new && last_page) {  // block-uniform
             if (warp == 0) {
@@ -422,21 +425,22 @@ __global__ void __launch_bounds__(THREADS) attention_decode_flat_kernel(const Fl
             __syncthreads();
         }
         const int lo = (p.window > 0 && cc.len - p.window > 0) ? cc.len - p.window : 0;
-        const int key0 = warp * 16;
         const int abs0 = cc.page * PAGE + key0;
         if (abs0 < cc.len && abs0 + 16 > lo) {  // warp-uniform: skip sixteen keys that are all hidden
             float sc[2][4];
-            qk_16keys<D>(sc, qf, sm.k[stage], key0, lane);
+            qk_16keys_at<D>(sc, qf, k_tiles + stage * TILE_BYTES, k_offset);
+            if (abs0 + 16 > cc.len || abs0 < lo) {  // warp-uniform: only the sixteen keys at an edge have hidden ones
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+                for (int n = 0; n < 2; ++n)
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const int key = abs0 + n * 8 + (lane & 3) * 2 + c;
-                    if (key >= cc.len || key < lo) sc[n][c] = sc[n][2 + c] = -INFINITY;
-                }
+                    for (int c = 0; c < 2; ++c) {
+                        const int key = abs0 + n * 8 + (lane & 3) * 2 + c;
+                        if (key >= cc.len || key < lo) sc[n][c] = sc[n][2 + c] = -INFINITY;
+                    }
+            }
             uint32_t pr[4];
             softmax_update<D>(sc, m, l, o, pr, p.sl2);
-            pv_16keys<D>(o, pr, sm.v[stage], key0, lane);
+            pv_16keys_at<D>(o, pr, v_tiles + stage * TILE_BYTES, v_offset);
         }
 
         if (last_page || it == count - 1) {

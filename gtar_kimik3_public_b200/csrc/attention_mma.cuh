@@ -43,6 +43,34 @@ __device__ __forceinline__ void load_tile_async(__nv_bfloat16* tile, const __nv_
     }
 }
 
+// A whole page (PAGE rows of D contiguous bfloat16) into a swizzled tile by N_THREADS threads: what the loop over
+// a sequence's pages does for every page, so it is written for that case.  A thread copies the same chunk of every
+// (N_THREADS / chunks a row)-th row; that distance is a multiple of eight rows, so the swizzle of its chunk is the
+// same for all of them and every copy is one instruction at a constant distance from the thread's first, in shared
+// and in global memory alike (the general loop above spends some fifteen instructions of index arithmetic a copy,
+// half of what a step of sixteen keys executed).  Rows at or beyond `valid_rows` are zero-filled.
+template <int D, int N_THREADS>
+__device__ __forceinline__ void load_page_async(__nv_bfloat16* tile, const __nv_bfloat16* src, int valid_rows, int tid) {
+    constexpr int CHUNKS = D / 8, ROWS_A_PASS = N_THREADS / CHUNKS, PASSES = PAGE / ROWS_A_PASS;
+    static_assert(N_THREADS % CHUNKS == 0 && ROWS_A_PASS % 8 == 0 && PAGE % ROWS_A_PASS == 0, "a pass must be whole groups of eight rows");
+    const int row0 = tid / CHUNKS, chunk = tid % CHUNKS;
+    const uint32_t dst = smem_u32(tile) + (uint32_t)swz<D>(row0, chunk) * 16;
+    const __nv_bfloat16* g = src + row0 * D + chunk * 8;
+    if (valid_rows >= PAGE) {
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i)  // the distances become immediates of the instruction
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + i * ROWS_A_PASS * CHUNKS * 16),
+                         "l"(g + i * ROWS_A_PASS * D));
+    } else {
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+            const bool valid = row0 + i * ROWS_A_PASS < valid_rows;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst + i * ROWS_A_PASS * CHUNKS * 16),
+                         "l"(valid ? g + i * ROWS_A_PASS * D : src), "r"(valid ? 16 : 0));
+        }
+    }
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -106,6 +134,62 @@ __device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (
     }
 }
 
+// The same two products for a loop over pages: the tile is given by its 32-bit shared-memory address and the lane's
+// place in it by a byte offset that the caller forms once (`k_lane_offset`, `v_lane_offset`).  The chunk of a later
+// k-step (or pair of dim tiles) differs from the first one's by an XOR inside the offset, (2 ks) ^ c ^ (row & 7) =
+// (2 ks) ^ (c ^ (row & 7)), so nothing of the index arithmetic is left in the loop but one addition an ldmatrix.
+template <int D>
+__device__ __forceinline__ uint32_t k_lane_offset(int key0, int lane) {
+    return (uint32_t)swz<D>(key0 + (lane & 7) + ((lane >> 4) << 3), (lane >> 3) & 1) * 16;
+}
+template <int D>
+__device__ __forceinline__ uint32_t v_lane_offset(int key0, int lane) {
+    return (uint32_t)swz<D>(key0 + (lane & 7) + (((lane >> 3) & 1) << 3), lane >> 4) * 16;
+}
+__device__ __forceinline__ void ldmatrix_x4_at(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_at(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+template <int D>
+__device__ __forceinline__ void qk_16keys_at(float (&s)[2][4], const uint32_t (&q)[D / 16][4], uint32_t k_tile, uint32_t offset) {
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t b[4];
+        ldmatrix_x4_at(b, k_tile + (offset ^ (uint32_t)(ks * 32)));
+        mma_16816(s[0], q[ks], b[0], b[1]);
+        mma_16816(s[1], q[ks], b[2], b[3]);
+    }
+}
+template <int D>
+__device__ __forceinline__ void pv_16keys_at(float (&o)[D / 8][4], const uint32_t (&p)[4], uint32_t v_tile, uint32_t offset) {
+#pragma unroll
+    for (int j = 0; j < D / 16; ++j) {
+        uint32_t b[4];
+        ldmatrix_x4_trans_at(b, v_tile + (offset ^ (uint32_t)(j * 32)));
+        mma_16816(o[2 * j], p, b[0], b[1]);
+        mma_16816(o[2 * j + 1], p, b[2], b[3]);
+    }
+}
+
+// 2^x by the hardware's approximation alone (relative error 2^-22; results below the normal range become zero, which
+// is what a probability that small is to a sum of 32-bit numbers): exp2f() wraps the same instruction in a range
+// check and two scalings, three more instructions for each of a step's exponentials.
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Running softmax over a 16-row tile.  A thread owns rows r0 = lane/4 and r0 + 8; index h = 0, 1.
 // Scores arrive raw; `sl2` = scale * log2(e).  Entries already set to -inf are masked.
 template <int D>
@@ -120,13 +204,13 @@ __device__ __forceinline__ void softmax_update(float (&s)[2][4], float (&m)[2], 
         const float m_new = fmaxf(m[h], mx * sl2);
         // a row that has seen no visible key yet keeps m = -inf; use 0 as the reference so exp2 gives 0, not NaN
         const float ref = m_new == -INFINITY ? 0.f : m_new;
-        const float corr = exp2f(m[h] - ref);
+        const float corr = m[h] == ref ? 1.f : exp2_fast(m[h] - ref);  // exactly one where the maximum stays
         float sum = 0.f;
 #pragma unroll
         for (int n = 0; n < 2; ++n)
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                const float e = exp2f(s[n][2 * h + c] * sl2 - ref);
+                const float e = exp2_fast(fmaf(s[n][2 * h + c], sl2, -ref));
                 s[n][2 * h + c] = e;
                 sum += e;
             }
@@ -193,13 +277,13 @@ __device__ __forceinline__ void softmax_page(float (&s)[8][4], float (&m)[2], fl
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float m_new = fmaxf(m[h], mx * sl2);
         const float ref = m_new == -INFINITY ? 0.f : m_new;
-        const float corr = exp2f(m[h] - ref);
+        const float corr = m[h] == ref ? 1.f : exp2_fast(m[h] - ref);
         float sum = 0.f;
 #pragma unroll
         for (int n = 0; n < 8; ++n)
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                const float e = exp2f(fmaf(s[n][2 * h + c], sl2, -ref));
+                const float e = exp2_fast(fmaf(s[n][2 * h + c], sl2, -ref));
                 s[n][2 * h + c] = e;
                 sum += e;
             }
