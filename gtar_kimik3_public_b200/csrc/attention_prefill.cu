@@ -95,8 +95,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(
             const int valid = min(PAGE, len - p * PAGE);
             const size_t base = ((size_t)page * n_kv + hk) * PAGE * D;
             const int stage = it % PF_STAGES;
-            load_tile_async<D>(sm.k[stage], k_pages + base, D, PAGE, valid, tid, PF_WARPS * 32);
-            load_tile_async<D>(sm.v[stage], v_pages + base, D, PAGE, valid, tid, PF_WARPS * 32);
+            load_page_async<D, PF_WARPS * 32>(sm.k[stage], k_pages + base, valid, tid);
+            load_page_async<D, PF_WARPS * 32>(sm.v[stage], v_pages + base, valid, tid);
         }
         cp_async_commit();
     };
