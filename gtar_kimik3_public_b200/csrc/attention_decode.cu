@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
             // is four steps further on in the same thread.
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
+                if (h * 8 >= group) continue;  // the upper eight rows of the tile hold no head of a group of up to eight
                 float x[D / 16][4];
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
                         for (int e = 0; e < 4; ++e) ss += x[ks][e] * x[ks][e];
                     ss += __shfl_xor_sync(0xffffffffu, ss, 1);
                     ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-                    const float inv = 1.0f / sqrtf(ss / (float)D + fused.eps);
+                    const float inv = rsqrtf(ss / (float)D + fused.eps);
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks)
 #pragma unroll
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         }
         if (fused.use_norm) {
             ss = warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss / (float)D + fused.eps);
+            const float inv = rsqrtf(ss / (float)D + fused.eps);
 #pragma unroll
             for (int hf = 0; hf < D / 64; ++hf)
 #pragma unroll
@@ -345,14 +346,14 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         if (mm != -INFINITY) {
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) {
-                const float f = exp2f(red_ml[(w * 16 + r) * 2] - mm);
+                const float f = exp2_fast(red_ml[(w * 16 + r) * 2] - mm);
                 ll += red_ml[(w * 16 + r) * 2 + 1] * f;
                 acc += red_o[(w * 16 + r) * D + c] * f;
             }
         }
         const int hq = hk * group + r;
         if (n_splits == 1) {
-            out[((size_t)seq * n_q + hq) * D + c] = __float2bfloat16_rn(acc / ll);
+            out[((size_t)seq * n_q + hq) * D + c] = __float2bfloat16_rn(__fdividef(acc, ll));
         } else if (cluster_merge) {
             // The splits of one (sequence, kv head) are one cluster: a block sends each of its partial outputs
             // straight into the shared memory of the block that merges that output, and its maxima and sums to
@@ -405,11 +406,11 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 #pragma unroll
             for (int sp = 0; sp < 8; ++sp)
                 if (sp < n_splits && ms[sp] != -INFINITY) {
-                    const float f = exp2f(ms[sp] - mm);
+                    const float f = exp2_fast(ms[sp] - mm);
                     ll += ls[sp] * f;
                     acc += os[sp] * f;
                 }
-            out[((size_t)seq * n_q + hk * group + r) * D + (idx % D)] = __float2bfloat16_rn(acc / ll);
+            out[((size_t)seq * n_q + hk * group + r) * D + (idx % D)] = __float2bfloat16_rn(__fdividef(acc, ll));
         }
     }
 }
@@ -431,7 +432,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
         float acc = 0.f;
         for (int s = 0; s < n_splits; ++s)
             if (ml[2 * s] != -INFINITY) acc += part_o[(row * n_splits + s) * D + c] * exp2f(ml[2 * s] - mm);
-        out[row * D + c] = __float2bfloat16_rn(acc / ll);
+        out[row * D + c] = __float2bfloat16_rn(__fdividef(acc, ll));
     }
 }
 

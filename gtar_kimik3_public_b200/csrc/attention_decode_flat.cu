@@ -104,7 +104,7 @@ __device__ __forceinline__ void merge_parts(const FlatParams& p, int pair, int b
 #pragma unroll
             for (int s = 0; s < 4; ++s)
                 if (ms[s] != -INFINITY) {
-                    const float f = exp2f(ms[s] - mm);
+                    const float f = exp2_fast(ms[s] - mm);
                     ll += ls[s] * f;
                     acc += os[s] * f;
                 }
@@ -113,13 +113,13 @@ __device__ __forceinline__ void merge_parts(const FlatParams& p, int pair, int b
             for (int s = 0; s < n_parts; ++s) {
                 const float ms = __ldcg(p.part_ml + ((id0 + s) * group + r) * 2);
                 if (ms != -INFINITY) {
-                    const float f = exp2f(ms - mm);
+                    const float f = exp2_fast(ms - mm);
                     ll += __ldcg(p.part_ml + ((id0 + s) * group + r) * 2 + 1) * f;
                     acc += __ldcg(p.part_o + ((id0 + s) * group + r) * D + c) * f;
                 }
             }
         }
-        p.out[((size_t)seq * p.n_q + hk * group + r) * D + c] = __float2bfloat16_rn(acc / ll);
+        p.out[((size_t)seq * p.n_q + hk * group + r) * D + c] = __float2bfloat16_rn(__fdividef(acc, ll));
     }
 }
 
@@ -313,6 +313,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_flat_kernel(const Fl
                 const float* sin_row = cos_row + D / 2;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
+                    if (h * 8 >= group) continue;  // the upper eight rows of the tile hold no head of a group of up to eight
                     float x[D / 16][4];
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) {
@@ -328,7 +329,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_flat_kernel(const Fl
                             for (int e = 0; e < 4; ++e) ss += x[ks][e] * x[ks][e];
                         ss += __shfl_xor_sync(0xffffffffu, ss, 1);
                         ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-                        const float inv = 1.0f / sqrtf(ss / (float)D + fused.eps);
+                        const float inv = rsqrtf(ss / (float)D + fused.eps);
 #pragma unroll
                         for (int ks = 0; ks < D / 16; ++ks)
 #pragma unroll
@@ -370,7 +371,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_flat_kernel(const Fl
                     }
                     if (fused.use_norm) {
                         ss = warp_sum(ss);
-                        const float inv = 1.0f / sqrtf(ss / (float)D + fused.eps);
+                        const float inv = rsqrtf(ss / (float)D + fused.eps);
 #pragma unroll
                         for (int hf = 0; hf < D / 64; ++hf)
 #pragma unroll
@@ -482,13 +483,13 @@ __global__ void __launch_bounds__(THREADS) attention_decode_flat_kernel(const Fl
                 if (mm != -INFINITY) {
 #pragma unroll
                     for (int w = 0; w < WARPS; ++w) {
-                        const float f = exp2f(red_ml[(w * group + r) * 2] - mm);
+                        const float f = exp2_fast(red_ml[(w * group + r) * 2] - mm);
                         ll += red_ml[(w * group + r) * 2 + 1] * f;
                         acc += red_o[(w * group + r) * D + c] * f;
                     }
                 }
                 if (n_parts == 1) {
-                    p.out[((size_t)cc.seq * p.n_q + cc.head * group + r) * D + c] = __float2bfloat16_rn(acc / ll);
+                    p.out[((size_t)cc.seq * p.n_q + cc.head * group + r) * D + c] = __float2bfloat16_rn(__fdividef(acc, ll));
                 } else {
                     p.part_o[(id * group + r) * D + c] = acc;
                     if (c == 0) {
