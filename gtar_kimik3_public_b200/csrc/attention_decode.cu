@@ -46,12 +46,11 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
     float* __restrict__ part_ml, const int* __restrict__ kv_len, const int* __restrict__ slots,
     const int* __restrict__ block_table, int n_q, int n_kv, int max_pages, float sl2, int window, int n_splits,
-    int cluster_merge, const FusedQkv fused) {
+    int cluster_merge, int group, const FusedQkv fused) {  // group = n_q / n_kv, divided on the host
     extern __shared__ __align__(128) unsigned char smem_raw[];
     DecodeSmem<D>& sm = *reinterpret_cast<DecodeSmem<D>*>(smem_raw);
     const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int group = n_q / n_kv;
     pdl_launch_dependents();
     // Two trips to memory before the wait, not one after another for every item: the length, the slot and the norm
     // weights first; then, from the length and the slot, the ids of the first pages and the rotation's row.
@@ -65,7 +64,15 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const int lo = (window > 0 && len - window > 0) ? len - window : 0;  // first visible key
     const int* pages = block_table + (size_t)slot * max_pages;
     const int first_page = lo / PAGE, end_page = (len + PAGE - 1) / PAGE;
-    const int per_split = (end_page - first_page + n_splits - 1) / n_splits;
+    // By shift and mask where the splits are a power of two (the host's choice always is): a division by a run-time
+    // number is a chain of some thirty dependent instructions, here in front of the first page's id and, for the
+    // places of the merged outputs, in the kernel's tail, where nothing hides it.
+    const bool pow2 = (n_splits & (n_splits - 1)) == 0;
+    const int split_shift = __ffs(n_splits) - 1;
+    const int units = (group * D + 31) / 32;  // the group's outputs are dealt out for merging in units of 32
+    const int cap = (pow2 ? (units + n_splits - 1) >> split_shift : (units + n_splits - 1) / n_splits) * 32;
+    const int pages_here = end_page - first_page + n_splits - 1;
+    const int per_split = pow2 ? pages_here >> split_shift : pages_here / n_splits;
     const int p_begin = first_page + split * per_split;
     const int p_end = min(p_begin + per_split, end_page);
     const int n_iter = max(p_end - p_begin, 0);
@@ -329,12 +336,6 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     __syncthreads();
     // With a cluster, outputs are dealt out in units of 32: unit u is merged by block u % n_splits, which holds
     // room for cap = (units a block can have) * 32 values from every block.
-    const int units = (group * D + 31) / 32;
-    const int cap = ((units + n_splits - 1) / n_splits) * 32;
-    // unit / n_splits and unit % n_splits by shift and mask where the splits are a power of two (the host's choice
-    // always is): these sit in the kernel's tail, where a division's chain of instructions hides behind nothing
-    const bool pow2 = (n_splits & (n_splits - 1)) == 0;
-    const int split_shift = __ffs(n_splits) - 1;
     auto unit_owner = [&](int unit) { return pow2 ? unit & (n_splits - 1) : unit % n_splits; };
     auto unit_place = [&](int unit) { return pow2 ? unit >> split_shift : unit / n_splits; };
     for (int idx = tid; idx < group * D; idx += WARPS * 32) {
@@ -457,7 +458,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
     gk_launch_cluster(attention_decode_kernel<D>, grid, dim3(WARPS * 32), smem, stream,
         dim3(cluster_merge ? n_splits : 1, 1, 1),
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
-        part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits, cluster_merge, fused);
+        part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits, cluster_merge, n_q / n_kv, fused);
     GK_CHECK_LAUNCH("attention_decode");
     if (n_splits > 1 && !cluster_merge) {
         gk_launch(attention_decode_merge_kernel<D>, dim3(n_seqs * n_q), dim3(D <= 64 ? 64 : 128), 0, stream,

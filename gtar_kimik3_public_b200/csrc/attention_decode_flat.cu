@@ -55,6 +55,7 @@ struct FlatParams {
     const int* slots;
     const int* block_table;
     int n_seqs, n_q, n_kv, max_pages, window;
+    int group;                       // n_q / n_kv, divided on the host
     float sl2;
 };
 
@@ -134,7 +135,7 @@ template <int D>
 __global__ void __launch_bounds__(THREADS) attention_decode_flat_kernel(const FlatParams p, const FusedQkv fused) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     FlatSmem<D>& sm = *reinterpret_cast<FlatSmem<D>*>(smem_raw);
-    const int group = p.n_q / p.n_kv;
+    const int group = p.group;
     const int record_slots = record_pieces<D>(group, fused.qkv != nullptr);
     // two records: what the pair in hand, and the next, need at their start (see below)
     uint4* records = reinterpret_cast<uint4*>(smem_raw + sizeof(FlatSmem<D>));
@@ -531,7 +532,7 @@ int allow_smem(size_t smem) {
 
 template <int D>
 int launch_flat(const FlatParams& p, const FusedQkv& fused, int n_blocks, cudaStream_t stream) {
-    const int group = p.n_q / p.n_kv;
+    const int group = p.group;
     const size_t smem = sizeof(FlatSmem<D>) + 2 * (size_t)record_pieces<D>(group, fused.qkv != nullptr) * 16 +
                         (size_t)WARPS * group * (D + 2) * sizeof(float) + ((size_t)p.n_seqs + 1) * sizeof(int);
     GK_REQUIRE(smem <= 227 * 1024, "attention_decode_flat: %d sequences with groups of %d heads need %zu bytes of shared memory",
@@ -597,6 +598,7 @@ GK_EXPORT int gk_attention_decode_flat_bf16(const void* q, const void* qkv, cons
     p.slots = slots;
     p.block_table = block_table;
     p.n_seqs = n_seqs;
+    p.group = group;
     p.n_q = n_q;
     p.n_kv = n_kv;
     p.max_pages = max_pages;

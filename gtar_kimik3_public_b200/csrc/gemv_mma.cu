@@ -70,7 +70,7 @@ __device__ __forceinline__ void copy16_async(void* smem_dst, const void* src, in
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+__device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 // ROW_SETS: sets of eight tokens, 1, 2 or 4.  An MMA takes two sets on its rows 0..7 and 8..15 (with one set the
 // upper rows are zero); with four sets (17 to 32 tokens) every weight piece goes through two MMAs' worth of
@@ -279,8 +279,8 @@ __global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS ==
                 total += row_ss[w][group];
                 total2 += row_ss[w][group + 8];
             }
-            const float inv = 1.0f / sqrtf(total / (float)p.k + p.norm_eps);
-            const float inv2 = 1.0f / sqrtf(total2 / (float)p.k + p.norm_eps);
+            const float inv = rsqrtf(total / (float)p.k + p.norm_eps);
+            const float inv2 = rsqrtf(total2 / (float)p.k + p.norm_eps);
             auto pack2 = [](float lo, float hi) {
                 __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
                 return *reinterpret_cast<uint32_t*>(&v);
