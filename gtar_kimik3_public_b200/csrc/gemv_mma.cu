@@ -345,10 +345,14 @@ __global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS ==
     // the activations of all tokens into shared memory; zeros for the rows that are no token and from K up to
     // the end of the last chunk any warp looks at
     const int x_pieces = cpw * WARPS * 4;  // 16-byte pieces of a row
-    for (int i = threadIdx.x; i < X_ROWS * x_pieces; i += THREADS) {
-        const int row = i / x_pieces, at = (i % x_pieces) * 8;
-        const bool in = row < p.tokens && at < p.k;
-        copy16_async(xs + (size_t)row * x_stride + at * 2, in ? p.x + (size_t)row * p.ldx + at : p.x, in ? 16 : 0);
+    // a thread takes the same piece of every row: no division by a run-time number behind the wait
+    for (int piece_at = threadIdx.x; piece_at < x_pieces; piece_at += THREADS) {
+        const int at = piece_at * 8;
+#pragma unroll 4
+        for (int row = 0; row < X_ROWS; ++row) {
+            const bool in = row < p.tokens && at < p.k;
+            copy16_async(xs + (size_t)row * x_stride + at * 2, in ? p.x + (size_t)row * p.ldx + at : p.x, in ? 16 : 0);
+        }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
