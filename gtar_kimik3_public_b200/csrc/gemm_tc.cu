@@ -416,7 +416,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 // of the block that will sum that row (a region beside its pipeline stages, which its own MMAs may
                 // still be reading), as [source block][column][row of the owner's share] float32.  The stores are
                 // posted: nobody waits for a trip between SMs, as a block that fetched the others' tiles would.
-                const int n_ranks = gridDim.z, rows_per = BM / n_ranks;
+                const int n_ranks = gridDim.z, rows_per = BM >> (__ffs(n_ranks) - 1);  // the splits are a power of two: no division in the output stage
                 const int owner = row_in_tile >> (__ffs(rows_per) - 1), row_local = row_in_tile & (rows_per - 1);  // a power of two
                 const uint32_t mine = smem_u32(split_sums) + (uint32_t)((int)blockIdx.z * rows_per * BN + row_local) * 4u;
                 uint32_t dst;
@@ -460,7 +460,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         if (warp >= 2) {
             // this block sums rows [rank * rows_per, (rank + 1) * rows_per) of the tile over all blocks
             const int n_ranks = gridDim.z, rank = blockIdx.z;
-            const int rows_per = BM / n_ranks;
+            const int rows_per = BM >> (__ffs(n_ranks) - 1);
             const uint32_t stage_addr = smem_u32(sm.a[0]);
             const int e = (warp - 2) * 32 + lane;
             // A thread takes four consecutive rows of one column at a time: one 16-byte load from every
@@ -594,8 +594,10 @@ __device__ __forceinline__ void qkv_head(const QkvEpilogue& e, float (&v)[HD], i
         dst = e.q_out + ((size_t)token * e.n_q + head) * HD;
     } else {
         const int hk = is_k ? head - e.n_q : head - e.n_q - e.n_kv;
-        const int page = e.block_table[(size_t)e.slots[e.tok_seq[token]] * e.max_pages + pos / e.page_size];
-        const size_t at = (((size_t)page * e.n_kv + hk) * e.page_size + (pos % e.page_size)) * HD;
+        // the library's pages hold 64 positions: then by shift and mask
+        const int page_index = e.page_size == 64 ? pos >> 6 : pos / e.page_size, in_page = e.page_size == 64 ? pos & 63 : pos % e.page_size;
+        const int page = e.block_table[(size_t)e.slots[e.tok_seq[token]] * e.max_pages + page_index];
+        const size_t at = (((size_t)page * e.n_kv + hk) * e.page_size + in_page) * HD;
         dst = (is_k ? e.k_pages : e.v_pages) + at;
     }
     const bool normed = (is_q || is_k) && e.use_norm, rotated = (is_q || is_k) && e.cos_table != nullptr;
@@ -604,7 +606,7 @@ __device__ __forceinline__ void qkv_head(const QkvEpilogue& e, float (&v)[HD], i
         float ss = 0.f;
 #pragma unroll
         for (int i = 0; i < HD; ++i) ss += v[i] * v[i];
-        inv = 1.0f / sqrtf(ss / (float)HD + e.eps);
+        inv = rsqrtf(ss / (float)HD + e.eps);
     }
     const void* w = is_q ? e.wq : e.wk;
     auto weight = [&](int i) {
