@@ -124,8 +124,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
             sm.sin[tid] = sn;
         }
     }
+    if (fused.qkv) __syncthreads();  // the constants above, for every warp: ahead of the wait, where the barrier costs nothing
     pdl_wait();
-    if (fused.qkv) __syncthreads();  // the constants above, for every warp
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s)
         if (s >= early) issue(s, s);
