@@ -154,6 +154,29 @@ __device__ __forceinline__ float ex2(float x) {  // 2^x, one MUFU instruction; 2
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two 32-bit numbers as one operand, and the instructions of this architecture that work on such pairs: the softmax
+// warps' time is the length of their instruction stream, so half as many multiply-adds and additions shorten a step.
+__device__ __forceinline__ uint64_t pair_of(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void halves_of(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma_pairs(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_pairs(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max_of_three(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 struct alignas(1024) Smem {
@@ -741,7 +764,8 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
                 {   // four independent chains keep the maximum off the critical path
                     float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                    for (int c = 0; c < 64; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(raw[c >> 5][c & 31]));
+                    for (int c = 0; c < 64; c += 2)
+                        m4[(c >> 1) & 3] = max_of_three(m4[(c >> 1) & 3], __uint_as_float(raw[c >> 5][c & 31]), __uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]));
                     mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
                 }
                 // the row's maximum over both halves
@@ -758,16 +782,20 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
                 }
                 const float ref = m_used == -INFINITY ? 0.f : m_used;
                 uint32_t packed[32];
-                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint64_t scale2 = pair_of(p.sl2, p.sl2), shift2 = pair_of(-ref, -ref);
+                uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};  // four running pairs of sums
 #pragma unroll
                 for (int c = 0; c < 64; c += 2) {
-                    const float e0 = ex2(fmaf(__uint_as_float(raw[c >> 5][c & 31]), p.sl2, -ref));
-                    const float e1 = ex2(fmaf(__uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]), p.sl2, -ref));
-                    sum4[(c >> 1) & 3] += e0 + e1;
+                    float x0, x1;
+                    halves_of(fma_pairs(pair_of(__uint_as_float(raw[c >> 5][c & 31]), __uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31])), scale2, shift2), x0, x1);
+                    const float e0 = ex2(x0), e1 = ex2(x1);
+                    sums[(c >> 1) & 3] = add_pairs(sums[(c >> 1) & 3], pair_of(e0, e1));
                     __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
                     packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
                 }
-                l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+                float sum_lo, sum_hi;
+                halves_of(add_pairs(add_pairs(sums[0], sums[1]), add_pairs(sums[2], sums[3])), sum_lo, sum_hi);
+                l = l * corr + (sum_lo + sum_hi);
                 // P and the accumulator may be touched only when the product of the step before has finished
                 if (g > 0) {
                     ok = mbar_wait(&sm.o_done, (g - 1) & 1);
@@ -1114,7 +1142,8 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc5_kernel(cons
                 {
                     float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                    for (int c = 0; c < 64; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(raw[c >> 5][c & 31]));
+                    for (int c = 0; c < 64; c += 2)
+                        m4[(c >> 1) & 3] = max_of_three(m4[(c >> 1) & 3], __uint_as_float(raw[c >> 5][c & 31]), __uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]));
                     mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
                 }
                 sm.row_max[g & 1][half][r] = mx;
@@ -1130,16 +1159,20 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc5_kernel(cons
                 }
                 const float ref = m_used == -INFINITY ? 0.f : m_used;
                 uint32_t packed[32];
-                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint64_t scale2 = pair_of(p.sl2, p.sl2), shift2 = pair_of(-ref, -ref);
+                uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};  // four running pairs of sums
 #pragma unroll
                 for (int c = 0; c < 64; c += 2) {
-                    const float e0 = ex2(fmaf(__uint_as_float(raw[c >> 5][c & 31]), p.sl2, -ref));
-                    const float e1 = ex2(fmaf(__uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]), p.sl2, -ref));
-                    sum4[(c >> 1) & 3] += e0 + e1;
+                    float x0, x1;
+                    halves_of(fma_pairs(pair_of(__uint_as_float(raw[c >> 5][c & 31]), __uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31])), scale2, shift2), x0, x1);
+                    const float e0 = ex2(x0), e1 = ex2(x1);
+                    sums[(c >> 1) & 3] = add_pairs(sums[(c >> 1) & 3], pair_of(e0, e1));
                     __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
                     packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
                 }
-                l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+                float sum_lo, sum_hi;
+                halves_of(add_pairs(add_pairs(sums[0], sums[1]), add_pairs(sums[2], sums[3])), sum_lo, sum_hi);
+                l = l * corr + (sum_lo + sum_hi);
                 if (g > 0) {
                     ok = mbar_wait(&sm.o_done, (g - 1) & 1);
                     if (!ok) break;
