@@ -592,12 +592,20 @@ def decode_flat_wins(n_seqs: int, n_kv: int, kv_len: int, page_size: int, sm_cou
 
     The evenly dealt kernel costs some 7 us more than the equal cut where that fits the device (partial results
     through scratch, a ticket per part, a merge by whoever comes last), so it is chosen where the equal cut fits
-    badly: where its blocks fill less than two thirds of the places they could have (and a block would still have 16
-    pages and more to stream), or where they come in waves of which the last is thin.  Measured, 28 layers of the
-    0.6B sizes, contexts of 2,048, ms a step with the equal cut against dealt evenly: 20 sequences 1.96 / 1.79,
-    24: 1.96 / 1.91, 40: 3.28 / 2.77, 48: 3.34 / 3.13, 56: 3.60 / 3.42; but 8: 0.90 / 1.11, 16: 1.35 / 1.53,
-    32: 2.05 / 2.24, 64: 3.64 / 3.65; with contexts of 8,192: 12 sequences 2.95 / 2.60, 20: 4.47 / 3.80, 40: 7.35 / 6.78, but
-    6 (48 pairs cut in four fill 68% of the places for clusters of four): 1.67 / 1.73."""
+    badly.  Measured, 28 layers of the 0.6B sizes, ms a step with the equal cut against dealt evenly:
+
+    * blocks that come in two waves of which the second is thin: contexts of 2,048, 40 sequences (320 pairs on 296
+      places) 2.86 / 2.57, 44: 2.88 / 2.78, but 48: 2.89 / 2.91, 52: 3.00 / 3.05, 56: 3.13 / 3.21, 60: 3.17 / 3.33; contexts
+      of 512, 40: 1.57 / 1.53; of 1,024, 40: 2.05 / 1.91 but 56: 2.16 / 2.26;
+    * three and more waves of clusters: contexts of 4,096, 40 sequences (five waves of clusters of four) 4.13 / 3.90; of
+      8,192, 40: 6.67 / 6.61;
+    * whole sequences a block that fill little more than half of the places and are long: 20 sequences of 4,096
+      2.57 / 2.34, of 8,192 4.06 / 3.70, but of 2,048 1.66 / 1.70; 24 of 2,048 1.71 / 1.83, of 4,096 2.72 / 2.70;
+    * clusters of eight that share SMs on long contexts: 32,768 tokens, 3 sequences 2.66 / 2.42, 4: 3.17 / 2.92; 16,384, 4:
+      2.09 / 2.05 but 3: 1.34 / 1.64, 6 (cut in four): 2.37 / 2.63; 8,192, 4: 1.19 / 1.45.
+
+    Elsewhere the equal cut is ahead: 8 sequences of 2,048 tokens 0.82 / 1.1, 12: 1.11 / 1.21, 16: 1.25 / 1.5, 32: 1.98 / 2.2,
+    64: 3.26 / 3.5; 12 of 8,192 (cut in two): 2.33 / 2.48."""
     splits = decode_splits(n_seqs, n_kv, kv_len, page_size, sm_count, cluster_places)
     if splits > 8:
         return False
@@ -611,14 +619,10 @@ def decode_flat_wins(n_seqs: int, n_kv: int, kv_len: int, page_size: int, sm_cou
     per_block = pairs * pages / flat_places  # pages a block streams when they are dealt evenly
     if waves == 1:
         if splits == 8 and pairs * 8 > sm_count:
-            # clusters of eight that share SMs stream long contexts badly (16,400 tokens: 4 sequences 2.43 / 2.09 ms,
-            # 32,800: 3 sequences 3.11 / 2.61, 4: 3.99 / 3.18; but 8,200: 3 sequences 1.13 / 1.30, 16,400: 3: 1.71 / 1.84)
-            # (the more of the SMs hold two blocks, the sooner: 8,200 tokens, 4 sequences: 1.56 / 1.45)
-            return per_block >= (16 if pairs * 8 > 1.5 * sm_count else 30)
-        if splits >= 4 and fill < 0.80 and per_block >= 30:
-            return True  # (16,384 tokens, 6 sequences cut in four: 3.03 / 2.72)
-        return fill < 0.66 and per_block >= 16
-    return waves >= 3 or fill < 0.86
+            # the more of the SMs hold two blocks of a cluster of eight, the sooner
+            return per_block >= (24 if pairs * 8 > 1.5 * sm_count else 30)
+        return splits == 1 and fill < 0.66 and per_block >= 28
+    return fill < (0.62 if waves == 2 else 0.92)
 
 
 def attention_decode(

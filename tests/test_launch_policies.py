@@ -77,16 +77,16 @@ def test_twenty_four_sequences_are_not_cut():
 
 
 def test_the_even_deal_where_the_equal_cut_fits_badly():
-    """Measured (28 layers of the 0.6B sizes, ms a step, equal cut / dealt evenly): contexts of 2,048: 20 sequences 1.96 /
-    1.79, 24: 1.96 / 1.91, 40: 3.28 / 2.77, 48: 3.34 / 3.13, 56: 3.60 / 3.42, but 8: 0.90 / 1.11, 16: 1.35 / 1.53, 32: 2.05 /
-    2.24, 64: 3.64 / 3.65; contexts of 8,192: 12: 2.95 / 2.60, 20: 4.47 / 3.80, but 6: 1.67 / 1.73."""
+    """Measured (28 layers of the 0.6B sizes, ms a step, equal cut / dealt evenly): contexts of 2,048: 40 sequences 2.86 /
+    2.57, 44: 2.88 / 2.78, 48: 2.89 / 2.91, but 8: 0.82 / 1.1, 16: 1.25 / 1.5, 20: 1.66 / 1.70, 24: 1.71 / 1.83, 32: 1.98 / 2.2,
+    56: 3.13 / 3.21, 64: 3.26 / 3.5; contexts of 8,192: 20: 4.06 / 3.70, but 6: 1.50 / 1.74, 12: 2.33 / 2.48."""
     from gtar_kimik3_public_b200.ops.functional import decode_flat_wins
 
     places = (296, 148, 71, 33)
     evenly = {b: decode_flat_wins(b, 8, 2560, 64, 148, places, 296) for b in (1, 8, 16, 20, 24, 32, 40, 48, 56, 64)}
-    assert evenly == {1: False, 8: False, 16: False, 20: True, 24: True, 32: False, 40: True, 48: True, 56: True, 64: False}
-    assert decode_flat_wins(12, 8, 7168, 64, 148, places, 296) and decode_flat_wins(20, 8, 7168, 64, 148, places, 296)
-    assert not decode_flat_wins(6, 8, 7168, 64, 148, places, 296)
+    assert evenly == {1: False, 8: False, 16: False, 20: False, 24: False, 32: False, 40: True, 48: True, 56: False, 64: False}
+    assert decode_flat_wins(20, 8, 7168, 64, 148, places, 296) and decode_flat_wins(20, 8, 3584, 64, 148, places, 296)
+    assert not decode_flat_wins(6, 8, 7168, 64, 148, places, 296) and not decode_flat_wins(12, 8, 7168, 64, 148, places, 296)
     # few pages a block: the parts, tickets and merges of the even deal cost more than it saves
     assert not decode_flat_wins(20, 8, 512, 64, 148, places, 296)
     # more than eight splits go through scratch and a second kernel: not this kernel's case
@@ -94,16 +94,17 @@ def test_the_even_deal_where_the_equal_cut_fits_badly():
 
 
 def test_the_even_deal_for_a_few_long_sequences():
-    """Clusters of eight that share SMs stream long contexts badly (ms a step, equal cut / dealt evenly: 16,400 tokens,
-    4 sequences 2.43 / 2.09, 6: 3.03 / 2.72; 32,800 tokens, 3: 3.11 / 2.61, 4: 3.99 / 3.18), but one and two sequences
-    (all their blocks have an SM each) and shorter contexts stay with the equal cut (8,200 tokens, 3: 1.13 / 1.30; 16,400
-    tokens, 3: 1.71 / 1.84).  The lengths below are the middles of the bounds that captured steps of those contexts get."""
+    """Clusters of eight that share SMs stream long contexts badly (ms a step, equal cut / dealt evenly: 32,768 tokens,
+    3 sequences 2.66 / 2.42, 4: 3.17 / 2.92; 16,384 tokens, 4: 2.09 / 2.05), but one and two sequences (all their blocks
+    have an SM each), shorter contexts and sequences cut in four stay with the equal cut (8,192 tokens, 3: 0.96 / 1.24,
+    4: 1.19 / 1.45; 16,384 tokens, 3: 1.34 / 1.64, 6: 2.37 / 2.63).  The lengths below are the middles of the bounds that
+    captured steps of those contexts get."""
     from gtar_kimik3_public_b200.ops.functional import decode_flat_wins
 
     places = (296, 148, 71, 33)
-    assert decode_flat_wins(4, 8, 20480, 64, 148, places, 296) and decode_flat_wins(6, 8, 20480, 64, 148, places, 296)
-    assert decode_flat_wins(3, 8, 36864, 64, 148, places, 296) and decode_flat_wins(4, 8, 36864, 64, 148, places, 296)
-    assert not decode_flat_wins(3, 8, 10240, 64, 148, places, 296) and not decode_flat_wins(3, 8, 20480, 64, 148, places, 296)
-    assert decode_flat_wins(4, 8, 10240, 64, 148, places, 296) and not decode_flat_wins(4, 8, 5120, 64, 148, places, 296)
+    assert decode_flat_wins(4, 8, 14336, 64, 148, places, 296) and not decode_flat_wins(6, 8, 14336, 64, 148, places, 296)
+    assert decode_flat_wins(3, 8, 28672, 64, 148, places, 296) and decode_flat_wins(4, 8, 28672, 64, 148, places, 296)
+    assert not decode_flat_wins(3, 8, 7168, 64, 148, places, 296) and not decode_flat_wins(3, 8, 14336, 64, 148, places, 296)
+    assert not decode_flat_wins(4, 8, 7168, 64, 148, places, 296) and not decode_flat_wins(4, 8, 5120, 64, 148, places, 296)
     for length in (10240, 20480, 36864):
         assert not decode_flat_wins(1, 8, length, 64, 148, places, 296) and not decode_flat_wins(2, 8, length, 64, 148, places, 296)
