@@ -571,16 +571,21 @@ def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, sm_co
     pages = max(1, -(-max_kv_len // page_size))
     places = 2 * sm_count
     fill = max(1, min(places // pairs, pages, 64))
-    if fill >= SCRATCH_SPLITS_FROM and max_kv_len >= 8192:
+    # (one and two sequences of 8,192 tokens are faster as clusters of eight, 0.83 and 0.91 ms a step against 0.85 and 0.98
+    # through scratch; of 16,384 tokens slower, 1.18 and 1.45 against 1.03 and 1.32)
+    if fill >= SCRATCH_SPLITS_FROM and max_kv_len >= 12288:
         return fill
     if cluster_places is None:
         cluster_places = tuple(places // c for c in (1, 2, 4, 8))
     at_once = dict(zip((1, 2, 4, 8), cluster_places))
 
     def estimate(splits: int) -> float:
-        # clusters of eight that have to share SMs cost more besides their pages than the eight say (four sequences of
-        # 2,048 tokens: 0.82 ms a step with four splits, 0.89 with eight; one and two sequences are faster with eight)
-        besides = 13.0 if splits == 8 and pairs * splits > sm_count else 8.0
+        # clusters of eight that have to share SMs cost more besides their pages than the eight say, the more of the SMs
+        # hold two of their blocks (four sequences of 2,048 tokens: 0.73 ms a step with four splits, 0.76 with eight; three
+        # sequences: 0.70 with four, 0.65 with eight; one and two sequences are faster with eight)
+        besides = 8.0
+        if splits == 8 and pairs * splits > sm_count:
+            besides = 13.0 if pairs * splits > 1.5 * sm_count else 10.0
         return -(-pairs // max(1, at_once[splits])) * (pages / splits + besides)
 
     return min((s for s in (1, 2, 4, 8) if s <= pages), key=lambda s: (estimate(s), s))

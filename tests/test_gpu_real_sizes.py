@@ -249,15 +249,15 @@ def _decode_many(tag, dtype, n_requests, kernel_log, expect):
 
 
 @pytest.mark.parametrize("n_seqs", [1, 2])
-def test_decode_beyond_8192_tokens_merges_its_splits_through_scratch(n_seqs, kernel_log):
-    """One and two sequences of more than 8,192 tokens: decode attention cuts each into more pieces than a cluster
+def test_decode_beyond_12288_tokens_merges_its_splits_through_scratch(n_seqs, kernel_log):
+    """One and two sequences of more than 12,288 tokens: decode attention cuts each into more pieces than a cluster
     holds, writes partial results to scratch memory and merges them in a second kernel."""
     from gtar_kimik3_public_b200.ops import functional as F
 
     tag, dtype = "tiny_long", "bfloat16"
-    lengths = [8300, 8250][:n_seqs]
+    lengths = [12400, 12350][:n_seqs]
     requests = requests_for(tag, lengths, seed=47)
-    engine = load_engine(tag, dtype, max_tokens=n_seqs * 8832, max_seqs=n_seqs)
+    engine = load_engine(tag, dtype, max_tokens=n_seqs * 12928, max_seqs=n_seqs)
     poison(engine)
     tail = 6
     engine.step([_entry(r, requests[r][:-tail], []) for r in range(n_seqs)])
@@ -267,11 +267,11 @@ def test_decode_beyond_8192_tokens_merges_its_splits_through_scratch(n_seqs, ker
         logits = engine.step([_entry(r, [requests[r][len(requests[r]) - tail + t]], [0]) for r in range(n_seqs)])
         for r in range(n_seqs):
             rows[r].append(logits[r:r + 1])
-    assert F.decode_splits(n_seqs, 1, 8832, 64, F.sm_count()) > 8
+    assert F.decode_splits(n_seqs, 1, 12928, 64, F.sm_count()) > 8
     assert "gk_attention_decode_bf16" in kernel_log and "gk_attention_decode_fused_bf16" not in kernel_log
     for r in range(n_seqs):
         n = len(requests[r])
-        check_against_plain(tag, dtype, requests[r], list(range(n - tail, n)), torch.cat(rows[r]), f"sequence {r} beyond 8,192 tokens")
+        check_against_plain(tag, dtype, requests[r], list(range(n - tail, n)), torch.cat(rows[r]), f"sequence {r} beyond 12,288 tokens")
     engine.end(list(range(n_seqs)))
     engine.check()
 

@@ -76,6 +76,17 @@ def test_twenty_four_sequences_are_not_cut():
     assert decode_splits(24, 8, 3584, 64, 148, places) == 1
 
 
+def test_three_sequences_take_eight_splits_and_short_contexts_no_scratch():
+    """Measured, ms a step: three sequences of 2,048 tokens 0.70 cut in four and 0.65 in eight (of 1,024: 0.62 / 0.60), four
+    sequences 0.73 / 0.76; one and two sequences of 8,192 tokens 0.83 and 0.91 as clusters of eight against 0.85 and 0.98
+    with 37 and 18 splits through scratch, but of 16,384 tokens 1.18 and 1.45 against 1.03 and 1.32."""
+    places = (296, 148, 71, 33)
+    assert decode_splits(3, 8, 2560, 64, 148, places) == 8 and decode_splits(3, 8, 1280, 64, 148, places) == 8
+    assert decode_splits(4, 8, 2560, 64, 148, places) == 4 and decode_splits(4, 8, 1280, 64, 148, places) == 4
+    assert decode_splits(1, 8, 10240, 64, 148, places) == 8 and decode_splits(2, 8, 10240, 64, 148, places) == 8
+    assert decode_splits(1, 8, 14336, 64, 148, places) == 37 and decode_splits(2, 8, 14336, 64, 148, places) == 18
+
+
 def test_the_even_deal_where_the_equal_cut_fits_badly():
     """Measured (28 layers of the 0.6B sizes, ms a step, equal cut / dealt evenly): contexts of 2,048: 40 sequences 2.86 /
     2.57, 44: 2.88 / 2.78, 48: 2.89 / 2.91, but 8: 0.82 / 1.1, 16: 1.25 / 1.5, 20: 1.66 / 1.70, 24: 1.71 / 1.83, 32: 1.98 / 2.2,

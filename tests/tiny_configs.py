@@ -53,9 +53,9 @@ TINY_C = {
     "max_position_embeddings": 512,
 }
 
-# The tiny_c model with room for sequences beyond 8,192 tokens, where decode attention cuts a sequence into more
+# The tiny_c model with room for sequences beyond 12,288 tokens, where decode attention cuts a sequence into more
 # pieces than a cluster holds and merges them through scratch memory and a second kernel.
-TINY_LONG = {**TINY_C, "max_position_embeddings": 8832}
+TINY_LONG = {**TINY_C, "max_position_embeddings": 12928}
 
 # The layer sizes of the three benchmark configurations (Qwen3-0.6B, 4B and 8B sizes) with few layers and a small
 # vocabulary, so that the plain implementation stays fast: at these sizes the engine takes the kernels that the
